@@ -1,0 +1,111 @@
+"""Shared by the tests: the tiny configurations, model folders, traces and comparisons.
+
+The tiny configurations differ in every size and option: head counts and groups,
+head size, widths that are no power of two, depth, vocabulary (one of them odd),
+rope_theta, the norms' eps, tying, the window, the page size.
+"""
+from __future__ import annotations
+
+import os
+import tempfile
+
+import numpy as np
+
+import plain_qwen2 as plain
+
+TINY_A = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 64,
+          "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2,
+          "intermediate_size": 128, "vocab_size": 256, "rope_theta": 10000.0, "rms_norm_eps": 1e-6,
+          "tie_word_embeddings": True, "use_sliding_window": False, "max_position_embeddings": 256,
+          "hidden_act": "silu"}
+TINY_B = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 96,
+          "num_hidden_layers": 3, "num_attention_heads": 3, "num_key_value_heads": 1,
+          "intermediate_size": 224, "vocab_size": 384, "rope_theta": 1000000.0, "rms_norm_eps": 1e-5,
+          "tie_word_embeddings": False, "use_sliding_window": False, "max_position_embeddings": 512,
+          "hidden_act": "silu"}
+# windowed upper layers, full multi-head attention, widths with odd factors, an odd vocabulary
+TINY_C = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 80,
+          "num_hidden_layers": 4, "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 16,
+          "intermediate_size": 176, "vocab_size": 301, "rope_theta": 500000.0, "rms_norm_eps": 3e-6,
+          "tie_word_embeddings": False, "use_sliding_window": True, "sliding_window": 24,
+          "max_window_layers": 2, "max_position_embeddings": 384, "hidden_act": "silu"}
+# head size given apart from the width (heads * head_dim != hidden_size), head size 64
+TINY_D = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 72,
+          "num_hidden_layers": 2, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64,
+          "intermediate_size": 200, "vocab_size": 272, "rope_theta": 20000.0, "rms_norm_eps": 1e-5,
+          "tie_word_embeddings": True, "use_sliding_window": False, "max_position_embeddings": 320,
+          "hidden_act": "silu"}
+
+CONFIGS = {"A": (TINY_A, 16), "B": (TINY_B, 32), "C": (TINY_C, 16), "D": (TINY_D, 32)}   # name -> (config, page size)
+
+# |engine - plain| <= TOL * max|plain| over the compared rows
+TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+MEAN_TOL = {"float32": 2e-5, "bfloat16": 6e-3}
+
+
+def make_weights(cfg, seed, dtype, sharp=None):
+    """Weights as the plain implementation will use them (bfloat16 runs: rounded to bfloat16)."""
+    if sharp is None:
+        # q and k scaled up so that attention is peaked and one wrong key shows;
+        # less so in bfloat16, where rounding of large scores is itself visible
+        sharp = 6.0 if dtype == "float32" else 2.0
+    w = plain.random_weights(cfg, seed, std=0.08, gain_std=0.1, sharp=sharp)
+    return plain.round_to_bf16(w) if dtype == "bfloat16" else w
+
+
+def model_folder(tmp_path, cfg, weights, dtype):
+    d = os.path.join(str(tmp_path), f"model_{abs(hash(str(sorted(cfg.items())))) % 10**8}_{dtype}")
+    plain.write_model_folder(d, cfg, weights, store="BF16" if dtype == "bfloat16" else "F32")
+    return d
+
+
+def token_ids(cfg, n, seed):
+    return np.random.default_rng(seed).integers(0, cfg["vocab_size"], size=n).tolist()
+
+
+def compare(got, want, dtype, what=""):
+    """got, want: [rows, vocab]."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape, f"{what}: shapes {got.shape} vs {want.shape}"
+    assert np.isfinite(got).all(), f"{what}: engine logits are not finite"
+    scale = np.abs(want).max()
+    err = np.abs(got - want)
+    worst = np.unravel_index(err.argmax(), err.shape)
+    assert err.max() <= TOL[dtype] * scale, (
+        f"{what}: max |diff| {err.max():.3e} at row {worst[0]} col {worst[1]} exceeds "
+        f"{TOL[dtype]:.0e} * {scale:.3e}; first bad row "
+        f"{int(np.argmax(err.max(axis=1) > TOL[dtype] * scale))}")
+    assert err.mean() <= MEAN_TOL[dtype] * scale, f"{what}: mean |diff| {err.mean():.3e} vs scale {scale:.3e}"
+
+
+class Replayer:
+    """Drives a ModelRunner like the replay tool does and collects logits by (request, position)."""
+
+    def __init__(self, runner, cache):
+        self.runner, self.cache = runner, cache
+        self.fed = {}
+        self.rows = {}
+
+    def step(self, entries, end=()):
+        """entries: list of (request id, tokens, want places)."""
+        from vllm_cpp_b200.engine.runner import StepEntry
+        batch = []
+        for rid, toks, want in entries:
+            if rid not in self.cache.requests:
+                self.cache.add_request(rid)
+                self.fed[rid] = 0
+            batch.append(StepEntry(rid, list(toks), list(want)))
+        logits = self.runner.step(batch).float().cpu().numpy()
+        i = 0
+        for rid, toks, want in entries:
+            for w in want:
+                self.rows[(rid, self.fed[rid] + w)] = logits[i].copy()
+                i += 1
+            self.fed[rid] += len(toks)
+        for rid in end:
+            self.cache.free_request(rid)
+            del self.fed[rid]
+
+    def logits_of(self, rid, positions):
+        return np.stack([self.rows[(rid, p)] for p in positions])

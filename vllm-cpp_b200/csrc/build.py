@@ -1,0 +1,144 @@
+"""Compiles the CUDA sources of this folder for sm_100a and loads the result.
+
+The kernels are plain ``extern "C"`` launchers that take raw device pointers and
+a stream, so they compile with ``nvcc`` alone (no framework headers, a few
+seconds per file) and are called through ``ctypes``.  The shared object is built
+on first use, in ``csrc/_build/`` when that folder can be written and in a
+per-user temporary folder otherwise, and is keyed by a hash of the sources and
+flags, so an edited source rebuilds and an unchanged one does not.
+
+There is no fallback: if ``nvcc`` is missing or a source does not compile, the
+import of ``csrc.ops`` fails with the compiler's output.
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import ctypes
+import fcntl
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import time
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+LIB_NAME = "libvcb_kernels.so"
+_lib = None
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def sources():
+    return sorted(f for f in os.listdir(_HERE) if f.endswith(".cu"))
+
+
+def _headers():
+    return sorted(f for f in os.listdir(_HERE) if f.endswith((".cuh", ".h")))
+
+
+def _find_nvcc() -> str:
+    cand = [os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"]
+    for c in cand:
+        if c and os.path.isfile(c) and os.access(c, os.X_OK):
+            return c
+    raise BuildError("nvcc not found (looked at $NVCC, PATH and /usr/local/cuda/bin/nvcc); "
+                     "the engine's kernels cannot be built and there is no fallback")
+
+
+def _source_hash() -> str:
+    h = hashlib.sha256()
+    for f in sources() + _headers():
+        h.update(f.encode())
+        with open(os.path.join(_HERE, f), "rb") as fh:
+            h.update(fh.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def _build_root() -> str:
+    env = os.environ.get("VLLM_CPP_B200_BUILD_DIR")
+    if env:
+        os.makedirs(env, exist_ok=True)
+        return env
+    in_tree = os.path.join(_HERE, "_build")
+    try:
+        os.makedirs(in_tree, exist_ok=True)
+        probe = os.path.join(in_tree, f".w{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.remove(probe)
+        return in_tree
+    except OSError:
+        d = os.path.join(tempfile.gettempdir(), f"vllm_cpp_b200_build_{os.getuid()}")
+        os.makedirs(d, exist_ok=True)
+        return d
+
+
+def _say(msg: str) -> None:
+    print(f"[vllm_cpp_b200 build] {msg}", file=sys.stderr, flush=True)
+
+
+def _compile_one(nvcc: str, src: str, obj: str, extra) -> str:
+    cmd = [nvcc] + NVCC_FLAGS + list(extra) + ["-I", _HERE, "-c", os.path.join(_HERE, src), "-o", obj]
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if p.returncode != 0:
+        raise BuildError(f"nvcc failed on {src}:\n{' '.join(cmd)}\n{p.stdout}")
+    return p.stdout
+
+
+def build(verbose: bool = False, ptxas_info: bool = False) -> str:
+    """Build the shared object if it is not there yet; return its path."""
+    root = _build_root()
+    out_dir = os.path.join(root, _source_hash())
+    lib_path = os.path.join(out_dir, LIB_NAME)
+    if os.path.isfile(lib_path):
+        return lib_path
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(root, ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if os.path.isfile(lib_path):
+                return lib_path
+            nvcc = _find_nvcc()
+            srcs = sources()
+            _say(f"compiling {len(srcs)} CUDA sources for sm_100a into {out_dir}")
+            t0 = time.time()
+            extra = ["-Xptxas", "-v"] if ptxas_info else []
+            objs = [os.path.join(out_dir, s[:-3] + ".o") for s in srcs]
+            with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
+                futs = {ex.submit(_compile_one, nvcc, s, o, extra): s for s, o in zip(srcs, objs)}
+                for n, fut in enumerate(concurrent.futures.as_completed(futs), 1):
+                    log = fut.result()
+                    _say(f"  [{n}/{len(srcs)}] {futs[fut]} done ({time.time() - t0:.0f}s)")
+                    if (verbose or ptxas_info) and log.strip():
+                        print(log, file=sys.stderr, flush=True)
+            tmp = lib_path + f".tmp{os.getpid()}"
+            cmd = [nvcc, "-shared", "-o", tmp] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"]
+            p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+            if p.returncode != 0:
+                raise BuildError(f"link failed:\n{' '.join(cmd)}\n{p.stdout}")
+            os.replace(tmp, lib_path)
+            for o in objs:
+                os.remove(o)
+            _say(f"built {LIB_NAME} in {time.time() - t0:.0f}s")
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+    return lib_path
+
+
+def load() -> ctypes.CDLL:
+    """The loaded kernel library (built first if needed)."""
+    global _lib
+    if _lib is None:
+        path = build()
+        try:
+            _lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise BuildError(f"cannot load {path}: {e}") from None
+    return _lib

@@ -1,0 +1,228 @@
+"""Python face of the CUDA kernels: argument checks, then one launch each.
+
+Tensors are ``torch`` CUDA tensors used as typed device buffers; the launchers
+get their pointers and the current stream.  Every function refuses what the
+kernel behind it cannot do with a :class:`KernelError` that says why.  Nothing
+here runs on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_F = ctypes.c_float
+
+_SIGNATURES = {
+    "vcb_embedding": [_P, _P, _P, _I, _I, _I, _P],
+    "vcb_add_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _P],
+    "vcb_silu_mul": [_P, _P, _I, _I, _I, _P],
+    "vcb_add_bias": [_P, _P, _I, _I, _I, _P],
+    "vcb_rope_cache_write": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "vcb_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "vcb_repetition_penalty": [_P, _I, _P, _P, _P, _I, _I, _P],
+    "vcb_sample": [_P, _I, _I, _P, _P, _P, _I, _P],
+}
+
+
+def lib():
+    """The kernel library; built and loaded on first use."""
+    global _lib
+    if _lib is None:
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this engine runs on an sm_100a GPU only and has no CPU path")
+        l = _build.load()
+        for name, sig in _SIGNATURES.items():
+            fn = getattr(l, name, None)
+            if fn is None:
+                raise KernelError(f"kernel library lacks {name}; rebuild it (delete csrc/_build)")
+            fn.argtypes = sig
+            fn.restype = _I
+        _lib = l
+    return _lib
+
+
+def register_signature(name: str, sig) -> None:
+    """Declare one more exported launcher (used by kernel files added later)."""
+    _SIGNATURES[name] = sig
+    if _lib is not None:
+        fn = getattr(_lib, name)
+        fn.argtypes = sig
+        fn.restype = _I
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == 10001:
+        raise KernelError(f"{what}: the kernel refused its arguments")
+    if code == 10002:
+        raise KernelError(f"{what}: size not supported by this kernel")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"storage type {dt} is not supported (float32 or bfloat16)")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _dev(t: torch.Tensor, name: str, dtype=None) -> int:
+    _need(t.is_cuda, f"{name} must live on the GPU")
+    _need(t.is_contiguous(), f"{name} must be contiguous")
+    if dtype is not None:
+        _need(t.dtype == dtype, f"{name} must be {dtype}, is {t.dtype}")
+    return t.data_ptr()
+
+
+# --------------------------------------------------------------------- ops
+def embedding(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual[t] = float(table[ids[t]]); ids int32 [n], residual float32 [n, hidden]."""
+    n, hidden = residual.shape
+    _need(table.dim() == 2 and table.shape[1] == hidden, "embedding table width differs from the residual's")
+    _need(ids.numel() == n, "one id per residual row")
+    _check(lib().vcb_embedding(_dev(table, "table"), _dev(ids, "ids", torch.int32),
+                               _dev(residual, "residual", torch.float32), n, hidden,
+                               dtype_code(table.dtype), _stream()), "embedding")
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor,
+                out: torch.Tensor, eps: float, row_index: Optional[torch.Tensor] = None) -> None:
+    """out = rmsnorm(residual (+ delta)) * gain; the sum is written back to residual unless rows are gathered."""
+    hidden = residual.shape[1]
+    n_rows = out.shape[0]
+    _need(out.shape[1] == hidden and gain.numel() == hidden, "add_rmsnorm: widths differ")
+    if delta is not None:
+        _need(delta.shape == residual.shape and delta.dtype == out.dtype, "add_rmsnorm: delta shape or type differs")
+    if row_index is None:
+        _need(n_rows == residual.shape[0], "add_rmsnorm: one output row per residual row")
+    else:
+        _need(row_index.numel() == n_rows, "add_rmsnorm: one row index per output row")
+    _check(lib().vcb_add_rmsnorm(_dev(residual, "residual", torch.float32),
+                                 None if delta is None else _dev(delta, "delta"),
+                                 _dev(gain, "gain", torch.float32), _dev(out, "out"),
+                                 None if row_index is None else _dev(row_index, "row_index", torch.int32),
+                                 n_rows, hidden, float(eps), dtype_code(out.dtype), _stream()), "add_rmsnorm")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, inter + i]."""
+    n, inter = out.shape
+    _need(gate_up.shape == (n, 2 * inter) and gate_up.dtype == out.dtype, "silu_mul: gate_up must be [n, 2*inter]")
+    _check(lib().vcb_silu_mul(_dev(gate_up, "gate_up"), _dev(out, "out"), n, inter,
+                              dtype_code(out.dtype), _stream()), "silu_mul")
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
+    """x[t, c] += bias[c] in place."""
+    rows, cols = x.shape
+    _need(bias.numel() == cols, "add_bias: one bias value per column")
+    _check(lib().vcb_add_bias(_dev(x, "x"), _dev(bias, "bias", torch.float32), rows, cols,
+                              dtype_code(x.dtype), _stream()), "add_bias")
+
+
+def rope_cache_write(qkv, bias, positions, req_of_token, block_table, denom, q_out, cache, *,
+                     num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int, pairing: int,
+                     page_size: int, write_kv: bool) -> None:
+    """Bias, rotation and cache write in one pass over the q/k/v product (see elementwise.cu)."""
+    n = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    _need(qkv.shape == (n, width), f"qkv must be [n, {width}], is {tuple(qkv.shape)}")
+    _need(q_out.shape == (n, num_heads * head_dim) and q_out.dtype == qkv.dtype, "q_out shape or type")
+    _need(head_dim % 2 == 0 and rotary_dim % 2 == 0 and 0 <= rotary_dim <= head_dim, "rotary_dim must be even and <= head_dim")
+    _need(cache.dtype == qkv.dtype, "cache and activations must share a storage type")
+    if rotary_dim:
+        _need(denom is not None and denom.numel() == rotary_dim // 2, "denom must hold rotary_dim/2 values")
+    if bias is not None:
+        _need(bias.numel() == width, "bias width")
+    _check(lib().vcb_rope_cache_write(
+        _dev(qkv, "qkv"), None if bias is None else _dev(bias, "bias", torch.float32),
+        _dev(positions, "positions", torch.int32), _dev(req_of_token, "req_of_token", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+        None if denom is None else _dev(denom, "denom", torch.float32), _dev(q_out, "q_out"),
+        _dev(cache, "cache"), n, num_heads, num_kv_heads, head_dim, rotary_dim, pairing, page_size,
+        1 if write_kv else 0, dtype_code(qkv.dtype), _stream()), "rope_cache_write")
+
+
+def attention_simt(q, cache, out, positions, req_of_token, block_table, *, num_heads: int,
+                   num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float) -> None:
+    n = q.shape[0]
+    _need(head_dim <= 256, f"head_dim {head_dim} exceeds 256, the largest this attention kernel takes")
+    _need(q.shape == (n, num_heads * head_dim) and out.shape == q.shape and out.dtype == q.dtype, "q/out shape")
+    _need(num_heads % num_kv_heads == 0, "num_heads must be a multiple of num_kv_heads")
+    _need(cache.dtype == q.dtype, "cache and q must share a storage type")
+    _check(lib().vcb_attention_simt(
+        _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(positions, "positions", torch.int32),
+        _dev(req_of_token, "req_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
+        block_table.shape[1], n, num_heads, num_kv_heads, head_dim, page_size, window, float(scale),
+        dtype_code(q.dtype), _stream()), "attention_simt")
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T in true 32-bit arithmetic; rows may be strided."""
+    m, k = a.shape
+    n = w.shape[0]
+    _need(w.shape[1] == k and out.shape == (m, n), "gemm_f32: shapes do not agree")
+    for t, name in ((a, "a"), (w, "w"), (out, "out")):
+        _need(t.is_cuda and t.dtype == torch.float32 and t.stride(1) == 1, f"gemm_f32: {name} must be float32 with unit inner stride")
+    _check(lib().vcb_gemm_f32(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k,
+                              a.stride(0), w.stride(0), out.stride(0), _stream()), "gemm_f32")
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x @ w^T.  float32: the engine's own FMA kernel.  bfloat16: the library
+    product (cuBLAS through torch.mm), float accumulation, out bfloat16 or float32."""
+    if x.dtype == torch.float32:
+        gemm_f32(x, w, out)
+        return
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear: operands must both be bfloat16")
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, w.t(), out=out)
+    else:
+        _need(out.dtype == torch.float32, "linear: out must be bfloat16 or float32")
+        try:
+            torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+        except (TypeError, RuntimeError):
+            out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))
+
+
+def repetition_penalty(logits, ids, row_start, penalty) -> None:
+    n, vocab = logits.shape
+    _check(lib().vcb_repetition_penalty(_dev(logits, "logits", torch.float32), logits.stride(0),
+                                        _dev(ids, "ids", torch.int32), _dev(row_start, "row_start", torch.int32),
+                                        _dev(penalty, "penalty", torch.float32), n, vocab, _stream()),
+           "repetition_penalty")
+
+
+def sample(logits, temperature, uniform, out) -> None:
+    """out[r] = argmax (temperature <= 0) or an inverse-CDF draw with uniform[r] in id order."""
+    n, vocab = logits.shape
+    _need(logits.is_cuda and logits.dtype == torch.float32 and logits.stride(1) == 1, "logits must be float32 rows")
+    _check(lib().vcb_sample(logits.data_ptr(), logits.stride(0), vocab, _dev(temperature, "temperature", torch.float32),
+                            _dev(uniform, "uniform", torch.float32), _dev(out, "out", torch.int32), n, _stream()),
+           "sample")

@@ -1,0 +1,114 @@
+"""Grouped-query self-attention over the paged cache.
+
+q = x Wq^T + bq, k = x Wk^T + bk, v = x Wv^T + bv (bias on q, k, v only in Qwen2:
+src/layers/attention.cpp:19-22,74-76); position encoding on q and k
+(:79); k and v go to the cache (:84-102); query head h reads kv head
+h // (heads / kv_heads) with scale 1/sqrt(d) (:126, src/attention/paged_attention.cu:19);
+the result is projected by Wo (:134).
+
+Unlike the reference, q, k and v are one product against [Wq; Wk; Wv]
+(concatenated at load), the bias, the rotation and the cache write are one kernel,
+a query at position p sees keys 0..p of its own request whatever the batch holds
+(the reference has no mask and relies on one token per call), and ``window`` > 0
+restricts that to the last ``window`` keys, the query's own included.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import numpy as np
+import torch
+
+from ..config.model_spec import PartSpec
+from ..csrc import ops
+from .base import (POSITION_ENCODINGS, Mixer, PagedKVSpec, ParamSpec, build_part, register_mixer)
+
+MAX_HEAD_DIM = 256
+
+
+@register_mixer("attention")
+class PagedAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 qkv_bias: bool, out_bias: bool, window: int, position: PartSpec, dtype, device):
+        if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads:
+            raise ValueError(f"attention: {num_heads} heads cannot share {num_kv_heads} kv heads")
+        if head_dim <= 0 or head_dim % 2:
+            raise ValueError(f"attention: head_dim {head_dim} must be positive and even")
+        if head_dim > MAX_HEAD_DIM:
+            raise ValueError(f"attention: head_dim {head_dim} exceeds {MAX_HEAD_DIM}, the largest the kernels take")
+        if out_bias:
+            raise ValueError("attention: a bias on the output projection is not built")
+        if window < 0:
+            raise ValueError("attention: window must be 0 (all keys) or positive")
+        self.hidden, self.nh, self.nkv, self.d = hidden_size, num_heads, num_kv_heads, head_dim
+        self.qkv_bias, self.window = bool(qkv_bias), int(window)
+        self.dtype, self.device = dtype, device
+        self.position = build_part(POSITION_ENCODINGS, "position encoding", position, dtype=dtype, device=device)
+        # 1/sqrtf(d) in float, as src/layers/attention.cpp:126 computes it
+        self.scale = float(np.float32(1.0) / np.sqrt(np.float32(head_dim)))
+        self.w_qkv = None
+        self.b_qkv = None
+        self.w_o = None
+
+    # -- tensors
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        q, kv = self.nh * self.d, self.nkv * self.d
+        specs = {"q_proj.weight": ParamSpec((q, self.hidden)),
+                 "k_proj.weight": ParamSpec((kv, self.hidden)),
+                 "v_proj.weight": ParamSpec((kv, self.hidden)),
+                 "o_proj.weight": ParamSpec((self.hidden, q))}
+        if self.qkv_bias:
+            specs.update({"q_proj.bias": ParamSpec((q,), "bias"),
+                          "k_proj.bias": ParamSpec((kv,), "bias"),
+                          "v_proj.bias": ParamSpec((kv,), "bias")})
+        for name, s in self.position.param_specs().items():
+            specs["position." + name] = s
+        return specs
+
+    def load_params(self, tensors):
+        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
+                                tensors["v_proj.weight"]], dim=0).contiguous()
+        self.w_o = tensors["o_proj.weight"].contiguous()
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"],
+                                    tensors["v_proj.bias"]], dim=0).contiguous()
+        self.position.load_params({k[len("position."):]: v for k, v in tensors.items()
+                                   if k.startswith("position.")})
+
+    # -- cache
+    def cache_spec(self):
+        return PagedKVSpec(self.nkv, self.d, self.window)
+
+    # -- run
+    def forward(self, x, out, step, cache, writes_cache, ws):
+        n = x.shape[0]
+        mark = ws.mark()
+        qkv = ws.take((n, (self.nh + 2 * self.nkv) * self.d), self.dtype)
+        ops.linear(x, self.w_qkv, qkv)
+        q = ws.take((n, self.nh * self.d), self.dtype)
+        block_table = step.block_tables[cache.group]
+        fused = self.position.fused()
+        bias = self.b_qkv
+        if fused is None:
+            # An encoding the fused kernel does not know: bias first, then the
+            # encoding's own code on q and k, then the plain copy into the cache.
+            if bias is not None:
+                ops.add_bias(qkv, bias)
+                bias = None
+            q3 = qkv[:, : self.nh * self.d].unflatten(1, (self.nh, self.d))
+            k3 = qkv[:, self.nh * self.d: (self.nh + self.nkv) * self.d].unflatten(1, (self.nkv, self.d))
+            self.position.apply(q3, k3, step.positions)
+            fused = {"rotary_dim": 0, "pairing": 0, "denom": None}
+        ops.rope_cache_write(qkv, bias, step.positions, step.req_of_token, block_table, fused["denom"], q,
+                             cache.pages, num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d,
+                             rotary_dim=fused["rotary_dim"], pairing=fused["pairing"],
+                             page_size=cache.page_size, write_kv=writes_cache)
+        attn = ws.take((n, self.nh * self.d), self.dtype)
+        self.attend(q, attn, step, cache, block_table)
+        ops.linear(attn, self.w_o, out)
+        ws.release(mark)
+
+    def attend(self, q, attn, step, cache, block_table):
+        ops.attention_simt(q, cache.pages, attn, step.positions, step.req_of_token, block_table,
+                           num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d,
+                           page_size=cache.page_size, window=self.window, scale=self.scale)

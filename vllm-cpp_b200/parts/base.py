@@ -1,0 +1,227 @@
+"""Interfaces and registries of the parts a decoder is put together from.
+
+A part is built from its own parameters only (sizes, constants), declares its
+tensors with local names, and runs on what the step hands it.  Five kinds are
+registered by name: mixers, feed-forwards, norms, position encodings and block
+arrangements.  The reference has these as fixed classes wired inside QwenModel
+(src/layers/attention.cpp, src/layers/mlp.cpp, src/kernels/layernorm.cu,
+src/kernels/rotary_embedding.cu, src/model/qwen.cpp:300-318).
+
+Adding a part: subclass the interface, decorate the class with the matching
+``register_*`` and name it in a ``PartSpec``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+
+
+# ----------------------------------------------------------------- parameters
+@dataclass
+class ParamSpec:
+    """One tensor of a part.
+
+    role "matrix": a product's weight, held in the compute type, random N(0, std).
+    role "bias":   added in float, held in float32, random N(0, std).
+    role "gain":   a norm's scale, held in float32, random 1 + N(0, gain_std).
+    """
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+
+
+# -------------------------------------------------------------------- caches
+@dataclass(frozen=True)
+class PagedKVSpec:
+    """Keys and values in pages.  ``window`` 0: all keys are kept; > 0: only the
+    last ``window`` keys are read, pages left of the window are given back."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size, one slot per live request, zero at admission."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class PagedKVView:
+    """What a mixer sees of a paged cache layer."""
+    pages: torch.Tensor          # [num_pages, 2, num_kv_heads, page_size, head_dim]
+    group: int                   # index into StepContext.block_tables
+    page_size: int
+
+
+@dataclass
+class StateView:
+    slots: torch.Tensor          # [num_slots, *shape]
+
+
+# ------------------------------------------------------------------ the step
+@dataclass
+class StepContext:
+    """One batch as the parts see it: device arrays plus host copies of the small ones.
+
+    Tokens are laid out request by request; request r owns rows
+    ``q_start[r] : q_start[r + 1]`` at positions ``ctx_lens[r] + 0, 1, …``.
+    """
+    n_tokens: int
+    n_reqs: int
+    token_ids: torch.Tensor              # int32 [n_tokens]
+    positions: torch.Tensor              # int32 [n_tokens]
+    req_of_token: torch.Tensor           # int32 [n_tokens]
+    q_start: torch.Tensor                # int32 [n_reqs + 1]
+    ctx_lens: torch.Tensor               # int32 [n_reqs], tokens in the cache before this step
+    block_tables: List[torch.Tensor]     # per paged group: int32 [n_reqs, max_blocks]
+    state_slots: torch.Tensor            # int32 [n_reqs]
+    logit_rows: torch.Tensor             # int32 [n_wanted]
+    n_logit_rows: int
+    h_q_start: List[int]
+    h_ctx_lens: List[int]
+    h_state_slots: List[int]
+    decode_only: bool                    # every request brings exactly one token
+    max_q_len: int
+    max_total_len: int                   # longest context after this step
+    extras: Dict[str, object] = field(default_factory=dict)   # per-step device arrays of kernels
+
+
+class Workspace:
+    """Bump allocator for a step's temporaries, reset at the start of each step.
+
+    ``take`` hands out views of one device buffer, so a step of a given size
+    touches the same addresses every time (needed under CUDA graphs) and makes no
+    device allocation once the buffer has reached its size.  The buffer grows on
+    demand outside graph capture.
+    """
+
+    def __init__(self, device, nbytes: int = 0):
+        self.device = device
+        self.buf = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        self.offset = 0
+        self.high_water = 0
+        self.frozen = False
+
+    def reset(self) -> None:
+        self.offset = 0
+
+    def mark(self) -> int:
+        return self.offset
+
+    def release(self, mark: int) -> None:
+        self.offset = mark
+
+    def take(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        numel = 1
+        for s in shape:
+            numel *= int(s)
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        start = (self.offset + 255) // 256 * 256
+        end = start + nbytes
+        if end > self.buf.numel():
+            if self.frozen:
+                raise RuntimeError(f"workspace of {self.buf.numel()} bytes is too small for this step "
+                                   f"({end} needed) and may not grow now")
+            new = torch.empty(max(end, int(self.buf.numel() * 1.5)), dtype=torch.uint8, device=self.device)
+            self.buf = new                   # views handed out earlier keep the old buffer alive
+        self.offset = end
+        self.high_water = max(self.high_water, end)
+        return self.buf[start:end].view(dtype).view(*shape)
+
+
+# --------------------------------------------------------------------- parts
+class Part:
+    """Common to all parts: declared tensors and their placement."""
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {}
+
+    def load_params(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Receives the tensors of ``param_specs`` (on the device, roles' types applied)."""
+
+
+class PositionEncoding(Part):
+    """How positions enter a mixer.
+
+    ``fused()`` returns the arguments of the built-in rotation
+    (``rotary_dim``, ``pairing``, ``denom``) when the encoding is one that the
+    fused bias + rotation + cache-write kernel performs, else None; then
+    ``apply`` is called on the biased q and k before the cache write.
+    """
+
+    def fused(self) -> Optional[dict]:
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        """In place.  q: [n, heads, d] and k: [n, kv_heads, d] strided views."""
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
+                row_index: Optional[torch.Tensor] = None) -> None:
+        """residual += delta (float32, in place, unless rows are gathered); out = norm(residual)."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    """Mixes information between the tokens of a request (attention here)."""
+
+    def cache_spec(self):
+        """PagedKVSpec, StateSpec or None."""
+        return None
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext, cache, writes_cache: bool,
+                ws: Workspace) -> None:
+        """x, out: [n_tokens, hidden] in the compute type."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext, ws: Workspace) -> None:
+        raise NotImplementedError
+
+
+class Block:
+    """Arrangement of a layer's parts around the residual stream."""
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+
+    def forward(self, residual: torch.Tensor, delta: torch.Tensor, has_delta: bool, step: StepContext,
+                cache, writes_cache: bool, ws: Workspace) -> bool:
+        """Runs the layer.  ``delta`` holds a pending addition to ``residual`` when
+        ``has_delta``; on return it holds this layer's pending addition.  Returns True."""
+        raise NotImplementedError
+
+
+# ----------------------------------------------------------------- registries
+MIXERS: Dict[str, Callable] = {}
+FEED_FORWARDS: Dict[str, Callable] = {}
+NORMS: Dict[str, Callable] = {}
+POSITION_ENCODINGS: Dict[str, Callable] = {}
+BLOCKS: Dict[str, Callable] = {}
+
+
+def _register(table, name):
+    def deco(cls):
+        table[name] = cls
+        return cls
+    return deco
+
+
+def register_mixer(name): return _register(MIXERS, name)
+def register_feed_forward(name): return _register(FEED_FORWARDS, name)
+def register_norm(name): return _register(NORMS, name)
+def register_position_encoding(name): return _register(POSITION_ENCODINGS, name)
+def register_block(name): return _register(BLOCKS, name)
+
+
+def build_part(table: Dict[str, Callable], what: str, spec, **context):
+    if spec.kind not in table:
+        raise ValueError(f"unknown {what} {spec.kind!r}; registered: {sorted(table)}")
+    return table[spec.kind](**spec.params, **context)

@@ -1,0 +1,44 @@
+"""Gated feed-forward: down( act(gate(x)) * up(x) ), no biases
+(src/layers/mlp.cpp:49-64; silu of src/kernels/activation.cu:8-10).
+
+gate and up are one product against the row-wise concatenation [W_gate; W_up],
+made at load; the reference runs them as two.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..csrc import ops
+from .base import FeedForward, ParamSpec, register_feed_forward
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str, dtype, device):
+        if activation != "silu":
+            raise ValueError(f"gated_mlp: activation {activation!r} is not built (only 'silu')")
+        self.hidden, self.inter = hidden_size, intermediate_size
+        self.dtype, self.device = dtype, device
+        self.w_gate_up = None     # [2*inter, hidden]
+        self.w_down = None        # [hidden, inter]
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"gate_proj.weight": ParamSpec((self.inter, self.hidden)),
+                "up_proj.weight": ParamSpec((self.inter, self.hidden)),
+                "down_proj.weight": ParamSpec((self.hidden, self.inter))}
+
+    def load_params(self, tensors):
+        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
+        self.w_down = tensors["down_proj.weight"].contiguous()
+
+    def forward(self, x, out, step, ws):
+        n = x.shape[0]
+        mark = ws.mark()
+        gate_up = ws.take((n, 2 * self.inter), self.dtype)
+        ops.linear(x, self.w_gate_up, gate_up)
+        act = ws.take((n, self.inter), self.dtype)
+        ops.silu_mul(gate_up, act)
+        ops.linear(act, self.w_down, out)
+        ws.release(mark)

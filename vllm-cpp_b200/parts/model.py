@@ -1,0 +1,127 @@
+"""A decoder put together from a ModelSpec: embedding, layers in their run order,
+final norm, output product.
+
+Flow of one step (src/model/qwen.cpp:291-328): ids -> embedding -> for each entry
+of the run order, the layer's block on the residual stream -> final norm ->
+lm_head.  Differences from the reference: the residual additions happen inside
+the norm kernels; only the rows whose logits are wanted go through the final norm
+and the output product (the reference computes logits for every token, :321-325);
+the output matrix is the embedding table when ``tie_word_embeddings`` is set and a
+tensor of its own otherwise (the reference overwrites the table with an untied
+lm_head, :228-233,279-281).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.model_spec import ModelSpec
+from ..csrc import ops
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, PagedKVSpec, ParamSpec, StateSpec, StepContext,
+                   Workspace, build_part)
+# importing the modules registers the built-in parts
+from . import attention as _attention, block as _block, mlp as _mlp, norm as _norm, position as _position  # noqa: F401
+
+TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device):
+        spec.validate()
+        self.spec, self.dtype, self.device = spec, dtype, device
+        self.hidden, self.vocab = spec.hidden_size, spec.vocab_size
+        ctx = {"dtype": dtype, "device": device}
+        self.blocks = []
+        for i, ls in enumerate(spec.layers):
+            if ls.block not in BLOCKS:
+                raise ValueError(f"layer {i}: unknown block arrangement {ls.block!r}; registered: {sorted(BLOCKS)}")
+            self.blocks.append(BLOCKS[ls.block](
+                mixer=build_part(MIXERS, "mixer", ls.mixer, **ctx),
+                feed_forward=build_part(FEED_FORWARDS, "feed-forward", ls.feed_forward, **ctx),
+                mixer_norm=build_part(NORMS, "norm", ls.mixer_norm, **ctx),
+                feed_forward_norm=build_part(NORMS, "norm", ls.feed_forward_norm, **ctx)))
+        self.final_norm = build_part(NORMS, "norm", spec.final_norm, **ctx)
+        self.embed: Optional[torch.Tensor] = None
+        self.lm_head: Optional[torch.Tensor] = None
+        self._check_cache_sharing()
+
+    # ------------------------------------------------------------------ cache
+    def cache_specs(self) -> List[object]:
+        """The cache need of every cache layer, in order (PagedKVSpec, StateSpec or None)."""
+        specs: List[object] = [None] * self.spec.num_cache_layers
+        for call in self.spec.run_order:
+            if call.writes_cache:
+                specs[call.cache] = self.blocks[call.layer].mixer.cache_spec()
+        return specs
+
+    def _check_cache_sharing(self) -> None:
+        specs = self.cache_specs()
+        for i, call in enumerate(self.spec.run_order):
+            if not call.writes_cache:
+                own = self.blocks[call.layer].mixer.cache_spec()
+                if own != specs[call.cache]:
+                    raise ValueError(f"run_order[{i}]: layer {call.layer} needs {own} but reads cache "
+                                     f"{call.cache} of kind {specs[call.cache]}")
+
+    # ---------------------------------------------------------------- tensors
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        """Every tensor of the model under its checkpoint name."""
+        s = self.spec
+        out = {s.embed_name: ParamSpec((self.vocab, self.hidden))}
+        for ls, blk in zip(s.layers, self.blocks):
+            for slot in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm"):
+                for local, ps in getattr(blk, slot).param_specs().items():
+                    out[ls.names[slot] + local] = ps
+        for local, ps in self.final_norm.param_specs().items():
+            out[s.final_norm_prefix + local] = ps
+        if not s.tie_word_embeddings:
+            out[s.lm_head_name] = ParamSpec((self.vocab, self.hidden))
+        return out
+
+    def placement(self, role: str) -> torch.dtype:
+        return self.dtype if role == "matrix" else torch.float32
+
+    def load_params(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """``tensors``: checkpoint name -> device tensor in the role's type (see weights/loader.py)."""
+        s = self.spec
+        self.embed = tensors[s.embed_name].contiguous()
+        self.lm_head = self.embed if s.tie_word_embeddings else tensors[s.lm_head_name].contiguous()
+        for ls, blk in zip(s.layers, self.blocks):
+            for slot in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm"):
+                prefix = ls.names[slot]
+                part = getattr(blk, slot)
+                part.load_params({local: tensors[prefix + local] for local in part.param_specs()})
+        self.final_norm.load_params({local: tensors[s.final_norm_prefix + local]
+                                     for local in self.final_norm.param_specs()})
+
+    def weight_bytes(self) -> int:
+        """Bytes of the matrices a decode step reads once (embedding rows excluded unless tied)."""
+        total = 0
+        for blk in self.blocks:
+            for part in (blk.mixer, blk.feed_forward):
+                for v in vars(part).values():
+                    if isinstance(v, torch.Tensor) and v.dim() == 2:
+                        total += v.numel() * v.element_size()
+        total += self.lm_head.numel() * self.lm_head.element_size()
+        return total
+
+    # -------------------------------------------------------------------- run
+    def forward(self, step: StepContext, caches: List[object], ws: Workspace,
+                logits: torch.Tensor) -> torch.Tensor:
+        """Runs the step's tokens; fills and returns logits[:n_logit_rows] (float32 [rows, vocab])."""
+        n = step.n_tokens
+        residual = ws.take((n, self.hidden), torch.float32)
+        delta = ws.take((n, self.hidden), self.dtype)
+        ops.embedding(self.embed, step.token_ids, residual)
+        has_delta = False
+        for call in self.spec.run_order:
+            has_delta = self.blocks[call.layer].forward(residual, delta, has_delta, step, caches[call.cache],
+                                                        call.writes_cache, ws)
+        m = step.n_logit_rows
+        out = logits[:m]
+        if m:
+            normed = ws.take((m, self.hidden), self.dtype)
+            self.final_norm.forward(residual, delta if has_delta else None, normed, step.logit_rows)
+            ops.linear(normed, self.lm_head, out)
+        return out
