@@ -48,7 +48,10 @@ def make_weights(cfg, seed, dtype, sharp=None):
     if sharp is None:
         # q and k scaled up so that attention is peaked and one wrong key shows;
         # less so in bfloat16, where rounding of large scores is itself visible
-        sharp = 6.0 if dtype == "float32" else 2.0
+        # The scores' standard deviation is (std * sharp)^2 * hidden; aim at 5 in
+        # 32-bit (a few keys carry nearly all the weight) and at 1.5 in bfloat16.
+        target = 5.0 if dtype == "float32" else 1.5
+        sharp = float(np.sqrt(target / cfg["hidden_size"]) / 0.08)
     w = plain.random_weights(cfg, seed, std=0.08, gain_std=0.1, sharp=sharp)
     return plain.round_to_bf16(w) if dtype == "bfloat16" else w
 
