@@ -1,0 +1,108 @@
+"""Generation through the Python entry point against the plain implementation:
+greedy and seeded sampling, requests alone and together, under a small token budget,
+and with so few pages that requests are preempted and recomputed."""
+import numpy as np
+import pytest
+
+import plain_qwen2 as plain
+from helpers import CONFIGS, make_weights, model_folder, token_ids
+
+pytestmark = pytest.mark.gpu
+
+
+def check_greedy(weights, cfg, prompt, out, dtype):
+    """Every generated token must be the plain implementation's choice given the tokens before
+    it, or lie within the logits' tolerance of that choice (a near tie decided by rounding)."""
+    from helpers import TOL
+    ids = list(prompt)
+    exact = 0
+    for tok in out:
+        logits = plain.forward(weights, cfg, ids)[-1]
+        best = plain.greedy(logits)
+        gap = (logits[best] - logits[tok]) / np.abs(logits).max()
+        assert gap <= 2 * TOL[dtype], f"token {tok} instead of {best}: gap {gap:.3e} after {len(ids)} tokens"
+        exact += tok == best
+        ids.append(tok)
+    return exact
+
+
+def make_llm(tmp_path, name, dtype, **kw):
+    from vllm_cpp_b200 import LLM
+    cfg, page = CONFIGS[name]
+    weights = make_weights(cfg, 21, dtype)
+    folder = model_folder(tmp_path, cfg, weights, dtype)
+    args = dict(dtype=dtype, block_size=page, num_gpu_blocks=64, max_num_seqs=8,
+                max_model_len=cfg["max_position_embeddings"], max_num_batched_tokens=256)
+    args.update(kw)
+    return cfg, weights, LLM(folder, **args)
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("C", "float32"), ("A", "bfloat16"),
+                                        ("D", "bfloat16")])
+def test_greedy_generation_matches_plain(tmp_path, name, dtype):
+    from vllm_cpp_b200 import SamplingParams
+    cfg, weights, llm = make_llm(tmp_path, name, dtype)
+    prompts = [token_ids(cfg, n, 50 + n) for n in (5, 17, 33)]       # the tiny workload of configuration A
+    outs = llm.generate(prompts, SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))
+    exact = sum(check_greedy(weights, cfg, p, o, dtype) for p, o in zip(prompts, outs))
+    assert all(len(o) == 8 for o in outs) and exact >= 20       # near ties are rare
+    assert not llm.engine.has_pending_work() and llm.engine.cache.num_free_pages() == 64
+
+
+def test_alone_together_budgeted_and_preempted_give_the_same_tokens(tmp_path):
+    """Configuration B's workload: prompts 1, 9, 40, 64, 100; a 24-token budget; temperature 0.8
+    with a fixed seed; 12 tokens each.  The draw is keyed by request seed and token index, so
+    the tokens may not depend on batching, on the budget or on preemption."""
+    from vllm_cpp_b200 import SamplingParams
+    name, dtype = "B", "float32"
+    cfg, _ = CONFIGS[name]
+    prompts = [token_ids(cfg, n, 70 + n) for n in (1, 9, 40, 64, 100)]
+    params = [SamplingParams(max_tokens=12, temperature=0.8, seed=1000 + i, ignore_eos=True) for i in range(5)]
+    _, weights, llm = make_llm(tmp_path, name, dtype)
+    alone = [llm.generate([p], sp)[0] for p, sp in zip(prompts, params)]
+    together = llm.generate(prompts, params)
+    _, _, budgeted = make_llm(tmp_path, name, dtype, max_tokens_per_step=24, max_num_batched_tokens=32)
+    cut = budgeted.generate(prompts, params)
+    # 7 pages of 32: the five requests need 9 at their longest, so some are preempted and recomputed
+    _, _, small = make_llm(tmp_path, name, dtype, num_gpu_blocks=7, max_tokens_per_step=24)
+    squeezed = small.generate(prompts, params)
+    assert small.engine.scheduler.num_preemptions > 0
+    assert together == alone and cut == alone and squeezed == alone
+    assert all(len(o) == 12 for o in alone)
+    # and the first sampled token of each is what the plain sampler draws from the plain logits
+    from vllm_cpp_b200.sampling.sampler import uniform_for
+    for p, sp, o in zip(prompts, params, alone):
+        logits = plain.forward(weights, cfg, p)[-1]
+        assert o[0] == plain.sample(logits, 0.8, 1.0, -1, 1.0, [], uniform_for(sp.seed, 0))
+
+
+def test_stop_token_and_length(tmp_path):
+    from vllm_cpp_b200 import SamplingParams
+    cfg, weights, llm = make_llm(tmp_path, "A", "float32")
+    p = token_ids(cfg, 12, 3)
+    free = llm.generate([p], SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True))[0]
+    stop = free[3]
+    out = llm.generate([p], SamplingParams(max_tokens=10, temperature=0.0, stop_token_ids=[stop]))[0]
+    assert out == free[:free.index(stop) + 1]
+    with pytest.raises(ValueError, match="context length"):
+        llm.generate([list(range(10))], SamplingParams(max_tokens=10_000))
+    with pytest.raises(ValueError, match="vocabulary"):
+        llm.generate([[cfg["vocab_size"]]], SamplingParams(max_tokens=1))
+    with pytest.raises(ValueError, match="at least one token"):
+        llm.generate([[]], SamplingParams(max_tokens=1))
+
+
+def test_long_decoding_stays_on_the_plain_logits(tmp_path):
+    """160 tokens decoded one by one after a 3-token prompt, replayed against the plain logits."""
+    from vllm_cpp_b200.engine.runner import StepEntry
+    for name, dtype in (("A", "float32"), ("C", "bfloat16")):
+        cfg, weights, llm = make_llm(tmp_path, name, dtype)
+        eng = llm.engine
+        ids = token_ids(cfg, 163, 9)
+        eng.cache.add_request("long")
+        rows = [eng.runner.step([StepEntry("long", ids[:3], [0, 1, 2])]).float().cpu().numpy()]
+        for t in range(3, len(ids)):
+            rows.append(eng.runner.step([StepEntry("long", ids[t:t + 1], [0])]).float().cpu().numpy())
+        eng.cache.free_request("long")
+        from helpers import compare
+        compare(np.concatenate(rows), plain.forward(weights, cfg, ids), dtype, f"{name} long decode")

@@ -8,3 +8,17 @@ from .config.registry import known_architectures, register_architecture, resolve
 from . import models as _models  # noqa: F401  (registers the architectures)
 
 __version__ = "0.1.0"
+
+
+def __getattr__(name):
+    # the entry points import the kernel library; load them only when asked for
+    if name == "LLM":
+        from .engine.llm import LLM
+        return LLM
+    if name == "Engine":
+        from .engine.llm_engine import Engine
+        return Engine
+    if name == "SamplingParams":
+        from .sampling.params import SamplingParams
+        return SamplingParams
+    raise AttributeError(name)

@@ -153,6 +153,16 @@ class CacheManager:
     def can_append(self, req_id, n_new: int) -> bool:
         return all(g.pool.can_allocate(n) for g, n in zip(self.paged, self.pages_needed(req_id, n_new)))
 
+    def max_appendable(self, req_id=None) -> int:
+        """Most tokens that the request (or, with None, a new request) could take now."""
+        if not self.paged:
+            return 1 << 30
+        if req_id is None:
+            return self.num_free_pages() * self.page_size
+        rc = self.requests[req_id]
+        return min((len(t) + g.pool.num_free) * self.page_size for g, t in zip(self.paged, rc.tables)) \
+            - rc.num_tokens
+
     def reserve(self, req_id, n_new: int) -> None:
         """Give the request pages for its next ``n_new`` tokens in every group, or none at all."""
         rc = self.requests[req_id]
@@ -169,7 +179,7 @@ class CacheManager:
         """The request now holds ``n_new`` more tokens; give back what windows have passed."""
         rc = self.requests[req_id]
         rc.num_tokens += n_new
-        if rc.num_tokens > min(len(t) for t in rc.tables) * self.page_size if rc.tables else False:
+        if rc.tables and rc.num_tokens > min(len(t) for t in rc.tables) * self.page_size:
             raise PageError(f"request {req_id!r} holds {rc.num_tokens} tokens but pages for fewer")
         for gi, g in enumerate(self.paged):
             w = g.spec.window

@@ -36,6 +36,7 @@ _SIGNATURES = {
     "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "vcb_repetition_penalty": [_P, _I, _P, _P, _P, _I, _I, _P],
     "vcb_sample": [_P, _I, _I, _P, _P, _P, _I, _P],
+    "vcb_sample_filtered": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
 }
 
 
@@ -226,3 +227,25 @@ def sample(logits, temperature, uniform, out) -> None:
     _check(lib().vcb_sample(logits.data_ptr(), logits.stride(0), vocab, _dev(temperature, "temperature", torch.float32),
                             _dev(uniform, "uniform", torch.float32), _dev(out, "out", torch.int32), n, _stream()),
            "sample")
+
+
+_filter_scratch: Optional[torch.Tensor] = None
+
+
+def sample_filtered(logits, temperature, uniform, top_p, top_k, out, scratch: Optional[torch.Tensor] = None) -> None:
+    """Redraws, in place in ``out``, the rows that have top-k or top-p set (see sampling.cu).
+    ``scratch``: float32, at least rows * vocab elements; one is kept and grown here if not given."""
+    global _filter_scratch
+    n, vocab = logits.shape
+    _need(logits.is_cuda and logits.dtype == torch.float32 and logits.stride(1) == 1, "logits must be float32 rows")
+    _need(vocab <= 1 << 20, f"top-k/top-p sampling takes vocabularies up to {1 << 20}, got {vocab}")
+    if scratch is None:
+        if _filter_scratch is None or _filter_scratch.numel() < n * vocab or _filter_scratch.device != logits.device:
+            _filter_scratch = torch.empty(n * vocab, dtype=torch.float32, device=logits.device)
+        scratch = _filter_scratch
+    _need(scratch.numel() >= n * vocab, "sample_filtered: scratch too small")
+    _check(lib().vcb_sample_filtered(logits.data_ptr(), logits.stride(0), vocab,
+                                     _dev(temperature, "temperature", torch.float32),
+                                     _dev(uniform, "uniform", torch.float32), _dev(top_p, "top_p", torch.float32),
+                                     _dev(top_k, "top_k", torch.int32), _dev(scratch, "scratch", torch.float32),
+                                     _dev(out, "out", torch.int32), n, _stream()), "sample_filtered")

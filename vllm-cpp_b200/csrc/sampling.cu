@@ -158,3 +158,165 @@ VCB_EXPORT int vcb_sample(const float* logits, int ld, int vocab, const float* t
     sample_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, ld, vocab, temperature, uniform, out);
     return vcb_last_error();
 }
+
+// --------------------------------------------------------- top-k / top-p
+// Rows with temperature > 0 and (top_p < 1 or top_k > 0) are drawn here, in order
+// of falling probability with ties by lower id, as the reference does after its
+// sort (src/sampler/sampler.cpp:52-71, src/sampler/topk_topp.cpp:8-35,49-56).
+// Nothing is sorted.  Every id gets the 52-bit key  (bits of e_i) << 20 | (0xFFFFF - i)
+// with e_i = exp((l_i - max) / T) >= 0, so a larger key means "earlier in the
+// reference's order".  With count(T) and sum(T) taken over the ids whose key is >= T:
+//   top-k keeps keys >= T_k, the largest T with count(T) >= k;
+//   top-p keeps keys >= T_p, the largest T with sum(T) >= p * sum(T_k);
+//   the draw returns the id of the largest T with sum(T) > u * sum(T_p).
+// Each threshold is found four bits at a time (13 passes over the row): a pass
+// bins the ids that agree with the bits found so far by their next four bits and
+// picks the largest digit for which the condition still holds.  The sums are
+// taken in a fixed order, so a row's result does not change from run to run.
+// e is kept in scratch memory supplied by the caller: rows * vocab floats.
+#define FILT_THREADS 1024
+enum { COND_COUNT_GE = 0, COND_SUM_GE = 1, COND_SUM_GT = 2 };
+
+__device__ __forceinline__ unsigned long long filt_key(float e, int id) {
+    return ((unsigned long long)__float_as_uint(e) << 20) | (unsigned long long)(0xFFFFF - id);
+}
+
+struct FiltShared {
+    float wsum[32][16];
+    int wcnt[32][16];
+    float tsum[16];
+    int tcnt[16];
+    int digit;
+    float above_sum, ge_sum;
+    int above_cnt, ge_cnt;
+};
+
+// The largest key T (52 bits) for which the condition holds, counting only ids with
+// key >= floor_key.  On return sh.ge_sum / sh.ge_cnt hold sum(T) / count(T).
+template <int COND>
+__device__ unsigned long long filt_search(const float* __restrict__ e, int vocab,
+                                          unsigned long long floor_key, float bound, FiltShared& sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    unsigned long long prefix = 0;
+    if (threadIdx.x == 0) { sh.above_sum = 0.0f; sh.above_cnt = 0; }
+    for (int shift = 48; shift >= 0; shift -= 4) {
+        float bs[16];
+        int bc[16];
+#pragma unroll
+        for (int v = 0; v < 16; ++v) { bs[v] = 0.0f; bc[v] = 0; }
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float ei = e[i];
+            const unsigned long long key = filt_key(ei, i);
+            if (key < floor_key) continue;
+            if ((key >> (shift + 4)) != (prefix >> (shift + 4))) continue;
+            const int d = (int)((key >> shift) & 15);
+#pragma unroll
+            for (int v = 0; v < 16; ++v)
+                if (d == v) { bs[v] += ei; bc[v] += 1; }
+        }
+#pragma unroll
+        for (int v = 0; v < 16; ++v) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                bs[v] += __shfl_xor_sync(0xffffffffu, bs[v], o);
+                bc[v] += __shfl_xor_sync(0xffffffffu, bc[v], o);
+            }
+        }
+        __syncthreads();
+        if (lane == 0) {
+#pragma unroll
+            for (int v = 0; v < 16; ++v) { sh.wsum[warp][v] = bs[v]; sh.wcnt[warp][v] = bc[v]; }
+        }
+        __syncthreads();
+        if (threadIdx.x < 16) {
+            float s = 0.0f;
+            int c = 0;
+            for (int w = 0; w < nwarps; ++w) { s += sh.wsum[w][threadIdx.x]; c += sh.wcnt[w][threadIdx.x]; }
+            sh.tsum[threadIdx.x] = s;
+            sh.tcnt[threadIdx.x] = c;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float s = sh.above_sum;
+            int c = sh.above_cnt;
+            int chosen = 0;
+            float chosen_above_s = s, chosen_s = s;
+            int chosen_above_c = c, chosen_c = c;
+            bool found = false;
+            for (int v = 15; v >= 0; --v) {
+                const float s_above = s;
+                const int c_above = c;
+                s += sh.tsum[v];
+                c += sh.tcnt[v];
+                bool ok;
+                if (COND == COND_COUNT_GE) ok = (float)c >= bound;
+                else if (COND == COND_SUM_GE) ok = s >= bound;
+                else ok = s > bound;
+                if (ok && !found) {
+                    found = true; chosen = v;
+                    chosen_above_s = s_above; chosen_above_c = c_above;
+                    chosen_s = s; chosen_c = c;
+                }
+            }
+            if (!found) {        // rounding at the very end of the row: take everything
+                chosen = 0; chosen_above_s = s - sh.tsum[0]; chosen_above_c = c - sh.tcnt[0];
+                chosen_s = s; chosen_c = c;
+            }
+            sh.digit = chosen;
+            sh.above_sum = chosen_above_s; sh.above_cnt = chosen_above_c;
+            sh.ge_sum = chosen_s; sh.ge_cnt = chosen_c;
+        }
+        __syncthreads();
+        prefix |= (unsigned long long)sh.digit << shift;
+    }
+    return prefix;
+}
+
+__global__ void __launch_bounds__(FILT_THREADS)
+sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temperature,
+                       const float* __restrict__ uniform, const float* __restrict__ top_p,
+                       const int* __restrict__ top_k, float* __restrict__ scratch, int* __restrict__ out) {
+    __shared__ FiltShared sh;
+    __shared__ float red[33];
+    const int row = blockIdx.x;
+    const float temp = temperature[row], p = top_p[row];
+    const int k = top_k[row];
+    if (!(temp > 0.0f) || !(p < 1.0f || k > 0)) return;      // sample_kernel has drawn this row
+    const float* l = logits + (size_t)row * ld;
+    float* e = scratch + (size_t)row * vocab;
+    const float inv_t = 1.0f / temp;
+
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, temp != 1.0f ? l[i] * inv_t : l[i]);
+    mx = block_max(mx, red);
+    float part = 0.0f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = expf((temp != 1.0f ? l[i] * inv_t : l[i]) - mx);
+        e[i] = v;
+        part += v;
+    }
+    float kept_sum = block_sum(part, red);        // also orders the writes of e before the reads below
+
+    unsigned long long floor_key = 0;
+    if (k > 0 && k < vocab) {
+        floor_key = filt_search<COND_COUNT_GE>(e, vocab, 0ull, (float)k, sh);
+        kept_sum = sh.ge_sum;
+    }
+    if (p < 1.0f) {
+        floor_key = filt_search<COND_SUM_GE>(e, vocab, floor_key, p * kept_sum, sh);
+        kept_sum = sh.ge_sum;
+    }
+    const unsigned long long t = filt_search<COND_SUM_GT>(e, vocab, floor_key, uniform[row] * kept_sum, sh);
+    if (threadIdx.x == 0) out[row] = 0xFFFFF - (int)(t & 0xFFFFFull);
+}
+
+VCB_EXPORT int vcb_sample_filtered(const float* logits, int ld, int vocab, const float* temperature,
+                                   const float* uniform, const float* top_p, const int* top_k,
+                                   float* scratch, int* out, int n_rows, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (vocab <= 0 || ld < vocab) return VCB_ERR_BAD_ARG;
+    if (vocab > (1 << 20)) return VCB_ERR_UNSUPPORTED;      // ids take 20 bits of the key
+    sample_filtered_kernel<<<n_rows, FILT_THREADS, 0, (cudaStream_t)stream>>>(
+        logits, ld, vocab, temperature, uniform, top_p, top_k, scratch, out);
+    return vcb_last_error();
+}
