@@ -1,0 +1,369 @@
+"""Each kernel alone against a plain numpy reference, at sizes other than the engine's
+tiny models: head sizes in steps of 16, odd head and group counts, widths and
+vocabularies that are no power of two, ragged edges of every tile."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def as_stored(a, dtype):
+    """float32 values as the device will hold them."""
+    return torch.from_numpy(np.asarray(a, dtype=np.float32)).to(DT[dtype]).float().numpy()
+
+
+def close(got, want, dtype, what, scale=None):
+    got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    scale = np.abs(want).max() if scale is None else scale
+    tol = 2e-6 if dtype == "float32" else 1e-2
+    err = np.abs(got - want).max()
+    assert err <= tol * scale, f"{what}: max |diff| {err:.3e} vs {tol} * {scale:.3e}"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from vllm_cpp_b200.csrc import ops
+    return ops
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding(ops, dtype):
+    rng = np.random.default_rng(0)
+    table = as_stored(rng.standard_normal((301, 88)), dtype)
+    ids = rng.integers(0, 301, size=37).astype(np.int32)
+    out = torch.empty((37, 88), dtype=torch.float32, device="cuda")
+    ops.embedding(dev(table, DT[dtype]), dev(ids), out)
+    assert np.array_equal(out.cpu().numpy(), plain.embedding(ids, table).astype(np.float32))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [48, 200, 3584, 5000])
+def test_add_rmsnorm(ops, dtype, hidden):
+    rng = np.random.default_rng(1)
+    res = rng.standard_normal((9, hidden)).astype(np.float32)
+    delta = as_stored(rng.standard_normal((9, hidden)), dtype)
+    gain = (1 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)
+    eps = 3e-5
+    # with delta: residual += delta, out = norm
+    r, out = dev(res), torch.empty((9, hidden), dtype=DT[dtype], device="cuda")
+    ops.add_rmsnorm(r, dev(delta, DT[dtype]), dev(gain), out, eps)
+    summed = res + delta
+    close(r.cpu().numpy(), summed, "float32", "residual sum")
+    close(out.float().cpu().numpy(), plain.rms_norm(summed.astype(np.float64), gain, eps), dtype, "norm")
+    # without delta the residual is untouched
+    r2 = dev(res)
+    ops.add_rmsnorm(r2, None, dev(gain), out, eps)
+    assert torch.equal(r2.cpu(), torch.from_numpy(res))
+    close(out.float().cpu().numpy(), plain.rms_norm(res.astype(np.float64), gain, eps), dtype, "norm no delta")
+    # gathered rows, one of them twice: nothing is written back
+    rows = np.array([7, 0, 7, 3], dtype=np.int32)
+    r3, out3 = dev(res), torch.empty((4, hidden), dtype=DT[dtype], device="cuda")
+    ops.add_rmsnorm(r3, dev(delta, DT[dtype]), dev(gain), out3, eps, dev(rows))
+    assert torch.equal(r3.cpu(), torch.from_numpy(res))
+    close(out3.float().cpu().numpy(), plain.rms_norm(summed[rows].astype(np.float64), gain, eps), dtype, "gathered")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul_and_bias(ops, dtype):
+    rng = np.random.default_rng(2)
+    gu = as_stored(3 * rng.standard_normal((5, 2 * 333)), dtype)
+    out = torch.empty((5, 333), dtype=DT[dtype], device="cuda")
+    ops.silu_mul(dev(gu, DT[dtype]), out)
+    close(out.float().cpu().numpy(), plain.silu(gu[:, :333].astype(np.float64)) * gu[:, 333:], dtype, "silu_mul")
+    x = as_stored(rng.standard_normal((4, 77)), dtype)
+    b = rng.standard_normal(77).astype(np.float32)
+    xd = dev(x, DT[dtype])
+    ops.add_bias(xd, dev(b))
+    close(xd.float().cpu().numpy(), x + b, dtype, "add_bias")
+
+
+def paged_layout(rng, n_reqs, max_len, page, n_pages):
+    """A random assignment of pages to requests: block tables [n_reqs, max_blocks]."""
+    blocks = -(-max_len // page)
+    assert n_reqs * blocks <= n_pages
+    perm = rng.permutation(n_pages)[: n_reqs * blocks].reshape(n_reqs, blocks)
+    return perm.astype(np.int32)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,d,rot,pairing", [(4, 2, 16, 16, 0), (3, 1, 32, 32, 0), (7, 7, 48, 24, 0),
+                                                   (2, 1, 128, 128, 0), (5, 5, 80, 80, 1), (6, 3, 64, 0, 0)])
+def test_rope_cache_write(ops, dtype, nh, nkv, d, rot, pairing):
+    rng = np.random.default_rng(3)
+    page, n_pages, n_reqs = 16, 12, 2
+    bt = paged_layout(rng, n_reqs, 80, page, n_pages)
+    req = np.array([0] * 9 + [1] * 4, dtype=np.int32)
+    pos = np.concatenate([np.arange(30, 39), np.arange(61, 65)]).astype(np.int32)     # crosses page edges
+    n = len(pos)
+    width = (nh + 2 * nkv) * d
+    qkv = as_stored(rng.standard_normal((n, width)), dtype)
+    bias = rng.standard_normal(width).astype(np.float32)
+    theta = 10000.0
+    denom = None
+    if rot:
+        j = np.arange(rot // 2, dtype=np.float32)
+        denom = np.power(np.float32(theta), (np.float32(2) * j) / np.float32(rot)).astype(np.float32)
+    cache = torch.zeros((n_pages, 2, nkv, page, d), dtype=DT[dtype], device="cuda")
+    q_out = torch.empty((n, nh * d), dtype=DT[dtype], device="cuda")
+    ops.rope_cache_write(dev(qkv, DT[dtype]), dev(bias), dev(pos), dev(req), dev(bt), None if denom is None else dev(denom),
+                         q_out, cache, num_heads=nh, num_kv_heads=nkv, head_dim=d, rotary_dim=rot, pairing=pairing,
+                         page_size=page, write_kv=True)
+    x = (qkv.astype(np.float64) + bias).reshape(n, nh + 2 * nkv, d)
+
+    def rotate(h):
+        if not rot:
+            return h
+        if pairing == 0:
+            return plain.rope(h, pos, theta, rot)
+        ang = plain.rope_angles(pos, theta, rot).astype(np.float64)[:, None, :]
+        out = h.copy()
+        a, b = h[..., 0:rot:2], h[..., 1:rot:2]
+        out[..., 0:rot:2] = a * np.cos(ang) - b * np.sin(ang)
+        out[..., 1:rot:2] = a * np.sin(ang) + b * np.cos(ang)
+        return out
+
+    q_ref, k_ref, v_ref = rotate(x[:, :nh]), rotate(x[:, nh:nh + nkv]), x[:, nh + nkv:]
+    close(q_out.float().cpu().numpy().reshape(n, nh, d), q_ref, dtype, "q")
+    c = cache.float().cpu().numpy()
+    for t in range(n):
+        pg, slot = bt[req[t], pos[t] // page], pos[t] % page
+        close(c[pg, 0, :, slot], k_ref[t], dtype, f"k of token {t}", scale=np.abs(k_ref).max())
+        close(c[pg, 1, :, slot], v_ref[t], dtype, f"v of token {t}", scale=np.abs(v_ref).max())
+    written = np.zeros((n_pages, page), dtype=bool)
+    for t in range(n):
+        written[bt[req[t], pos[t] // page], pos[t] % page] = True
+    assert not c.transpose(0, 3, 1, 2, 4)[~written].any(), "a slot that no token owns was written"
+    # write_kv off leaves the cache alone
+    cache2 = torch.zeros_like(cache)
+    ops.rope_cache_write(dev(qkv, DT[dtype]), dev(bias), dev(pos), dev(req), dev(bt), None if denom is None else dev(denom),
+                         q_out, cache2, num_heads=nh, num_kv_heads=nkv, head_dim=d, rotary_dim=rot, pairing=pairing,
+                         page_size=page, write_kv=False)
+    assert not cache2.any()
+
+
+def reference_attention(q, k, v, q_lens, ctx_lens, nh, nkv, window):
+    """q: [n, nh, d] for all requests' new tokens; k, v: per request [len, nkv, d] (whole sequences)."""
+    out = np.zeros_like(q)
+    t0 = 0
+    group = nh // nkv
+    d = q.shape[-1]
+    for r, (ql, cl) in enumerate(zip(q_lens, ctx_lens)):
+        for i in range(ql):
+            p = cl + i
+            lo = max(0, p - window + 1) if window else 0
+            for h in range(nh):
+                s = (k[r][lo:p + 1, h // group] @ q[t0 + i, h]) / np.sqrt(np.float32(d))
+                w = np.exp(s - s.max())
+                out[t0 + i, h] = (w / w.sum()) @ v[r][lo:p + 1, h // group]
+        t0 += ql
+    return out
+
+
+def attention_case(rng, dtype, nh, nkv, d, page, q_lens, ctx_lens, spike=True):
+    n_reqs = len(q_lens)
+    total = [c + q for c, q in zip(ctx_lens, q_lens)]
+    n_pages = sum(-(-t // page) for t in total) + 3
+    bt_rows = []
+    perm = list(rng.permutation(n_pages))
+    max_blocks = max(-(-t // page) for t in total) + 1
+    bt = np.full((n_reqs, max_blocks), -1, dtype=np.int32)
+    for r, t in enumerate(total):
+        for b in range(-(-t // page)):
+            bt[r, b] = perm.pop()
+    k = [as_stored(rng.standard_normal((t, nkv, d)), dtype) for t in total]
+    v = [as_stored(rng.standard_normal((t, nkv, d)), dtype) for t in total]
+    n = sum(q_lens)
+    q = as_stored(rng.standard_normal((n, nh, d)), dtype)
+    if spike:
+        # one far key per request gets a score that stands out: q of the last token points at key 1
+        t0 = 0
+        for r, ql in enumerate(q_lens):
+            if total[r] > 3:
+                k[r][1] = as_stored(k[r][1] * 3.0, dtype)
+                q[t0 + ql - 1] = as_stored(np.repeat(k[r][1], nh // nkv, axis=0) * 0.7, dtype)
+            t0 += ql
+    cache = np.zeros((n_pages, 2, nkv, page, d), dtype=np.float32)
+    for r, t in enumerate(total):
+        for p in range(t):
+            cache[bt[r, p // page], 0, :, p % page] = k[r][p]
+            cache[bt[r, p // page], 1, :, p % page] = v[r][p]
+    q_start = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    pos = np.concatenate([np.arange(c, c + ql) for c, ql in zip(ctx_lens, q_lens)]).astype(np.int32)
+    req = np.concatenate([np.full(ql, r) for r, ql in enumerate(q_lens)]).astype(np.int32)
+    return dict(q=q, k=k, v=v, cache=cache, bt=bt, q_start=q_start, pos=pos, req=req, n=n)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,d,page,window", [(4, 2, 16, 16, 0), (3, 1, 32, 32, 0), (5, 5, 48, 16, 20),
+                                                   (14, 2, 64, 16, 0), (2, 2, 256, 16, 0), (6, 3, 112, 48, 37)])
+def test_attention_simt(ops, dtype, nh, nkv, d, page, window):
+    rng = np.random.default_rng(4)
+    q_lens, ctx_lens = [1, 33, 2, 1], [300, 17, 0, 63]
+    c = attention_case(rng, dtype, nh, nkv, d, page, q_lens, ctx_lens)
+    out = torch.empty((c["n"], nh * d), dtype=DT[dtype], device="cuda")
+    ops.attention_simt(dev(c["q"].reshape(c["n"], -1), DT[dtype]), dev(c["cache"], DT[dtype]), out, dev(c["pos"]),
+                       dev(c["req"]), dev(c["bt"]), num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page,
+                       window=window, scale=float(np.float32(1) / np.sqrt(np.float32(d))))
+    want = reference_attention(c["q"].astype(np.float64), c["k"], c["v"], q_lens, ctx_lens, nh, nkv, window)
+    close(out.float().cpu().numpy().reshape(c["n"], nh, d), want, dtype, "attention_simt")
+
+
+@pytest.mark.parametrize("nh,nkv,d,page,window", [(28, 4, 128, 16, 0), (6, 2, 64, 32, 0), (3, 3, 64, 16, 40),
+                                                   (8, 1, 128, 16, 100), (40, 2, 128, 64, 0)])
+def test_attention_prefill_mma(ops, nh, nkv, d, page, window):
+    rng = np.random.default_rng(5)
+    q_lens, ctx_lens = [70, 1, 2, 129, 5], [0, 500, 63, 64, 1000]      # tile and page edges on both sides
+    c = attention_case(rng, "bfloat16", nh, nkv, d, page, q_lens, ctx_lens)
+    group = nh // nkv
+    tiles = [(r, k * 64) for r, ql in enumerate(q_lens) for k in range(-(-ql * group // 64))]
+    out = torch.zeros((c["n"], nh * d), dtype=torch.bfloat16, device="cuda")
+    ops.attention_prefill_mma(dev(c["q"].reshape(c["n"], -1), torch.bfloat16), dev(c["cache"], torch.bfloat16), out,
+                              dev(c["q_start"]), dev(np.array(ctx_lens, dtype=np.int32)), dev(c["bt"]),
+                              dev(np.array([t[0] for t in tiles], dtype=np.int32)),
+                              dev(np.array([t[1] for t in tiles], dtype=np.int32)),
+                              num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page, window=window,
+                              scale=float(np.float32(1) / np.sqrt(np.float32(d))))
+    want = reference_attention(c["q"].astype(np.float64), c["k"], c["v"], q_lens, ctx_lens, nh, nkv, window)
+    close(out.float().cpu().numpy().reshape(c["n"], nh, d), want, "bfloat16", "attention_prefill_mma")
+
+
+@pytest.mark.parametrize("nsplit", [1, 3, 8])
+@pytest.mark.parametrize("nh,nkv,d,page,window", [(28, 4, 128, 16, 0), (6, 2, 64, 32, 0), (3, 3, 64, 16, 40),
+                                                   (40, 2, 128, 16, 0), (16, 1, 128, 16, 200)])
+def test_attention_decode_mma(ops, nsplit, nh, nkv, d, page, window):
+    rng = np.random.default_rng(6)
+    ctx_lens = [0, 1, 63, 64, 65, 777, 2000]
+    q_lens = [1] * len(ctx_lens)
+    c = attention_case(rng, "bfloat16", nh, nkv, d, page, q_lens, ctx_lens)
+    n = c["n"]
+    out = torch.zeros((n, nh * d), dtype=torch.bfloat16, device="cuda")
+    part_o = torch.empty(n * nh * nsplit * d, dtype=torch.float32, device="cuda")
+    part_ml = torch.empty(n * nh * nsplit * 2, dtype=torch.float32, device="cuda")
+    ops.attention_decode_mma(dev(c["q"].reshape(n, -1), torch.bfloat16), dev(c["cache"], torch.bfloat16), out,
+                             dev(c["q_start"]), dev(np.array(ctx_lens, dtype=np.int32)), dev(c["bt"]), None, n, nsplit,
+                             part_o, part_ml, num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page,
+                             window=window, scale=float(np.float32(1) / np.sqrt(np.float32(d))))
+    want = reference_attention(c["q"].astype(np.float64), c["k"], c["v"], q_lens, ctx_lens, nh, nkv, window)
+    close(out.float().cpu().numpy().reshape(n, nh, d), want, "bfloat16", f"attention_decode_mma nsplit={nsplit}")
+    # a request list picks and reorders requests
+    sel = np.array([5, 2], dtype=np.int32)
+    out2 = torch.zeros_like(out)
+    ops.attention_decode_mma(dev(c["q"].reshape(n, -1), torch.bfloat16), dev(c["cache"], torch.bfloat16), out2,
+                             dev(c["q_start"]), dev(np.array(ctx_lens, dtype=np.int32)), dev(c["bt"]), dev(sel), 2, nsplit,
+                             part_o, part_ml, num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page,
+                             window=window, scale=float(np.float32(1) / np.sqrt(np.float32(d))))
+    got2 = out2.float().cpu().numpy().reshape(n, nh, d)
+    close(got2[[5, 2]], want[[5, 2]], "bfloat16", "decode with a request list")
+    assert not got2[[0, 1, 3, 4, 6]].any()
+
+
+def test_attention_refuses_what_it_cannot_do(ops):
+    q = torch.zeros((1, 2 * 80), dtype=torch.bfloat16, device="cuda")
+    z = torch.zeros(4, dtype=torch.int32, device="cuda")
+    cache = torch.zeros((2, 2, 2, 16, 80), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="head sizes"):
+        ops.attention_prefill_mma(q, cache, q, z, z, z.view(1, 4), z[:1], z[:1], num_heads=2, num_kv_heads=2,
+                                  head_dim=80, page_size=16, window=0, scale=1.0)
+    with pytest.raises(ops.KernelError, match="256"):
+        ops.attention_simt(torch.zeros((1, 272), dtype=torch.float32, device="cuda"), cache.float(), q.float(), z[:1],
+                           z[:1], z.view(1, 4), num_heads=1, num_kv_heads=1, head_dim=272, page_size=16, window=0, scale=1.0)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (7, 130, 33), (64, 64, 16), (200, 301, 96), (3, 1000, 513)])
+def test_gemm_f32_is_true_32_bit(ops, m, n, k):
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    # values with many mantissa bits: a product in TF32 or bfloat16 would miss by about 1e-3
+    out = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    ops.gemm_f32(dev(a), dev(w), out)
+    want = a.astype(np.float64) @ w.astype(np.float64).T
+    err = np.abs(out.cpu().numpy() - want).max()
+    assert err <= 1e-6 * np.sqrt(k) * np.abs(want).max() + 1e-6, f"max |diff| {err:.3e}"
+    # strided rows of a wider buffer
+    big = torch.zeros((m, n + 5), dtype=torch.float32, device="cuda")
+    ops.gemm_f32(dev(a), dev(w), big[:, 2:2 + n])
+    assert torch.equal(big[:, 2:2 + n], out) and not big[:, :2].any() and not big[:, 2 + n:].any()
+
+
+def test_linear_bfloat16_float_output(ops):
+    rng = np.random.default_rng(8)
+    a, w = as_stored(rng.standard_normal((5, 96)), "bfloat16"), as_stored(rng.standard_normal((301, 96)), "bfloat16")
+    out32 = torch.empty((5, 301), dtype=torch.float32, device="cuda")
+    ops.linear(dev(a, torch.bfloat16), dev(w, torch.bfloat16), out32)
+    want = a.astype(np.float64) @ w.astype(np.float64).T
+    assert np.abs(out32.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()
+    out16 = torch.empty((5, 301), dtype=torch.bfloat16, device="cuda")
+    ops.linear(dev(a, torch.bfloat16), dev(w, torch.bfloat16), out16)
+    close(out16.float().cpu().numpy(), want, "bfloat16", "linear bf16")
+
+
+def test_sampling_greedy_and_temperature(ops):
+    rng = np.random.default_rng(9)
+    vocab, rows = 1237, 6
+    logits = (3 * rng.standard_normal((rows, vocab))).astype(np.float32)
+    logits[0, 77] = logits[0, 900] = logits[0].max() + 1          # a tie: the lower id wins
+    logits[1, 0] = 50.0
+    temps = np.array([0.0, 0.0, 0.7, 1.0, 1.3, -1.0], dtype=np.float32)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    for trial in range(20):
+        u = rng.random(rows).astype(np.float32)
+        ops.sample(dev(logits), dev(temps), dev(u), out)
+        got = out.cpu().numpy()
+        for r in range(rows):
+            want = plain.sample(logits[r], float(temps[r]), 1.0, -1, 1.0, [], float(u[r]))
+            if got[r] != want:                                    # rounding of the running sum at a boundary
+                p = plain.softmax(logits[r] / max(temps[r], 1e-9))
+                c = np.cumsum(p.astype(np.float64))
+                assert abs(got[r] - want) == 1 and min(abs(c[got[r]] - u[r]), abs(c[want] - u[r])) < 1e-5, (r, got[r], want)
+    assert got[0] == 77 and got[1] == 0
+    # u just below 1 gives the last id with any mass; u = 0 the first
+    ops.sample(dev(logits), dev(temps), dev(np.zeros(rows, dtype=np.float32)), out)
+    assert out.cpu().numpy()[3] == 0
+
+
+def test_sampling_top_k_top_p_and_penalty(ops):
+    rng = np.random.default_rng(10)
+    vocab, rows = 997, 8
+    logits = (2.5 * rng.standard_normal((rows, vocab))).astype(np.float32)
+    logits[2, 5] = logits[2, 400] = logits[2].max() + 0.5         # tie inside the kept set
+    temps = np.array([1.0, 0.8, 1.0, 1.2, 1.0, 0.0, 1.0, 0.9], dtype=np.float32)
+    top_k = np.array([5, -1, 2, 50, 1, 3, -1, 997], dtype=np.int32)
+    top_p = np.array([1.0, 0.5, 1.0, 0.9, 1.0, 0.5, 1.0, 0.3], dtype=np.float32)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    mismatches = 0
+    for trial in range(25):
+        u = rng.random(rows).astype(np.float32)
+        ops.sample(dev(logits), dev(temps), dev(u), out)
+        ops.sample_filtered(dev(logits), dev(temps), dev(u), dev(top_p), dev(top_k), out)
+        got = out.cpu().numpy()
+        for r in range(rows):
+            want = plain.sample(logits[r], float(temps[r]), float(top_p[r]), int(top_k[r]), 1.0, [], float(u[r]))
+            if got[r] != want:
+                # only a knife-edge of the running sums may differ: the two ids are neighbours in
+                # the reference's order
+                p = plain.softmax(logits[r] * (np.float32(1) / temps[r]) if temps[r] > 0 else logits[r])
+                order = plain.order_by_probability(p, list(range(vocab)))
+                assert abs(order.index(got[r]) - order.index(want)) == 1, (r, got[r], want)
+                mismatches += 1
+    assert mismatches <= 3
+    assert got[4] == int(np.argmax(logits[4]))                    # top_k = 1 is the largest
+    # repetition penalty: each generated id once, l > 0 ? l / p : l * p
+    l = dev(logits.copy())
+    ids = np.array([3, 9, 9 + 0, 500, 7], dtype=np.int32)          # row 0: {3, 9}, row 1: none, row 2: {500, 7}
+    start = np.array([0, 2, 2, 4, 4, 4, 4, 4, 4], dtype=np.int32)
+    pen = np.array([1.5, 1.0, 2.0, 1, 1, 1, 1, 1], dtype=np.float32)
+    ops.repetition_penalty(l, dev(np.array([3, 9, 500, 7], dtype=np.int32)), dev(start), dev(pen))
+    want = logits.copy()
+    want[0] = plain.repetition_penalty(logits[0], [3, 9, 3], 1.5)
+    want[2] = plain.repetition_penalty(logits[2], [500, 7], 2.0)
+    assert np.allclose(l.cpu().numpy(), want, rtol=1e-6)

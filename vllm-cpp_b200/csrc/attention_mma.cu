@@ -1,0 +1,529 @@
+// Paged grouped-query attention on tensor cores for bfloat16, head sizes 64 and 128.
+//
+// Two kernels share the tile loader and the fragment code:
+//   * attention_prefill_kernel: portions of prompts of any length (and, in mixed
+//     batches, single tokens).  The query heads that share one kv head are packed
+//     into the row dimension: row = token * G + head_in_group, G = heads / kv_heads,
+//     so one K/V tile in shared memory serves all G heads.  A CTA of 4 warps owns
+//     64 such rows and walks the keys 0..p (or the window) in tiles of 64.
+//   * attention_decode_kernel: one query token per request.  Its G rows fill one
+//     16-row fragment; the context is split over gridDim.x CTAs, and inside a CTA
+//     each warp takes 16 of every 64 keys.  Partial (max, sum, output) triples are
+//     merged across warps in shared memory and across CTAs by
+//     attention_combine_kernel through scratch memory in global memory.
+// Scores, softmax statistics and output accumulators are float; the probabilities
+// are rounded to bfloat16 for the P*V product, as K and V are stored.
+//
+// K/V tiles come from the pages with 16-byte cp.async copies in a multi-stage ring;
+// rows are XOR-swizzled in units of 16 bytes so that ldmatrix reads are free of
+// bank conflicts.  Keys outside [lo, hi) are zero-filled, never read: their pages
+// may have been given back (window) or not exist yet.
+//
+// Replaces paged_attention_kernel (src/attention/paged_attention.cu:7-93) for the
+// bfloat16 path; attention_simt.cu is its plain counterpart.
+#include "common.cuh"
+
+#define BN 64            // keys per tile
+#define BM 64            // rows per CTA in the prefill kernel
+#define NTHREADS 128
+
+struct MmaAttnArgs {
+    const __nv_bfloat16* q;        // [n_tokens, nh * d]
+    const __nv_bfloat16* cache;    // [pages][2][nkv][page][d]
+    __nv_bfloat16* out;            // [n_tokens, nh * d]
+    const int* q_start;            // [n_reqs + 1]
+    const int* ctx_lens;           // [n_reqs]
+    const int* block_table;        // [n_reqs, bt_stride]
+    const int* req_list;           // decode: requests to process (null: 0..n-1); prefill: tile -> request
+    const int* tile_row0;          // prefill: tile -> first packed row
+    float* part_o;                 // decode scratch: [n_list, nh, splits, d]
+    float* part_ml;                // decode scratch: [n_list, nh, splits, 2]
+    int bt_stride, nh, nkv, page, window;
+    float scale;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of element (row, 16-byte chunk) in a tile of rows of D bfloat16.
+template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    return (uint32_t)(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
+}
+
+// One K tile and one V tile of BN keys starting at key kb (a multiple of BN) of kv
+// head g.  Keys outside [lo, hi) are filled with zeros.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(uint32_t sk, uint32_t sv, int kb, int lo, int hi,
+                                             const int* __restrict__ bt, const __nv_bfloat16* __restrict__ cache,
+                                             int g, int page, int nkv) {
+    constexpr int CH = D / 8;
+    const size_t page_elems = (size_t)2 * nkv * page * D;
+    const size_t v_off = (size_t)nkv * page * D;
+    for (int idx = threadIdx.x; idx < BN * CH; idx += NTHREADS) {
+        const int key = idx / CH, c = idx % CH;
+        const int j = kb + key;
+        const bool valid = j >= lo && j < hi;
+        const __nv_bfloat16* src = cache;
+        if (valid) {
+            const int pg = bt[j / page];
+            src = cache + (size_t)pg * page_elems + ((size_t)g * page + (j % page)) * D + c * 8;
+        }
+        const uint32_t off = swz<D>(key, c);
+        cp_async_16(sk + off, src, valid ? 16 : 0);
+        cp_async_16(sv + off, valid ? src + v_off : src, valid ? 16 : 0);
+    }
+}
+
+// S[16 x 8*NB] += Q[16 x D] * K[keys key0 .. key0 + 8*NB)^T, K tile at sk.
+template <int D, int NB>
+__device__ __forceinline__ void qk_product(float (&s)[NB][4], const uint32_t (&qf)[D / 16][4], uint32_t sk, int key0) {
+    const int lane = threadIdx.x & 31;
+    const int mi = lane >> 3, r8 = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+        for (int nb = 0; nb < NB; nb += 2) {
+            uint32_t b[4];
+            const int key = key0 + (nb + (mi >> 1)) * 8 + r8;
+            ldmatrix_x4(b, sk + swz<D>(key, ks * 2 + (mi & 1)));
+            mma_bf16(s[nb], qf[ks], b[0], b[1]);
+            mma_bf16(s[nb + 1], qf[ks], b[2], b[3]);
+        }
+    }
+}
+
+// O[16 x D] += P[16 x 16*KK] * V[keys key0 .. key0 + 16*KK), V tile at sv.  pf[kk] is P's A fragment.
+template <int D, int KK>
+__device__ __forceinline__ void pv_product(float (&o)[D / 8][4], const uint32_t (&pf)[KK][4], uint32_t sv, int key0) {
+    const int lane = threadIdx.x & 31;
+    const int mi = lane >> 3, r8 = lane & 7;
+#pragma unroll
+    for (int kk = 0; kk < KK; ++kk) {
+#pragma unroll
+        for (int nd = 0; nd < D / 8; nd += 2) {
+            uint32_t b[4];
+            const int key = key0 + kk * 16 + (mi & 1) * 8 + r8;
+            ldmatrix_x4_trans(b, sv + swz<D>(key, nd + (mi >> 1)));
+            mma_bf16(o[nd], pf[kk], b[0], b[1]);
+            mma_bf16(o[nd + 1], pf[kk], b[2], b[3]);
+        }
+    }
+}
+
+// Q rows -> A fragments.  The tile at sq holds 16 rows per warp slot `wrow0`.
+template <int D>
+__device__ __forceinline__ void load_q_frags(uint32_t (&qf)[D / 16][4], uint32_t sq, int wrow0) {
+    const int lane = threadIdx.x & 31;
+    const int mi = lane >> 3, r8 = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+        ldmatrix_x4(qf[ks], sq + swz<D>(wrow0 + (mi & 1) * 8 + r8, ks * 2 + (mi >> 1)));
+}
+
+// ------------------------------------------------------------------ decode
+template <int D, int STAGES>
+__global__ void __launch_bounds__(NTHREADS)
+attention_decode_kernel(MmaAttnArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int TILE_BYTES = BN * D * 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int split = blockIdx.x, nsplit = gridDim.x, g = blockIdx.y, li = blockIdx.z;
+    const int r = a.req_list ? a.req_list[li] : li;
+    const int G = a.nh / a.nkv;
+    const int t = a.q_start[r];
+    const int pos = a.ctx_lens[r];                       // the single token's position
+    const int hi = pos + 1;
+    const int lo = a.window > 0 ? max(0, hi - a.window) : 0;
+    const int* bt = a.block_table + (size_t)r * a.bt_stride;
+
+    const int tile0 = lo / BN, tile1 = (hi + BN - 1) / BN;
+    const int per = (tile1 - tile0 + nsplit - 1) / nsplit;
+    const int my0 = tile0 + split * per, my1 = min(tile1, my0 + per);
+
+    const uint32_t s_base = smem_u32(smem);
+    const uint32_t sq = s_base;                          // [16][D] bf16
+    const uint32_t s_tiles = s_base + 16 * D * 2;        // STAGES x (K, V)
+    float* red_o = reinterpret_cast<float*>(smem + 16 * D * 2);          // reused after the loop: [4][16][D]
+    float* red_ml = reinterpret_cast<float*>(smem + 16 * D * 2 + 4 * 16 * D * 4);   // [4][16][2]
+
+    for (int mt = 0; mt * 16 < G; ++mt) {
+        __syncthreads();
+        // Q rows of this group: row i -> head g*G + mt*16 + i
+        for (int idx = threadIdx.x; idx < 16 * (D / 8); idx += NTHREADS) {
+            const int row = idx / (D / 8), c = idx % (D / 8);
+            const int hg = mt * 16 + row;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (hg < G) v = *reinterpret_cast<const uint4*>(a.q + ((size_t)t * a.nh + g * G + hg) * D + c * 8);
+            *reinterpret_cast<uint4*>(smem + swz<D>(row, c)) = v;
+        }
+        __syncthreads();
+        uint32_t qf[D / 16][4];
+        load_q_frags<D>(qf, sq, 0);
+
+        float o[D / 8][4];
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+        float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;   // rows lane/4 and lane/4 + 8
+
+        // prologue
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (my0 + s < my1)
+                load_kv_tile<D>(s_tiles + s * 2 * TILE_BYTES, s_tiles + s * 2 * TILE_BYTES + TILE_BYTES,
+                                (my0 + s) * BN, lo, hi, bt, a.cache, g, a.page, a.nkv);
+            cp_async_commit();
+        }
+        for (int tile = my0; tile < my1; ++tile) {
+            cp_async_wait<STAGES - 2>();
+            __syncthreads();
+            {   // refill the stage that was consumed in the previous iteration
+                const int nt = tile + STAGES - 1;
+                const int st = (nt - my0) % STAGES;
+                if (nt < my1)
+                    load_kv_tile<D>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
+                                    nt * BN, lo, hi, bt, a.cache, g, a.page, a.nkv);
+                cp_async_commit();
+            }
+            const int st = (tile - my0) % STAGES;
+            const uint32_t sk = s_tiles + st * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
+            const int kb = tile * BN + warp * 16;        // this warp's 16 keys
+            float s[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
+            qk_product<D, 2>(s, qf, sk, warp * 16);
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = kb + nb * 8 + (lane & 3) * 2 + (e & 1);
+                    s[nb][e] = (j >= lo && j < hi) ? s[nb][e] * a.scale : -INFINITY;
+                }
+            // all rows of a decode tile share the position, but keep the two row sets apart
+            float ta = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+            float tb = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+            ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 1)); ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 2));
+            tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 1)); tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 2));
+            (void)tmax;
+            const float na = fmaxf(m_a, ta), nb_ = fmaxf(m_b, tb);
+            const float sa = na == -INFINITY ? 0.0f : na, sb = nb_ == -INFINITY ? 0.0f : nb_;
+            const float ca = expf(m_a - sa), cb = expf(m_b - sb);      // m = -inf: exp(-inf) = 0, sums are 0 anyway
+            m_a = na; m_b = nb_;
+            uint32_t pf[1][4];
+            float p[2][4];
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb) {
+                p[nb][0] = expf(s[nb][0] - sa); p[nb][1] = expf(s[nb][1] - sa);
+                p[nb][2] = expf(s[nb][2] - sb); p[nb][3] = expf(s[nb][3] - sb);
+            }
+            l_a = l_a * ca + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
+            l_b = l_b * cb + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) { o[i][0] *= ca; o[i][1] *= ca; o[i][2] *= cb; o[i][3] *= cb; }
+            pf[0][0] = pack_bf16(p[0][0], p[0][1]); pf[0][1] = pack_bf16(p[0][2], p[0][3]);
+            pf[0][2] = pack_bf16(p[1][0], p[1][1]); pf[0][3] = pack_bf16(p[1][2], p[1][3]);
+            pv_product<D, 1>(o, pf, sv, warp * 16);
+        }
+        cp_async_wait<0>();
+        __syncthreads();                                 // tiles are dead: reuse the memory for the merge
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        const int ra = lane >> 2, rb = ra + 8;
+#pragma unroll
+        for (int nd = 0; nd < D / 8; ++nd) {
+            const int col = nd * 8 + (lane & 3) * 2;
+            float* pa = red_o + ((size_t)(warp * 16 + ra)) * D + col;
+            float* pb = red_o + ((size_t)(warp * 16 + rb)) * D + col;
+            pa[0] = o[nd][0]; pa[1] = o[nd][1]; pb[0] = o[nd][2]; pb[1] = o[nd][3];
+        }
+        if ((lane & 3) == 0) {
+            red_ml[(warp * 16 + ra) * 2] = m_a; red_ml[(warp * 16 + ra) * 2 + 1] = l_a;
+            red_ml[(warp * 16 + rb) * 2] = m_b; red_ml[(warp * 16 + rb) * 2 + 1] = l_b;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 16 * D; idx += NTHREADS) {
+            const int row = idx / D, dim = idx % D;
+            const int hg = mt * 16 + row;
+            if (hg >= G) continue;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mx = fmaxf(mx, red_ml[(w * 16 + row) * 2]);
+            float acc = 0.0f, l = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float mw = red_ml[(w * 16 + row) * 2];
+                if (mw == -INFINITY) continue;
+                const float f = expf(mw - mx);
+                acc += red_o[((size_t)(w * 16 + row)) * D + dim] * f;
+                l += red_ml[(w * 16 + row) * 2 + 1] * f;
+            }
+            const int head = g * G + hg;
+            if (nsplit == 1) {
+                a.out[((size_t)t * a.nh + head) * D + dim] = __float2bfloat16_rn(acc / l);
+            } else {
+                const size_t pi = ((size_t)li * a.nh + head) * nsplit + split;
+                a.part_o[pi * D + dim] = acc;
+                if (dim == 0) { a.part_ml[pi * 2] = mx; a.part_ml[pi * 2 + 1] = l; }
+            }
+        }
+    }
+}
+
+// out[t, head, :] = sum_s part_o[s] * exp(m_s - m) / sum_s l_s * exp(m_s - m)
+__global__ void attention_combine_kernel(MmaAttnArgs a, int nsplit, int d) {
+    const int li = blockIdx.y, head = blockIdx.x;
+    const int r = a.req_list ? a.req_list[li] : li;
+    const int t = a.q_start[r];
+    const size_t p0 = ((size_t)li * a.nh + head) * nsplit;
+    float mx = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, a.part_ml[(p0 + s) * 2]);
+    for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
+        float acc = 0.0f, l = 0.0f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float ms = a.part_ml[(p0 + s) * 2];
+            if (ms == -INFINITY) continue;
+            const float f = expf(ms - mx);
+            acc += a.part_o[(p0 + s) * d + dim] * f;
+            l += a.part_ml[(p0 + s) * 2 + 1] * f;
+        }
+        a.out[((size_t)t * a.nh + head) * d + dim] = __float2bfloat16_rn(acc / l);
+    }
+}
+
+// ----------------------------------------------------------------- prefill
+template <int D, int STAGES>
+__global__ void __launch_bounds__(NTHREADS)
+attention_prefill_kernel(MmaAttnArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int TILE_BYTES = BN * D * 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = a.req_list[blockIdx.x];
+    const int row0 = a.tile_row0[blockIdx.x];
+    const int g = blockIdx.y;
+    const int G = a.nh / a.nkv;
+    const int q0 = a.q_start[r], q_len = a.q_start[r + 1] - q0, ctx = a.ctx_lens[r];
+    const int rows_total = q_len * G;
+    const int* bt = a.block_table + (size_t)r * a.bt_stride;
+
+    const uint32_t s_base = smem_u32(smem);
+    const uint32_t sq = s_base;                          // [BM][D]
+    const uint32_t s_tiles = s_base + BM * D * 2;
+
+    // Q tile: packed row -> (token, head in group)
+    for (int idx = threadIdx.x; idx < BM * (D / 8); idx += NTHREADS) {
+        const int row = idx / (D / 8), c = idx % (D / 8);
+        const int pr = row0 + row;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (pr < rows_total) {
+            const int tt = pr / G, hg = pr % G;
+            v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + tt) * a.nh + g * G + hg) * D + c * 8);
+        }
+        *reinterpret_cast<uint4*>(smem + swz<D>(row, c)) = v;
+    }
+    // positions of this thread's two rows
+    const int pra = row0 + warp * 16 + (lane >> 2), prb = pra + 8;
+    const int pos_a = ctx + min(pra, rows_total - 1) / G, pos_b = ctx + min(prb, rows_total - 1) / G;
+    const bool live_a = pra < rows_total, live_b = prb < rows_total;
+    // keys that any row of the tile can see
+    const int last_row = min(row0 + BM, rows_total) - 1;
+    const int hi = ctx + last_row / G + 1;
+    const int lo = a.window > 0 ? max(0, ctx + row0 / G + 1 - a.window) : 0;
+    const int tile0 = lo / BN, tile1 = (hi + BN - 1) / BN;
+
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (tile0 + s < tile1)
+            load_kv_tile<D>(s_tiles + s * 2 * TILE_BYTES, s_tiles + s * 2 * TILE_BYTES + TILE_BYTES,
+                            (tile0 + s) * BN, lo, hi, bt, a.cache, g, a.page, a.nkv);
+        cp_async_commit();
+    }
+    __syncthreads();                                     // Q tile written
+    uint32_t qf[D / 16][4];
+    load_q_frags<D>(qf, sq, warp * 16);
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
+    // the smallest position among this warp's rows: tiles wholly at or below it need no mask
+    const int wpos_min = ctx + min(row0 + warp * 16, rows_total - 1) / G;
+    const int wlo_max = a.window > 0 ? ctx + min(row0 + warp * 16 + 15, rows_total - 1) / G + 1 - a.window : 0;
+
+    for (int tile = tile0; tile < tile1; ++tile) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        {
+            const int nt = tile + STAGES - 1;
+            const int st = (nt - tile0) % STAGES;
+            if (nt < tile1)
+                load_kv_tile<D>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
+                                nt * BN, lo, hi, bt, a.cache, g, a.page, a.nkv);
+            cp_async_commit();
+        }
+        const int st = (tile - tile0) % STAGES;
+        const uint32_t sk = s_tiles + st * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
+        const int kb = tile * BN;
+        float s[BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
+        qk_product<D, BN / 8>(s, qf, sk, 0);
+        const bool need_mask = (kb + BN - 1 > wpos_min) || (kb < wlo_max) || !live_b;
+#pragma unroll
+        for (int nb = 0; nb < BN / 8; ++nb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = s[nb][e] * a.scale;
+                if (need_mask) {
+                    const int j = kb + nb * 8 + (lane & 3) * 2 + (e & 1);
+                    const int pos = (e < 2) ? pos_a : pos_b;
+                    const bool live = (e < 2) ? live_a : live_b;
+                    const bool ok = live && j <= pos && (a.window <= 0 || j > pos - a.window);
+                    if (!ok) v = -INFINITY;
+                }
+                s[nb][e] = v;
+            }
+        float ta = -INFINITY, tb = -INFINITY;
+#pragma unroll
+        for (int nb = 0; nb < BN / 8; ++nb) {
+            ta = fmaxf(ta, fmaxf(s[nb][0], s[nb][1]));
+            tb = fmaxf(tb, fmaxf(s[nb][2], s[nb][3]));
+        }
+        ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 1)); ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 2));
+        tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 1)); tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 2));
+        const float na = fmaxf(m_a, ta), nb_ = fmaxf(m_b, tb);
+        const float sa = na == -INFINITY ? 0.0f : na, sb = nb_ == -INFINITY ? 0.0f : nb_;
+        const float ca = expf(m_a - sa), cb = expf(m_b - sb);
+        m_a = na; m_b = nb_;
+        uint32_t pf[BN / 16][4];
+        float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+            float p[2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int nb = kk * 2 + h;
+                p[h][0] = expf(s[nb][0] - sa); p[h][1] = expf(s[nb][1] - sa);
+                p[h][2] = expf(s[nb][2] - sb); p[h][3] = expf(s[nb][3] - sb);
+                sum_a += p[h][0] + p[h][1];
+                sum_b += p[h][2] + p[h][3];
+            }
+            pf[kk][0] = pack_bf16(p[0][0], p[0][1]); pf[kk][1] = pack_bf16(p[0][2], p[0][3]);
+            pf[kk][2] = pack_bf16(p[1][0], p[1][1]); pf[kk][3] = pack_bf16(p[1][2], p[1][3]);
+        }
+        l_a = l_a * ca + sum_a;
+        l_b = l_b * cb + sum_b;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[i][0] *= ca; o[i][1] *= ca; o[i][2] *= cb; o[i][3] *= cb; }
+        pv_product<D, BN / 16>(o, pf, sv, 0);
+    }
+    cp_async_wait<0>();
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    const float ia = 1.0f / l_a, ib = 1.0f / l_b;
+    __nv_bfloat16* oa = live_a ? a.out + ((size_t)(q0 + pra / G) * a.nh + g * G + pra % G) * D : nullptr;
+    __nv_bfloat16* ob = live_b ? a.out + ((size_t)(q0 + prb / G) * a.nh + g * G + prb % G) * D : nullptr;
+#pragma unroll
+    for (int nd = 0; nd < D / 8; ++nd) {
+        const int col = nd * 8 + (lane & 3) * 2;
+        if (live_a) *reinterpret_cast<uint32_t*>(oa + col) = pack_bf16(o[nd][0] * ia, o[nd][1] * ia);
+        if (live_b) *reinterpret_cast<uint32_t*>(ob + col) = pack_bf16(o[nd][2] * ib, o[nd][3] * ib);
+    }
+}
+
+// ---------------------------------------------------------------- launchers
+template <int D>
+static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStream_t s) {
+    constexpr int STAGES = 3;
+    const size_t tiles = 16 * D * 2 + (size_t)STAGES * 2 * BN * D * 2;
+    const size_t merge = 16 * D * 2 + 4 * 16 * D * 4 + 4 * 16 * 2 * 4;
+    const size_t smem = tiles > merge ? tiles : merge;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(nsplit, a.nkv, n_list);
+    attention_decode_kernel<D, STAGES><<<grid, NTHREADS, smem, s>>>(a);
+    int err = vcb_last_error();
+    if (err || nsplit == 1) return err;
+    attention_combine_kernel<<<dim3(a.nh, n_list), D <= 64 ? 64 : 128, 0, s>>>(a, nsplit, D);
+    return vcb_last_error();
+}
+
+template <int D>
+static int launch_prefill(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
+    constexpr int STAGES = 2;
+    const size_t smem = BM * D * 2 + (size_t)STAGES * 2 * BN * D * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(n_tiles, a.nkv);
+    attention_prefill_kernel<D, STAGES><<<grid, NTHREADS, smem, s>>>(a);
+    return vcb_last_error();
+}
+
+static int check_common(int nh, int nkv, int d, int page, int window) {
+    if (nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || window < 0) return VCB_ERR_BAD_ARG;
+    if (d != 64 && d != 128) return VCB_ERR_UNSUPPORTED;
+    return 0;
+}
+
+// Scratch for the split-KV merge: part_o needs n_list*nh*nsplit*d floats, part_ml n_list*nh*nsplit*2.
+VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* out, const int* q_start,
+                                        const int* ctx_lens, const int* block_table, int bt_stride,
+                                        const int* req_list, int n_list, int nsplit, float* part_o,
+                                        float* part_ml, int nh, int nkv, int d, int page, int window,
+                                        float scale, void* stream) {
+    if (n_list <= 0) return 0;
+    int c = check_common(nh, nkv, d, page, window);
+    if (c) return c;
+    if (nsplit < 1 || (nsplit > 1 && (!part_o || !part_ml))) return VCB_ERR_BAD_ARG;
+    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
+                  block_table, req_list, nullptr, part_o, part_ml, bt_stride, nh, nkv, page, window, scale};
+    cudaStream_t s = (cudaStream_t)stream;
+    return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
+}
+
+VCB_EXPORT int vcb_attention_prefill_mma(const void* q, const void* cache, void* out, const int* q_start,
+                                         const int* ctx_lens, const int* block_table, int bt_stride,
+                                         const int* tile_req, const int* tile_row0, int n_tiles, int nh,
+                                         int nkv, int d, int page, int window, float scale, void* stream) {
+    if (n_tiles <= 0) return 0;
+    int c = check_common(nh, nkv, d, page, window);
+    if (c) return c;
+    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
+                  block_table, tile_req, tile_row0, nullptr, nullptr, bt_stride, nh, nkv, page, window, scale};
+    cudaStream_t s = (cudaStream_t)stream;
+    return d == 64 ? launch_prefill<64>(a, n_tiles, s) : launch_prefill<128>(a, n_tiles, s);
+}

@@ -34,6 +34,8 @@ _SIGNATURES = {
     "vcb_rope_cache_write": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "vcb_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "vcb_repetition_penalty": [_P, _I, _P, _P, _P, _I, _I, _P],
     "vcb_sample": [_P, _I, _I, _P, _P, _P, _I, _P],
     "vcb_sample_filtered": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
@@ -70,8 +72,24 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Launches of this library's own kernels so far (library products are not counted)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    """Account for kernels that ran inside a replayed CUDA graph."""
+    global _launches
+    _launches += n
+
+
 def _check(code: int, what: str) -> None:
+    global _launches
     if code == 0:
+        _launches += 1
         return
     if code == 10001:
         raise KernelError(f"{what}: the kernel refused its arguments")
@@ -184,6 +202,48 @@ def attention_simt(q, cache, out, positions, req_of_token, block_table, *, num_h
         dtype_code(q.dtype), _stream()), "attention_simt")
 
 
+MMA_HEAD_DIMS = (64, 128)
+
+
+def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list, n_list: int, nsplit: int,
+                         part_o, part_ml, *, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                         window: int, scale: float) -> None:
+    """Split-KV tensor-core attention for requests that bring one token each (bfloat16)."""
+    _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attention_decode_mma is a bfloat16 kernel")
+    _need(head_dim in MMA_HEAD_DIMS, f"attention_decode_mma takes head sizes {MMA_HEAD_DIMS}, got {head_dim}")
+    if nsplit > 1:
+        need = n_list * num_heads * nsplit
+        _need(part_o is not None and part_o.numel() >= need * head_dim and part_ml.numel() >= need * 2,
+              "attention_decode_mma: scratch for the split merge is too small")
+    _check(lib().vcb_attention_decode_mma(
+        _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
+        _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
+        block_table.shape[1], None if req_list is None else _dev(req_list, "req_list", torch.int32),
+        n_list, nsplit, None if part_o is None else _dev(part_o, "part_o", torch.float32),
+        None if part_ml is None else _dev(part_ml, "part_ml", torch.float32),
+        num_heads, num_kv_heads, head_dim, page_size, window, float(scale), _stream()), "attention_decode_mma")
+    if nsplit > 1:
+        add_launches(1)          # the merge kernel
+
+
+def attention_prefill_mma(q, cache, out, q_start, ctx_lens, block_table, tile_req, tile_row0, *,
+                          num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
+                          scale: float) -> None:
+    """Tensor-core attention for portions of any length; tiles of 64 packed rows (bfloat16)."""
+    _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attention_prefill_mma is a bfloat16 kernel")
+    _need(head_dim in MMA_HEAD_DIMS, f"attention_prefill_mma takes head sizes {MMA_HEAD_DIMS}, got {head_dim}")
+    n_tiles = tile_req.numel()
+    _need(tile_row0.numel() == n_tiles, "one first row per tile")
+    _check(lib().vcb_attention_prefill_mma(
+        _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
+        _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
+        block_table.shape[1], _dev(tile_req, "tile_req", torch.int32), _dev(tile_row0, "tile_row0", torch.int32),
+        n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale), _stream()),
+        "attention_prefill_mma")
+
+
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M,N] = a[M,K] @ w[N,K]^T in true 32-bit arithmetic; rows may be strided."""
     m, k = a.shape
@@ -249,3 +309,18 @@ def sample_filtered(logits, temperature, uniform, top_p, top_k, out, scratch: Op
                                      _dev(uniform, "uniform", torch.float32), _dev(top_p, "top_p", torch.float32),
                                      _dev(top_k, "top_k", torch.int32), _dev(scratch, "scratch", torch.float32),
                                      _dev(out, "out", torch.int32), n, _stream()), "sample_filtered")
+
+
+_scratch = {}
+
+
+def scratch(name: str, numel: int, device) -> torch.Tensor:
+    """A float32 device buffer of at least ``numel`` elements, kept under ``name`` and grown
+    when needed.  Kernels that merge partial results through global memory use it."""
+    t = _scratch.get(name)
+    if t is None or t.numel() < numel or t.device != torch.device(device):
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError(f"scratch buffer {name!r} must be sized before a CUDA graph is captured")
+        t = torch.empty(max(numel, 1024), dtype=torch.float32, device=device)
+        _scratch[name] = t
+    return t

@@ -77,7 +77,7 @@ class ModelRunner:
         self._copy_pending = False
         self.use_cuda_graphs = use_cuda_graphs
         self.graphs: Dict[tuple, object] = {}
-        self.launches = 0
+        self.last_meta_bytes = 0
 
     def _meta_ints(self, n: int, r: int, m: int) -> int:
         return (3 * _align(n) + _align(r + 1) + 2 * _align(r) + _align(m)
@@ -191,6 +191,7 @@ class ModelRunner:
         self.meta_dev[:off].copy_(self.meta_host[:off], non_blocking=True)
         self._copy_done.record()
         self._copy_pending = True
+        self.last_meta_bytes = off * 4
 
         def dev(name, shape=None):
             o, c = sections[name]
@@ -205,4 +206,4 @@ class ModelRunner:
             h_q_start=[int(x) for x in qs], h_ctx_lens=list(ctx_lens), h_state_slots=list(slots),
             decode_only=all(q == 1 for q in q_lens), max_q_len=max(q_lens),
             max_total_len=max(c + q for c, q in zip(ctx_lens, q_lens)),
-            extras={name: dev("x:" + name) for name in extra})
+            extras={name: dev("x:" + name, arr.shape) for name, arr in extra.items()})

@@ -108,7 +108,52 @@ class PagedAttention(Mixer):
         ops.linear(attn, self.w_o, out)
         ws.release(mark)
 
+    # -- work lists and kernel choice
+    TILE_ROWS = 64           # packed rows (token x head in group) per CTA of the prefill kernel
+    SM_COUNT = 148
+
+    def _tensor_core_path(self) -> bool:
+        return self.dtype == torch.bfloat16 and self.d in ops.MMA_HEAD_DIMS
+
+    def step_arrays(self):
+        """Work list of the prefill kernel: for every request that brings tokens, its tiles of
+        TILE_ROWS packed rows, as [2, n_tiles] = (request index, first row)."""
+        if not self._tensor_core_path():
+            return {}
+        group = self.nh // self.nkv
+        rows = self.TILE_ROWS
+
+        def tiles(host):
+            if all(q == 1 for q in host.q_lens):
+                return np.zeros((2, 0), dtype=np.int32)         # decode-only steps use the split-KV kernel
+            req, row0 = [], []
+            for r, q in enumerate(host.q_lens):
+                for k in range(-(-q * group // rows)):
+                    req.append(r)
+                    row0.append(k * rows)
+            return np.array([req, row0], dtype=np.int32)
+
+        return {f"attn_tiles_g{group}": tiles}
+
     def attend(self, q, attn, step, cache, block_table):
+        if self._tensor_core_path():
+            kw = dict(num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d, page_size=cache.page_size,
+                      window=self.window, scale=self.scale)
+            if step.decode_only:
+                longest = step.max_total_len if self.window <= 0 else min(step.max_total_len, self.window + 64)
+                nsplit = max(1, min(-(-longest // 64), -(-2 * self.SM_COUNT // (step.n_reqs * self.nkv)), 32))
+                part_o = part_ml = None
+                if nsplit > 1:
+                    need = step.n_reqs * self.nh * nsplit
+                    part_o = ops.scratch("attn_part_o", need * self.d, q.device)
+                    part_ml = ops.scratch("attn_part_ml", need * 2, q.device)
+                ops.attention_decode_mma(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, None,
+                                         step.n_reqs, nsplit, part_o, part_ml, **kw)
+            else:
+                tiles = step.extras[f"attn_tiles_g{self.nh // self.nkv}"]
+                ops.attention_prefill_mma(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table,
+                                          tiles[0], tiles[1], **kw)
+            return
         ops.attention_simt(q, cache.pages, attn, step.positions, step.req_of_token, block_table,
                            num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d,
                            page_size=cache.page_size, window=self.window, scale=self.scale)
