@@ -115,6 +115,10 @@ def main() -> int:
                     help="fewer layers than the 28 of the configuration (recorded in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="run one part only (for profiling); the other fields of the line are null")
+    ap.add_argument("--no-cuda-graphs", action="store_true",
+                    help="launch every kernel of a decode step directly (for a profiler's launch list)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -140,7 +144,8 @@ def main() -> int:
     pages = max_batch * (CONTEXT // 16 + 2) + PREFILL_TOKENS // 16 + 16
     ecfg = EngineConfig(load_format="random", model_config=cfg, seed=0, dtype="bfloat16", block_size=16,
                         num_gpu_blocks=pages, max_num_seqs=max_batch, max_model_len=CONTEXT + 16,
-                        max_num_batched_tokens=PREFILL_TOKENS, max_tokens_per_step=PREFILL_TOKENS)
+                        max_num_batched_tokens=PREFILL_TOKENS, max_tokens_per_step=PREFILL_TOKENS,
+                        use_cuda_graphs=not a.no_cuda_graphs)
     t0 = time.time()
     engine = Engine(ecfg)
     runner, cache = engine.runner, engine.cache
@@ -174,11 +179,13 @@ def main() -> int:
         torch.cuda.synchronize()
         launches0 = ops.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.nvtx.range_push("timed_decode")
         e0.record()
         for k in range(n_warm, n_warm + n_steps):
             one(k)
         e1.record()
         torch.cuda.synchronize()
+        torch.cuda.nvtx.range_pop()
         ms = e0.elapsed_time(e1) / n_steps
         launches = ops.launch_count() - launches0
         kv_bytes = batch * (CONTEXT - n_steps / 2) * nums["kv_bytes_per_token"]
@@ -193,26 +200,35 @@ def main() -> int:
             toks = rng.integers(0, vocab, size=PREFILL_TOKENS).tolist()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if k >= n_warm:
+                torch.cuda.nvtx.range_push("timed_prefill")
             e0.record()
             runner.step([StepEntry("p", toks, [PREFILL_TOKENS - 1])])
             e1.record()
             torch.cuda.synchronize()
+            if k >= n_warm:
+                torch.cuda.nvtx.range_pop()
             cache.free_request("p")
             if k >= n_warm:
                 times.append(e0.elapsed_time(e1))
         return statistics.median(times)
 
     def time_e2e(batch, n_steps, n_warm):
-        """Wall time of engine.step() in steady decode: pinned inputs in, sampled ids out, every step."""
-        prompt_len = CONTEXT - n_steps - n_warm - 1
-        sp = SamplingParams(max_tokens=n_steps + n_warm + 1, temperature=0.0, ignore_eos=True)
-        for i in range(batch):
-            engine.add_request(rng.integers(0, vocab, size=prompt_len).tolist(), sp)
-        while any(s.remaining > 1 or s.output_len == 0 for s in engine.sequences.values()) \
-                or len(engine.scheduler.waiting):
-            engine.step()                               # prompts, in portions
+        """Wall time of engine.step() in steady decode: pinned inputs in, sampled ids out, every step.
+        Prompts are fed first (in portions, some requests already decoding beside them); the timed
+        steps start when every request decodes, and end before the first one finishes."""
+        portions = -(-CONTEXT // PREFILL_TOKENS)
+        slack = batch * portions + 2
+        budget = n_steps + n_warm + slack
+        prompt_len = CONTEXT - budget
+        sp = SamplingParams(max_tokens=budget, temperature=0.0, ignore_eos=True)
+        ids = [engine.add_request(rng.integers(0, vocab, size=prompt_len).tolist(), sp) for _ in range(batch)]
+        seqs = [engine.sequences[i] for i in ids]
+        while engine.scheduler.waiting or any(s.remaining > 1 or s.output_len == 0 for s in seqs):
+            engine.step()
         for _ in range(n_warm):
             engine.step()
+        assert all(s.output_len + n_steps <= budget for s in seqs) and len(engine.scheduler.running) == batch
         torch.cuda.synchronize()
         t = time.perf_counter()
         produced = 0
@@ -220,15 +236,26 @@ def main() -> int:
             produced += len(engine.step())
         torch.cuda.synchronize()
         dt = time.perf_counter() - t
+        assert produced == batch * n_steps
         h2d = int(runner.last_meta_bytes) + 5 * 4 * batch
-        while engine.has_pending_work():
-            engine.step()
+        for i in ids:
+            engine.abort_request(i)
         return produced / dt, h2d, 4 * batch
 
+    if a.only == "prefill":
+        ms = time_prefill(max(1, min(steps, 3)), 2)
+        print(json.dumps({"metric": METRIC, "only": "prefill", "prefill_ms": round(ms, 3),
+                          "value": round(PREFILL_TOKENS / (ms * 1e-3), 1), "unit": "tokens/s"}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     ms, launches, kv_bytes = time_decode(a.batch, steps, warmup)
     clock_info = clocks.stop()
+    if a.only == "decode":
+        print(json.dumps({"metric": METRIC, "only": "decode", "batch": a.batch, "ms_per_step": round(ms, 4),
+                          "value": round(a.batch / (ms * 1e-3), 1), "unit": "tokens/s", "gpu_launches": launches,
+                          "cuda_graphs": not a.no_cuda_graphs, "clocks": clock_info}))
+        return 0
 
     weight_bytes = nums["matrix_params"] * 2
     step_bytes = weight_bytes + kv_bytes

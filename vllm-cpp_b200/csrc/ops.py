@@ -312,6 +312,12 @@ def sample_filtered(logits, temperature, uniform, top_p, top_k, out, scratch: Op
 
 
 _scratch = {}
+_scratch_epoch = 0
+
+
+def scratch_epoch() -> int:
+    """Changes whenever a scratch buffer moves; captured CUDA graphs that used one are stale then."""
+    return _scratch_epoch
 
 
 def scratch(name: str, numel: int, device) -> torch.Tensor:
@@ -323,4 +329,6 @@ def scratch(name: str, numel: int, device) -> torch.Tensor:
             raise KernelError(f"scratch buffer {name!r} must be sized before a CUDA graph is captured")
         t = torch.empty(max(numel, 1024), dtype=torch.float32, device=device)
         _scratch[name] = t
+        global _scratch_epoch
+        _scratch_epoch += 1
     return t

@@ -77,6 +77,8 @@ class ModelRunner:
         self._copy_pending = False
         self.use_cuda_graphs = use_cuda_graphs
         self.graphs: Dict[tuple, object] = {}
+        self._graph_seen: Dict[tuple, int] = {}
+        self._graph_sig = None
         self.last_meta_bytes = 0
 
     def _meta_ints(self, n: int, r: int, m: int) -> int:
@@ -89,11 +91,57 @@ class ModelRunner:
         in the order of the entries and of each entry's ``want``.  The tensor is a
         view of the runner's logits buffer and is overwritten by the next step."""
         step = self._prepare(entries)
-        self.ws.reset()
-        out = self.model.forward(step, self.views, self.ws, self.logits)
+        if self.use_cuda_graphs and step.decode_only and step.n_logit_rows == step.n_reqs:
+            out = self._run_decode_graph(step)
+        else:
+            self.ws.reset()
+            out = self.model.forward(step, self.views, self.ws, self.logits)
         for e in entries:
             self.cache.commit(e.req_id, len(e.tokens))
         return out
+
+    # ---------------------------------------------------------- CUDA graphs
+    def _buffers_signature(self):
+        from ..csrc import ops
+        return (self.meta_dev.data_ptr(), self.ws.buf.data_ptr(), self.logits.data_ptr(), ops.scratch_epoch())
+
+    def _run_decode_graph(self, step: StepContext) -> torch.Tensor:
+        """A step in which every request brings one token and wants its logits has a fixed shape
+        for a given number of requests: its launches are captured once and replayed.  The first
+        step of a shape runs directly (it also sizes workspace and scratch), the second is
+        captured, later ones replay.  The metadata copy and the sampling stay outside the graph."""
+        from ..csrc import ops
+        key = (step.n_reqs, step.split_len)
+        sig = self._buffers_signature()
+        if sig != self._graph_sig:
+            self.graphs.clear()             # a buffer moved: recorded addresses are stale
+            self._graph_seen.clear()
+            self._graph_sig = sig
+        entry = self.graphs.get(key)
+        if entry is None:
+            if self._graph_seen.get(key, 0) < 1:
+                self._graph_seen[key] = 1
+                self.ws.reset()
+                out = self.model.forward(step, self.views, self.ws, self.logits)
+                self._graph_sig = self._buffers_signature()
+                return out
+            graph = torch.cuda.CUDAGraph()
+            self.ws.reset()
+            self.ws.frozen = True
+            before = ops.launch_count()
+            try:
+                with torch.cuda.graph(graph):
+                    self.model.forward(step, self.views, self.ws, self.logits)
+            finally:
+                self.ws.frozen = False
+            captured = ops.launch_count() - before
+            ops.add_launches(-captured)     # recorded, not run
+            entry = (graph, captured)
+            self.graphs[key] = entry
+        graph, captured = entry
+        graph.replay()
+        ops.add_launches(captured)
+        return self.logits[: step.n_logit_rows]
 
     def _prepare(self, entries: List[StepEntry]) -> StepContext:
         if not entries:
@@ -206,4 +254,5 @@ class ModelRunner:
             h_q_start=[int(x) for x in qs], h_ctx_lens=list(ctx_lens), h_state_slots=list(slots),
             decode_only=all(q == 1 for q in q_lens), max_q_len=max(q_lens),
             max_total_len=max(c + q for c, q in zip(ctx_lens, q_lens)),
+            split_len=max(256, 1 << (max(c + q for c, q in zip(ctx_lens, q_lens)) - 1).bit_length()),
             extras={name: dev("x:" + name, arr.shape) for name, arr in extra.items()})

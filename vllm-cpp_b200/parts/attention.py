@@ -140,7 +140,11 @@ class PagedAttention(Mixer):
             kw = dict(num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d, page_size=cache.page_size,
                       window=self.window, scale=self.scale)
             if step.decode_only:
-                longest = step.max_total_len if self.window <= 0 else min(step.max_total_len, self.window + 64)
+                # the split count depends on the context only through its power-of-two bucket, so
+                # that a captured step stays valid while the contexts grow inside the bucket
+                longest = step.split_len or step.max_total_len
+                if self.window > 0:
+                    longest = min(longest, self.window + 64)
                 nsplit = max(1, min(-(-longest // 64), -(-2 * self.SM_COUNT // (step.n_reqs * self.nkv)), 32))
                 part_o = part_ml = None
                 if nsplit > 1:

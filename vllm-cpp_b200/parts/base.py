@@ -86,6 +86,7 @@ class StepContext:
     decode_only: bool                    # every request brings exactly one token
     max_q_len: int
     max_total_len: int                   # longest context after this step
+    split_len: int = 0                   # max_total_len rounded up to a power of two (stable kernel shapes)
     extras: Dict[str, object] = field(default_factory=dict)   # per-step device arrays of kernels
 
 
