@@ -81,21 +81,25 @@ template <int D>
 __device__ __forceinline__ void load_kv_tile(uint32_t sk, uint32_t sv, int kb, int lo, int hi,
                                              const int* __restrict__ bt, const __nv_bfloat16* __restrict__ cache,
                                              int g, int page, int nkv) {
-    constexpr int CH = D / 8;
-    const size_t page_elems = (size_t)2 * nkv * page * D;
-    const size_t v_off = (size_t)nkv * page * D;
-    for (int idx = threadIdx.x; idx < BN * CH; idx += NTHREADS) {
-        const int key = idx / CH, c = idx % CH;
-        const int j = kb + key;
-        const bool valid = j >= lo && j < hi;
-        const __nv_bfloat16* src = cache;
-        if (valid) {
-            const int pg = bt[j / page];
-            src = cache + (size_t)pg * page_elems + ((size_t)g * page + (j % page)) * D + c * 8;
-        }
-        const uint32_t off = swz<D>(key, c);
-        cp_async_16(sk + off, src, valid ? 16 : 0);
-        cp_async_16(sv + off, valid ? src + v_off : src, valid ? 16 : 0);
+    constexpr int CH = D / 8;                   // 16-byte chunks per row
+    constexpr int TPR = NTHREADS / BN;          // threads per key row
+    constexpr int CPT = CH / TPR;               // chunks per thread
+    static_assert(NTHREADS % BN == 0 && CH % TPR == 0, "tile loader shape");
+    const int key = threadIdx.x / TPR, c0 = (threadIdx.x % TPR) * CPT;
+    const int j = kb + key;
+    const bool valid = j >= lo && j < hi;
+    const __nv_bfloat16* src = cache;
+    if (valid) {
+        const int pg = bt[j / page];
+        src = cache + (size_t)pg * ((size_t)2 * nkv * page * D) + ((size_t)g * page + (j % page)) * D + c0 * 8;
+    }
+    const __nv_bfloat16* vsrc = valid ? src + (size_t)nkv * page * D : src;
+    const int bytes = valid ? 16 : 0;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const uint32_t off = swz<D>(key, c0 + c);
+        cp_async_16(sk + off, valid ? src + c * 8 : src, bytes);
+        cp_async_16(sv + off, valid ? vsrc + c * 8 : vsrc, bytes);
     }
 }
 

@@ -70,18 +70,100 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     }
 }
 
+// Same computation with 16-byte accesses and the row held in registers between the
+// sum of squares and the scaling, so global memory is read once.  Needs hidden % 4 == 0
+// and hidden <= 4 * NV * blockDim.x.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&a);
+        u.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+template <typename T, int NV>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                       const float* __restrict__ gain, T* __restrict__ out,
+                                       const int* __restrict__ row_index, int hidden, float eps) {
+    __shared__ float scratch[33];
+    const int o = blockIdx.x;
+    const int row = row_index ? row_index[o] : o;
+    float* res = residual + (size_t)row * hidden;
+    const T* dl = delta ? delta + (size_t)row * hidden : nullptr;
+    T* dst = out + (size_t)o * hidden;
+    const bool write_back = (row_index == nullptr) && (delta != nullptr);
+    const int nvec = hidden >> 2;
+    float4 x[NV];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < nvec) {
+            float4 v = Vec4<float>::load(res + 4 * i);
+            if (dl) {
+                const float4 d = Vec4<T>::load(dl + 4 * i);
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            }
+            if (write_back) Vec4<float>::store(res + 4 * i, v);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            x[k] = v;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < nvec) {
+            const float4 g = Vec4<float>::load(gain + 4 * i);
+            float4 v = x[k];
+            v.x = (v.x * r) * g.x; v.y = (v.y * r) * g.y; v.z = (v.z * r) * g.z; v.w = (v.w * r) * g.w;
+            Vec4<T>::store(dst + 4 * i, v);
+        }
+    }
+}
+
+template <typename T>
+static void launch_add_rmsnorm(float* residual, const T* delta, const float* gain, T* out, const int* row_index,
+                               int n_rows, int hidden, float eps, cudaStream_t s) {
+    const bool aligned = (hidden % 4 == 0) && ((((uintptr_t)residual | (uintptr_t)gain) & 15) == 0) &&
+                         ((((uintptr_t)delta | (uintptr_t)out) & 7) == 0);
+    const int nvec = hidden / 4;
+    if (aligned && nvec <= 128 * 4)
+        add_rmsnorm_vec_kernel<T, 4><<<n_rows, 128, 0, s>>>(residual, delta, gain, out, row_index, hidden, eps);
+    else if (aligned && nvec <= 256 * 4)
+        add_rmsnorm_vec_kernel<T, 4><<<n_rows, 256, 0, s>>>(residual, delta, gain, out, row_index, hidden, eps);
+    else if (aligned && nvec <= 1024 * 8)
+        add_rmsnorm_vec_kernel<T, 8><<<n_rows, 1024, 0, s>>>(residual, delta, gain, out, row_index, hidden, eps);
+    else {
+        const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+        add_rmsnorm_kernel<T><<<n_rows, threads, 0, s>>>(residual, delta, gain, out, row_index, hidden, eps);
+    }
+}
+
 VCB_EXPORT int vcb_add_rmsnorm(float* residual, const void* delta, const float* gain, void* out,
                                const int* row_index, int n_rows, int hidden, float eps, int dtype,
                                void* stream) {
     if (n_rows <= 0) return 0;
-    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VCB_F32)
-        add_rmsnorm_kernel<float><<<n_rows, threads, 0, s>>>(residual, (const float*)delta, gain,
-                                                              (float*)out, row_index, hidden, eps);
+        launch_add_rmsnorm<float>(residual, (const float*)delta, gain, (float*)out, row_index, n_rows, hidden, eps, s);
     else if (dtype == VCB_BF16)
-        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, s>>>(
-            residual, (const __nv_bfloat16*)delta, gain, (__nv_bfloat16*)out, row_index, hidden, eps);
+        launch_add_rmsnorm<__nv_bfloat16>(residual, (const __nv_bfloat16*)delta, gain, (__nv_bfloat16*)out,
+                                          row_index, n_rows, hidden, eps, s);
     else
         return VCB_ERR_BAD_ARG;
     return vcb_last_error();
@@ -144,63 +226,49 @@ struct RopeCacheArgs {
 };
 
 template <typename T>
-__global__ void rope_cache_kernel(RopeCacheArgs a) {
+__global__ void rope_cache_kernel(RopeCacheArgs a, int heads_per_block) {
     const int t = blockIdx.x;
     const int nheads = a.nh + 2 * a.nkv;
     const int half = a.d / 2, rhalf = a.rot / 2;
+    const int h = blockIdx.y * heads_per_block + threadIdx.x / half;
+    const int j = threadIdx.x % half;
+    if (h >= nheads || threadIdx.x >= heads_per_block * half) return;
     const int pos = a.positions[t];
-    const T* src = (const T*)a.qkv + (size_t)t * nheads * a.d;
-    T* qdst = (T*)a.q_out + (size_t)t * a.nh * a.d;
-    T* kdst = nullptr;
-    T* vdst = nullptr;
-    if (a.write_kv) {
+    const T* src = (const T*)a.qkv + (size_t)t * nheads * a.d + (size_t)h * a.d;
+    int ia, ib;
+    if (j < rhalf) {                          // the pair that q and k rotate (v: the same slots, unrotated)
+        if (a.pairing == 0) { ia = j; ib = j + rhalf; }
+        else                { ia = 2 * j; ib = 2 * j + 1; }
+    } else {                                  // beyond the rotary part: pass through
+        ia = a.rot + 2 * (j - rhalf); ib = ia + 1;
+    }
+    float xa = to_f32<T>(src[ia]);
+    float xb = to_f32<T>(src[ib]);
+    if (a.bias) { xa += a.bias[h * a.d + ia]; xb += a.bias[h * a.d + ib]; }
+    if (h < a.nh + a.nkv && j < rhalf) {
+        const float ang = (float)pos / a.denom[j];
+        float sn, cs;
+        sincosf(ang, &sn, &cs);
+        const float ra = xa * cs - xb * sn;
+        const float rb = xa * sn + xb * cs;
+        xa = ra; xb = rb;
+    }
+    T* dst;
+    if (h < a.nh) {
+        dst = (T*)a.q_out + (size_t)t * a.nh * a.d + (size_t)h * a.d;
+    } else {
+        if (!a.write_kv) return;
         const int r = a.req_of_token[t];
         const int pg = a.block_table[(size_t)r * a.bt_stride + pos / a.page];
         const int slot = pos % a.page;
         // [page][2][nkv][slot][d]
         T* base = (T*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
-        kdst = base + (size_t)slot * a.d;
-        vdst = base + (size_t)a.nkv * a.page * a.d + (size_t)slot * a.d;
+        const int kvh = h < a.nh + a.nkv ? h - a.nh : h - a.nh - a.nkv;
+        const size_t which = h < a.nh + a.nkv ? 0 : (size_t)a.nkv * a.page * a.d;
+        dst = base + which + ((size_t)kvh * a.page + slot) * a.d;
     }
-    const int items = nheads * half;
-    for (int it = threadIdx.x; it < items; it += blockDim.x) {
-        const int h = it / half, j = it % half;
-        int ia, ib;
-        bool rotate = false;
-        if (h < a.nh + a.nkv && j < rhalf) {
-            rotate = true;
-            if (a.pairing == 0) { ia = j; ib = j + rhalf; }
-            else                { ia = 2 * j; ib = 2 * j + 1; }
-        } else if (j < rhalf) {               // v head, slots that q/k rotate: plain pair
-            if (a.pairing == 0) { ia = j; ib = j + rhalf; }
-            else                { ia = 2 * j; ib = 2 * j + 1; }
-        } else {                              // beyond the rotary part: pass through
-            ia = a.rot + 2 * (j - rhalf); ib = ia + 1;
-        }
-        float xa = to_f32<T>(src[h * a.d + ia]);
-        float xb = to_f32<T>(src[h * a.d + ib]);
-        if (a.bias) { xa += a.bias[h * a.d + ia]; xb += a.bias[h * a.d + ib]; }
-        if (rotate) {
-            const float ang = (float)pos / a.denom[j];
-            float sn, cs;
-            sincosf(ang, &sn, &cs);
-            const float ra = xa * cs - xb * sn;
-            const float rb = xa * sn + xb * cs;
-            xa = ra; xb = rb;
-        }
-        if (h < a.nh) {
-            qdst[h * a.d + ia] = from_f32<T>(xa);
-            qdst[h * a.d + ib] = from_f32<T>(xb);
-        } else if (a.write_kv) {
-            if (h < a.nh + a.nkv) {
-                T* p = kdst + (size_t)(h - a.nh) * a.page * a.d;
-                p[ia] = from_f32<T>(xa); p[ib] = from_f32<T>(xb);
-            } else {
-                T* p = vdst + (size_t)(h - a.nh - a.nkv) * a.page * a.d;
-                p[ia] = from_f32<T>(xa); p[ib] = from_f32<T>(xb);
-            }
-        }
-    }
+    dst[ia] = from_f32<T>(xa);
+    dst[ib] = from_f32<T>(xb);
 }
 
 VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const int* positions,
@@ -213,11 +281,15 @@ VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const in
         return VCB_ERR_BAD_ARG;
     RopeCacheArgs a{qkv, bias, positions, req_of_token, block_table, denom, q_out, cache,
                     bt_stride, nh, nkv, d, rot, pairing, page, write_kv};
-    const int items = (nh + 2 * nkv) * (d / 2);
-    const int threads = items >= 1024 ? 256 : (items >= 256 ? 128 : 64);
+    const int half = d / 2, nheads = nh + 2 * nkv;
+    int hpb = 128 / half;                      // heads per CTA: about 128 threads
+    if (hpb < 1) hpb = 1;
+    if (hpb > nheads) hpb = nheads;
+    const int threads = ((hpb * half + 31) / 32) * 32;
+    dim3 grid(n_tokens, (nheads + hpb - 1) / hpb);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VCB_F32) rope_cache_kernel<float><<<n_tokens, threads, 0, s>>>(a);
-    else if (dtype == VCB_BF16) rope_cache_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(a);
+    if (dtype == VCB_F32) rope_cache_kernel<float><<<grid, threads, 0, s>>>(a, hpb);
+    else if (dtype == VCB_BF16) rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(a, hpb);
     else return VCB_ERR_BAD_ARG;
     return vcb_last_error();
 }

@@ -89,7 +89,18 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
     // The largest logit and its lowest id; the maximum is also softmax's shift.
     float bv = -INFINITY;
     int bi = vocab;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) argmax_combine(bv, bi, l[i], i);
+    if ((((uintptr_t)l) & 15) == 0) {
+        const int nvec = vocab >> 2;
+        const float4* l4 = reinterpret_cast<const float4*>(l);
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+            const float4 v = l4[i];
+            argmax_combine(bv, bi, v.x, 4 * i); argmax_combine(bv, bi, v.y, 4 * i + 1);
+            argmax_combine(bv, bi, v.z, 4 * i + 2); argmax_combine(bv, bi, v.w, 4 * i + 3);
+        }
+        for (int i = (nvec << 2) + threadIdx.x; i < vocab; i += blockDim.x) argmax_combine(bv, bi, l[i], i);
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) argmax_combine(bv, bi, l[i], i);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);

@@ -145,7 +145,9 @@ class PagedAttention(Mixer):
                 longest = step.split_len or step.max_total_len
                 if self.window > 0:
                     longest = min(longest, self.window + 64)
-                nsplit = max(1, min(-(-longest // 64), -(-2 * self.SM_COUNT // (step.n_reqs * self.nkv)), 32))
+                # as many splits as fill the GPU once: two CTAs fit an SM, a second wave would
+                # double the time
+                nsplit = max(1, min(-(-longest // 64), 2 * self.SM_COUNT // (step.n_reqs * self.nkv), 32))
                 part_o = part_ml = None
                 if nsplit > 1:
                     need = step.n_reqs * self.nh * nsplit
