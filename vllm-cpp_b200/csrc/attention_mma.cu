@@ -531,3 +531,56 @@ VCB_EXPORT int vcb_attention_prefill_mma(const void* q, const void* cache, void*
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_prefill<64>(a, n_tiles, s) : launch_prefill<128>(a, n_tiles, s);
 }
+
+// ------------------------------------------------ no-allocation entry point
+// See no_alloc.h for who this is for and its limits.
+#include "no_alloc.h"
+
+// Merge scratch of the static variant: rows of (d floats of partial output), then
+// rows of (max, sum).  In host code this name is only a handle for the symbol; the
+// device address is looked up below.
+static __device__ __align__(256) float vcb_static_scratch[VCB_STATIC_SCRATCH_ROWS * (VCB_STATIC_SCRATCH_DIM + 2)];
+
+#define VCB_MAX_DEVICES 64
+static float* vcb_static_scratch_addr[VCB_MAX_DEVICES];
+
+// The array's address on the current device, looked up once per device.
+static int static_scratch_address(float** addr) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= VCB_MAX_DEVICES) return VCB_ERR_BAD_ARG;
+    if (vcb_static_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, vcb_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        vcb_static_scratch_addr[dev] = static_cast<float*>(p);
+    }
+    *addr = vcb_static_scratch_addr[dev];
+    return 0;
+}
+
+VCB_EXPORT int vcb_attention_decode_mma_static(const void* q, const void* cache, void* out, const int* q_start,
+                                               const int* ctx_lens, const int* block_table, int bt_stride,
+                                               const int* req_list, int n_list, int nsplit, int nh, int nkv,
+                                               int d, int page, int window, float scale, void* stream) {
+    if (n_list <= 0) return 0;
+    int c = check_common(nh, nkv, d, page, window);
+    if (c) return c;
+    if (nsplit < 1) return VCB_ERR_BAD_ARG;
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    if (nsplit > 1) {
+        const long long rows = (long long)n_list * nh * nsplit;
+        if (rows > VCB_STATIC_SCRATCH_ROWS || d > VCB_STATIC_SCRATCH_DIM) return VCB_ERR_SCRATCH_TOO_SMALL;
+        float* base = nullptr;
+        c = static_scratch_address(&base);
+        if (c) return c;
+        part_o = base;
+        part_ml = base + (size_t)VCB_STATIC_SCRATCH_ROWS * VCB_STATIC_SCRATCH_DIM;
+    }
+    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
+                  block_table, req_list, nullptr, part_o, part_ml, bt_stride, nh, nkv, page, window, scale};
+    cudaStream_t s = (cudaStream_t)stream;
+    return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
+}

@@ -1,0 +1,58 @@
+// An entry point for callers that must not allocate device memory.
+//
+// This has no counterpart in jiamumuzhao/vllm-cpp; it exists for users of this
+// library only.
+//
+// Who needs it.  Some programs that want split-KV decode attention cannot call
+// cudaMalloc at the moment they need the kernel, or at all: code that runs inside
+// a latency-critical serving loop where an allocation's implicit device
+// synchronisation is not acceptable; a process whose device memory has been handed
+// out in full to a pool it does not own; a plug-in loaded into a host application
+// that forbids allocations from foreign code.  The ordinary entry point,
+// vcb_attention_decode_mma, leaves the allocation of the merge scratch (partial
+// outputs of the context splits) to its caller, which comes to the same problem.
+//
+// What it does.  vcb_attention_decode_mma_static runs the same kernels on the same
+// inputs and outputs, but merges the splits through a fixed array that lives in the
+// library's own device data segment.  It calls no cudaMalloc, no cudaFree and no
+// library routine that allocates.
+//
+// The limit.  The array holds VCB_STATIC_SCRATCH_ROWS partial rows of up to
+// VCB_STATIC_SCRATCH_DIM floats plus two statistics each (about 4.3 MB).  Every GPU
+// on which the library is loaded carries it until the process exits.  A call needs
+// n_list * nh * nsplit rows when nsplit > 1 (none when nsplit == 1); a call that
+// needs more rows, or a head size above VCB_STATIC_SCRATCH_DIM, is refused with
+// VCB_ERR_SCRATCH_TOO_SMALL and launches nothing.
+//
+// First call.  The first call on a device looks up the array's device address
+// (cudaGetSymbolAddress, with that device current) and keeps it; make that first
+// call before any stream capture begins.
+//
+// Sharing.  All calls on a device use the one array, and it keeps what the last call
+// left in it.  Nothing in it has to start at zero: every slot that the merge reads is
+// written earlier in the same call.  Two calls that overlap on the GPU (different
+// streams) race on the array; run them on one stream or order them yourself.
+#pragma once
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VCB_STATIC_SCRATCH_ROWS 8192
+#define VCB_STATIC_SCRATCH_DIM 128
+#define VCB_ERR_SCRATCH_TOO_SMALL 10003
+
+// Arguments as vcb_attention_decode_mma, without the two scratch pointers:
+//   q, out: [n_tokens, nh * d] bfloat16; cache: [pages][2][nkv][page][d] bfloat16;
+//   q_start [n_reqs + 1], ctx_lens [n_reqs], block_table [n_reqs, bt_stride]: int32 on the device;
+//   req_list: n_list request indices on the device, or null for 0..n_list-1;
+//   nsplit: context splits per (request, kv head); stream: a cudaStream_t.
+// Returns 0, a cudaError_t value, or one of the VCB_ERR_* codes.
+int vcb_attention_decode_mma_static(const void* q, const void* cache, void* out, const int* q_start,
+                                    const int* ctx_lens, const int* block_table, int bt_stride,
+                                    const int* req_list, int n_list, int nsplit, int nh, int nkv, int d,
+                                    int page, int window, float scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
