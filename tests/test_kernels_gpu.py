@@ -248,9 +248,10 @@ def test_attention_decode_mma(ops, nsplit, nh, nkv, d, page, window):
     out = torch.zeros((n, nh * d), dtype=torch.bfloat16, device="cuda")
     part_o = torch.empty(n * nh * nsplit * d, dtype=torch.float32, device="cuda")
     part_ml = torch.empty(n * nh * nsplit * 2, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(n * nkv, dtype=torch.int32, device="cuda")
     ops.attention_decode_mma(dev(c["q"].reshape(n, -1), torch.bfloat16), dev(c["cache"], torch.bfloat16), out,
                              dev(c["q_start"]), dev(np.array(ctx_lens, dtype=np.int32)), dev(c["bt"]), None, n, nsplit,
-                             part_o, part_ml, num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page,
+                             part_o, part_ml, counters, num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page,
                              window=window, scale=float(np.float32(1) / np.sqrt(np.float32(d))))
     want = reference_attention(c["q"].astype(np.float64), c["k"], c["v"], q_lens, ctx_lens, nh, nkv, window)
     close(out.float().cpu().numpy().reshape(n, nh, d), want, "bfloat16", f"attention_decode_mma nsplit={nsplit}")
@@ -259,7 +260,7 @@ def test_attention_decode_mma(ops, nsplit, nh, nkv, d, page, window):
     out2 = torch.zeros_like(out)
     ops.attention_decode_mma(dev(c["q"].reshape(n, -1), torch.bfloat16), dev(c["cache"], torch.bfloat16), out2,
                              dev(c["q_start"]), dev(np.array(ctx_lens, dtype=np.int32)), dev(c["bt"]), dev(sel), 2, nsplit,
-                             part_o, part_ml, num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page,
+                             part_o, part_ml, counters, num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page,
                              window=window, scale=float(np.float32(1) / np.sqrt(np.float32(d))))
     got2 = out2.float().cpu().numpy().reshape(n, nh, d)
     close(got2[[5, 2]], want[[5, 2]], "bfloat16", "decode with a request list")

@@ -54,7 +54,8 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
         want = torch.zeros_like(q)
         part_o = torch.empty(n_req * nh * nsplit * d, dtype=torch.float32, device="cuda")
         part_ml = torch.empty(n_req * nh * nsplit * 2, dtype=torch.float32, device="cuda")
-        ops.attention_decode_mma(q, cache, want, q_start, ctx, bt, None, n_req, nsplit, part_o, part_ml,
+        counters = torch.zeros(n_req * nkv, dtype=torch.int32, device="cuda")
+        ops.attention_decode_mma(q, cache, want, q_start, ctx, bt, None, n_req, nsplit, part_o, part_ml, counters,
                                  num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page, window=window,
                                  scale=scale)
         got = torch.zeros_like(q)
@@ -73,9 +74,11 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
               bt.shape[1], None, 2, 1, 6, 2, 64, 16, 0, 0.125, stream) == 0
     torch.cuda.synchronize()
     assert got.float().abs().sum().item() > 0
+    # 44 requests x 6 heads x 32 splits = 8448 rows: more than the array holds
+    q, cache, q_start, ctx, bt = _case(10, 44, 6, 2, 64, 16, 100)
     untouched = torch.zeros_like(q)
-    too_many = ROWS_LIMIT // (2 * 6) + 1
+    too_many = 32                                   # the most splits the kernel takes
     assert fn(q.data_ptr(), cache.data_ptr(), untouched.data_ptr(), q_start.data_ptr(), ctx.data_ptr(), bt.data_ptr(),
-              bt.shape[1], None, 2, too_many, 6, 2, 64, 16, 0, 0.125, stream) == ERR_TOO_SMALL
+              bt.shape[1], None, 44, too_many, 6, 2, 64, 16, 0, 0.125, stream) == ERR_TOO_SMALL
     torch.cuda.synchronize()
     assert not untouched.any()

@@ -9,10 +9,13 @@
 //   * attention_decode_kernel: one query token per request.  Its G rows fill one
 //     16-row fragment; the context is split over gridDim.x CTAs, and inside a CTA
 //     each warp takes 16 of every 64 keys.  Partial (max, sum, output) triples are
-//     merged across warps in shared memory and across CTAs by
-//     attention_combine_kernel through scratch memory in global memory.
+//     merged across warps in shared memory and across CTAs through scratch memory
+//     in global memory: every CTA of a (request, kv head) takes a ticket when its
+//     partials are written, and the one that draws the last ticket merges them.
 // Scores, softmax statistics and output accumulators are float; the probabilities
-// are rounded to bfloat16 for the P*V product, as K and V are stored.
+// are rounded to bfloat16 for the P*V product, as K and V are stored.  Exponentials
+// are ex2.approx on scores pre-multiplied by log2(e) (this file is the bfloat16 path;
+// the plain kernel of attention_simt.cu uses expf).
 //
 // K/V tiles come from the pages with 16-byte cp.async copies in a multi-stage ring;
 // rows are XOR-swizzled in units of 16 bytes so that ldmatrix reads are free of
@@ -37,7 +40,8 @@ struct MmaAttnArgs {
     const int* req_list;           // decode: requests to process (null: 0..n-1); prefill: tile -> request
     const int* tile_row0;          // prefill: tile -> first packed row
     float* part_o;                 // decode scratch: [n_list, nh, splits, d]
-    float* part_ml;                // decode scratch: [n_list, nh, splits, 2]
+    float* part_ml;                // decode scratch: [n_list, nh, splits, 2]  (max in log2 units, sum)
+    int* counters;                 // decode scratch: [n_list, nkv] tickets, zero between launches
     int bt_stride, nh, nkv, page, window;
     float scale;
 };
@@ -70,38 +74,56 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+#define LOG2E 1.4426950408889634f
+
 // Byte offset of element (row, 16-byte chunk) in a tile of rows of D bfloat16.
 template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
 }
 
-// One K tile and one V tile of BN keys starting at key kb (a multiple of BN) of kv
-// head g.  Keys outside [lo, hi) are filled with zeros.
-template <int D>
-__device__ __forceinline__ void load_kv_tile(uint32_t sk, uint32_t sv, int kb, int lo, int hi,
-                                             const int* __restrict__ bt, const __nv_bfloat16* __restrict__ cache,
-                                             int g, int page, int nkv) {
-    constexpr int CH = D / 8;                   // 16-byte chunks per row
-    constexpr int TPR = NTHREADS / BN;          // threads per key row
-    constexpr int CPT = CH / TPR;               // chunks per thread
-    static_assert(NTHREADS % BN == 0 && CH % TPR == 0, "tile loader shape");
-    const int key = threadIdx.x / TPR, c0 = (threadIdx.x % TPR) * CPT;
-    const int j = kb + key;
-    const bool valid = j >= lo && j < hi;
-    const __nv_bfloat16* src = cache;
-    if (valid) {
-        const int pg = bt[j / page];
-        src = cache + (size_t)pg * ((size_t)2 * nkv * page * D) + ((size_t)g * page + (j % page)) * D + c0 * 8;
+// Loads one K tile and one V tile of BN keys of kv head g per call.  Each thread owns
+// one key row of the tile (a fixed share of its 16-byte chunks).  The row's page id is
+// fetched from the block table one tile ahead (prefetch) so that the table's latency
+// is not on the path of the copy that needs it.  Keys outside [lo, hi) are zero-filled.
+template <int D, int NT>
+struct KVLoader {
+    static constexpr int CH = D / 8;            // 16-byte chunks per row
+    static constexpr int TPR = NT / BN;         // threads per key row
+    static constexpr int CPT = CH / TPR;        // chunks per thread
+    static_assert(NT % BN == 0 && CH % TPR == 0, "tile loader shape");
+    const int* bt;
+    const __nv_bfloat16* cache;
+    int g, page, nkv, lo, hi, key, c0, pg;
+
+    __device__ __forceinline__ void init(const int* bt_, const __nv_bfloat16* cache_, int g_, int page_, int nkv_,
+                                         int lo_, int hi_) {
+        bt = bt_; cache = cache_; g = g_; page = page_; nkv = nkv_; lo = lo_; hi = hi_;
+        key = threadIdx.x / TPR; c0 = (threadIdx.x % TPR) * CPT; pg = -1;
     }
-    const __nv_bfloat16* vsrc = valid ? src + (size_t)nkv * page * D : src;
-    const int bytes = valid ? 16 : 0;
+    __device__ __forceinline__ void prefetch(int kb) {
+        const int j = kb + key;
+        pg = (j >= lo && j < hi) ? bt[j / page] : -1;
+    }
+    __device__ __forceinline__ void issue(uint32_t sk, uint32_t sv, int kb) const {
+        const int j = kb + key;
+        const bool valid = pg >= 0;
+        const __nv_bfloat16* src = cache;
+        if (valid) src = cache + (size_t)pg * ((size_t)2 * nkv * page * D) + ((size_t)g * page + (j % page)) * D + c0 * 8;
+        const __nv_bfloat16* vsrc = valid ? src + (size_t)nkv * page * D : src;
+        const int bytes = valid ? 16 : 0;
 #pragma unroll
-    for (int c = 0; c < CPT; ++c) {
-        const uint32_t off = swz<D>(key, c0 + c);
-        cp_async_16(sk + off, valid ? src + c * 8 : src, bytes);
-        cp_async_16(sv + off, valid ? vsrc + c * 8 : vsrc, bytes);
+        for (int c = 0; c < CPT; ++c) {
+            const uint32_t off = swz<D>(key, c0 + c);
+            cp_async_16(sk + off, valid ? src + c * 8 : src, bytes);
+            cp_async_16(sv + off, valid ? vsrc + c * 8 : vsrc, bytes);
+        }
     }
-}
+};
 
 // S[16 x 8*NB] += Q[16 x D] * K[keys key0 .. key0 + 8*NB)^T, K tile at sk.
 template <int D, int NB>
@@ -164,6 +186,7 @@ attention_decode_kernel(MmaAttnArgs a) {
     const int hi = pos + 1;
     const int lo = a.window > 0 ? max(0, hi - a.window) : 0;
     const int* bt = a.block_table + (size_t)r * a.bt_stride;
+    const float sl2 = a.scale * LOG2E;                   // scores in units of log2
 
     const int tile0 = lo / BN, tile1 = (hi + BN - 1) / BN;
     const int per = (tile1 - tile0 + nsplit - 1) / nsplit;
@@ -195,11 +218,15 @@ attention_decode_kernel(MmaAttnArgs a) {
         float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;   // rows lane/4 and lane/4 + 8
 
         // prologue
+        KVLoader<D, NTHREADS> ld;
+        ld.init(bt, a.cache, g, a.page, a.nkv, lo, hi);
+        if (my0 < my1) ld.prefetch(my0 * BN);
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
-            if (my0 + s < my1)
-                load_kv_tile<D>(s_tiles + s * 2 * TILE_BYTES, s_tiles + s * 2 * TILE_BYTES + TILE_BYTES,
-                                (my0 + s) * BN, lo, hi, bt, a.cache, g, a.page, a.nkv);
+            if (my0 + s < my1) {
+                ld.issue(s_tiles + s * 2 * TILE_BYTES, s_tiles + s * 2 * TILE_BYTES + TILE_BYTES, (my0 + s) * BN);
+                if (my0 + s + 1 < my1) ld.prefetch((my0 + s + 1) * BN);
+            }
             cp_async_commit();
         }
         for (int tile = my0; tile < my1; ++tile) {
@@ -208,9 +235,10 @@ attention_decode_kernel(MmaAttnArgs a) {
             {   // refill the stage that was consumed in the previous iteration
                 const int nt = tile + STAGES - 1;
                 const int st = (nt - my0) % STAGES;
-                if (nt < my1)
-                    load_kv_tile<D>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
-                                    nt * BN, lo, hi, bt, a.cache, g, a.page, a.nkv);
+                if (nt < my1) {
+                    ld.issue(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES, nt * BN);
+                    if (nt + 1 < my1) ld.prefetch((nt + 1) * BN);
+                }
                 cp_async_commit();
             }
             const int st = (tile - my0) % STAGES;
@@ -226,7 +254,7 @@ attention_decode_kernel(MmaAttnArgs a) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int j = kb + nb * 8 + (lane & 3) * 2 + (e & 1);
-                    s[nb][e] = (j >= lo && j < hi) ? s[nb][e] * a.scale : -INFINITY;
+                    s[nb][e] = (j >= lo && j < hi) ? s[nb][e] * sl2 : -INFINITY;
                 }
             // all rows of a decode tile share the position, but keep the two row sets apart
             float ta = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -236,14 +264,14 @@ attention_decode_kernel(MmaAttnArgs a) {
             (void)tmax;
             const float na = fmaxf(m_a, ta), nb_ = fmaxf(m_b, tb);
             const float sa = na == -INFINITY ? 0.0f : na, sb = nb_ == -INFINITY ? 0.0f : nb_;
-            const float ca = expf(m_a - sa), cb = expf(m_b - sb);      // m = -inf: exp(-inf) = 0, sums are 0 anyway
+            const float ca = fast_exp2(m_a - sa), cb = fast_exp2(m_b - sb);      // m = -inf: exp(-inf) = 0, sums are 0 anyway
             m_a = na; m_b = nb_;
             uint32_t pf[1][4];
             float p[2][4];
 #pragma unroll
             for (int nb = 0; nb < 2; ++nb) {
-                p[nb][0] = expf(s[nb][0] - sa); p[nb][1] = expf(s[nb][1] - sa);
-                p[nb][2] = expf(s[nb][2] - sb); p[nb][3] = expf(s[nb][3] - sb);
+                p[nb][0] = fast_exp2(s[nb][0] - sa); p[nb][1] = fast_exp2(s[nb][1] - sa);
+                p[nb][2] = fast_exp2(s[nb][2] - sb); p[nb][3] = fast_exp2(s[nb][3] - sb);
             }
             l_a = l_a * ca + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
             l_b = l_b * cb + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
@@ -282,7 +310,7 @@ attention_decode_kernel(MmaAttnArgs a) {
             for (int w = 0; w < 4; ++w) {
                 const float mw = red_ml[(w * 16 + row) * 2];
                 if (mw == -INFINITY) continue;
-                const float f = expf(mw - mx);
+                const float f = fast_exp2(mw - mx);
                 acc += red_o[((size_t)(w * 16 + row)) * D + dim] * f;
                 l += red_ml[(w * 16 + row) * 2 + 1] * f;
             }
@@ -296,27 +324,40 @@ attention_decode_kernel(MmaAttnArgs a) {
             }
         }
     }
-}
+    if (nsplit == 1) return;
 
-// out[t, head, :] = sum_s part_o[s] * exp(m_s - m) / sum_s l_s * exp(m_s - m)
-__global__ void attention_combine_kernel(MmaAttnArgs a, int nsplit, int d) {
-    const int li = blockIdx.y, head = blockIdx.x;
-    const int r = a.req_list ? a.req_list[li] : li;
-    const int t = a.q_start[r];
-    const size_t p0 = ((size_t)li * a.nh + head) * nsplit;
-    float mx = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, a.part_ml[(p0 + s) * 2]);
-    for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
-        float acc = 0.0f, l = 0.0f;
-        for (int s = 0; s < nsplit; ++s) {
-            const float ms = a.part_ml[(p0 + s) * 2];
-            if (ms == -INFINITY) continue;
-            const float f = expf(ms - mx);
-            acc += a.part_o[(p0 + s) * d + dim] * f;
-            l += a.part_ml[(p0 + s) * 2 + 1] * f;
-        }
-        a.out[((size_t)t * a.nh + head) * d + dim] = __float2bfloat16_rn(acc / l);
+    // Merge of the splits.  This CTA's partials are in global memory; the CTA that takes
+    // the last ticket of this (request, kv head) sees all of them and writes the output:
+    // out[t, head, :] = sum_s part_o[s] * 2^(m_s - m) / sum_s l_s * 2^(m_s - m).
+    __shared__ int s_ticket;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_ticket = atomicAdd(&a.counters[li * a.nkv + g], 1);
+    __syncthreads();
+    if (s_ticket != nsplit - 1) return;
+    __threadfence();
+    // factors 2^(m_s - m) / sum per (head, split): one warp per head, one lane per split
+    float* fac = reinterpret_cast<float*>(smem);           // [G][32], the tiles are dead
+    for (int hg = warp; hg < G; hg += NTHREADS / 32) {
+        const size_t p0 = ((size_t)li * a.nh + g * G + hg) * nsplit;
+        float ms = -INFINITY, ls = 0.0f;
+        if (lane < nsplit) { ms = __ldcg(a.part_ml + (p0 + lane) * 2); ls = __ldcg(a.part_ml + (p0 + lane) * 2 + 1); }
+        const float mx = warp_max(ms);
+        const float f = ms == -INFINITY ? 0.0f : fast_exp2(ms - mx);
+        const float total = warp_sum(ls * f);
+        fac[hg * 32 + lane] = f / total;
     }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
+        const int hg = idx / D, dim = idx % D;
+        const int head = g * G + hg;
+        const float* po = a.part_o + ((size_t)li * a.nh + head) * nsplit * D + dim;
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int sp = 0; sp < nsplit; ++sp) acc += __ldcg(po + (size_t)sp * D) * fac[hg * 32 + sp];
+        a.out[((size_t)t * a.nh + head) * D + dim] = __float2bfloat16_rn(acc);
+    }
+    if (threadIdx.x == 0) a.counters[li * a.nkv + g] = 0;       // ready for the next launch
 }
 
 // ----------------------------------------------------------------- prefill
@@ -333,6 +374,7 @@ attention_prefill_kernel(MmaAttnArgs a) {
     const int q0 = a.q_start[r], q_len = a.q_start[r + 1] - q0, ctx = a.ctx_lens[r];
     const int rows_total = q_len * G;
     const int* bt = a.block_table + (size_t)r * a.bt_stride;
+    const float sl2 = a.scale * LOG2E;                   // scores in units of log2
 
     const uint32_t s_base = smem_u32(smem);
     const uint32_t sq = s_base;                          // [BM][D]
@@ -359,11 +401,15 @@ attention_prefill_kernel(MmaAttnArgs a) {
     const int lo = a.window > 0 ? max(0, ctx + row0 / G + 1 - a.window) : 0;
     const int tile0 = lo / BN, tile1 = (hi + BN - 1) / BN;
 
+    KVLoader<D, NTHREADS> ld;
+    ld.init(bt, a.cache, g, a.page, a.nkv, lo, hi);
+    if (tile0 < tile1) ld.prefetch(tile0 * BN);
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (tile0 + s < tile1)
-            load_kv_tile<D>(s_tiles + s * 2 * TILE_BYTES, s_tiles + s * 2 * TILE_BYTES + TILE_BYTES,
-                            (tile0 + s) * BN, lo, hi, bt, a.cache, g, a.page, a.nkv);
+        if (tile0 + s < tile1) {
+            ld.issue(s_tiles + s * 2 * TILE_BYTES, s_tiles + s * 2 * TILE_BYTES + TILE_BYTES, (tile0 + s) * BN);
+            if (tile0 + s + 1 < tile1) ld.prefetch((tile0 + s + 1) * BN);
+        }
         cp_async_commit();
     }
     __syncthreads();                                     // Q tile written
@@ -384,9 +430,10 @@ attention_prefill_kernel(MmaAttnArgs a) {
         {
             const int nt = tile + STAGES - 1;
             const int st = (nt - tile0) % STAGES;
-            if (nt < tile1)
-                load_kv_tile<D>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
-                                nt * BN, lo, hi, bt, a.cache, g, a.page, a.nkv);
+            if (nt < tile1) {
+                ld.issue(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES, nt * BN);
+                if (nt + 1 < tile1) ld.prefetch((nt + 1) * BN);
+            }
             cp_async_commit();
         }
         const int st = (tile - tile0) % STAGES;
@@ -401,7 +448,7 @@ attention_prefill_kernel(MmaAttnArgs a) {
         for (int nb = 0; nb < BN / 8; ++nb)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                float v = s[nb][e] * a.scale;
+                float v = s[nb][e] * sl2;
                 if (need_mask) {
                     const int j = kb + nb * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = (e < 2) ? pos_a : pos_b;
@@ -421,7 +468,7 @@ attention_prefill_kernel(MmaAttnArgs a) {
         tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 1)); tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 2));
         const float na = fmaxf(m_a, ta), nb_ = fmaxf(m_b, tb);
         const float sa = na == -INFINITY ? 0.0f : na, sb = nb_ == -INFINITY ? 0.0f : nb_;
-        const float ca = expf(m_a - sa), cb = expf(m_b - sb);
+        const float ca = fast_exp2(m_a - sa), cb = fast_exp2(m_b - sb);
         m_a = na; m_b = nb_;
         uint32_t pf[BN / 16][4];
         float sum_a = 0.0f, sum_b = 0.0f;
@@ -431,8 +478,8 @@ attention_prefill_kernel(MmaAttnArgs a) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int nb = kk * 2 + h;
-                p[h][0] = expf(s[nb][0] - sa); p[h][1] = expf(s[nb][1] - sa);
-                p[h][2] = expf(s[nb][2] - sb); p[h][3] = expf(s[nb][3] - sb);
+                p[h][0] = fast_exp2(s[nb][0] - sa); p[h][1] = fast_exp2(s[nb][1] - sa);
+                p[h][2] = fast_exp2(s[nb][2] - sb); p[h][3] = fast_exp2(s[nb][3] - sb);
                 sum_a += p[h][0] + p[h][1];
                 sum_b += p[h][2] + p[h][3];
             }
@@ -475,9 +522,6 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
     }
     dim3 grid(nsplit, a.nkv, n_list);
     attention_decode_kernel<D, STAGES><<<grid, NTHREADS, smem, s>>>(a);
-    int err = vcb_last_error();
-    if (err || nsplit == 1) return err;
-    attention_combine_kernel<<<dim3(a.nh, n_list), D <= 64 ? 64 : 128, 0, s>>>(a, nsplit, D);
     return vcb_last_error();
 }
 
@@ -503,18 +547,20 @@ static int check_common(int nh, int nkv, int d, int page, int window) {
     return 0;
 }
 
-// Scratch for the split-KV merge: part_o needs n_list*nh*nsplit*d floats, part_ml n_list*nh*nsplit*2.
+// Scratch for the split-KV merge (nsplit > 1): part_o needs n_list*nh*nsplit*d floats, part_ml
+// n_list*nh*nsplit*2 floats, counters n_list*nkv ints that are zero when the kernel starts (it
+// leaves them zero).
 VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* out, const int* q_start,
                                         const int* ctx_lens, const int* block_table, int bt_stride,
                                         const int* req_list, int n_list, int nsplit, float* part_o,
-                                        float* part_ml, int nh, int nkv, int d, int page, int window,
-                                        float scale, void* stream) {
+                                        float* part_ml, int* counters, int nh, int nkv, int d, int page,
+                                        int window, float scale, void* stream) {
     if (n_list <= 0) return 0;
     int c = check_common(nh, nkv, d, page, window);
     if (c) return c;
-    if (nsplit < 1 || (nsplit > 1 && (!part_o || !part_ml))) return VCB_ERR_BAD_ARG;
+    if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, req_list, nullptr, part_o, part_ml, bt_stride, nh, nkv, page, window, scale};
+                  block_table, req_list, nullptr, part_o, part_ml, counters, bt_stride, nh, nkv, page, window, scale};
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
@@ -527,7 +573,7 @@ VCB_EXPORT int vcb_attention_prefill_mma(const void* q, const void* cache, void*
     int c = check_common(nh, nkv, d, page, window);
     if (c) return c;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, tile_req, tile_row0, nullptr, nullptr, bt_stride, nh, nkv, page, window, scale};
+                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, bt_stride, nh, nkv, page, window, scale};
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_prefill<64>(a, n_tiles, s) : launch_prefill<128>(a, n_tiles, s);
 }
@@ -541,22 +587,31 @@ VCB_EXPORT int vcb_attention_prefill_mma(const void* q, const void* cache, void*
 // device address is looked up below.
 static __device__ __align__(256) float vcb_static_scratch[VCB_STATIC_SCRATCH_ROWS * (VCB_STATIC_SCRATCH_DIM + 2)];
 
+// Tickets of the split merge, one per (request, kv head); cleared before every launch.
+static __device__ __align__(256) int vcb_static_counters[VCB_STATIC_SCRATCH_ROWS];
+
 #define VCB_MAX_DEVICES 64
 static float* vcb_static_scratch_addr[VCB_MAX_DEVICES];
+static int* vcb_static_counters_addr[VCB_MAX_DEVICES];
 
 // The array's address on the current device, looked up once per device.
-static int static_scratch_address(float** addr) {
+static int static_scratch_address(float** addr, int** counters) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= VCB_MAX_DEVICES) return VCB_ERR_BAD_ARG;
-    if (vcb_static_scratch_addr[dev] == nullptr) {
+    if (vcb_static_scratch_addr[dev] == nullptr || vcb_static_counters_addr[dev] == nullptr) {
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, vcb_static_scratch);
         if (e != cudaSuccess) return (int)e;
+        void* pc = nullptr;
+        e = cudaGetSymbolAddress(&pc, vcb_static_counters);
+        if (e != cudaSuccess) return (int)e;
         vcb_static_scratch_addr[dev] = static_cast<float*>(p);
+        vcb_static_counters_addr[dev] = static_cast<int*>(pc);
     }
     *addr = vcb_static_scratch_addr[dev];
+    *counters = vcb_static_counters_addr[dev];
     return 0;
 }
 
@@ -567,20 +622,24 @@ VCB_EXPORT int vcb_attention_decode_mma_static(const void* q, const void* cache,
     if (n_list <= 0) return 0;
     int c = check_common(nh, nkv, d, page, window);
     if (c) return c;
-    if (nsplit < 1) return VCB_ERR_BAD_ARG;
+    if (nsplit < 1 || nsplit > 32) return VCB_ERR_BAD_ARG;
     float* part_o = nullptr;
     float* part_ml = nullptr;
+    int* counters = nullptr;
+    cudaStream_t s = (cudaStream_t)stream;
     if (nsplit > 1) {
         const long long rows = (long long)n_list * nh * nsplit;
         if (rows > VCB_STATIC_SCRATCH_ROWS || d > VCB_STATIC_SCRATCH_DIM) return VCB_ERR_SCRATCH_TOO_SMALL;
         float* base = nullptr;
-        c = static_scratch_address(&base);
+        c = static_scratch_address(&base, &counters);
         if (c) return c;
         part_o = base;
         part_ml = base + (size_t)VCB_STATIC_SCRATCH_ROWS * VCB_STATIC_SCRATCH_DIM;
+        // the tickets must start at zero whatever an earlier call left behind
+        cudaError_t e = cudaMemsetAsync(counters, 0, sizeof(int) * (size_t)n_list * nkv, s);
+        if (e != cudaSuccess) return (int)e;
     }
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, req_list, nullptr, part_o, part_ml, bt_stride, nh, nkv, page, window, scale};
-    cudaStream_t s = (cudaStream_t)stream;
+                  block_table, req_list, nullptr, part_o, part_ml, counters, bt_stride, nh, nkv, page, window, scale};
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }

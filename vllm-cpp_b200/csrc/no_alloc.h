@@ -18,7 +18,8 @@
 // library routine that allocates.
 //
 // The limit.  The array holds VCB_STATIC_SCRATCH_ROWS partial rows of up to
-// VCB_STATIC_SCRATCH_DIM floats plus two statistics each (about 4.3 MB).  Every GPU
+// VCB_STATIC_SCRATCH_DIM floats plus two statistics each, and one ticket counter per
+// row (about 4.3 MB in all).  Every GPU
 // on which the library is loaded carries it until the process exits.  A call needs
 // n_list * nh * nsplit rows when nsplit > 1 (none when nsplit == 1); a call that
 // needs more rows, or a head size above VCB_STATIC_SCRATCH_DIM, is refused with
@@ -29,8 +30,10 @@
 // call before any stream capture begins.
 //
 // Sharing.  All calls on a device use the one array, and it keeps what the last call
-// left in it.  Nothing in it has to start at zero: every slot that the merge reads is
-// written earlier in the same call.  Two calls that overlap on the GPU (different
+// left in it.  The partial results need no clearing: every slot that the merge reads is
+// written earlier in the same call.  The tickets by which the splits of a (request,
+// kv head) find out who merges must start at zero; the entry point clears them on the
+// caller's stream before each launch.  Two calls that overlap on the GPU (different
 // streams) race on the array; run them on one stream or order them yourself.
 #pragma once
 

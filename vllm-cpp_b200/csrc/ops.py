@@ -34,7 +34,7 @@ _SIGNATURES = {
     "vcb_rope_cache_write": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "vcb_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "vcb_repetition_penalty": [_P, _I, _P, _P, _P, _I, _I, _P],
     "vcb_sample": [_P, _I, _I, _P, _P, _P, _I, _P],
@@ -206,7 +206,7 @@ MMA_HEAD_DIMS = (64, 128)
 
 
 def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list, n_list: int, nsplit: int,
-                         part_o, part_ml, *, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                         part_o, part_ml, counters, *, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
                          window: int, scale: float) -> None:
     """Split-KV tensor-core attention for requests that bring one token each (bfloat16)."""
     _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
@@ -214,7 +214,8 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
     _need(head_dim in MMA_HEAD_DIMS, f"attention_decode_mma takes head sizes {MMA_HEAD_DIMS}, got {head_dim}")
     if nsplit > 1:
         need = n_list * num_heads * nsplit
-        _need(part_o is not None and part_o.numel() >= need * head_dim and part_ml.numel() >= need * 2,
+        _need(part_o is not None and part_o.numel() >= need * head_dim and part_ml.numel() >= need * 2
+              and counters is not None and counters.numel() >= n_list * num_kv_heads,
               "attention_decode_mma: scratch for the split merge is too small")
     _check(lib().vcb_attention_decode_mma(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
@@ -222,9 +223,8 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
         block_table.shape[1], None if req_list is None else _dev(req_list, "req_list", torch.int32),
         n_list, nsplit, None if part_o is None else _dev(part_o, "part_o", torch.float32),
         None if part_ml is None else _dev(part_ml, "part_ml", torch.float32),
+        None if counters is None else _dev(counters, "counters", torch.int32),
         num_heads, num_kv_heads, head_dim, page_size, window, float(scale), _stream()), "attention_decode_mma")
-    if nsplit > 1:
-        add_launches(1)          # the merge kernel
 
 
 def attention_prefill_mma(q, cache, out, q_start, ctx_lens, block_table, tile_req, tile_row0, *,
@@ -318,6 +318,20 @@ _scratch_epoch = 0
 def scratch_epoch() -> int:
     """Changes whenever a scratch buffer moves; captured CUDA graphs that used one are stale then."""
     return _scratch_epoch
+
+
+def zeroed_ints(name: str, numel: int, device) -> torch.Tensor:
+    """An int32 device buffer of at least ``numel`` zeros, kept under ``name``.  Kernels that
+    count tickets in it leave it zero again."""
+    t = _scratch.get(name)
+    if t is None or t.numel() < numel or t.device != torch.device(device):
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError(f"scratch buffer {name!r} must be sized before a CUDA graph is captured")
+        t = torch.zeros(max(numel, 1024), dtype=torch.int32, device=device)
+        _scratch[name] = t
+        global _scratch_epoch
+        _scratch_epoch += 1
+    return t
 
 
 def scratch(name: str, numel: int, device) -> torch.Tensor:

@@ -148,13 +148,14 @@ class PagedAttention(Mixer):
                 # as many splits as fill the GPU once: two CTAs fit an SM, a second wave would
                 # double the time
                 nsplit = max(1, min(-(-longest // 64), 2 * self.SM_COUNT // (step.n_reqs * self.nkv), 32))
-                part_o = part_ml = None
+                part_o = part_ml = counters = None
                 if nsplit > 1:
                     need = step.n_reqs * self.nh * nsplit
                     part_o = ops.scratch("attn_part_o", need * self.d, q.device)
                     part_ml = ops.scratch("attn_part_ml", need * 2, q.device)
+                    counters = ops.zeroed_ints("attn_tickets", step.n_reqs * self.nkv, q.device)
                 ops.attention_decode_mma(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, None,
-                                         step.n_reqs, nsplit, part_o, part_ml, **kw)
+                                         step.n_reqs, nsplit, part_o, part_ml, counters, **kw)
             else:
                 tiles = step.extras[f"attn_tiles_g{self.nh // self.nkv}"]
                 ops.attention_prefill_mma(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table,
