@@ -368,3 +368,27 @@ def test_sampling_top_k_top_p_and_penalty(ops):
     want[0] = plain.repetition_penalty(logits[0], [3, 9, 3], 1.5)
     want[2] = plain.repetition_penalty(logits[2], [500, 7], 2.0)
     assert np.allclose(l.cpu().numpy(), want, rtol=1e-6)
+
+
+@pytest.mark.parametrize("m,n,k,plan", [
+    (8, 256, 512, (True, 16, 1)), (1, 128, 64, (True, 16, 1)), (8, 4608, 3584, None), (5, 300, 200, (True, 16, 3)),
+    (33, 1000, 1024, (True, 64, 2)), (64, 3584, 18944, None), (100, 384, 576, (True, 128, 1)),
+    (300, 520, 448, (False, 256, 1)), (2048, 1024, 512, (False, 256, 2)), (130, 130, 72, (False, 256, 1)),
+    (16, 152064, 256, None)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_gemm_bf16_tcgen05(ops, m, n, k, plan, out_dtype):
+    """The tcgen05 + TMA product against a float64 product of the same bfloat16 operands: both
+    orientations, every tile width, split-K, ragged edges in rows, columns and K."""
+    rng = np.random.default_rng(11)
+    x, w = as_stored(rng.standard_normal((m, k)), "bfloat16"), as_stored(rng.standard_normal((n, k)) * 0.1, "bfloat16")
+    out = torch.full((m, n), float("nan"), dtype=DT[out_dtype], device="cuda")
+    for _ in range(2):                                  # twice: tickets must be zero again after a launch
+        ops.gemm_bf16_tcgen05(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out, plan)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    tol = 1e-5 if out_dtype == "float32" else 1e-2
+    err = np.abs(got - want).max()
+    assert err <= tol * np.abs(want).max(), f"max |diff| {err:.3e} vs scale {np.abs(want).max():.3e}"

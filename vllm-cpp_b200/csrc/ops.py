@@ -36,6 +36,7 @@ _SIGNATURES = {
     "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+    "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
     "vcb_repetition_penalty": [_P, _I, _P, _P, _P, _I, _I, _P],
     "vcb_sample": [_P, _I, _I, _P, _P, _P, _I, _P],
     "vcb_sample_filtered": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
@@ -253,6 +254,67 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         _need(t.is_cuda and t.dtype == torch.float32 and t.stride(1) == 1, f"gemm_f32: {name} must be float32 with unit inner stride")
     _check(lib().vcb_gemm_f32(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k,
                               a.stride(0), w.stride(0), out.stride(0), _stream()), "gemm_f32")
+
+
+SM_COUNT = 148
+_status: Optional[torch.Tensor] = None
+STATUS_MEANING = {1: "the TMA producer waited too long for a free stage", 2: "the MMA issuer waited too long for a loaded stage",
+                  3: "the epilogue waited too long for the accumulator"}
+
+
+def status_tensor(device) -> torch.Tensor:
+    """The device word in which kernels with bounded waits record a wait that ran out."""
+    global _status
+    if _status is None or _status.device != torch.device(device):
+        _status = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status
+
+
+def check_status() -> None:
+    """Raise if a kernel gave up on a wait since the last check (synchronises)."""
+    if _status is None:
+        return
+    code = int(_status.item())
+    if code:
+        _status.zero_()
+        raise KernelError(f"a tcgen05 kernel gave up on a bounded wait: {STATUS_MEANING.get(code, code)}")
+
+
+def tcgen05_plan(tokens: int, features: int, k: int):
+    """(swapped, bn, splits) for out[tokens, features] = x[tokens, k] @ w[features, k]^T."""
+    slabs = -(-k // 64)
+    if tokens <= 128:
+        bn = 16 if tokens <= 16 else 32 if tokens <= 32 else 64 if tokens <= 64 else 128
+        tiles = -(-features // 128)
+        splits = max(1, min(SM_COUNT // tiles, slabs // 8, 8))
+        return True, bn, splits
+    tiles = -(-tokens // 128) * -(-features // 256)
+    return False, 256, max(1, min(SM_COUNT // tiles, slabs // 8, 4))
+
+
+def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=None) -> None:
+    """out = x @ w^T on tcgen05 tensor cores fed by TMA (see gemm_tcgen05.cu); out bfloat16 or float32."""
+    m, k = x.shape
+    n = w.shape[0]
+    _need(w.shape[1] == k and out.shape == (m, n), "gemm_bf16_tcgen05: shapes do not agree")
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "gemm_bf16_tcgen05: operands must be bfloat16")
+    _need(out.dtype in (torch.bfloat16, torch.float32) and out.stride(1) == 1 and x.stride(1) == 1 and w.stride(1) == 1,
+          "gemm_bf16_tcgen05: unit inner strides, out bfloat16 or float32")
+    _need(k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0,
+          "gemm_bf16_tcgen05: TMA needs K and the row strides to be multiples of 8 and 16-byte aligned bases")
+    swapped, bn, splits = plan or tcgen05_plan(m, n, k)
+    partial = tickets = None
+    if splits > 1:
+        _need(out.stride(0) == n, "gemm_bf16_tcgen05: split-K needs a dense output")
+        partial = scratch("gemm_partial", splits * m * n, out.device)
+        tickets = zeroed_ints("gemm_tickets", 4096, out.device)
+    p, q = (w, x) if swapped else (x, w)
+    _check(lib().vcb_gemm_bf16_tcgen05(p.data_ptr(), p.shape[0], p.stride(0), q.data_ptr(), q.shape[0], q.stride(0), k,
+                                       out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0,
+                                       1 if swapped else 0, bn, splits,
+                                       None if partial is None else partial.data_ptr(),
+                                       None if tickets is None else tickets.data_ptr(),
+                                       status_tensor(out.device).data_ptr(), _stream()), "gemm_bf16_tcgen05")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
