@@ -370,20 +370,21 @@ def test_sampling_top_k_top_p_and_penalty(ops):
     assert np.allclose(l.cpu().numpy(), want, rtol=1e-6)
 
 
-@pytest.mark.parametrize("m,n,k,plan", [
-    (8, 256, 512, (True, 16, 1)), (1, 128, 64, (True, 16, 1)), (8, 4608, 3584, None), (5, 300, 200, (True, 16, 3)),
-    (33, 1000, 1024, (True, 64, 2)), (64, 3584, 18944, None), (100, 384, 576, (True, 128, 1)),
-    (300, 520, 448, (False, 256, 1)), (2048, 1024, 512, (False, 256, 2)), (130, 130, 72, (False, 256, 1)),
-    (16, 152064, 256, None)])
+@pytest.mark.parametrize("m,n,k,plan,ctas", [
+    (8, 256, 512, (True, 16), 148), (1, 128, 64, (True, 16), 148), (8, 4608, 3584, None, 148), (5, 300, 200, (True, 16), 3),
+    (33, 1000, 1024, (True, 64), 7), (64, 3584, 18944, None, 148), (100, 384, 576, (True, 128), 148),
+    (300, 520, 448, (False, 256), 148), (2048, 1024, 512, (False, 256), 5), (130, 130, 72, (False, 256), 1),
+    (16, 152064, 256, None, 148), (200, 700, 1032, (False, 128), 11), (40, 640, 8192, (True, 64), 148)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
-def test_gemm_bf16_tcgen05(ops, m, n, k, plan, out_dtype):
+def test_gemm_bf16_tcgen05(ops, m, n, k, plan, ctas, out_dtype):
     """The tcgen05 + TMA product against a float64 product of the same bfloat16 operands: both
-    orientations, every tile width, split-K, ragged edges in rows, columns and K."""
+    orientations, every tile width, runs of (tile, slab) units that split tiles between CTAs in
+    every way, ragged edges in rows, columns and K."""
     rng = np.random.default_rng(11)
     x, w = as_stored(rng.standard_normal((m, k)), "bfloat16"), as_stored(rng.standard_normal((n, k)) * 0.1, "bfloat16")
     out = torch.full((m, n), float("nan"), dtype=DT[out_dtype], device="cuda")
     for _ in range(2):                                  # twice: tickets must be zero again after a launch
-        ops.gemm_bf16_tcgen05(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out, plan)
+        ops.gemm_bf16_tcgen05(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out, plan, ctas)
     torch.cuda.synchronize()
     ops.check_status()
     want = x.astype(np.float64) @ w.astype(np.float64).T

@@ -2,18 +2,26 @@
 //   D[i, j] = sum_k P[i, k] * Q[j, k],   P: [rows_p, K], Q: [rows_q, K], both row-major
 // tcgen05.mma (kind::f16, bfloat16 in, float accumulate in tensor memory) fed by TMA
 // (cp.async.bulk.tensor, 128-byte swizzle) through a ring of shared-memory stages
-// guarded by mbarriers, one CTA per 128 x BN tile of D and per slice of K.
+// guarded by mbarriers.
 //
-// Two uses with the same kernel.  Prefill: P = activations (tokens), Q = weights, the
-// tile is stored as it is: C[token, feature].  Decode: P = weights, Q = the few tokens
-// of the step ("swap A and B"): the 128 rows of the tensor-core tile are weight rows,
-// so a step with 8 tokens streams every weight once at full tile efficiency, and the
-// tile is stored transposed: C[token, feature].  K can be split over CTAs so that
-// products with few output tiles still fill the GPU; partial tiles meet in global
-// scratch memory and the CTA that takes a tile's last ticket adds them up.
+// Two uses with the same kernel.  Prefill: P = activations (tokens), Q = weights, a
+// 128 x BN tile is stored as it is: C[token, feature].  Decode: P = weights, Q = the few
+// tokens of the step ("swap A and B"): the 128 rows of the tensor-core tile are weight
+// rows, so a step with 8 tokens streams every weight once at full tile efficiency, and the
+// tile is stored transposed: C[token, feature].
+//
+// Work is cut stream-K fashion: the (tile, 64-wide k slab) pairs of the whole product are
+// numbered tile by tile and dealt out in equal contiguous runs to one persistent CTA per
+// SM, so every SM streams the same number of bytes whatever the shape.  A CTA's run is a
+// sequence of segments (a tile and a range of its slabs).  A segment that covers all of K
+// is stored directly; the others leave float partial tiles in global scratch memory, take
+// a ticket of their tile, and the CTA that draws the tile's last ticket adds them up.  No
+// CTA ever waits for another.  The ring of stages runs on across segments, and two
+// accumulators in tensor memory alternate, so loads and MMAs of the next segment overlap
+// the read-back of the last.
 //
 // Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory and
-// issues the MMAs (one elected lane each), warps 2-5 read the accumulator back
+// issues the MMAs (one elected lane each), warps 2-5 read the accumulators back
 // (tcgen05.ld, each warp its own 32 lanes) and store.  No load uses cluster multicast.
 // Every wait on an mbarrier is bounded; a wait that runs out records where in *status,
 // the CTA stops issuing work, frees its tensor memory and returns.
@@ -34,10 +42,26 @@ constexpr uint32_t SPIN_LIMIT = 1u << 22;     // try_wait attempts before a wait
 
 struct GemmArgs {
     void* out;
-    float* partial;              // [splits][out rows][ldc] floats when splits > 1
-    int* tickets;                // one per output tile, zero between launches
+    float* partial;              // [ctas][2][BN][128] floats: a CTA's first and last segment
+    int* tickets;                // one per tile, zero between launches
     int* status;                 // 0, or the code of the first wait that ran out
-    int ldc, out_f32, swapped, rows_p, rows_q, k_slabs, splits, out_rows;
+    int ldc, out_f32, swapped, rows_p, rows_q;
+    int k_slabs, tiles_p, units_per_cta, total_units;
+};
+
+// The segments of one CTA's run of (tile, slab) units.
+struct Segments {
+    int u, end, slabs;
+    __device__ Segments(const GemmArgs& a, int cta)
+        : u(cta * a.units_per_cta), end(min((cta + 1) * a.units_per_cta, a.total_units)), slabs(a.k_slabs) {}
+    __device__ bool next(int& tile, int& s0, int& s1) {
+        if (u >= end) return false;
+        tile = u / slabs;
+        s0 = u - tile * slabs;
+        s1 = min(slabs, s0 + end - u);
+        u += s1 - s0;
+        return true;
+    }
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -99,29 +123,30 @@ __host__ __device__ constexpr uint32_t instr_desc(int n) {
 }
 
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmArgs a) {
     constexpr int Q_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
-    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;        // tensor memory comes in powers of two from 32 columns
+    constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators; powers of two from 32 columns
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES), acc_bar = smem_addr(bars + 2 * STAGES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
+    const uint32_t acc_full0 = smem_addr(bars + 2 * STAGES), acc_empty0 = smem_addr(bars + 2 * STAGES + 2);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* flags = reinterpret_cast<volatile int*>(tmem_slot + 1);      // [0] abort, [1] ticket
     const uint32_t tiles0 = smem_addr(smem);
-
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int p0 = blockIdx.x * BM, q0 = blockIdx.y * BN, split = blockIdx.z;
-    const int per = (a.k_slabs + a.splits - 1) / a.splits;
-    const int slab0 = split * per;
-    const int n_slabs = max(0, min(a.k_slabs, slab0 + per) - slab0);
+    const int cta = blockIdx.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(acc_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 4); }
         flags[0] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -139,94 +164,133 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     if (warp == 0) {
         // ---- TMA producer
         if (lane == 0) {
-            for (int it = 0; it < n_slabs; ++it) {
-                const int s = it % STAGES;
-                const uint32_t phase = (it / STAGES) & 1;
-                if (flags[0] || !mbar_wait(empty0 + 8 * s, phase ^ 1)) {
-                    if (!flags[0]) { flags[0] = 1; atomicCAS(a.status, 0, 1); }
-                    break;
+            Segments seg(a, cta);
+            int tile, s0, s1, it = 0;
+            while (!flags[0] && seg.next(tile, s0, s1)) {
+                const int p0 = (tile % a.tiles_p) * BM, q0 = (tile / a.tiles_p) * BN;
+                for (int slab = s0; slab < s1; ++slab, ++it) {
+                    const int s = it % STAGES;
+                    if (flags[0] || !mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) {
+                        if (!flags[0]) { flags[0] = 1; atomicCAS(a.status, 0, 1); }
+                        break;
+                    }
+                    mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                    const uint32_t dst = tiles0 + s * STAGE_BYTES;
+                    tma_load_2d(dst, &map_p, full0 + 8 * s, slab * BK, p0);
+                    tma_load_2d(dst + P_BYTES, &map_q, full0 + 8 * s, slab * BK, q0);
                 }
-                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                const uint32_t dst = tiles0 + s * STAGE_BYTES;
-                tma_load_2d(dst, &map_p, full0 + 8 * s, (slab0 + it) * BK, p0);
-                tma_load_2d(dst + P_BYTES, &map_q, full0 + 8 * s, (slab0 + it) * BK, q0);
             }
         }
     } else if (warp == 1) {
         // ---- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(BN);
-            int it = 0;
-            for (; it < n_slabs; ++it) {
-                const int s = it % STAGES;
-                const uint32_t phase = (it / STAGES) & 1;
-                if (flags[0] || !mbar_wait(full0 + 8 * s, phase)) {
-                    if (!flags[0]) { flags[0] = 1; atomicCAS(a.status, 0, 2); }
+            Segments seg(a, cta);
+            int tile, s0, s1, it = 0, n = 0;
+            while (!flags[0] && seg.next(tile, s0, s1)) {
+                const int buf = n & 1;
+                if (!mbar_wait(acc_empty0 + 8 * buf, ((n >> 1) & 1) ^ 1)) {
+                    if (!flags[0]) { flags[0] = 1; atomicCAS(a.status, 0, 4); }
                     break;
                 }
                 tc_fence_after();
-                const uint32_t pa = tiles0 + s * STAGE_BYTES, qa = pa + P_BYTES;
+                const uint32_t acc = tmem_d + buf * BN;
+                for (int slab = s0; slab < s1; ++slab, ++it) {
+                    const int s = it % STAGES;
+                    if (flags[0] || !mbar_wait(full0 + 8 * s, (it / STAGES) & 1)) {
+                        if (!flags[0]) { flags[0] = 1; atomicCAS(a.status, 0, 2); }
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t pa = tiles0 + s * STAGE_BYTES, qa = pa + P_BYTES;
 #pragma unroll
-                for (int j = 0; j < BK / UMMA_K; ++j)
-                    tc_mma(tmem_d, smem_desc(pa + j * UMMA_K * 2), smem_desc(qa + j * UMMA_K * 2), idesc,
-                           (it > 0 || j > 0) ? 1u : 0u);
-                tc_commit(empty0 + 8 * s);          // the stage is free once these MMAs have read it
+                    for (int j = 0; j < BK / UMMA_K; ++j)
+                        tc_mma(acc, smem_desc(pa + j * UMMA_K * 2), smem_desc(qa + j * UMMA_K * 2), idesc,
+                               (slab > s0 || j > 0) ? 1u : 0u);
+                    tc_commit(empty0 + 8 * s);      // the stage is free once these MMAs have read it
+                }
+                tc_commit(acc_full0 + 8 * buf);     // the accumulator is complete once all MMAs are done
+                ++n;
             }
-            tc_commit(acc_bar);                     // the accumulator is complete once all MMAs are done
         }
     } else {
         // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) ..
         const int lg = warp & 3;
-        const int i = p0 + lg * 32 + lane;          // row of P this thread holds
-        bool ok = !flags[0] && mbar_wait(acc_bar, 0);
-        if (!ok && !flags[0]) { flags[0] = 1; atomicCAS(a.status, 0, 3); }
-        ok = ok && !flags[0];
-        tc_fence_after();
-        float* part = a.splits > 1 ? a.partial + (size_t)split * a.out_rows * a.ldc : nullptr;
-        if (ok) {
+        const int r = lg * 32 + lane;               // row of the tile this thread holds
+        const int U = a.units_per_cta, S = a.k_slabs;
+        Segments seg(a, cta);
+        int tile, s0, s1, n = 0;
+        while (seg.next(tile, s0, s1)) {
+            const int buf = n & 1;
+            if (flags[0] || !mbar_wait(acc_full0 + 8 * buf, (n >> 1) & 1)) {
+                if (!flags[0]) { flags[0] = 1; atomicCAS(a.status, 0, 3); }
+                break;
+            }
+            tc_fence_after();
+            const int p0 = (tile % a.tiles_p) * BM, q0 = (tile / a.tiles_p) * BN;
+            const int i = p0 + r;
+            const bool whole = (s0 == 0 && s1 == S);
+            // a CTA's run starts inside at most one tile and ends inside at most one: two scratch slots
+            float* part = whole ? nullptr
+                                : a.partial + ((size_t)cta * 2 + (cta * U >= tile * S ? 0 : 1)) * BN * BM;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 uint32_t v[16];
-                if (n_slabs > 0) {
-                    tc_ld16(tmem_d + ((uint32_t)(lg * 32) << 16) + c, v);
-                } else {
+                tc_ld16(tmem_d + ((uint32_t)(lg * 32) << 16) + buf * BN + c, v);
+                if (part) {
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) v[e] = 0;
-                }
-                if (i >= a.rows_p) continue;
+                    for (int e = 0; e < 16; ++e) part[(c + e) * BM + r] = __uint_as_float(v[e]);
+                } else if (i < a.rows_p) {
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const int j = q0 + c + e;
-                    if (j >= a.rows_q) break;
-                    const size_t idx = a.swapped ? (size_t)j * a.ldc + i : (size_t)i * a.ldc + j;
-                    const float f = __uint_as_float(v[e]);
-                    if (part) part[idx] = f;
-                    else if (a.out_f32) reinterpret_cast<float*>(a.out)[idx] = f;
-                    else reinterpret_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16_rn(f);
-                }
-            }
-        }
-        if (part) {
-            // partial tiles of all splits meet here; the last CTA of this tile adds them up
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) flags[1] = atomicAdd(&a.tickets[blockIdx.y * gridDim.x + blockIdx.x], 1);
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (flags[1] == a.splits - 1) {
-                __threadfence();
-                if (i < a.rows_p) {
-                    for (int c = 0; c < BN; ++c) {
-                        const int j = q0 + c;
+                    for (int e = 0; e < 16; ++e) {
+                        const int j = q0 + c + e;
                         if (j >= a.rows_q) break;
                         const size_t idx = a.swapped ? (size_t)j * a.ldc + i : (size_t)i * a.ldc + j;
-                        float f = 0.0f;
-                        for (int sp = 0; sp < a.splits; ++sp) f += __ldcg(a.partial + (size_t)sp * a.out_rows * a.ldc + idx);
-                        if (a.out_f32) reinterpret_cast<float*>(a.out)[idx] = f;
-                        else reinterpret_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16_rn(f);
+                        if (a.out_f32) reinterpret_cast<float*>(a.out)[idx] = __uint_as_float(v[e]);
+                        else reinterpret_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16_rn(__uint_as_float(v[e]));
                     }
                 }
-                if (threadIdx.x == 64) a.tickets[blockIdx.y * gridDim.x + blockIdx.x] = 0;
             }
+            // the accumulator has been read: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+            ++n;
+            if (!part) continue;
+            // partial tile: take a ticket; the last of the tile's segments to arrive adds them up
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) flags[1] = atomicAdd(&a.tickets[tile], 1);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int first_cta = (tile * S) / U;
+            const int nseg = ((tile + 1) * S - 1) / U - first_cta + 1;
+            const bool last = flags[1] == nseg - 1;
+            asm volatile("bar.sync 1, 128;" ::: "memory");       // flags[1] is read before the next segment writes it
+            if (!last) continue;
+            __threadfence();
+            if (i < a.rows_p) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 8) {
+                    float acc[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+                    for (int sg = 0; sg < nseg; ++sg) {
+                        const int x = first_cta + sg;
+                        const float* src = a.partial + ((size_t)x * 2 + (x * U >= tile * S ? 0 : 1)) * BN * BM + r;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[e] += __ldcg(src + (c + e) * BM);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int j = q0 + c + e;
+                        if (j >= a.rows_q) break;
+                        const size_t idx = a.swapped ? (size_t)j * a.ldc + i : (size_t)i * a.ldc + j;
+                        if (a.out_f32) reinterpret_cast<float*>(a.out)[idx] = acc[e];
+                        else reinterpret_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16_rn(acc[e]);
+                    }
+                }
+            }
+            if (threadIdx.x == 64) a.tickets[tile] = 0;       // ready for the next launch
         }
     }
     // An aborted CTA may still have copies in flight: give each armed stage a bounded chance to land.
@@ -272,7 +336,7 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int bo
 }
 
 template <int BN, int STAGES>
-int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, cudaStream_t s) {
+int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int ctas, cudaStream_t s) {
     constexpr size_t smem = (size_t)STAGES * (P_BYTES + BN * BK * 2) + 1024 + 256;
     static bool configured = false;
     if (!configured) {
@@ -280,8 +344,7 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, cuda
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((a.rows_p + BM - 1) / BM, (a.rows_q + BN - 1) / BN, a.splits);
-    gemm_tcgen05_kernel<BN, STAGES><<<grid, GEMM_THREADS, smem, s>>>(mp, mq, a);
+    gemm_tcgen05_kernel<BN, STAGES><<<ctas, GEMM_THREADS, smem, s>>>(mp, mq, a);
     return vcb_last_error();
 }
 
@@ -291,31 +354,36 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, cuda
 //   swapped = 0: P = activations [rows_p = tokens], Q = weights [rows_q = features]: out[p, q]
 //   swapped = 1: P = weights [rows_p = features], Q = activations [rows_q = tokens]:  out[q, p]
 // bn: columns of the tensor-core tile (16, 32, 64, 128 or 256; rows_q is cut into tiles of bn).
-// splits > 1 needs partial (splits * out_rows * ldc floats) and tickets (one zeroed int per tile).
+// max_ctas: persistent CTAs (one per SM).  Scratch: partial holds max_ctas * 2 * bn * 128 floats,
+// tickets one zeroed int per tile (the kernel leaves them zero).
 VCB_EXPORT int vcb_gemm_bf16_tcgen05(const void* p, int rows_p, int ldp, const void* q, int rows_q, int ldq, int k,
-                                     void* out, int ldc, int out_f32, int swapped, int bn, int splits,
-                                     float* partial, int* tickets, int* status, void* stream) {
+                                     void* out, int ldc, int out_f32, int swapped, int bn, int max_ctas,
+                                     float* partial, int* tickets, int n_tickets, int* status, void* stream) {
     if (rows_p <= 0 || rows_q <= 0) return 0;
-    if (k <= 0 || splits < 1 || !status) return VCB_ERR_BAD_ARG;
+    if (k <= 0 || max_ctas < 1 || !status || !partial || !tickets) return VCB_ERR_BAD_ARG;
     // TMA needs 16-byte aligned bases and row strides
     if ((k % 8) || (ldp % 8) || (ldq % 8) || (((uintptr_t)p | (uintptr_t)q) & 15)) return VCB_ERR_UNSUPPORTED;
-    if (splits > 1 && (!partial || !tickets)) return VCB_ERR_BAD_ARG;
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return VCB_ERR_BAD_ARG;
     const int k_slabs = (k + BK - 1) / BK;
-    if (splits > k_slabs) splits = k_slabs;
+    const int tiles_p = (rows_p + BM - 1) / BM, tiles_q = (rows_q + bn - 1) / bn;
+    const long long total = (long long)tiles_p * tiles_q * k_slabs;
+    if (tiles_p * tiles_q > n_tickets || total > (1ll << 30)) return VCB_ERR_UNSUPPORTED;
+    // equal runs of (tile, slab) units, at least four slabs each
+    int ctas = (int)(total / 4 < 1 ? 1 : (total / 4 < max_ctas ? total / 4 : max_ctas));
+    const int per = (int)((total + ctas - 1) / ctas);
+    ctas = (int)((total + per - 1) / per);
     CUtensorMap mp, mq;
     int c = make_map(&mp, p, rows_p, k, ldp, BM);
     if (c) return c;
     c = make_map(&mq, q, rows_q, k, ldq, bn);
     if (c) return c;
-    GemmArgs a{out, partial, tickets, status, ldc, out_f32, swapped, rows_p, rows_q, k_slabs, splits,
-               swapped ? rows_q : rows_p};
+    GemmArgs a{out, partial, tickets, status, ldc, out_f32, swapped, rows_p, rows_q, k_slabs, tiles_p, per, (int)total};
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
-        case 16: return launch<16, 10>(mp, mq, a, s);
-        case 32: return launch<32, 9>(mp, mq, a, s);
-        case 64: return launch<64, 8>(mp, mq, a, s);
-        case 128: return launch<128, 6>(mp, mq, a, s);
-        case 256: return launch<256, 4>(mp, mq, a, s);
-        default: return VCB_ERR_BAD_ARG;
+        case 16: return launch<16, 10>(mp, mq, a, ctas, s);
+        case 32: return launch<32, 9>(mp, mq, a, ctas, s);
+        case 64: return launch<64, 8>(mp, mq, a, ctas, s);
+        case 128: return launch<128, 6>(mp, mq, a, ctas, s);
+        default: return launch<256, 4>(mp, mq, a, ctas, s);
     }
 }

@@ -36,7 +36,7 @@ _SIGNATURES = {
     "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
-    "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
     "vcb_repetition_penalty": [_P, _I, _P, _P, _P, _I, _I, _P],
     "vcb_sample": [_P, _I, _I, _P, _P, _P, _I, _P],
     "vcb_sample_filtered": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
@@ -259,7 +259,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 SM_COUNT = 148
 _status: Optional[torch.Tensor] = None
 STATUS_MEANING = {1: "the TMA producer waited too long for a free stage", 2: "the MMA issuer waited too long for a loaded stage",
-                  3: "the epilogue waited too long for the accumulator"}
+                  3: "the epilogue waited too long for the accumulator", 4: "the MMA issuer waited too long for a free accumulator"}
 
 
 def status_tensor(device) -> torch.Tensor:
@@ -281,18 +281,17 @@ def check_status() -> None:
 
 
 def tcgen05_plan(tokens: int, features: int, k: int):
-    """(swapped, bn, splits) for out[tokens, features] = x[tokens, k] @ w[features, k]^T."""
-    slabs = -(-k // 64)
+    """(swapped, bn) for out[tokens, features] = x[tokens, k] @ w[features, k]^T: few tokens put the
+    weights on the 128-row side of the tensor-core tile."""
     if tokens <= 128:
-        bn = 16 if tokens <= 16 else 32 if tokens <= 32 else 64 if tokens <= 64 else 128
-        tiles = -(-features // 128)
-        splits = max(1, min(SM_COUNT // tiles, slabs // 8, 8))
-        return True, bn, splits
-    tiles = -(-tokens // 128) * -(-features // 256)
-    return False, 256, max(1, min(SM_COUNT // tiles, slabs // 8, 4))
+        return True, (16 if tokens <= 16 else 32 if tokens <= 32 else 64 if tokens <= 64 else 128)
+    return False, 256
 
 
-def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=None) -> None:
+GEMM_MAX_TICKETS = 16384
+
+
+def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=None, max_ctas: int = SM_COUNT) -> None:
     """out = x @ w^T on tcgen05 tensor cores fed by TMA (see gemm_tcgen05.cu); out bfloat16 or float32."""
     m, k = x.shape
     n = w.shape[0]
@@ -302,19 +301,15 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=
           "gemm_bf16_tcgen05: unit inner strides, out bfloat16 or float32")
     _need(k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0,
           "gemm_bf16_tcgen05: TMA needs K and the row strides to be multiples of 8 and 16-byte aligned bases")
-    swapped, bn, splits = plan or tcgen05_plan(m, n, k)
-    partial = tickets = None
-    if splits > 1:
-        _need(out.stride(0) == n, "gemm_bf16_tcgen05: split-K needs a dense output")
-        partial = scratch("gemm_partial", splits * m * n, out.device)
-        tickets = zeroed_ints("gemm_tickets", 4096, out.device)
+    swapped, bn = plan or tcgen05_plan(m, n, k)
+    partial = scratch("gemm_partial", SM_COUNT * 2 * 256 * 128, out.device)
+    tickets = zeroed_ints("gemm_tickets", GEMM_MAX_TICKETS, out.device)
     p, q = (w, x) if swapped else (x, w)
     _check(lib().vcb_gemm_bf16_tcgen05(p.data_ptr(), p.shape[0], p.stride(0), q.data_ptr(), q.shape[0], q.stride(0), k,
                                        out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0,
-                                       1 if swapped else 0, bn, splits,
-                                       None if partial is None else partial.data_ptr(),
-                                       None if tickets is None else tickets.data_ptr(),
-                                       status_tensor(out.device).data_ptr(), _stream()), "gemm_bf16_tcgen05")
+                                       1 if swapped else 0, bn, min(max_ctas, SM_COUNT), partial.data_ptr(),
+                                       tickets.data_ptr(), GEMM_MAX_TICKETS, status_tensor(out.device).data_ptr(),
+                                       _stream()), "gemm_bf16_tcgen05")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
