@@ -137,6 +137,10 @@ def main() -> int:
     from vllm_cpp_b200.engine.llm_engine import Engine
     from vllm_cpp_b200.engine.runner import StepEntry
 
+    if os.environ.get("VCB_PDL") is not None:                # experiment switches, for profiling
+        ops.set_pdl(os.environ["VCB_PDL"] != "0")
+    if os.environ.get("VCB_TCGEN05") is not None:
+        ops.set_tcgen05_linear(os.environ["VCB_TCGEN05"] != "0")
     cfg = dict(QWEN25_7B, num_hidden_layers=a.layers)
     nums = model_numbers(cfg)
     peaks = load_peaks()

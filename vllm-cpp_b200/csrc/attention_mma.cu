@@ -177,6 +177,7 @@ __global__ void __launch_bounds__(NTHREADS)
 attention_decode_kernel(MmaAttnArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int TILE_BYTES = BN * D * 2;
+    pdl_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, nsplit = gridDim.x, g = blockIdx.y, li = blockIdx.z;
     const int r = a.req_list ? a.req_list[li] : li;
@@ -366,6 +367,7 @@ __global__ void __launch_bounds__(NTHREADS)
 attention_prefill_kernel(MmaAttnArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int TILE_BYTES = BN * D * 2;
+    pdl_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = a.req_list[blockIdx.x];
     const int row0 = a.tile_row0[blockIdx.x];
@@ -521,7 +523,7 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
         configured = true;
     }
     dim3 grid(nsplit, a.nkv, n_list);
-    attention_decode_kernel<D, STAGES><<<grid, NTHREADS, smem, s>>>(a);
+    vcb_launch(attention_decode_kernel<D, STAGES>, grid, NTHREADS, smem, s, a);
     return vcb_last_error();
 }
 
@@ -537,7 +539,7 @@ static int launch_prefill(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
         configured = true;
     }
     dim3 grid(n_tiles, a.nkv);
-    attention_prefill_kernel<D, STAGES><<<grid, NTHREADS, smem, s>>>(a);
+    vcb_launch(attention_prefill_kernel<D, STAGES>, grid, NTHREADS, smem, s, a);
     return vcb_last_error();
 }
 

@@ -31,6 +31,7 @@ struct AttnArgs {
 template <typename T>
 __global__ void attention_simt_kernel(AttnArgs a) {
     extern __shared__ float qs_all[];
+    pdl_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * ATT_WARPS + warp;
     if (item >= (long long)a.n_tokens * a.nh) return;
@@ -107,8 +108,8 @@ VCB_EXPORT int vcb_attention_simt(const void* q, const void* cache, void* out, c
     const int blocks = (int)((items + ATT_WARPS - 1) / ATT_WARPS);
     const size_t smem = (size_t)ATT_WARPS * d * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VCB_F32) attention_simt_kernel<float><<<blocks, ATT_WARPS * 32, smem, s>>>(a);
-    else if (dtype == VCB_BF16) attention_simt_kernel<__nv_bfloat16><<<blocks, ATT_WARPS * 32, smem, s>>>(a);
+    if (dtype == VCB_F32) vcb_launch(attention_simt_kernel<float>, blocks, ATT_WARPS * 32, smem, s, a);
+    else if (dtype == VCB_BF16) vcb_launch(attention_simt_kernel<__nv_bfloat16>, blocks, ATT_WARPS * 32, smem, s, a);
     else return VCB_ERR_BAD_ARG;
     return vcb_last_error();
 }

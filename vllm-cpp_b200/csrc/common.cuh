@@ -72,3 +72,32 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 static inline int vcb_last_error() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch
+// Kernels of a step are launched so that the next kernel in the stream may begin while the
+// previous one still runs: its CTAs become resident, set themselves up (and, in the matrix
+// products, start streaming weights, which depend on nothing) and then block in
+// griddepcontrol.wait until the previous kernel has completed and its writes are visible.
+// Every kernel launched this way executes pdl_start() (or its two halves) before it touches
+// memory that another kernel writes or reads.  With the switch off, launches are ordinary.
+extern int vcb_pdl_enabled;                 // defined in elementwise.cu; set by vcb_set_pdl
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_start() { pdl_launch_dependents(); pdl_wait(); }
+
+template <typename... KArgs, typename... Args>
+static inline void vcb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = vcb_pdl_enabled ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -10,12 +10,16 @@
 // src/kernels/rotary_embedding.cu:8-45, src/layers/attention.cpp:84-102).
 #include "common.cuh"
 
+int vcb_pdl_enabled = 0;
+VCB_EXPORT void vcb_set_pdl(int on) { vcb_pdl_enabled = on ? 1 : 0; }
+
 // ---------------------------------------------------------------- embedding
 // residual[t, :] = float(table[ids[t], :]).  The residual stream is float in
 // both precisions.  Ids are validated on the host.
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ residual, int hidden) {
+    pdl_start();
     const int t = blockIdx.x;
     const T* row = table + (size_t)ids[t] * hidden;
     float* out = residual + (size_t)t * hidden;
@@ -28,9 +32,9 @@ VCB_EXPORT int vcb_embedding(const void* table, const int* ids, float* residual,
     const int threads = hidden >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VCB_F32)
-        embedding_kernel<float><<<n_tokens, threads, 0, s>>>((const float*)table, ids, residual, hidden);
+        vcb_launch(embedding_kernel<float>, n_tokens, threads, 0, s, (const float*)table, ids, residual, hidden);
     else if (dtype == VCB_BF16)
-        embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>((const __nv_bfloat16*)table, ids, residual, hidden);
+        vcb_launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden);
     else
         return VCB_ERR_BAD_ARG;
     return vcb_last_error();
@@ -47,6 +51,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
                                    const float* __restrict__ gain, T* __restrict__ out,
                                    const int* __restrict__ row_index, int hidden, float eps) {
     __shared__ float scratch[33];
+    pdl_start();
     const int o = blockIdx.x;
     const int row = row_index ? row_index[o] : o;
     float* res = residual + (size_t)row * hidden;
@@ -99,6 +104,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
                                        const float* __restrict__ gain, T* __restrict__ out,
                                        const int* __restrict__ row_index, int hidden, float eps) {
     __shared__ float scratch[33];
+    pdl_start();
     const int o = blockIdx.x;
     const int row = row_index ? row_index[o] : o;
     float* res = residual + (size_t)row * hidden;
@@ -143,14 +149,14 @@ static void launch_add_rmsnorm(float* residual, const T* delta, const float* gai
                          ((((uintptr_t)delta | (uintptr_t)out) & 7) == 0);
     const int nvec = hidden / 4;
     if (aligned && nvec <= 128 * 4)
-        add_rmsnorm_vec_kernel<T, 4><<<n_rows, 128, 0, s>>>(residual, delta, gain, out, row_index, hidden, eps);
+        vcb_launch(add_rmsnorm_vec_kernel<T, 4>, n_rows, 128, 0, s, residual, delta, gain, out, row_index, hidden, eps);
     else if (aligned && nvec <= 256 * 4)
-        add_rmsnorm_vec_kernel<T, 4><<<n_rows, 256, 0, s>>>(residual, delta, gain, out, row_index, hidden, eps);
+        vcb_launch(add_rmsnorm_vec_kernel<T, 4>, n_rows, 256, 0, s, residual, delta, gain, out, row_index, hidden, eps);
     else if (aligned && nvec <= 1024 * 8)
-        add_rmsnorm_vec_kernel<T, 8><<<n_rows, 1024, 0, s>>>(residual, delta, gain, out, row_index, hidden, eps);
+        vcb_launch(add_rmsnorm_vec_kernel<T, 8>, n_rows, 1024, 0, s, residual, delta, gain, out, row_index, hidden, eps);
     else {
         const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-        add_rmsnorm_kernel<T><<<n_rows, threads, 0, s>>>(residual, delta, gain, out, row_index, hidden, eps);
+        vcb_launch(add_rmsnorm_kernel<T>, n_rows, threads, 0, s, residual, delta, gain, out, row_index, hidden, eps);
     }
 }
 
@@ -174,6 +180,7 @@ VCB_EXPORT int vcb_add_rmsnorm(float* residual, const void* delta, const float* 
 // (src/kernels/activation.cu:8-10,34-39), evaluated in float with expf.
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
+    pdl_start();
     const int t = blockIdx.y;
     const T* g = gu + (size_t)t * 2 * inter;
     const T* u = g + inter;
@@ -188,6 +195,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 // Eight elements per thread with 16-byte accesses (bfloat16, inter % 8 == 0).
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                        int inter, size_t n_vec) {
+    pdl_start();
     const int vpr = inter >> 3;                       // vectors per row
     for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += (size_t)gridDim.x * blockDim.x) {
         const size_t t = v / vpr;
@@ -215,7 +223,7 @@ VCB_EXPORT int vcb_silu_mul(const void* gu, void* out, int n_tokens, int inter, 
         const size_t n_vec = (size_t)n_tokens * (inter >> 3);
         size_t blocks = (n_vec + 255) / 256;
         if (blocks > 148 * 16) blocks = 148 * 16;
-        silu_mul_bf16x8_kernel<<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, n_vec);
+        vcb_launch(silu_mul_bf16x8_kernel, (int)blocks, 256, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, n_vec);
         return vcb_last_error();
     }
     const int threads = 256;
@@ -223,9 +231,9 @@ VCB_EXPORT int vcb_silu_mul(const void* gu, void* out, int n_tokens, int inter, 
     if (bx > 64) bx = 64;
     dim3 grid(bx, n_tokens);
     if (dtype == VCB_F32)
-        silu_mul_kernel<float><<<grid, threads, 0, s>>>((const float*)gu, (float*)out, inter);
+        vcb_launch(silu_mul_kernel<float>, grid, threads, 0, s, (const float*)gu, (float*)out, inter);
     else if (dtype == VCB_BF16)
-        silu_mul_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter);
+        vcb_launch(silu_mul_kernel<__nv_bfloat16>, grid, threads, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter);
     else
         return VCB_ERR_BAD_ARG;
     return vcb_last_error();
@@ -257,6 +265,7 @@ struct RopeCacheArgs {
 
 template <typename T>
 __global__ void rope_cache_kernel(RopeCacheArgs a, int heads_per_block) {
+    pdl_start();
     const int t = blockIdx.x;
     const int nheads = a.nh + 2 * a.nkv;
     const int half = a.d / 2, rhalf = a.rot / 2;
@@ -318,8 +327,8 @@ VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const in
     const int threads = ((hpb * half + 31) / 32) * 32;
     dim3 grid(n_tokens, (nheads + hpb - 1) / hpb);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VCB_F32) rope_cache_kernel<float><<<grid, threads, 0, s>>>(a, hpb);
-    else if (dtype == VCB_BF16) rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(a, hpb);
+    if (dtype == VCB_F32) vcb_launch(rope_cache_kernel<float>, grid, threads, 0, s, a, hpb);
+    else if (dtype == VCB_BF16) vcb_launch(rope_cache_kernel<__nv_bfloat16>, grid, threads, 0, s, a, hpb);
     else return VCB_ERR_BAD_ARG;
     return vcb_last_error();
 }
@@ -329,6 +338,7 @@ VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const in
 // path of a position encoding that the fused kernel does not know uses it.
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, int cols) {
+    pdl_start();
     T* row = x + (size_t)blockIdx.x * cols;
     for (int c = threadIdx.x; c < cols; c += blockDim.x) row[c] = from_f32<T>(to_f32<T>(row[c]) + bias[c]);
 }
@@ -336,8 +346,8 @@ __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bia
 VCB_EXPORT int vcb_add_bias(void* x, const float* bias, int rows, int cols, int dtype, void* stream) {
     if (rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VCB_F32) add_bias_kernel<float><<<rows, 256, 0, s>>>((float*)x, bias, cols);
-    else if (dtype == VCB_BF16) add_bias_kernel<__nv_bfloat16><<<rows, 256, 0, s>>>((__nv_bfloat16*)x, bias, cols);
+    if (dtype == VCB_F32) vcb_launch(add_bias_kernel<float>, rows, 256, 0, s, (float*)x, bias, cols);
+    else if (dtype == VCB_BF16) vcb_launch(add_bias_kernel<__nv_bfloat16>, rows, 256, 0, s, (__nv_bfloat16*)x, bias, cols);
     else return VCB_ERR_BAD_ARG;
     return vcb_last_error();
 }

@@ -17,6 +17,7 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
                 int M, int N, int K, int lda, int ldw, int ldc) {
     __shared__ float As[GK][GT + 1];
     __shared__ float Ws[GK][GT + 1];
+    pdl_start();
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     const int m0 = blockIdx.y * GT, n0 = blockIdx.x * GT;
     float acc[4][4];
@@ -67,6 +68,6 @@ VCB_EXPORT int vcb_gemm_f32(const float* A, const float* W, float* C, int M, int
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || lda < K || ldw < K || ldc < N) return VCB_ERR_BAD_ARG;
     dim3 grid((N + GT - 1) / GT, (M + GT - 1) / GT);
-    gemm_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+    vcb_launch(gemm_f32_kernel, grid, 256, 0, (cudaStream_t)stream, A, W, C, M, N, K, lda, ldw, ldc);
     return vcb_last_error();
 }

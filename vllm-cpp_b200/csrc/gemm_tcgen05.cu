@@ -127,6 +127,19 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// One (tile, slab) unit after the other of a CTA's run.
+struct Units {
+    Segments seg;
+    int tile, s0, s1, slab;
+    bool ok;
+    __device__ Units(const GemmArgs& a, int cta) : seg(a, cta) { ok = seg.next(tile, s0, s1); slab = s0; }
+    __device__ void advance() {
+        if (++slab >= s1) { ok = seg.next(tile, s0, s1); slab = s0; }
+    }
+    __device__ int p0(const GemmArgs& a) const { return (tile % a.tiles_p) * BM; }
+    __device__ int q0(const GemmArgs& a, int bn) const { return (tile / a.tiles_p) * bn; }
+};
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmArgs a) {
@@ -143,6 +156,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     const uint32_t tiles0 = smem_addr(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cta = blockIdx.x;
+    pdl_launch_dependents();            // the next kernel may set itself up while this one streams
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -162,23 +176,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     const uint32_t tmem_d = *tmem_slot;
 
     if (warp == 0) {
-        // ---- TMA producer
+        // ---- TMA producer.  With the weights on the P side (decode), P tiles of the first
+        // stages are requested before the previous kernel has finished: weights depend on
+        // nothing.  The activations (Q) follow once griddepcontrol.wait has returned.
         if (lane == 0) {
-            Segments seg(a, cta);
-            int tile, s0, s1, it = 0;
-            while (!flags[0] && seg.next(tile, s0, s1)) {
-                const int p0 = (tile % a.tiles_p) * BM, q0 = (tile / a.tiles_p) * BN;
-                for (int slab = s0; slab < s1; ++slab, ++it) {
-                    const int s = it % STAGES;
-                    if (flags[0] || !mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) {
-                        if (!flags[0]) { flags[0] = 1; atomicCAS(a.status, 0, 1); }
-                        break;
-                    }
+            Units ahead(a, cta), units(a, cta);
+            int it_p = 0, it_q = 0;
+            if (a.swapped) {
+                for (; ahead.ok && it_p < STAGES; ++it_p, ahead.advance()) {
+                    const int s = it_p % STAGES;
                     mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                    const uint32_t dst = tiles0 + s * STAGE_BYTES;
-                    tma_load_2d(dst, &map_p, full0 + 8 * s, slab * BK, p0);
-                    tma_load_2d(dst + P_BYTES, &map_q, full0 + 8 * s, slab * BK, q0);
+                    tma_load_2d(tiles0 + s * STAGE_BYTES, &map_p, full0 + 8 * s, ahead.slab * BK, ahead.p0(a));
                 }
+            }
+            pdl_wait();
+            for (; it_q < it_p; ++it_q, units.advance()) {
+                const int s = it_q % STAGES;
+                tma_load_2d(tiles0 + s * STAGE_BYTES + P_BYTES, &map_q, full0 + 8 * s, units.slab * BK, units.q0(a, BN));
+            }
+            for (; units.ok && !flags[0]; ++it_q, units.advance()) {
+                const int s = it_q % STAGES;
+                if (!mbar_wait(empty0 + 8 * s, ((it_q / STAGES) & 1) ^ 1)) {
+                    if (!flags[0]) { flags[0] = 1; atomicCAS(a.status, 0, 1); }
+                    break;
+                }
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                const uint32_t dst = tiles0 + s * STAGE_BYTES;
+                tma_load_2d(dst, &map_p, full0 + 8 * s, units.slab * BK, units.p0(a));
+                tma_load_2d(dst + P_BYTES, &map_q, full0 + 8 * s, units.slab * BK, units.q0(a, BN));
             }
         }
     } else if (warp == 1) {
@@ -220,6 +245,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         const int U = a.units_per_cta, S = a.k_slabs;
         Segments seg(a, cta);
         int tile, s0, s1, n = 0;
+        pdl_wait();                                 // nothing is written before the previous kernel is done
         while (seg.next(tile, s0, s1)) {
             const int buf = n & 1;
             if (flags[0] || !mbar_wait(acc_full0 + 8 * buf, (n >> 1) & 1)) {
@@ -344,7 +370,7 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_tcgen05_kernel<BN, STAGES><<<ctas, GEMM_THREADS, smem, s>>>(mp, mq, a);
+    vcb_launch(gemm_tcgen05_kernel<BN, STAGES>, ctas, GEMM_THREADS, smem, s, mp, mq, a);
     return vcb_last_error();
 }
 

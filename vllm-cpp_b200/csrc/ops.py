@@ -43,6 +43,17 @@ _SIGNATURES = {
 }
 
 
+_pdl = True
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch of this library's kernels on or off (see common.cuh)."""
+    global _pdl
+    _pdl = bool(on)
+    if _lib is not None:
+        _lib.vcb_set_pdl(1 if _pdl else 0)
+
+
 def lib():
     """The kernel library; built and loaded on first use."""
     global _lib
@@ -56,6 +67,9 @@ def lib():
                 raise KernelError(f"kernel library lacks {name}; rebuild it (delete csrc/_build)")
             fn.argtypes = sig
             fn.restype = _I
+        l.vcb_set_pdl.argtypes = [_I]
+        l.vcb_set_pdl.restype = None
+        l.vcb_set_pdl(1 if _pdl else 0)
         _lib = l
     return _lib
 
@@ -312,13 +326,31 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=
                                        _stream()), "gemm_bf16_tcgen05")
 
 
+TCGEN05_MAX_TOKENS = 128      # up to here the engine's own tcgen05 product runs; above, the library's
+_tcgen05_linear = True
+
+
+def set_tcgen05_linear(on: bool) -> None:
+    """Use this library's tcgen05 product for bfloat16 products with few tokens (default) or cuBLAS for all."""
+    global _tcgen05_linear
+    _tcgen05_linear = bool(on)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out = x @ w^T.  float32: the engine's own FMA kernel.  bfloat16: the library
-    product (cuBLAS through torch.mm), float accumulation, out bfloat16 or float32."""
+    """out = x @ w^T.  float32: the engine's own FMA kernel.  bfloat16 with up to TCGEN05_MAX_TOKENS
+    rows (decode steps, short portions): the engine's tcgen05 + TMA kernel with the weights on the
+    128-row side of the tile.  bfloat16 with more rows: the library product (cuBLAS through
+    torch.mm, float accumulation).  out is bfloat16 or float32."""
     if x.dtype == torch.float32:
         gemm_f32(x, w, out)
         return
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear: operands must both be bfloat16")
+    m, k = x.shape
+    if (_tcgen05_linear and m <= TCGEN05_MAX_TOKENS and k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.stride(1) == 1 and x.stride(1) == 1
+            and w.stride(1) == 1 and -(-w.shape[0] // 128) <= GEMM_MAX_TICKETS):
+        gemm_bf16_tcgen05(x, w, out)
+        return
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:

@@ -51,6 +51,7 @@ class Sampler:
     def __init__(self, device, max_rows: int, vocab: int):
         self.device, self.vocab = device, vocab
         self.cap = max(1, max_rows)
+        self.steps_since_check = 0
         self._alloc()
 
     def _alloc(self):
@@ -102,4 +103,8 @@ class Sampler:
                                 self.d_float[2, :m].contiguous(), self.d_int[0, :m].contiguous(), out)
         self.h_out[:m].copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        self.steps_since_check += 1
+        if self.steps_since_check >= 64:          # a kernel that gave up on a bounded wait says so here
+            self.steps_since_check = 0
+            ops.check_status()
         return self.h_out[:m].tolist()
