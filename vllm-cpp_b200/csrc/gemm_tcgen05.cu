@@ -20,6 +20,14 @@
 // accumulators in tensor memory alternate, so loads and MMAs of the next segment overlap
 // the read-back of the last.
 //
+// Weight layout for decode.  A TMA tensor copy pays for every 128-byte row piece of its box
+// (about 7 cycles each on this part, measured: 35 GB/s per SM whatever the shape), which is
+// below what a weight-bound product needs.  So the weights can also be given pre-tiled:
+// the matrix cut into 128-row x 64-column tiles, each stored as the 16 KB image that the
+// 128-byte-swizzled TMA copy would have produced in shared memory (vcb_tile_weights makes
+// it once at load).  A stage is then filled by one plain bulk copy (cp.async.bulk) of 16 KB
+// of contiguous memory, and only the few activation rows still go through a tensor map.
+//
 // Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory and
 // issues the MMAs (one elected lane each), warps 2-5 read the accumulators back
 // (tcgen05.ld, each warp its own 32 lanes) and store.  No load uses cluster multicast.
@@ -45,6 +53,7 @@ struct GemmArgs {
     float* partial;              // [ctas][2][BN][128] floats: a CTA's first and last segment
     int* tickets;                // one per tile, zero between launches
     int* status;                 // 0, or the code of the first wait that ran out
+    const uint8_t* p_tiled;      // P as 16 KB tile images [tiles_p][k_slabs], or null: P comes through map_p
     int ldc, out_f32, swapped, rows_p, rows_q;
     int k_slabs, tiles_p, units_per_cta, total_units;
 };
@@ -87,6 +96,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -186,7 +199,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 for (; ahead.ok && it_p < STAGES; ++it_p, ahead.advance()) {
                     const int s = it_p % STAGES;
                     mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                    tma_load_2d(tiles0 + s * STAGE_BYTES, &map_p, full0 + 8 * s, ahead.slab * BK, ahead.p0(a));
+                    if (a.p_tiled)
+                        bulk_load(tiles0 + s * STAGE_BYTES,
+                                  a.p_tiled + ((size_t)(ahead.tile % a.tiles_p) * a.k_slabs + ahead.slab) * P_BYTES,
+                                  P_BYTES, full0 + 8 * s);
+                    else
+                        tma_load_2d(tiles0 + s * STAGE_BYTES, &map_p, full0 + 8 * s, ahead.slab * BK, ahead.p0(a));
                 }
             }
             pdl_wait();
@@ -202,7 +220,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 }
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 const uint32_t dst = tiles0 + s * STAGE_BYTES;
-                tma_load_2d(dst, &map_p, full0 + 8 * s, units.slab * BK, units.p0(a));
+                if (a.p_tiled)
+                    bulk_load(dst, a.p_tiled + ((size_t)(units.tile % a.tiles_p) * a.k_slabs + units.slab) * P_BYTES,
+                              P_BYTES, full0 + 8 * s);
+                else
+                    tma_load_2d(dst, &map_p, full0 + 8 * s, units.slab * BK, units.p0(a));
                 tma_load_2d(dst + P_BYTES, &map_q, full0 + 8 * s, units.slab * BK, units.q0(a, BN));
             }
         }
@@ -376,19 +398,65 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int 
 
 }  // namespace
 
+// One thread per 16-byte chunk of the tiled image: tile (tp, slab), row r, chunk c of the
+// row-major matrix goes to chunk c ^ (r % 8) of row r of the tile, which is the 128-byte
+// swizzle of the TMA copy.  Rows beyond the matrix and columns beyond K are zero.
+__global__ void tile_weights_kernel(const __nv_bfloat16* __restrict__ w, int rows, int k, int ld, int k_slabs,
+                                    uint4* __restrict__ out, size_t n_chunks) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n_chunks; idx += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(idx & 7), r = (int)((idx >> 3) & 127);
+        const size_t tile = idx >> 10;
+        const int slab = (int)(tile % k_slabs);
+        const size_t tp = tile / k_slabs;
+        const size_t row = tp * BM + r;
+        const int col = slab * BK + c * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < (size_t)rows) {
+            if (col + 8 <= k && (ld % 8) == 0) {
+                v = *reinterpret_cast<const uint4*>(w + row * ld + col);
+            } else {
+                __nv_bfloat16 tmp[8];
+                for (int e = 0; e < 8; ++e) tmp[e] = col + e < k ? w[row * ld + col + e] : __float2bfloat16_rn(0.0f);
+                v = *reinterpret_cast<uint4*>(tmp);
+            }
+        }
+        out[(tile << 10) + ((size_t)r << 3) + (c ^ (r & 7))] = v;
+    }
+}
+
+// Bytes of the tiled image of a [rows, k] matrix.
+VCB_EXPORT long long vcb_tiled_weight_bytes(int rows, int k) {
+    return (long long)((rows + BM - 1) / BM) * ((k + BK - 1) / BK) * P_BYTES;
+}
+
+// out (vcb_tiled_weight_bytes(rows, k) bytes, 16-byte aligned) = the tiled image of w.
+VCB_EXPORT int vcb_tile_weights(const void* w, int rows, int k, int ld, void* out, void* stream) {
+    if (rows <= 0 || k <= 0 || ld < k || ((uintptr_t)out & 15) || ((uintptr_t)w & 15)) return VCB_ERR_BAD_ARG;
+    const int k_slabs = (k + BK - 1) / BK;
+    const size_t n_chunks = (size_t)((rows + BM - 1) / BM) * k_slabs * 1024;
+    size_t blocks = (n_chunks + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    tile_weights_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)w, rows, k, ld, k_slabs,
+                                                                       (uint4*)out, n_chunks);
+    return vcb_last_error();
+}
+
 // out[r, c] (row stride ldc, bfloat16 or float) = sum_k ...
 //   swapped = 0: P = activations [rows_p = tokens], Q = weights [rows_q = features]: out[p, q]
 //   swapped = 1: P = weights [rows_p = features], Q = activations [rows_q = tokens]:  out[q, p]
 // bn: columns of the tensor-core tile (16, 32, 64, 128 or 256; rows_q is cut into tiles of bn).
 // max_ctas: persistent CTAs (one per SM).  Scratch: partial holds max_ctas * 2 * bn * 128 floats,
 // tickets one zeroed int per tile (the kernel leaves them zero).
-VCB_EXPORT int vcb_gemm_bf16_tcgen05(const void* p, int rows_p, int ldp, const void* q, int rows_q, int ldq, int k,
-                                     void* out, int ldc, int out_f32, int swapped, int bn, int max_ctas,
-                                     float* partial, int* tickets, int n_tickets, int* status, void* stream) {
+// p_tiled: P as made by vcb_tile_weights (then p and ldp are not used), or null.
+VCB_EXPORT int vcb_gemm_bf16_tcgen05(const void* p, int rows_p, int ldp, const void* p_tiled, const void* q, int rows_q,
+                                     int ldq, int k, void* out, int ldc, int out_f32, int swapped, int bn,
+                                     int max_ctas, float* partial, int* tickets, int n_tickets, int* status,
+                                     void* stream) {
     if (rows_p <= 0 || rows_q <= 0) return 0;
     if (k <= 0 || max_ctas < 1 || !status || !partial || !tickets) return VCB_ERR_BAD_ARG;
     // TMA needs 16-byte aligned bases and row strides
-    if ((k % 8) || (ldp % 8) || (ldq % 8) || (((uintptr_t)p | (uintptr_t)q) & 15)) return VCB_ERR_UNSUPPORTED;
+    if ((k % 8) || (ldq % 8) || (((uintptr_t)q | (uintptr_t)p_tiled) & 15)) return VCB_ERR_UNSUPPORTED;
+    if (!p_tiled && ((ldp % 8) || ((uintptr_t)p & 15))) return VCB_ERR_UNSUPPORTED;
     if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return VCB_ERR_BAD_ARG;
     const int k_slabs = (k + BK - 1) / BK;
     const int tiles_p = (rows_p + BM - 1) / BM, tiles_q = (rows_q + bn - 1) / bn;
@@ -399,11 +467,11 @@ VCB_EXPORT int vcb_gemm_bf16_tcgen05(const void* p, int rows_p, int ldp, const v
     const int per = (int)((total + ctas - 1) / ctas);
     ctas = (int)((total + per - 1) / per);
     CUtensorMap mp, mq;
-    int c = make_map(&mp, p, rows_p, k, ldp, BM);
+    int c = make_map(&mq, q, rows_q, k, ldq, bn);
     if (c) return c;
-    c = make_map(&mq, q, rows_q, k, ldq, bn);
-    if (c) return c;
-    GemmArgs a{out, partial, tickets, status, ldc, out_f32, swapped, rows_p, rows_q, k_slabs, tiles_p, per, (int)total};
+    if (p_tiled) mp = mq;                       // not used by the kernel
+    else if ((c = make_map(&mp, p, rows_p, k, ldp, BM))) return c;
+    GemmArgs a{out, partial, tickets, status, (const uint8_t*)p_tiled, ldc, out_f32, swapped, rows_p, rows_q, k_slabs, tiles_p, per, (int)total};
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
         case 16: return launch<16, 10>(mp, mq, a, ctas, s);

@@ -36,7 +36,8 @@ _SIGNATURES = {
     "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
-    "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
+    "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
+    "vcb_tile_weights": [_P, _I, _I, _I, _P, _P],
     "vcb_repetition_penalty": [_P, _I, _P, _P, _P, _I, _I, _P],
     "vcb_sample": [_P, _I, _I, _P, _P, _P, _I, _P],
     "vcb_sample_filtered": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
@@ -305,8 +306,33 @@ def tcgen05_plan(tokens: int, features: int, k: int):
 GEMM_MAX_TICKETS = 16384
 
 
-def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=None, max_ctas: int = SM_COUNT) -> None:
-    """out = x @ w^T on tcgen05 tensor cores fed by TMA (see gemm_tcgen05.cu); out bfloat16 or float32."""
+_tiled = {}
+
+
+def tile_weights(w: torch.Tensor) -> torch.Tensor:
+    """The pre-tiled image of a weight matrix for decode products (see gemm_tcgen05.cu): made once,
+    kept beside the matrix, and used by ``linear`` whenever the weights sit on the 128-row side."""
+    key = (w.data_ptr(), tuple(w.shape), w.stride(0))
+    t = _tiled.get(key)
+    if t is None:
+        _need(w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1, "tile_weights: a bfloat16 matrix")
+        rows, k = w.shape
+        nbytes = -(-rows // 128) * -(-k // 64) * 16384
+        t = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+        _check(lib().vcb_tile_weights(w.data_ptr(), rows, k, w.stride(0), t.data_ptr(), _stream()), "tile_weights")
+        _tiled[key] = t
+    return t
+
+
+def tiled_weights_of(w: torch.Tensor) -> Optional[torch.Tensor]:
+    return _tiled.get((w.data_ptr(), tuple(w.shape), w.stride(0)))
+
+
+def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=None, max_ctas: int = SM_COUNT,
+                      use_tiled: bool = True) -> None:
+    """out = x @ w^T on tcgen05 tensor cores fed by TMA (see gemm_tcgen05.cu); out bfloat16 or float32.
+    When the weights are the 128-row operand and tile_weights(w) has been made, the image is used
+    (``use_tiled`` False forces the tensor-map path)."""
     m, k = x.shape
     n = w.shape[0]
     _need(w.shape[1] == k and out.shape == (m, n), "gemm_bf16_tcgen05: shapes do not agree")
@@ -319,38 +345,40 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=
     partial = scratch("gemm_partial", SM_COUNT * 2 * 256 * 128, out.device)
     tickets = zeroed_ints("gemm_tickets", GEMM_MAX_TICKETS, out.device)
     p, q = (w, x) if swapped else (x, w)
-    _check(lib().vcb_gemm_bf16_tcgen05(p.data_ptr(), p.shape[0], p.stride(0), q.data_ptr(), q.shape[0], q.stride(0), k,
+    tiled = tiled_weights_of(w) if (swapped and use_tiled) else None
+    _check(lib().vcb_gemm_bf16_tcgen05(p.data_ptr(), p.shape[0], p.stride(0),
+                                       None if tiled is None else tiled.data_ptr(),
+                                       q.data_ptr(), q.shape[0], q.stride(0), k,
                                        out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0,
                                        1 if swapped else 0, bn, min(max_ctas, SM_COUNT), partial.data_ptr(),
                                        tickets.data_ptr(), GEMM_MAX_TICKETS, status_tensor(out.device).data_ptr(),
                                        _stream()), "gemm_bf16_tcgen05")
 
 
-TCGEN05_MAX_TOKENS = 128      # up to here the engine's own tcgen05 product runs; above, the library's
+TCGEN05_MAX_TOKENS = 128      # up to here the engine's own tcgen05 product may run; above, the library's
 _tcgen05_linear = True
+# (features, k, token bucket) -> True if the tcgen05 kernel was measured faster than cuBLAS here
+_linear_choice = {}
 
 
 def set_tcgen05_linear(on: bool) -> None:
-    """Use this library's tcgen05 product for bfloat16 products with few tokens (default) or cuBLAS for all."""
+    """Allow this library's tcgen05 product for bfloat16 products with few tokens (default), or cuBLAS for all."""
     global _tcgen05_linear
     _tcgen05_linear = bool(on)
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out = x @ w^T.  float32: the engine's own FMA kernel.  bfloat16 with up to TCGEN05_MAX_TOKENS
-    rows (decode steps, short portions): the engine's tcgen05 + TMA kernel with the weights on the
-    128-row side of the tile.  bfloat16 with more rows: the library product (cuBLAS through
-    torch.mm, float accumulation).  out is bfloat16 or float32."""
-    if x.dtype == torch.float32:
-        gemm_f32(x, w, out)
-        return
-    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear: operands must both be bfloat16")
+def token_bucket(m: int) -> int:
+    return 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128
+
+
+def _tcgen05_ok(x, w, out) -> bool:
     m, k = x.shape
-    if (_tcgen05_linear and m <= TCGEN05_MAX_TOKENS and k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+    return (m <= TCGEN05_MAX_TOKENS and k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.stride(1) == 1 and x.stride(1) == 1
-            and w.stride(1) == 1 and -(-w.shape[0] // 128) <= GEMM_MAX_TICKETS):
-        gemm_bf16_tcgen05(x, w, out)
-        return
+            and w.stride(1) == 1 and -(-w.shape[0] // 128) <= GEMM_MAX_TICKETS)
+
+
+def _library_mm(x, w, out) -> None:
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:
@@ -359,6 +387,51 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
             torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
         except (TypeError, RuntimeError):
             out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))
+
+
+def tune_linear(weights, out_dtype=torch.bfloat16, reps: int = 6) -> None:
+    """Measure, for one shape of weight matrix and each bucket of token counts, whether the engine's
+    tcgen05 product or the library's is faster on this device, and remember the choice.
+    ``weights``: matrices of the same shape (the same projection of several layers), used in
+    rotation so that the L2 cache cannot serve them."""
+    n, k = weights[0].shape
+    dev_ = weights[0].device
+    for bucket, m in ((16, 8), (32, 32), (64, 64), (128, 128)):
+        x = torch.randn(m, k, device=dev_).to(torch.bfloat16)
+        out = torch.empty(m, n, dtype=out_dtype, device=dev_)
+        if not _tcgen05_ok(x, weights[0], out):
+            continue
+        times = []
+        for fn in (lambda w: gemm_bf16_tcgen05(x, w, out), lambda w: _library_mm(x, w, out)):
+            for i in range(2):
+                fn(weights[i % len(weights)])
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(reps):
+                fn(weights[i % len(weights)])
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        _linear_choice[(n, k, bucket, out_dtype)] = times[0] <= times[1]
+    check_status()
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x @ w^T.  float32: the engine's own FMA kernel.  bfloat16 with up to TCGEN05_MAX_TOKENS
+    rows (decode steps, short portions): the engine's tcgen05 + TMA kernel with the weights on the
+    128-row side of the tile, where ``tune_linear`` measured it faster than the library (and always
+    when nothing was measured); otherwise the library product (cuBLAS through torch.mm, float
+    accumulation).  out is bfloat16 or float32."""
+    if x.dtype == torch.float32:
+        gemm_f32(x, w, out)
+        return
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear: operands must both be bfloat16")
+    if _tcgen05_linear and _tcgen05_ok(x, w, out) and \
+            _linear_choice.get((w.shape[0], w.shape[1], token_bucket(x.shape[0]), out.dtype), True):
+        gemm_bf16_tcgen05(x, w, out)
+        return
+    _library_mm(x, w, out)
 
 
 def repetition_penalty(logits, ids, row_start, penalty) -> None:

@@ -58,6 +58,7 @@ def build(cfg: EngineConfig) -> Tuple[DecoderModel, CacheManager, ModelRunner]:
     torch.backends.cuda.matmul.allow_tf32 = False
     with torch.cuda.device(device), torch.no_grad():
         model = build_model(cfg, device)
+        model.prepare_products()
         specs = model.cache_specs()
         max_model_len = min(cfg.max_model_len, model.spec.max_position_embeddings)
         if cfg.num_gpu_blocks is not None:

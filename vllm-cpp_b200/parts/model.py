@@ -95,6 +95,27 @@ class DecoderModel:
         self.final_norm.load_params({local: tensors[s.final_norm_prefix + local]
                                      for local in self.final_norm.param_specs()})
 
+    def prepare_products(self, tune: bool = True) -> None:
+        """bfloat16 only: measure for every shape of weight matrix whether the engine's tcgen05
+        product or the library's is faster for few tokens, and make the pre-tiled images of the
+        matrices for which the engine's kernel was chosen (see csrc/gemm_tcgen05.cu)."""
+        if self.dtype != torch.bfloat16:
+            return
+        by_shape = {}
+        for blk in self.blocks:
+            for part in (blk.mixer, blk.feed_forward):
+                for v in vars(part).values():
+                    if isinstance(v, torch.Tensor) and v.dim() == 2 and v.dtype == torch.bfloat16:
+                        by_shape.setdefault((tuple(v.shape), torch.bfloat16), []).append(v)
+        by_shape.setdefault((tuple(self.lm_head.shape), torch.float32), []).append(self.lm_head)
+        for (shape, out_dtype), mats in by_shape.items():
+            if tune:
+                ops.tune_linear(mats[:8], out_dtype)
+            chosen = any(ops._linear_choice.get((shape[0], shape[1], b, out_dtype), True) for b in (16, 32, 64, 128))
+            if chosen and shape[1] % 8 == 0:
+                for m in mats:
+                    ops.tile_weights(m)
+
     def weight_bytes(self) -> int:
         """Bytes of the matrices a decode step reads once (embedding rows excluded unless tied)."""
         total = 0
