@@ -112,3 +112,14 @@ class Replayer:
 
     def logits_of(self, rid, positions):
         return np.stack([self.rows[(rid, p)] for p in positions])
+
+
+def kv_row_pos(d, esize, slot):
+    """Where the elements of a cache row are stored (the layout the engine documents in
+    csrc/common.cuh): rows that are a multiple of 128 bytes keep their 16-byte chunks XOR-swizzled
+    by the slot number; stored[pos[e]] = logical[e]."""
+    e = np.arange(d)
+    if (d * esize) % 128:
+        return e
+    per = 16 // esize
+    return ((e // per) ^ (slot & 7)) * per + e % per

@@ -6,6 +6,7 @@ import pytest
 import torch
 
 import plain_qwen2 as plain
+from helpers import kv_row_pos
 
 pytestmark = pytest.mark.gpu
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
@@ -134,10 +135,12 @@ def test_rope_cache_write(ops, dtype, nh, nkv, d, rot, pairing):
     q_ref, k_ref, v_ref = rotate(x[:, :nh]), rotate(x[:, nh:nh + nkv]), x[:, nh + nkv:]
     close(q_out.float().cpu().numpy().reshape(n, nh, d), q_ref, dtype, "q")
     c = cache.float().cpu().numpy()
+    esize = 4 if dtype == "float32" else 2
     for t in range(n):
         pg, slot = bt[req[t], pos[t] // page], pos[t] % page
-        close(c[pg, 0, :, slot], k_ref[t], dtype, f"k of token {t}", scale=np.abs(k_ref).max())
-        close(c[pg, 1, :, slot], v_ref[t], dtype, f"v of token {t}", scale=np.abs(v_ref).max())
+        where = kv_row_pos(d, esize, slot)             # the row's chunks are stored swizzled by the slot
+        close(c[pg, 0, :, slot][:, where], k_ref[t], dtype, f"k of token {t}", scale=np.abs(k_ref).max())
+        close(c[pg, 1, :, slot][:, where], v_ref[t], dtype, f"v of token {t}", scale=np.abs(v_ref).max())
     written = np.zeros((n_pages, page), dtype=bool)
     for t in range(n):
         written[bt[req[t], pos[t] // page], pos[t] % page] = True
@@ -192,10 +195,12 @@ def attention_case(rng, dtype, nh, nkv, d, page, q_lens, ctx_lens, spike=True):
                 q[t0 + ql - 1] = as_stored(np.repeat(k[r][1], nh // nkv, axis=0) * 0.7, dtype)
             t0 += ql
     cache = np.zeros((n_pages, 2, nkv, page, d), dtype=np.float32)
+    esize = 4 if dtype == "float32" else 2
     for r, t in enumerate(total):
         for p in range(t):
-            cache[bt[r, p // page], 0, :, p % page] = k[r][p]
-            cache[bt[r, p // page], 1, :, p % page] = v[r][p]
+            where = kv_row_pos(d, esize, p % page)
+            cache[bt[r, p // page], 0, :, p % page][:, where] = k[r][p]
+            cache[bt[r, p // page], 1, :, p % page][:, where] = v[r][p]
     q_start = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
     pos = np.concatenate([np.arange(c, c + ql) for c, ql in zip(ctx_lens, q_lens)]).astype(np.int32)
     req = np.concatenate([np.full(ql, r) for r, ql in enumerate(q_lens)]).astype(np.int32)

@@ -17,10 +17,16 @@
 // are ex2.approx on scores pre-multiplied by log2(e) (this file is the bfloat16 path;
 // the plain kernel of attention_simt.cu uses expf).
 //
-// K/V tiles come from the pages with 16-byte cp.async copies in a multi-stage ring;
-// rows are XOR-swizzled in units of 16 bytes so that ldmatrix reads are free of
-// bank conflicts.  Keys outside [lo, hi) are zero-filled, never read: their pages
-// may have been given back (window) or not exist yet.
+// Loading.  The cache stores every row already in the XOR-swizzled chunk order that
+// ldmatrix wants (kv_row_pos in common.cuh), so a run of slots of a page is a ready-made
+// piece of a shared-memory tile.  A fifth warp is the producer: for every tile of 64 keys
+// it issues one bulk copy (cp.async.bulk, the TMA unit, no tensor map, no multicast) per
+// page piece of K and of V into a ring of stages, completing on the stage's mbarrier; the
+// four consumer warps wait on that barrier and hand the stage back on another.  No thread
+// that computes ever waits on a global load.  Pages wholly outside [lo, hi) may have been
+// given back (window) or not exist yet: a page that does exist is copied in their place
+// (their scores are masked, their finite values multiply a probability of zero).  Waits on
+// mbarriers are bounded; one that runs out is recorded in *status.
 //
 // Replaces paged_attention_kernel (src/attention/paged_attention.cu:7-93) for the
 // bfloat16 path; attention_simt.cu is its plain counterpart.
@@ -28,7 +34,8 @@
 
 #define BN 64            // keys per tile
 #define BM 64            // rows per CTA in the prefill kernel
-#define NTHREADS 128
+#define NTHREADS 128     // consumer threads (4 warps); warp 4 is the producer
+#define BLOCK_THREADS 160
 
 struct MmaAttnArgs {
     const __nv_bfloat16* q;        // [n_tokens, nh * d]
@@ -42,19 +49,13 @@ struct MmaAttnArgs {
     float* part_o;                 // decode scratch: [n_list, nh, splits, d]
     float* part_ml;                // decode scratch: [n_list, nh, splits, 2]  (max in log2 units, sum)
     int* counters;                 // decode scratch: [n_list, nkv] tickets, zero between launches
+    int* status;                   // nonzero after a bounded wait ran out (may be null)
     int bt_stride, nh, nkv, page, window;
     float scale;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -86,44 +87,28 @@ template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
 }
 
-// Loads one K tile and one V tile of BN keys of kv head g per call.  Each thread owns
-// one key row of the tile (a fixed share of its 16-byte chunks).  The row's page id is
-// fetched from the block table one tile ahead (prefetch) so that the table's latency
-// is not on the path of the copy that needs it.  Keys outside [lo, hi) are zero-filled.
-template <int D, int NT>
-struct KVLoader {
-    static constexpr int CH = D / 8;            // 16-byte chunks per row
-    static constexpr int TPR = NT / BN;         // threads per key row
-    static constexpr int CPT = CH / TPR;        // chunks per thread
-    static_assert(NT % BN == 0 && CH % TPR == 0, "tile loader shape");
-    const int* bt;
-    const __nv_bfloat16* cache;
-    int g, page, nkv, lo, hi, key, c0, pg;
-
-    __device__ __forceinline__ void init(const int* bt_, const __nv_bfloat16* cache_, int g_, int page_, int nkv_,
-                                         int lo_, int hi_) {
-        bt = bt_; cache = cache_; g = g_; page = page_; nkv = nkv_; lo = lo_; hi = hi_;
-        key = threadIdx.x / TPR; c0 = (threadIdx.x % TPR) * CPT; pg = -1;
-    }
-    __device__ __forceinline__ void prefetch(int kb) {
-        const int j = kb + key;
-        pg = (j >= lo && j < hi) ? bt[j / page] : -1;
-    }
-    __device__ __forceinline__ void issue(uint32_t sk, uint32_t sv, int kb) const {
-        const int j = kb + key;
-        const bool valid = pg >= 0;
-        const __nv_bfloat16* src = cache;
-        if (valid) src = cache + (size_t)pg * ((size_t)2 * nkv * page * D) + ((size_t)g * page + (j % page)) * D + c0 * 8;
-        const __nv_bfloat16* vsrc = valid ? src + (size_t)nkv * page * D : src;
-        const int bytes = valid ? 16 : 0;
-#pragma unroll
-        for (int c = 0; c < CPT; ++c) {
-            const uint32_t off = swz<D>(key, c0 + c);
-            cp_async_16(sk + off, valid ? src + c * 8 : src, bytes);
-            cp_async_16(sv + off, valid ? vsrc + c * 8 : vsrc, bytes);
-        }
-    }
-};
+// The producer warp's share of one tile of BN keys starting at key kb of kv head g: lanes 0-7
+// each copy one page piece of K, lanes 8-15 the same pieces of V (a tile spans at most
+// BN / 16 + 1 pages).  Lane 0 has armed the stage's barrier with the tile's byte count.
+template <int D>
+__device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t bar, int kb, int lo, int hi,
+                                             const int* __restrict__ bt, const __nv_bfloat16* __restrict__ cache,
+                                             int g, int page, int nkv, int lane) {
+    if (lane >= 16) return;
+    const int piece = lane & 7;
+    const int first_page = kb / page;
+    const int start = piece == 0 ? kb : (first_page + piece) * page;       // first key of the piece
+    if (start >= kb + BN) return;
+    const int end = min((start / page + 1) * page, kb + BN);
+    // the page itself if any of it is visible, else the page of the last visible key
+    const int lp = start / page;
+    const bool visible = lp * page < hi && (lp + 1) * page > lo;
+    const int pg = bt[visible ? lp : (hi - 1) / page];
+    const __nv_bfloat16* src = cache + (size_t)pg * ((size_t)2 * nkv * page * D) + ((size_t)g * page + (start % page)) * D;
+    const uint32_t off = (uint32_t)(start - kb) * D * 2, bytes = (uint32_t)(end - start) * D * 2;
+    if (lane < 8) cx_bulk_load(sk + off, src, bytes, bar);
+    else cx_bulk_load(sv + off, src + (size_t)nkv * page * D, bytes, bar);
+}
 
 // S[16 x 8*NB] += Q[16 x D] * K[keys key0 .. key0 + 8*NB)^T, K tile at sk.
 template <int D, int NB>
@@ -173,12 +158,13 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[D / 16][4], uint32_t
 
 // ------------------------------------------------------------------ decode
 template <int D, int STAGES>
-__global__ void __launch_bounds__(NTHREADS)
+__global__ void __launch_bounds__(BLOCK_THREADS)
 attention_decode_kernel(MmaAttnArgs a) {
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];
     constexpr int TILE_BYTES = BN * D * 2;
     pdl_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool producer = warp == 4;
     const int split = blockIdx.x, nsplit = gridDim.x, g = blockIdx.y, li = blockIdx.z;
     const int r = a.req_list ? a.req_list[li] : li;
     const int G = a.nh / a.nkv;
@@ -193,113 +179,111 @@ attention_decode_kernel(MmaAttnArgs a) {
     const int per = (tile1 - tile0 + nsplit - 1) / nsplit;
     const int my0 = tile0 + split * per, my1 = min(tile1, my0 + per);
 
-    const uint32_t s_base = smem_u32(smem);
-    const uint32_t sq = s_base;                          // [16][D] bf16
-    const uint32_t s_tiles = s_base + 16 * D * 2;        // STAGES x (K, V)
-    float* red_o = reinterpret_cast<float*>(smem + 16 * D * 2);          // reused after the loop: [4][16][D]
-    float* red_ml = reinterpret_cast<float*>(smem + 16 * D * 2 + 4 * 16 * D * 4);   // [4][16][2]
+    // [STAGES x (K, V) tiles][Q: 16 x D][barriers]; the merge buffers reuse the tiles
+    const uint32_t s_tiles = smem_u32(smem);
+    unsigned char* q_ptr = smem + (size_t)STAGES * 2 * TILE_BYTES;
+    const uint32_t sq = smem_u32(q_ptr);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(q_ptr + 16 * D * 2);
+    const uint32_t full0 = cx_smem(bars), empty0 = cx_smem(bars + STAGES);
+    float* red_o = reinterpret_cast<float*>(smem);                          // [4][16][D]
+    float* red_ml = reinterpret_cast<float*>(smem + 4 * 16 * D * 4);        // [4][16][2]
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { cx_mbar_init(full0 + 8 * s, 1); cx_mbar_init(empty0 + 8 * s, 4); }
+        cx_mbar_init_fence();
+    }
+    int it = 0;                                          // tiles handled so far: stage and phase of the ring
+    bool gave_up = false;
 
     for (int mt = 0; mt * 16 < G; ++mt) {
-        __syncthreads();
+        __syncthreads();                                 // barriers initialised; last round's merge has been read
         // Q rows of this group: row i -> head g*G + mt*16 + i
-        for (int idx = threadIdx.x; idx < 16 * (D / 8); idx += NTHREADS) {
+        for (int idx = threadIdx.x; idx < 16 * (D / 8); idx += BLOCK_THREADS) {
             const int row = idx / (D / 8), c = idx % (D / 8);
             const int hg = mt * 16 + row;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (hg < G) v = *reinterpret_cast<const uint4*>(a.q + ((size_t)t * a.nh + g * G + hg) * D + c * 8);
-            *reinterpret_cast<uint4*>(smem + swz<D>(row, c)) = v;
+            *reinterpret_cast<uint4*>(q_ptr + swz<D>(row, c)) = v;
         }
         __syncthreads();
-        uint32_t qf[D / 16][4];
-        load_q_frags<D>(qf, sq, 0);
-
         float o[D / 8][4];
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
         float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;   // rows lane/4 and lane/4 + 8
 
-        // prologue
-        KVLoader<D, NTHREADS> ld;
-        ld.init(bt, a.cache, g, a.page, a.nkv, lo, hi);
-        if (my0 < my1) ld.prefetch(my0 * BN);
-#pragma unroll
-        for (int s = 0; s < STAGES - 1; ++s) {
-            if (my0 + s < my1) {
-                ld.issue(s_tiles + s * 2 * TILE_BYTES, s_tiles + s * 2 * TILE_BYTES + TILE_BYTES, (my0 + s) * BN);
-                if (my0 + s + 1 < my1) ld.prefetch((my0 + s + 1) * BN);
+        if (producer) {
+            for (int tile = my0; tile < my1; ++tile, ++it) {
+                const int st = it % STAGES;
+                if (!cx_mbar_wait(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) gave_up = true;
+                if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, 2 * TILE_BYTES);
+                __syncwarp();
+                produce_tile<D>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
+                                full0 + 8 * st, tile * BN, lo, hi, bt, a.cache, g, a.page, a.nkv, lane);
             }
-            cp_async_commit();
-        }
-        for (int tile = my0; tile < my1; ++tile) {
-            cp_async_wait<STAGES - 2>();
-            __syncthreads();
-            {   // refill the stage that was consumed in the previous iteration
-                const int nt = tile + STAGES - 1;
-                const int st = (nt - my0) % STAGES;
-                if (nt < my1) {
-                    ld.issue(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES, nt * BN);
-                    if (nt + 1 < my1) ld.prefetch((nt + 1) * BN);
+        } else {
+            uint32_t qf[D / 16][4];
+            load_q_frags<D>(qf, sq, 0);
+            for (int tile = my0; tile < my1; ++tile, ++it) {
+                const int st = it % STAGES;
+                if (!cx_mbar_wait(full0 + 8 * st, (it / STAGES) & 1)) gave_up = true;
+                const uint32_t sk = s_tiles + st * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
+                const int kb = tile * BN + warp * 16;    // this warp's 16 keys
+                float s[2][4];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
+                qk_product<D, 2>(s, qf, sk, warp * 16);
+#pragma unroll
+                for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = kb + nb * 8 + (lane & 3) * 2 + (e & 1);
+                        s[nb][e] = (j >= lo && j < hi) ? s[nb][e] * sl2 : -INFINITY;
+                    }
+                // all rows of a decode tile share the position, but keep the two row sets apart
+                float ta = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+                float tb = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+                ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 1)); ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 2));
+                tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 1)); tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 2));
+                const float na = fmaxf(m_a, ta), nb_ = fmaxf(m_b, tb);
+                const float sa = na == -INFINITY ? 0.0f : na, sb = nb_ == -INFINITY ? 0.0f : nb_;
+                const float ca = fast_exp2(m_a - sa), cb = fast_exp2(m_b - sb);   // m = -inf: 2^-inf = 0, sums are 0 anyway
+                m_a = na; m_b = nb_;
+                uint32_t pf[1][4];
+                float p[2][4];
+#pragma unroll
+                for (int nb = 0; nb < 2; ++nb) {
+                    p[nb][0] = fast_exp2(s[nb][0] - sa); p[nb][1] = fast_exp2(s[nb][1] - sa);
+                    p[nb][2] = fast_exp2(s[nb][2] - sb); p[nb][3] = fast_exp2(s[nb][3] - sb);
                 }
-                cp_async_commit();
+                l_a = l_a * ca + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
+                l_b = l_b * cb + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
+#pragma unroll
+                for (int i = 0; i < D / 8; ++i) { o[i][0] *= ca; o[i][1] *= ca; o[i][2] *= cb; o[i][3] *= cb; }
+                pf[0][0] = pack_bf16(p[0][0], p[0][1]); pf[0][1] = pack_bf16(p[0][2], p[0][3]);
+                pf[0][2] = pack_bf16(p[1][0], p[1][1]); pf[0][3] = pack_bf16(p[1][2], p[1][3]);
+                pv_product<D, 1>(o, pf, sv, warp * 16);
+                __syncwarp();
+                if (lane == 0) cx_mbar_arrive(empty0 + 8 * st);      // this warp is done with the stage
             }
-            const int st = (tile - my0) % STAGES;
-            const uint32_t sk = s_tiles + st * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
-            const int kb = tile * BN + warp * 16;        // this warp's 16 keys
-            float s[2][4];
+        }
+        __syncthreads();                                 // every copy has landed and been read: reuse the tiles
+        if (!producer) {
+            l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+            l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+            const int ra = lane >> 2, rb = ra + 8;
 #pragma unroll
-            for (int i = 0; i < 2; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
-            qk_product<D, 2>(s, qf, sk, warp * 16);
-            float tmax = -INFINITY;
-#pragma unroll
-            for (int nb = 0; nb < 2; ++nb)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int j = kb + nb * 8 + (lane & 3) * 2 + (e & 1);
-                    s[nb][e] = (j >= lo && j < hi) ? s[nb][e] * sl2 : -INFINITY;
-                }
-            // all rows of a decode tile share the position, but keep the two row sets apart
-            float ta = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-            float tb = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-            ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 1)); ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 2));
-            tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 1)); tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 2));
-            (void)tmax;
-            const float na = fmaxf(m_a, ta), nb_ = fmaxf(m_b, tb);
-            const float sa = na == -INFINITY ? 0.0f : na, sb = nb_ == -INFINITY ? 0.0f : nb_;
-            const float ca = fast_exp2(m_a - sa), cb = fast_exp2(m_b - sb);      // m = -inf: exp(-inf) = 0, sums are 0 anyway
-            m_a = na; m_b = nb_;
-            uint32_t pf[1][4];
-            float p[2][4];
-#pragma unroll
-            for (int nb = 0; nb < 2; ++nb) {
-                p[nb][0] = fast_exp2(s[nb][0] - sa); p[nb][1] = fast_exp2(s[nb][1] - sa);
-                p[nb][2] = fast_exp2(s[nb][2] - sb); p[nb][3] = fast_exp2(s[nb][3] - sb);
+            for (int nd = 0; nd < D / 8; ++nd) {
+                const int col = nd * 8 + (lane & 3) * 2;
+                float* pa = red_o + ((size_t)(warp * 16 + ra)) * D + col;
+                float* pb = red_o + ((size_t)(warp * 16 + rb)) * D + col;
+                pa[0] = o[nd][0]; pa[1] = o[nd][1]; pb[0] = o[nd][2]; pb[1] = o[nd][3];
             }
-            l_a = l_a * ca + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
-            l_b = l_b * cb + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
-#pragma unroll
-            for (int i = 0; i < D / 8; ++i) { o[i][0] *= ca; o[i][1] *= ca; o[i][2] *= cb; o[i][3] *= cb; }
-            pf[0][0] = pack_bf16(p[0][0], p[0][1]); pf[0][1] = pack_bf16(p[0][2], p[0][3]);
-            pf[0][2] = pack_bf16(p[1][0], p[1][1]); pf[0][3] = pack_bf16(p[1][2], p[1][3]);
-            pv_product<D, 1>(o, pf, sv, warp * 16);
-        }
-        cp_async_wait<0>();
-        __syncthreads();                                 // tiles are dead: reuse the memory for the merge
-        l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
-        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-        const int ra = lane >> 2, rb = ra + 8;
-#pragma unroll
-        for (int nd = 0; nd < D / 8; ++nd) {
-            const int col = nd * 8 + (lane & 3) * 2;
-            float* pa = red_o + ((size_t)(warp * 16 + ra)) * D + col;
-            float* pb = red_o + ((size_t)(warp * 16 + rb)) * D + col;
-            pa[0] = o[nd][0]; pa[1] = o[nd][1]; pb[0] = o[nd][2]; pb[1] = o[nd][3];
-        }
-        if ((lane & 3) == 0) {
-            red_ml[(warp * 16 + ra) * 2] = m_a; red_ml[(warp * 16 + ra) * 2 + 1] = l_a;
-            red_ml[(warp * 16 + rb) * 2] = m_b; red_ml[(warp * 16 + rb) * 2 + 1] = l_b;
+            if ((lane & 3) == 0) {
+                red_ml[(warp * 16 + ra) * 2] = m_a; red_ml[(warp * 16 + ra) * 2 + 1] = l_a;
+                red_ml[(warp * 16 + rb) * 2] = m_b; red_ml[(warp * 16 + rb) * 2 + 1] = l_b;
+            }
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < 16 * D; idx += NTHREADS) {
+        for (int idx = threadIdx.x; idx < 16 * D; idx += BLOCK_THREADS) {
             const int row = idx / D, dim = idx % D;
             const int hg = mt * 16 + row;
             if (hg >= G) continue;
@@ -325,6 +309,7 @@ attention_decode_kernel(MmaAttnArgs a) {
             }
         }
     }
+    if (gave_up && a.status) atomicCAS(a.status, 0, 5);
     if (nsplit == 1) return;
 
     // Merge of the splits.  This CTA's partials are in global memory; the CTA that takes
@@ -339,7 +324,7 @@ attention_decode_kernel(MmaAttnArgs a) {
     __threadfence();
     // factors 2^(m_s - m) / sum per (head, split): one warp per head, one lane per split
     float* fac = reinterpret_cast<float*>(smem);           // [G][32], the tiles are dead
-    for (int hg = warp; hg < G; hg += NTHREADS / 32) {
+    for (int hg = warp; hg < G; hg += BLOCK_THREADS / 32) {
         const size_t p0 = ((size_t)li * a.nh + g * G + hg) * nsplit;
         float ms = -INFINITY, ls = 0.0f;
         if (lane < nsplit) { ms = __ldcg(a.part_ml + (p0 + lane) * 2); ls = __ldcg(a.part_ml + (p0 + lane) * 2 + 1); }
@@ -349,7 +334,7 @@ attention_decode_kernel(MmaAttnArgs a) {
         fac[hg * 32 + lane] = f / total;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < G * D; idx += NTHREADS) {
+    for (int idx = threadIdx.x; idx < G * D; idx += BLOCK_THREADS) {
         const int hg = idx / D, dim = idx % D;
         const int head = g * G + hg;
         const float* po = a.part_o + ((size_t)li * a.nh + head) * nsplit * D + dim;
@@ -363,12 +348,13 @@ attention_decode_kernel(MmaAttnArgs a) {
 
 // ----------------------------------------------------------------- prefill
 template <int D, int STAGES>
-__global__ void __launch_bounds__(NTHREADS)
+__global__ void __launch_bounds__(BLOCK_THREADS)
 attention_prefill_kernel(MmaAttnArgs a) {
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];
     constexpr int TILE_BYTES = BN * D * 2;
     pdl_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool producer = warp == 4;
     const int r = a.req_list[blockIdx.x];
     const int row0 = a.tile_row0[blockIdx.x];
     const int g = blockIdx.y;
@@ -378,12 +364,18 @@ attention_prefill_kernel(MmaAttnArgs a) {
     const int* bt = a.block_table + (size_t)r * a.bt_stride;
     const float sl2 = a.scale * LOG2E;                   // scores in units of log2
 
-    const uint32_t s_base = smem_u32(smem);
-    const uint32_t sq = s_base;                          // [BM][D]
-    const uint32_t s_tiles = s_base + BM * D * 2;
-
+    // [STAGES x (K, V) tiles][Q: BM x D][barriers]
+    const uint32_t s_tiles = smem_u32(smem);
+    unsigned char* q_ptr = smem + (size_t)STAGES * 2 * TILE_BYTES;
+    const uint32_t sq = smem_u32(q_ptr);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(q_ptr + BM * D * 2);
+    const uint32_t full0 = cx_smem(bars), empty0 = cx_smem(bars + STAGES);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { cx_mbar_init(full0 + 8 * s, 1); cx_mbar_init(empty0 + 8 * s, 4); }
+        cx_mbar_init_fence();
+    }
     // Q tile: packed row -> (token, head in group)
-    for (int idx = threadIdx.x; idx < BM * (D / 8); idx += NTHREADS) {
+    for (int idx = threadIdx.x; idx < BM * (D / 8); idx += BLOCK_THREADS) {
         const int row = idx / (D / 8), c = idx % (D / 8);
         const int pr = row0 + row;
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -391,30 +383,33 @@ attention_prefill_kernel(MmaAttnArgs a) {
             const int tt = pr / G, hg = pr % G;
             v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + tt) * a.nh + g * G + hg) * D + c * 8);
         }
-        *reinterpret_cast<uint4*>(smem + swz<D>(row, c)) = v;
+        *reinterpret_cast<uint4*>(q_ptr + swz<D>(row, c)) = v;
     }
-    // positions of this thread's two rows
-    const int pra = row0 + warp * 16 + (lane >> 2), prb = pra + 8;
-    const int pos_a = ctx + min(pra, rows_total - 1) / G, pos_b = ctx + min(prb, rows_total - 1) / G;
-    const bool live_a = pra < rows_total, live_b = prb < rows_total;
     // keys that any row of the tile can see
     const int last_row = min(row0 + BM, rows_total) - 1;
     const int hi = ctx + last_row / G + 1;
     const int lo = a.window > 0 ? max(0, ctx + row0 / G + 1 - a.window) : 0;
     const int tile0 = lo / BN, tile1 = (hi + BN - 1) / BN;
+    __syncthreads();                                     // barriers initialised, Q tile written
+    bool gave_up = false;
 
-    KVLoader<D, NTHREADS> ld;
-    ld.init(bt, a.cache, g, a.page, a.nkv, lo, hi);
-    if (tile0 < tile1) ld.prefetch(tile0 * BN);
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (tile0 + s < tile1) {
-            ld.issue(s_tiles + s * 2 * TILE_BYTES, s_tiles + s * 2 * TILE_BYTES + TILE_BYTES, (tile0 + s) * BN);
-            if (tile0 + s + 1 < tile1) ld.prefetch((tile0 + s + 1) * BN);
+    if (producer) {
+        for (int tile = tile0, it = 0; tile < tile1; ++tile, ++it) {
+            const int st = it % STAGES;
+            if (!cx_mbar_wait(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) gave_up = true;
+            if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, 2 * TILE_BYTES);
+            __syncwarp();
+            produce_tile<D>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
+                            full0 + 8 * st, tile * BN, lo, hi, bt, a.cache, g, a.page, a.nkv, lane);
         }
-        cp_async_commit();
+        if (gave_up && a.status) atomicCAS(a.status, 0, 6);
+        return;
     }
-    __syncthreads();                                     // Q tile written
+
+    // positions of this thread's two rows
+    const int pra = row0 + warp * 16 + (lane >> 2), prb = pra + 8;
+    const int pos_a = ctx + min(pra, rows_total - 1) / G, pos_b = ctx + min(prb, rows_total - 1) / G;
+    const bool live_a = pra < rows_total, live_b = prb < rows_total;
     uint32_t qf[D / 16][4];
     load_q_frags<D>(qf, sq, warp * 16);
 
@@ -426,19 +421,9 @@ attention_prefill_kernel(MmaAttnArgs a) {
     const int wpos_min = ctx + min(row0 + warp * 16, rows_total - 1) / G;
     const int wlo_max = a.window > 0 ? ctx + min(row0 + warp * 16 + 15, rows_total - 1) / G + 1 - a.window : 0;
 
-    for (int tile = tile0; tile < tile1; ++tile) {
-        cp_async_wait<STAGES - 2>();
-        __syncthreads();
-        {
-            const int nt = tile + STAGES - 1;
-            const int st = (nt - tile0) % STAGES;
-            if (nt < tile1) {
-                ld.issue(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES, nt * BN);
-                if (nt + 1 < tile1) ld.prefetch((nt + 1) * BN);
-            }
-            cp_async_commit();
-        }
-        const int st = (tile - tile0) % STAGES;
+    for (int tile = tile0, it = 0; tile < tile1; ++tile, ++it) {
+        const int st = it % STAGES;
+        if (!cx_mbar_wait(full0 + 8 * st, (it / STAGES) & 1)) gave_up = true;
         const uint32_t sk = s_tiles + st * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
         const int kb = tile * BN;
         float s[BN / 8][4];
@@ -493,8 +478,10 @@ attention_prefill_kernel(MmaAttnArgs a) {
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) { o[i][0] *= ca; o[i][1] *= ca; o[i][2] *= cb; o[i][3] *= cb; }
         pv_product<D, BN / 16>(o, pf, sv, 0);
+        __syncwarp();
+        if (lane == 0) cx_mbar_arrive(empty0 + 8 * st);          // this warp is done with the stage
     }
-    cp_async_wait<0>();
+    if (gave_up && a.status) atomicCAS(a.status, 0, 6);
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
     const float ia = 1.0f / l_a, ib = 1.0f / l_b;
@@ -512,9 +499,7 @@ attention_prefill_kernel(MmaAttnArgs a) {
 template <int D>
 static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStream_t s) {
     constexpr int STAGES = 3;
-    const size_t tiles = 16 * D * 2 + (size_t)STAGES * 2 * BN * D * 2;
-    const size_t merge = 16 * D * 2 + 4 * 16 * D * 4 + 4 * 16 * 2 * 4;
-    const size_t smem = tiles > merge ? tiles : merge;
+    const size_t smem = (size_t)STAGES * 2 * BN * D * 2 + 16 * D * 2 + 2 * STAGES * 8 + 64;   // tiles, Q, barriers
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES>,
@@ -523,14 +508,14 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
         configured = true;
     }
     dim3 grid(nsplit, a.nkv, n_list);
-    vcb_launch(attention_decode_kernel<D, STAGES>, grid, NTHREADS, smem, s, a);
+    vcb_launch(attention_decode_kernel<D, STAGES>, grid, BLOCK_THREADS, smem, s, a);
     return vcb_last_error();
 }
 
 template <int D>
 static int launch_prefill(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
     constexpr int STAGES = 2;
-    const size_t smem = BM * D * 2 + (size_t)STAGES * 2 * BN * D * 2;
+    const size_t smem = (size_t)STAGES * 2 * BN * D * 2 + BM * D * 2 + 2 * STAGES * 8 + 64;     // tiles, Q, barriers
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D, STAGES>,
@@ -539,7 +524,7 @@ static int launch_prefill(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
         configured = true;
     }
     dim3 grid(n_tiles, a.nkv);
-    vcb_launch(attention_prefill_kernel<D, STAGES>, grid, NTHREADS, smem, s, a);
+    vcb_launch(attention_prefill_kernel<D, STAGES>, grid, BLOCK_THREADS, smem, s, a);
     return vcb_last_error();
 }
 
@@ -556,13 +541,13 @@ VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* 
                                         const int* ctx_lens, const int* block_table, int bt_stride,
                                         const int* req_list, int n_list, int nsplit, float* part_o,
                                         float* part_ml, int* counters, int nh, int nkv, int d, int page,
-                                        int window, float scale, void* stream) {
+                                        int window, float scale, int* status, void* stream) {
     if (n_list <= 0) return 0;
     int c = check_common(nh, nkv, d, page, window);
     if (c) return c;
     if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, req_list, nullptr, part_o, part_ml, counters, bt_stride, nh, nkv, page, window, scale};
+                  block_table, req_list, nullptr, part_o, part_ml, counters, status, bt_stride, nh, nkv, page, window, scale};
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
@@ -570,12 +555,13 @@ VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* 
 VCB_EXPORT int vcb_attention_prefill_mma(const void* q, const void* cache, void* out, const int* q_start,
                                          const int* ctx_lens, const int* block_table, int bt_stride,
                                          const int* tile_req, const int* tile_row0, int n_tiles, int nh,
-                                         int nkv, int d, int page, int window, float scale, void* stream) {
+                                         int nkv, int d, int page, int window, float scale, int* status,
+                                         void* stream) {
     if (n_tiles <= 0) return 0;
     int c = check_common(nh, nkv, d, page, window);
     if (c) return c;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, bt_stride, nh, nkv, page, window, scale};
+                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, bt_stride, nh, nkv, page, window, scale};
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_prefill<64>(a, n_tiles, s) : launch_prefill<128>(a, n_tiles, s);
 }
@@ -628,6 +614,7 @@ VCB_EXPORT int vcb_attention_decode_mma_static(const void* q, const void* cache,
     float* part_o = nullptr;
     float* part_ml = nullptr;
     int* counters = nullptr;
+    int* status = nullptr;                  // a wait that runs out only ends the kernel early here
     cudaStream_t s = (cudaStream_t)stream;
     if (nsplit > 1) {
         const long long rows = (long long)n_list * nh * nsplit;
@@ -642,6 +629,6 @@ VCB_EXPORT int vcb_attention_decode_mma_static(const void* q, const void* cache,
         if (e != cudaSuccess) return (int)e;
     }
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, req_list, nullptr, part_o, part_ml, counters, bt_stride, nh, nkv, page, window, scale};
+                  block_table, req_list, nullptr, part_o, part_ml, counters, status, bt_stride, nh, nkv, page, window, scale};
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }

@@ -4,7 +4,8 @@
 //
 // One warp per (query token, query head).  The query at position p of request r
 // attends keys j of the same request with  j <= p  and, when window > 0,
-// j > p - window;  key j lives in page block_table[r, j / page], slot j % page.
+// j > p - window;  key j lives in page block_table[r, j / page], slot j % page, its row in the
+// chunk order of kv_row_pos (common.cuh).
 // Scores, softmax and the output accumulation are float; softmax is computed
 // online over chunks of 32 keys (one key per lane).
 //
@@ -63,8 +64,9 @@ __global__ void attention_simt_kernel(AttnArgs a) {
             const int pg = bt[j / a.page];
             koff = (unsigned long long)pg * page_elems + ((size_t)g * a.page + (j % a.page)) * a.d;
             const T* kr = cache + koff;
+            const int slot = j % a.page;
             float acc = 0.0f;
-            for (int i = 0; i < a.d; ++i) acc += qs[i] * to_f32<T>(kr[i]);
+            for (int i = 0; i < a.d; ++i) acc += qs[i] * to_f32<T>(kr[kv_row_pos(i, slot, a.d, (int)sizeof(T))]);
             s = acc;
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -78,10 +80,11 @@ __global__ void attention_simt_kernel(AttnArgs a) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const unsigned long long off = __shfl_sync(0xffffffffu, koff, jj);
             const T* vr = cache + off + v_off;
+            const int slot = (kb + jj) % a.page;
 #pragma unroll
             for (int k = 0; k < ATT_MAX_D / 32; ++k) {
                 const int dim = lane + 32 * k;
-                if (dim < a.d) o[k] += pj * to_f32<T>(vr[dim]);
+                if (dim < a.d) o[k] += pj * to_f32<T>(vr[kv_row_pos(dim, slot, a.d, (int)sizeof(T))]);
             }
         }
         m = m_new;

@@ -73,6 +73,53 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 
 static inline int vcb_last_error() { return (int)cudaGetLastError(); }
 
+// ---- layout of a cache row
+// A page holds [k|v][kv head][slot][head dim].  When a row (one slot of one head) is a multiple
+// of 128 bytes, its 16-byte chunks are stored XOR-swizzled by the slot number: chunk c of slot s
+// lives at chunk c ^ (s & 7).  A run of slots of a page is then, byte for byte, the image that
+// the tensor-core attention kernels want in shared memory (conflict-free ldmatrix), and one
+// plain bulk copy brings it there.  Rows of other sizes are stored as they are.
+__host__ __device__ __forceinline__ int kv_row_pos(int elem, int slot, int d, int esize) {
+    if ((d * esize) & 127) return elem;
+    const int per_chunk = 16 / esize;
+    const int chunk = elem / per_chunk, within = elem - chunk * per_chunk;
+    return ((chunk ^ (slot & 7)) * per_chunk) + within;
+}
+
+// ---- mbarriers and bulk copies (shared by the kernels that stage memory asynchronously)
+#define CX_SPIN_LIMIT (1u << 22)
+__device__ __forceinline__ uint32_t cx_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cx_mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void cx_mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void cx_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cx_mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait for the phase with the given parity.  False: gave up.
+__device__ __forceinline__ bool cx_mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < CX_SPIN_LIMIT; ++spin) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.b32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// Contiguous global -> shared copy by the TMA unit; completes on the mbarrier.  No multicast.
+__device__ __forceinline__ void cx_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
 // ---- programmatic dependent launch
 // Kernels of a step are launched so that the next kernel in the stream may begin while the
 // previous one still runs: its CTAs become resident, set themselves up (and, in the matrix

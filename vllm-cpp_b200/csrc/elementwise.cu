@@ -245,7 +245,7 @@ VCB_EXPORT int vcb_silu_mul(const void* gu, void* out, int n_tokens, int inter, 
 //   q, k, v get their bias (float); q and k heads are rotated over the first
 //   `rot` elements of each head; q goes to q_out [n_tokens, nh*d]; k and v go to
 //   page block_table[r, p / page] slot p % page of this layer's cache, laid out
-//   [page][k|v][kv_head][slot][d].
+//   [page][k|v][kv_head][slot][d], each row in the chunk order of kv_row_pos (common.cuh).
 // Rotation (src/kernels/rotary_embedding.cu:18-33, table of src/model/qwen.cpp:119-128):
 //   angle = p / denom[j],  denom[j] = theta^(2j/rot)  (computed on the host in float)
 //   pairing 0 ("half"):        (a, b) = (x[j], x[j + rot/2])
@@ -292,22 +292,23 @@ __global__ void rope_cache_kernel(RopeCacheArgs a, int heads_per_block) {
         const float rb = xa * sn + xb * cs;
         xa = ra; xb = rb;
     }
-    T* dst;
     if (h < a.nh) {
-        dst = (T*)a.q_out + (size_t)t * a.nh * a.d + (size_t)h * a.d;
-    } else {
-        if (!a.write_kv) return;
-        const int r = a.req_of_token[t];
-        const int pg = a.block_table[(size_t)r * a.bt_stride + pos / a.page];
-        const int slot = pos % a.page;
-        // [page][2][nkv][slot][d]
-        T* base = (T*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
-        const int kvh = h < a.nh + a.nkv ? h - a.nh : h - a.nh - a.nkv;
-        const size_t which = h < a.nh + a.nkv ? 0 : (size_t)a.nkv * a.page * a.d;
-        dst = base + which + ((size_t)kvh * a.page + slot) * a.d;
+        T* dst = (T*)a.q_out + (size_t)t * a.nh * a.d + (size_t)h * a.d;
+        dst[ia] = from_f32<T>(xa);
+        dst[ib] = from_f32<T>(xb);
+        return;
     }
-    dst[ia] = from_f32<T>(xa);
-    dst[ib] = from_f32<T>(xb);
+    if (!a.write_kv) return;
+    const int r = a.req_of_token[t];
+    const int pg = a.block_table[(size_t)r * a.bt_stride + pos / a.page];
+    const int slot = pos % a.page;
+    // [page][2][nkv][slot][d], rows in the layout of kv_row_pos
+    T* base = (T*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
+    const int kvh = h < a.nh + a.nkv ? h - a.nh : h - a.nh - a.nkv;
+    const size_t which = h < a.nh + a.nkv ? 0 : (size_t)a.nkv * a.page * a.d;
+    T* dst = base + which + ((size_t)kvh * a.page + slot) * a.d;
+    dst[kv_row_pos(ia, slot, a.d, (int)sizeof(T))] = from_f32<T>(xa);
+    dst[kv_row_pos(ib, slot, a.d, (int)sizeof(T))] = from_f32<T>(xb);
 }
 
 VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const int* positions,

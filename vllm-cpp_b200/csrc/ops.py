@@ -34,8 +34,8 @@ _SIGNATURES = {
     "vcb_rope_cache_write": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "vcb_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
-    "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+    "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+    "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
     "vcb_tile_weights": [_P, _I, _I, _I, _P, _P],
     "vcb_repetition_penalty": [_P, _I, _P, _P, _P, _I, _I, _P],
@@ -240,7 +240,8 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
         n_list, nsplit, None if part_o is None else _dev(part_o, "part_o", torch.float32),
         None if part_ml is None else _dev(part_ml, "part_ml", torch.float32),
         None if counters is None else _dev(counters, "counters", torch.int32),
-        num_heads, num_kv_heads, head_dim, page_size, window, float(scale), _stream()), "attention_decode_mma")
+        num_heads, num_kv_heads, head_dim, page_size, window, float(scale),
+        status_tensor(q.device).data_ptr(), _stream()), "attention_decode_mma")
 
 
 def attention_prefill_mma(q, cache, out, q_start, ctx_lens, block_table, tile_req, tile_row0, *,
@@ -256,8 +257,8 @@ def attention_prefill_mma(q, cache, out, q_start, ctx_lens, block_table, tile_re
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
         _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], _dev(tile_req, "tile_req", torch.int32), _dev(tile_row0, "tile_row0", torch.int32),
-        n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale), _stream()),
-        "attention_prefill_mma")
+        n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale),
+        status_tensor(q.device).data_ptr(), _stream()), "attention_prefill_mma")
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -274,7 +275,8 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 SM_COUNT = 148
 _status: Optional[torch.Tensor] = None
 STATUS_MEANING = {1: "the TMA producer waited too long for a free stage", 2: "the MMA issuer waited too long for a loaded stage",
-                  3: "the epilogue waited too long for the accumulator", 4: "the MMA issuer waited too long for a free accumulator"}
+                  3: "the epilogue waited too long for the accumulator", 4: "the MMA issuer waited too long for a free accumulator",
+                  5: "decode attention waited too long for a cache tile", 6: "prefill attention waited too long for a cache tile"}
 
 
 def status_tensor(device) -> torch.Tensor:
@@ -292,7 +294,7 @@ def check_status() -> None:
     code = int(_status.item())
     if code:
         _status.zero_()
-        raise KernelError(f"a tcgen05 kernel gave up on a bounded wait: {STATUS_MEANING.get(code, code)}")
+        raise KernelError(f"a kernel gave up on a bounded wait: {STATUS_MEANING.get(code, code)}")
 
 
 def tcgen05_plan(tokens: int, features: int, k: int):
