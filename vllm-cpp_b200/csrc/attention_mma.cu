@@ -32,6 +32,8 @@
 // bfloat16 path; attention_simt.cu is its plain counterpart.
 #include "common.cuh"
 
+#include <cstdlib>
+
 #define BN 64            // keys per tile
 #define BM 64            // rows per CTA in the prefill kernel
 #define NTHREADS 128     // consumer threads (4 warps); warp 4 is the producer
@@ -90,7 +92,7 @@ template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 // The producer warp's share of one tile of BN keys starting at key kb of kv head g: lanes 0-7
 // each copy one page piece of K, lanes 8-15 the same pieces of V (a tile spans at most
 // BN / 16 + 1 pages).  Lane 0 has armed the stage's barrier with the tile's byte count.
-template <int D>
+template <int D, int TK>
 __device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t bar, int kb, int lo, int hi,
                                              const int* __restrict__ bt, const __nv_bfloat16* __restrict__ cache,
                                              int g, int page, int nkv, int lane) {
@@ -98,8 +100,8 @@ __device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t 
     const int piece = lane & 7;
     const int first_page = kb / page;
     const int start = piece == 0 ? kb : (first_page + piece) * page;       // first key of the piece
-    if (start >= kb + BN) return;
-    const int end = min((start / page + 1) * page, kb + BN);
+    if (start >= kb + TK) return;
+    const int end = min((start / page + 1) * page, kb + TK);
     // the page itself if any of it is visible, else the page of the last visible key
     const int lp = start / page;
     const bool visible = lp * page < hi && (lp + 1) * page > lo;
@@ -216,8 +218,8 @@ attention_decode_kernel(MmaAttnArgs a) {
                 if (!cx_mbar_wait(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) gave_up = true;
                 if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, 2 * TILE_BYTES);
                 __syncwarp();
-                produce_tile<D>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
-                                full0 + 8 * st, tile * BN, lo, hi, bt, a.cache, g, a.page, a.nkv, lane);
+                produce_tile<D, BN>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
+                                    full0 + 8 * st, tile * BN, lo, hi, bt, a.cache, g, a.page, a.nkv, lane);
             }
         } else {
             uint32_t qf[D / 16][4];
@@ -347,11 +349,11 @@ attention_decode_kernel(MmaAttnArgs a) {
 }
 
 // ----------------------------------------------------------------- prefill
-template <int D, int STAGES>
-__global__ void __launch_bounds__(BLOCK_THREADS)
+template <int D, int TK, int STAGES, int MINB>
+__global__ void __launch_bounds__(BLOCK_THREADS, MINB)
 attention_prefill_kernel(MmaAttnArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    constexpr int TILE_BYTES = BN * D * 2;
+    constexpr int TILE_BYTES = TK * D * 2;
     pdl_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool producer = warp == 4;
@@ -389,7 +391,7 @@ attention_prefill_kernel(MmaAttnArgs a) {
     const int last_row = min(row0 + BM, rows_total) - 1;
     const int hi = ctx + last_row / G + 1;
     const int lo = a.window > 0 ? max(0, ctx + row0 / G + 1 - a.window) : 0;
-    const int tile0 = lo / BN, tile1 = (hi + BN - 1) / BN;
+    const int tile0 = lo / TK, tile1 = (hi + TK - 1) / TK;
     __syncthreads();                                     // barriers initialised, Q tile written
     bool gave_up = false;
 
@@ -399,8 +401,8 @@ attention_prefill_kernel(MmaAttnArgs a) {
             if (!cx_mbar_wait(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) gave_up = true;
             if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, 2 * TILE_BYTES);
             __syncwarp();
-            produce_tile<D>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
-                            full0 + 8 * st, tile * BN, lo, hi, bt, a.cache, g, a.page, a.nkv, lane);
+            produce_tile<D, TK>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
+                                full0 + 8 * st, tile * TK, lo, hi, bt, a.cache, g, a.page, a.nkv, lane);
         }
         if (gave_up && a.status) atomicCAS(a.status, 0, 6);
         return;
@@ -425,14 +427,14 @@ attention_prefill_kernel(MmaAttnArgs a) {
         const int st = it % STAGES;
         if (!cx_mbar_wait(full0 + 8 * st, (it / STAGES) & 1)) gave_up = true;
         const uint32_t sk = s_tiles + st * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
-        const int kb = tile * BN;
-        float s[BN / 8][4];
+        const int kb = tile * TK;
+        float s[TK / 8][4];
 #pragma unroll
-        for (int i = 0; i < BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
-        qk_product<D, BN / 8>(s, qf, sk, 0);
-        const bool need_mask = (kb + BN - 1 > wpos_min) || (kb < wlo_max) || !live_b;
+        for (int i = 0; i < TK / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
+        qk_product<D, TK / 8>(s, qf, sk, 0);
+        const bool need_mask = (kb + TK - 1 > wpos_min) || (kb < wlo_max) || !live_b;
 #pragma unroll
-        for (int nb = 0; nb < BN / 8; ++nb)
+        for (int nb = 0; nb < TK / 8; ++nb)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float v = s[nb][e] * sl2;
@@ -447,7 +449,7 @@ attention_prefill_kernel(MmaAttnArgs a) {
             }
         float ta = -INFINITY, tb = -INFINITY;
 #pragma unroll
-        for (int nb = 0; nb < BN / 8; ++nb) {
+        for (int nb = 0; nb < TK / 8; ++nb) {
             ta = fmaxf(ta, fmaxf(s[nb][0], s[nb][1]));
             tb = fmaxf(tb, fmaxf(s[nb][2], s[nb][3]));
         }
@@ -457,10 +459,10 @@ attention_prefill_kernel(MmaAttnArgs a) {
         const float sa = na == -INFINITY ? 0.0f : na, sb = nb_ == -INFINITY ? 0.0f : nb_;
         const float ca = fast_exp2(m_a - sa), cb = fast_exp2(m_b - sb);
         m_a = na; m_b = nb_;
-        uint32_t pf[BN / 16][4];
+        uint32_t pf[TK / 16][4];
         float sum_a = 0.0f, sum_b = 0.0f;
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
+        for (int kk = 0; kk < TK / 16; ++kk) {
             float p[2][4];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -477,7 +479,7 @@ attention_prefill_kernel(MmaAttnArgs a) {
         l_b = l_b * cb + sum_b;
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) { o[i][0] *= ca; o[i][1] *= ca; o[i][2] *= cb; o[i][3] *= cb; }
-        pv_product<D, BN / 16>(o, pf, sv, 0);
+        pv_product<D, TK / 16>(o, pf, sv, 0);
         __syncwarp();
         if (lane == 0) cx_mbar_arrive(empty0 + 8 * st);          // this warp is done with the stage
     }
@@ -512,20 +514,29 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
     return vcb_last_error();
 }
 
-template <int D>
-static int launch_prefill(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
-    constexpr int STAGES = 2;
-    const size_t smem = (size_t)STAGES * 2 * BN * D * 2 + BM * D * 2 + 2 * STAGES * 8 + 64;     // tiles, Q, barriers
+template <int D, int TK, int STAGES, int MINB>
+static int launch_prefill_variant(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
+    const size_t smem = (size_t)STAGES * 2 * TK * D * 2 + BM * D * 2 + 2 * STAGES * 8 + 64;     // tiles, Q, barriers
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D, STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D, TK, STAGES, MINB>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(n_tiles, a.nkv);
-    vcb_launch(attention_prefill_kernel<D, STAGES>, grid, BLOCK_THREADS, smem, s, a);
+    vcb_launch(attention_prefill_kernel<D, TK, STAGES, MINB>, grid, BLOCK_THREADS, smem, s, a);
     return vcb_last_error();
+}
+
+template <int D>
+static int launch_prefill(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
+    static int variant = getenv("VCB_PREFILL_VARIANT") ? atoi(getenv("VCB_PREFILL_VARIANT")) : 2;
+    if (variant == 1) return launch_prefill_variant<D, 32, 3, 3>(a, n_tiles, s);
+    if (variant == 2) return launch_prefill_variant<D, 32, 4, 2>(a, n_tiles, s);
+    if (variant == 3) return launch_prefill_variant<D, 64, 3, 1>(a, n_tiles, s);
+    if (variant == 4) return launch_prefill_variant<D, 64, 2, 2>(a, n_tiles, s);
+    return launch_prefill_variant<D, 32, 4, 2>(a, n_tiles, s);
 }
 
 static int check_common(int nh, int nkv, int d, int page, int window) {

@@ -126,12 +126,16 @@ class PagedAttention(Mixer):
         def tiles(host):
             if all(q == 1 for q in host.q_lens):
                 return np.zeros((2, 0), dtype=np.int32)         # decode-only steps use the split-KV kernel
-            req, row0 = [], []
-            for r, q in enumerate(host.q_lens):
+            req, row0, keys = [], [], []
+            for r, (q, ctx) in enumerate(zip(host.q_lens, host.ctx_lens)):
                 for k in range(-(-q * group // rows)):
                     req.append(r)
                     row0.append(k * rows)
-            return np.array([req, row0], dtype=np.int32)
+                    keys.append(ctx + min(q, ((k + 1) * rows + group - 1) // group))   # keys its last row sees
+            # CTAs start in list order: the tiles with the most keys go first, so that the short
+            # ones fill the tail instead of the other way round (causal work is triangular)
+            order = np.argsort(-np.asarray(keys), kind="stable")
+            return np.array([req, row0], dtype=np.int32)[:, order]
 
         return {f"attn_tiles_g{group}": tiles}
 
