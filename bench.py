@@ -117,6 +117,8 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only (for profiling); the other fields of the line are null")
+    ap.add_argument("--no-pdl", action="store_true", help="ordinary launches instead of programmatic dependent launch")
+    ap.add_argument("--library-gemm", action="store_true", help="cuBLAS for every bfloat16 product (no tcgen05 kernel)")
     ap.add_argument("--no-cuda-graphs", action="store_true",
                     help="launch every kernel of a decode step directly (for a profiler's launch list)")
     a = ap.parse_args()
@@ -137,10 +139,10 @@ def main() -> int:
     from vllm_cpp_b200.engine.llm_engine import Engine
     from vllm_cpp_b200.engine.runner import StepEntry
 
-    if os.environ.get("VCB_PDL") is not None:                # experiment switches, for profiling
-        ops.set_pdl(os.environ["VCB_PDL"] != "0")
-    if os.environ.get("VCB_TCGEN05") is not None:
-        ops.set_tcgen05_linear(os.environ["VCB_TCGEN05"] != "0")
+    if a.no_pdl:
+        ops.set_pdl(False)
+    if a.library_gemm:
+        ops.set_tcgen05_linear(False)
     cfg = dict(QWEN25_7B, num_hidden_layers=a.layers)
     nums = model_numbers(cfg)
     peaks = load_peaks()

@@ -404,3 +404,27 @@ def test_gemm_bf16_tcgen05(ops, m, n, k, plan, ctas, out_dtype):
         assert np.isfinite(got).all()
         err = np.abs(got - want).max()
         assert err <= tol * np.abs(want).max(), f"tiled={tiled}: max |diff| {err:.3e} vs scale {np.abs(want).max():.3e}"
+
+
+def test_device_sampler_on_the_reference_samplers_golden_rows(ops):
+    """The device sampler on the rows for which tests/golden holds the reference sampler's answers."""
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(__file__), "golden", "sampler_golden.json")) as f:
+        cases = json.load(f)["cases"]
+    logits = np.array([c["logits"] for c in cases], dtype=np.float32)
+    temps = np.array([c["temperature"] for c in cases], dtype=np.float32)
+    u = np.array([c["u"] for c in cases], dtype=np.float32)
+    top_p = np.array([c["top_p"] for c in cases], dtype=np.float32)
+    top_k = np.array([c["top_k"] for c in cases], dtype=np.int32)
+    out = torch.empty(len(cases), dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits), dev(temps), dev(u), out)
+    ops.sample_filtered(dev(logits), dev(temps), dev(u), dev(top_p), dev(top_k), out)
+    got = out.cpu().numpy()
+    wrong = [i for i, c in enumerate(cases) if got[i] != c["token"]]
+    for i in wrong:                                   # only a knife-edge of a running sum may differ
+        p = plain.softmax(logits[i] * (np.float32(1) / temps[i]) if temps[i] > 0 else logits[i])
+        order = plain.order_by_probability(p, list(range(logits.shape[1])))
+        assert abs(order.index(int(got[i])) - order.index(cases[i]["token"])) == 1 or \
+            abs(int(got[i]) - cases[i]["token"]) == 1, (i, got[i], cases[i]["token"])
+    assert len(wrong) <= 2

@@ -79,3 +79,17 @@ def test_folder_round_trip(tmp_path):
     plain.write_model_folder(str(tmp_path / "m"), cfg, w, store="BF16")
     cfg2, w2 = plain.read_model_folder(str(tmp_path / "m"))
     assert cfg2 == cfg and all(np.array_equal(w[k], w2[k]) for k in w)
+
+
+def test_plain_sampler_equals_the_reference_sampler_code():
+    """tests/golden/sampler_golden.json holds what the reference's own host sampler
+    (src/sampler/sampler.cpp, src/sampler/topk_topp.cpp, compiled by tests/golden/make_sampler_golden.sh)
+    returns for 48 seeded rows: greedy, temperature, top-k, top-p, ties."""
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(__file__), "golden", "sampler_golden.json")) as f:
+        cases = json.load(f)["cases"]
+    assert len(cases) == 48
+    for c in cases:
+        tok = plain.sample(np.array(c["logits"], dtype=np.float32), c["temperature"], c["top_p"], c["top_k"], 1.0, [], c["u"])
+        assert tok == c["token"], c

@@ -32,8 +32,6 @@
 // bfloat16 path; attention_simt.cu is its plain counterpart.
 #include "common.cuh"
 
-#include <cstdlib>
-
 #define BN 64            // keys per tile
 #define BM 64            // rows per CTA in the prefill kernel
 #define NTHREADS 128     // consumer threads (4 warps); warp 4 is the producer
@@ -529,13 +527,10 @@ static int launch_prefill_variant(const MmaAttnArgs& a, int n_tiles, cudaStream_
     return vcb_last_error();
 }
 
+// 32-key tiles in a ring of four stages, two CTAs per SM: the best of the shapes tried
+// (64-key tiles with two or three stages, 32-key tiles with three CTAs per SM were within 2 %).
 template <int D>
 static int launch_prefill(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
-    static int variant = getenv("VCB_PREFILL_VARIANT") ? atoi(getenv("VCB_PREFILL_VARIANT")) : 2;
-    if (variant == 1) return launch_prefill_variant<D, 32, 3, 3>(a, n_tiles, s);
-    if (variant == 2) return launch_prefill_variant<D, 32, 4, 2>(a, n_tiles, s);
-    if (variant == 3) return launch_prefill_variant<D, 64, 3, 1>(a, n_tiles, s);
-    if (variant == 4) return launch_prefill_variant<D, 64, 2, 2>(a, n_tiles, s);
     return launch_prefill_variant<D, 32, 4, 2>(a, n_tiles, s);
 }
 
