@@ -406,6 +406,53 @@ def test_gemm_bf16_tcgen05(ops, m, n, k, plan, ctas, out_dtype):
         assert err <= tol * np.abs(want).max(), f"tiled={tiled}: max |diff| {err:.3e} vs scale {np.abs(want).max():.3e}"
 
 
+@pytest.mark.parametrize("m,n,k,ctas", [(8, 3584, 512, 148), (1, 128, 64, 148), (5, 300, 200, 3), (33, 1000, 1024, 7),
+                                        (64, 3584, 4736, 148), (100, 384, 576, 148), (128, 200, 1088, 11)])
+def test_gemm_bf16_tcgen05_fused_norm(ops, m, n, k, ctas):
+    """A product that ends a residual branch (residual += x w^T; out = residual * gain; sums of squares
+    left in parts) followed by a product that applies the rows' factor, against the same done plainly:
+    y = rmsnorm(residual + x w^T) w2^T.  Tiles split between CTAs, ragged feature counts."""
+    rng = np.random.default_rng(5)
+    x = as_stored(rng.standard_normal((m, k)), "bfloat16")
+    w = as_stored(rng.standard_normal((n, k)) * 0.1, "bfloat16")
+    n2 = 264
+    w2 = as_stored(rng.standard_normal((n2, -(-n // 8) * 8)) * 0.1, "bfloat16")[:, :n]
+    res = rng.standard_normal((m, n)).astype(np.float32) * 2
+    gain = (1 + 0.3 * rng.standard_normal(n)).astype(np.float32)
+    eps = 1e-5
+    new_res = res.astype(np.float64) + x.astype(np.float64) @ w.astype(np.float64).T
+    rstd = 1.0 / np.sqrt((new_res ** 2).mean(axis=1, keepdims=True) + eps)
+    scaled = new_res * gain
+    if n % 8:
+        return pytest.skip("the second product needs K a multiple of 8")
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    w2d = dev(np.ascontiguousarray(w2), torch.bfloat16)
+    ops.tile_weights(wd)
+    for rep in range(2):
+        rd, gd = dev(res), dev(gain)
+        parts = ops.sumsq_parts(n)
+        ss = torch.full((parts + 1, m + 3), float("nan"), device="cuda")
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        fuse = ops.ResidualNorm(rd, gd, ss, eps)
+        ops.gemm_bf16_tcgen05(xd, wd, out, None, ctas, fuse=fuse)
+        y = torch.full((m, n2), float("nan"), dtype=torch.float32, device="cuda")
+        ops.gemm_bf16_tcgen05(out, w2d, y, None, ctas, x_scale=fuse.scale())
+        torch.cuda.synchronize()
+        ops.check_status()
+        got_res = rd.cpu().numpy()
+        assert np.abs(got_res - new_res).max() <= 1e-5 * np.abs(new_res).max() + 4e-7 * np.sqrt(k) * np.abs(new_res).max()
+        got_ss = ss[:parts, :m].cpu().numpy().astype(np.float64).sum(axis=0)
+        assert np.allclose(got_ss, (new_res ** 2).sum(axis=1), rtol=1e-5)
+        assert torch.isnan(ss[parts]).all() and torch.isnan(ss[:, m:]).all()       # nothing written outside
+        got_out = out.float().cpu().numpy()
+        assert np.abs(got_out - scaled).max() <= 4e-3 * np.abs(scaled).max() + 1e-6
+        # second product: on the bfloat16 values the first one stored
+        want_y = (got_out.astype(np.float64) * rstd) @ w2.astype(np.float64).T
+        got_y = y.cpu().numpy()
+        assert np.isfinite(got_y).all()
+        assert np.abs(got_y - want_y).max() <= (4e-7 * np.sqrt(n) + 2e-6) * np.abs(want_y).max()
+
+
 def test_device_sampler_on_the_reference_samplers_golden_rows(ops):
     """The device sampler on the rows for which tests/golden holds the reference sampler's answers."""
     import json

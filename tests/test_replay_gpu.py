@@ -139,6 +139,53 @@ def test_mixed_requests_reusing_pages(tmp_path, name, dtype):
         compare(rp.logits_of(rid, range(len(ids))), plain.forward(weights, cfg, ids), dtype, f"{name} mixed {rid}")
 
 
+@pytest.fixture
+def pinned_tcgen05():
+    """Every bfloat16 product with few tokens on this library's tcgen05 kernel: nothing is measured at load."""
+    from vllm_cpp_b200.csrc import ops
+    saved = dict(ops._linear_choice)
+    ops._linear_choice.clear()
+    ops.set_linear_tuning(False)
+    yield ops
+    ops.set_linear_tuning(True)
+    ops._linear_choice.update(saved)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_norms_fused_into_products(tmp_path, pinned_tcgen05, name):
+    """Steps of up to 128 tokens run no norm kernel between products: the product before a norm adds
+    into the residual stream and applies the gain, the one after applies the rows' factor.  Portions,
+    decoding and mixed steps against the plain implementation, and a count of the norm kernels left."""
+    ops = pinned_tcgen05
+    cfg, page = CONFIGS[name]
+    cfg, weights, cache, runner = build(tmp_path, name, "bfloat16", num_pages=4 * (-(-120 // page)) + 1)
+    assert all(b.mixer.fuses_norm(8) and b.feed_forward.fuses_norm(128) for b in runner.model.blocks)
+    calls = []
+    keep = ops.add_rmsnorm
+    ops.add_rmsnorm = lambda *a, **k: (calls.append(1), keep(*a, **k))[1]
+    try:
+        rp = Replayer(runner, cache)
+        ids = token_ids(cfg, 150, 41)
+        rp.step([("r", ids[:100], range(100))])
+        assert len(calls) == 2, "one norm after the embedding, one before the output product"
+        rp.step([("r", ids[100:102], range(2))])
+        for t in range(102, 150):
+            rp.step([("r", ids[t:t + 1], [0])])
+        rp.step([("x", [3, 4], [])], end=["r", "x"])
+        compare(rp.logits_of("r", range(150)), plain.forward(weights, cfg, ids), "bfloat16", f"{name} fused norms")
+        del calls[:]
+        rp.step([("big", token_ids(cfg, 129, 42), [128])], end=["big"])     # above 128 tokens: the norm kernels run
+        assert len(calls) == 2 * cfg["num_hidden_layers"] + 1
+    finally:
+        ops.add_rmsnorm = keep
+    rp = Replayer(runner, cache)
+    todo, steps = mixed_trace(cfg, seed=12)
+    for entries, end in steps:
+        rp.step(entries, end)
+    for rid, ids, _ in todo:
+        compare(rp.logits_of(rid, range(len(ids))), plain.forward(weights, cfg, ids), "bfloat16", f"{name} fused mixed {rid}")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(tmp_path, dtype):
     """bin/trace_run as a user calls it: JSON lines in, <step>.f32 files and 'done' lines out."""

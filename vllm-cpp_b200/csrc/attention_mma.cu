@@ -162,9 +162,13 @@ __global__ void __launch_bounds__(BLOCK_THREADS)
 attention_decode_kernel(MmaAttnArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     constexpr int TILE_BYTES = BN * D * 2;
-    pdl_start();
+    // The step's index arrays were copied in before its first kernel, and every cache row below the
+    // request's newest position was written by an earlier step: both are read before
+    // griddepcontrol.wait, while the kernel that rotates and stores this step's row still runs.
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool producer = warp == 4;
+    bool waited = false;                                 // producer: griddepcontrol.wait has been executed
     const int split = blockIdx.x, nsplit = gridDim.x, g = blockIdx.y, li = blockIdx.z;
     const int r = a.req_list ? a.req_list[li] : li;
     const int G = a.nh / a.nkv;
@@ -196,15 +200,18 @@ attention_decode_kernel(MmaAttnArgs a) {
 
     for (int mt = 0; mt * 16 < G; ++mt) {
         __syncthreads();                                 // barriers initialised; last round's merge has been read
-        // Q rows of this group: row i -> head g*G + mt*16 + i
-        for (int idx = threadIdx.x; idx < 16 * (D / 8); idx += BLOCK_THREADS) {
-            const int row = idx / (D / 8), c = idx % (D / 8);
-            const int hg = mt * 16 + row;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (hg < G) v = *reinterpret_cast<const uint4*>(a.q + ((size_t)t * a.nh + g * G + hg) * D + c * 8);
-            *reinterpret_cast<uint4*>(q_ptr + swz<D>(row, c)) = v;
+        if (!producer) {
+            // Q rows of this group: row i -> head g*G + mt*16 + i (written by the previous kernel)
+            pdl_wait();
+            for (int idx = threadIdx.x; idx < 16 * (D / 8); idx += NTHREADS) {
+                const int row = idx / (D / 8), c = idx % (D / 8);
+                const int hg = mt * 16 + row;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (hg < G) v = *reinterpret_cast<const uint4*>(a.q + ((size_t)t * a.nh + g * G + hg) * D + c * 8);
+                *reinterpret_cast<uint4*>(q_ptr + swz<D>(row, c)) = v;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");   // the four consumer warps only
         }
-        __syncthreads();
         float o[D / 8][4];
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
@@ -213,6 +220,7 @@ attention_decode_kernel(MmaAttnArgs a) {
         if (producer) {
             for (int tile = my0; tile < my1; ++tile, ++it) {
                 const int st = it % STAGES;
+                if (!waited && (tile + 1) * BN > pos) { pdl_wait(); waited = true; }   // the tile with this step's row
                 if (!cx_mbar_wait(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) gave_up = true;
                 if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, 2 * TILE_BYTES);
                 __syncwarp();
@@ -265,6 +273,7 @@ attention_decode_kernel(MmaAttnArgs a) {
                 if (lane == 0) cx_mbar_arrive(empty0 + 8 * st);      // this warp is done with the stage
             }
         }
+        if (producer && !waited) { pdl_wait(); waited = true; }   // nothing is written before the previous kernel is done
         __syncthreads();                                 // every copy has landed and been read: reuse the tiles
         if (!producer) {
             l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);

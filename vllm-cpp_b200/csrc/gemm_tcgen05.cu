@@ -34,6 +34,15 @@
 // Every wait on an mbarrier is bounded; a wait that runs out records where in *status,
 // the CTA stops issuing work, frees its tensor memory and returns.
 //
+// Fused RMSNorm (decode).  norm(x) W^T = rsqrt(mean(x^2) + eps) * ((x * gain) W^T): the per-token factor
+// can be applied after the product.  So the product that ends a residual branch (attention's output
+// projection, the feed-forward's down projection) can, in its epilogue, add its tile into the float
+// residual stream, store bfloat16(residual * gain of the next norm) as the next product's input and
+// leave the sums of squares of the new residual, one partial per epilogue warp and token; and the
+// next product sums those partials and multiplies its accumulators by the factor before storing.
+// No norm kernel runs between the two.  The partials are summed in a fixed order: results do not
+// depend on the order in which CTAs finish.
+//
 // Replaces cublasGemmEx of the reference (src/layers/linear.cpp:70-77).
 #include "common.cuh"
 
@@ -56,6 +65,14 @@ struct GemmArgs {
     const uint8_t* p_tiled;      // P as 16 KB tile images [tiles_p][k_slabs], or null: P comes through map_p
     int ldc, out_f32, swapped, rows_p, rows_q;
     int k_slabs, tiles_p, units_per_cta, total_units;
+    // Fused norm, swapped products with one tile of tokens only (see the epilogue):
+    const float* scale_sumsq;    // [scale_parts][scale_ld]: partial sums of squares per token, or null
+    int scale_parts, scale_ld;
+    float scale_inv_width, scale_eps;
+    float* residual;             // [tokens][ldr] float: the product is added into it, or null
+    const float* gain;           // [rows_p]: out = bfloat16(residual * gain)
+    float* sumsq_out;            // [tiles_p * 4][sumsq_ld]: sums of squares of the new residual, per epilogue warp
+    int ldr, sumsq_ld;
 };
 
 // The segments of one CTA's run of (tile, slab) units.
@@ -268,15 +285,79 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         Segments seg(a, cta);
         int tile, s0, s1, n = 0;
         pdl_wait();                                 // nothing is written before the previous kernel is done
+        float* rstd_s = reinterpret_cast<float*>(const_cast<int*>(flags + 2));      // [BN]
+        if (a.scale_sumsq) {
+            // the factor of every token: rsqrt(sum of the partials / width + eps); a warp per token,
+            // a lane per partial, summed in a fixed order
+            for (int j = lg; j < a.rows_q && j < BN; j += 4) {
+                float sum = 0.0f;
+                for (int part = lane; part < a.scale_parts; part += 32) sum += __ldcg(a.scale_sumsq + (size_t)part * a.scale_ld + j);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                if (lane == 0) rstd_s[j] = rsqrtf(sum * a.scale_inv_width + a.scale_eps);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        // Stores eight or sixteen finished columns c .. c + NE of row r (element (i, q0 + c + e)).
+        constexpr int PRE = BN <= 32 ? BN : 1;
+        auto emit = [&](const auto& v, int c, int i, int q0, int tile_p, const float* pre) {
+            constexpr int NE = (int)(sizeof(v) / sizeof(float));
+            const bool row_ok = i < a.rows_p;
+            if (a.residual) {                       // swapped, one tile of tokens: j = c + e is the token
+                const float g = row_ok ? a.gain[i] : 0.0f;
+                float x[NE];
+#pragma unroll
+                for (int e = 0; e < NE; ++e) {      // all loads first: the stores below would order them
+                    const int j = q0 + c + e;
+                    if (PRE > 1) x[e] = pre[c + e];
+                    else x[e] = (row_ok && j < a.rows_q) ? __ldcg(a.residual + (size_t)j * a.ldr + i) : 0.0f;
+                }
+#pragma unroll
+                for (int e = 0; e < NE; ++e) {
+                    const int j = q0 + c + e;
+                    if (j >= a.rows_q) break;       // the same for the whole warp
+                    if (row_ok) {
+                        x[e] += a.scale_sumsq ? v[e] * rstd_s[j] : v[e];
+                        a.residual[(size_t)j * a.ldr + i] = x[e];
+                        reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)j * a.ldc + i] = __float2bfloat16_rn(x[e] * g);
+                    }
+                    float sq = x[e] * x[e];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                    if (lane == 0) a.sumsq_out[(size_t)(tile_p * 4 + lg) * a.sumsq_ld + j] = sq;
+                }
+                return;
+            }
+            if (!row_ok) return;
+#pragma unroll
+            for (int e = 0; e < NE; ++e) {
+                const int j = q0 + c + e;
+                if (j >= a.rows_q) break;
+                const size_t idx = a.swapped ? (size_t)j * a.ldc + i : (size_t)i * a.ldc + j;
+                const float x = a.scale_sumsq ? v[e] * rstd_s[j] : v[e];
+                if (a.out_f32) reinterpret_cast<float*>(a.out)[idx] = x;
+                else reinterpret_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16_rn(x);
+            }
+        };
         while (seg.next(tile, s0, s1)) {
             const int buf = n & 1;
+            const int tile_p = tile % a.tiles_p;
+            const int p0 = tile_p * BM, q0 = (tile / a.tiles_p) * BN;
+            const int i = p0 + r;
+            // narrow tiles: the residual values this tile may be added to are fetched while the MMAs run
+            [[maybe_unused]] float res_pre[PRE];
+            if constexpr (PRE > 1) {
+                if (a.residual) {
+#pragma unroll
+                    for (int e = 0; e < PRE; ++e)
+                        res_pre[e] = (i < a.rows_p && q0 + e < a.rows_q) ? __ldcg(a.residual + (size_t)(q0 + e) * a.ldr + i) : 0.0f;
+                }
+            }
             if (flags[0] || !mbar_wait(acc_full0 + 8 * buf, (n >> 1) & 1)) {
                 if (!flags[0]) { flags[0] = 1; atomicCAS(a.status, 0, 3); }
                 break;
             }
             tc_fence_after();
-            const int p0 = (tile % a.tiles_p) * BM, q0 = (tile / a.tiles_p) * BN;
-            const int i = p0 + r;
             const bool whole = (s0 == 0 && s1 == S);
             // a CTA's run starts inside at most one tile and ends inside at most one: two scratch slots
             float* part = whole ? nullptr
@@ -288,15 +369,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 if (part) {
 #pragma unroll
                     for (int e = 0; e < 16; ++e) part[(c + e) * BM + r] = __uint_as_float(v[e]);
-                } else if (i < a.rows_p) {
+                } else {
+                    float f[16];
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const int j = q0 + c + e;
-                        if (j >= a.rows_q) break;
-                        const size_t idx = a.swapped ? (size_t)j * a.ldc + i : (size_t)i * a.ldc + j;
-                        if (a.out_f32) reinterpret_cast<float*>(a.out)[idx] = __uint_as_float(v[e]);
-                        else reinterpret_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16_rn(__uint_as_float(v[e]));
-                    }
+                    for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[e]);
+                    emit(f, c, i, q0, tile_p, res_pre);
                 }
             }
             // the accumulator has been read: hand it back to the MMA warp
@@ -316,27 +393,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             asm volatile("bar.sync 1, 128;" ::: "memory");       // flags[1] is read before the next segment writes it
             if (!last) continue;
             __threadfence();
-            if (i < a.rows_p) {
 #pragma unroll 1
-                for (int c = 0; c < BN; c += 8) {
-                    float acc[8];
+            for (int c = 0; c < BN; c += 8) {
+                if (q0 + c >= a.rows_q) break;
+                float acc[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
-                    for (int sg = 0; sg < nseg; ++sg) {
-                        const int x = first_cta + sg;
-                        const float* src = a.partial + ((size_t)x * 2 + (x * U >= tile * S ? 0 : 1)) * BN * BM + r;
+                for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+                for (int sg = 0; sg < nseg; ++sg) {
+                    const int x = first_cta + sg;
+                    const float* src = a.partial + ((size_t)x * 2 + (x * U >= tile * S ? 0 : 1)) * BN * BM + r;
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) acc[e] += __ldcg(src + (c + e) * BM);
-                    }
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const int j = q0 + c + e;
-                        if (j >= a.rows_q) break;
-                        const size_t idx = a.swapped ? (size_t)j * a.ldc + i : (size_t)i * a.ldc + j;
-                        if (a.out_f32) reinterpret_cast<float*>(a.out)[idx] = acc[e];
-                        else reinterpret_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16_rn(acc[e]);
-                    }
+                    for (int e = 0; e < 8; ++e) acc[e] += __ldcg(src + (c + e) * BM);
                 }
+                emit(acc, c, i, q0, tile_p, res_pre);
             }
             if (threadIdx.x == 64) a.tickets[tile] = 0;       // ready for the next launch
         }
@@ -385,7 +454,7 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int bo
 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int ctas, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * (P_BYTES + BN * BK * 2) + 1024 + 256;
+    constexpr size_t smem = (size_t)STAGES * (P_BYTES + BN * BK * 2) + 1024 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -444,20 +513,34 @@ VCB_EXPORT int vcb_tile_weights(const void* w, int rows, int k, int ld, void* ou
 // out[r, c] (row stride ldc, bfloat16 or float) = sum_k ...
 //   swapped = 0: P = activations [rows_p = tokens], Q = weights [rows_q = features]: out[p, q]
 //   swapped = 1: P = weights [rows_p = features], Q = activations [rows_q = tokens]:  out[q, p]
-// bn: columns of the tensor-core tile (16, 32, 64, 128 or 256; rows_q is cut into tiles of bn).
+// bn: columns of the tensor-core tile (16, 32, 64, 128 or 256: with 128 rows the tensor core takes multiples of 16; rows_q is cut into tiles of bn).
 // max_ctas: persistent CTAs (one per SM).  Scratch: partial holds max_ctas * 2 * bn * 128 floats,
 // tickets one zeroed int per tile (the kernel leaves them zero).
 // p_tiled: P as made by vcb_tile_weights (then p and ldp are not used), or null.
-VCB_EXPORT int vcb_gemm_bf16_tcgen05(const void* p, int rows_p, int ldp, const void* p_tiled, const void* q, int rows_q,
-                                     int ldq, int k, void* out, int ldc, int out_f32, int swapped, int bn,
-                                     int max_ctas, float* partial, int* tickets, int n_tickets, int* status,
-                                     void* stream) {
+//
+// Fused norm (both optional, swapped products with rows_q <= bn only):
+//   scale_sumsq [scale_parts][scale_ld]: row j of the result is multiplied by
+//       rsqrt(sum_part scale_sumsq[part][j] / scale_width + scale_eps);
+//   residual [rows_q][ldr] float, gain [rows_p] float, sumsq_out [4 * ceil(rows_p / 128)][sumsq_ld]:
+//       residual += result; out (bfloat16) = residual * gain; sumsq_out = partial sums over the features
+//       of residual^2 for every token.
+VCB_EXPORT int vcb_gemm_bf16_tcgen05_fused(const void* p, int rows_p, int ldp, const void* p_tiled, const void* q,
+                                           int rows_q, int ldq, int k, void* out, int ldc, int out_f32, int swapped,
+                                           int bn, int max_ctas, float* partial, int* tickets, int n_tickets,
+                                           int* status, const float* scale_sumsq, int scale_parts, int scale_ld,
+                                           int scale_width, float scale_eps, float* residual, int ldr,
+                                           const float* gain, float* sumsq_out, int sumsq_ld, void* stream) {
     if (rows_p <= 0 || rows_q <= 0) return 0;
     if (k <= 0 || max_ctas < 1 || !status || !partial || !tickets) return VCB_ERR_BAD_ARG;
     // TMA needs 16-byte aligned bases and row strides
     if ((k % 8) || (ldq % 8) || (((uintptr_t)q | (uintptr_t)p_tiled) & 15)) return VCB_ERR_UNSUPPORTED;
     if (!p_tiled && ((ldp % 8) || ((uintptr_t)p & 15))) return VCB_ERR_UNSUPPORTED;
     if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return VCB_ERR_BAD_ARG;
+    if (scale_sumsq || residual) {
+        if (!swapped || rows_q > bn || bn > 128) return VCB_ERR_UNSUPPORTED;
+        if (scale_sumsq && (scale_parts < 1 || scale_ld < rows_q || scale_width < 1)) return VCB_ERR_BAD_ARG;
+        if (residual && (!gain || !sumsq_out || out_f32 || ldr < rows_p || sumsq_ld < rows_q)) return VCB_ERR_BAD_ARG;
+    }
     const int k_slabs = (k + BK - 1) / BK;
     const int tiles_p = (rows_p + BM - 1) / BM, tiles_q = (rows_q + bn - 1) / bn;
     const long long total = (long long)tiles_p * tiles_q * k_slabs;
@@ -471,13 +554,25 @@ VCB_EXPORT int vcb_gemm_bf16_tcgen05(const void* p, int rows_p, int ldp, const v
     if (c) return c;
     if (p_tiled) mp = mq;                       // not used by the kernel
     else if ((c = make_map(&mp, p, rows_p, k, ldp, BM))) return c;
-    GemmArgs a{out, partial, tickets, status, (const uint8_t*)p_tiled, ldc, out_f32, swapped, rows_p, rows_q, k_slabs, tiles_p, per, (int)total};
+    GemmArgs a{out, partial, tickets, status, (const uint8_t*)p_tiled, ldc, out_f32, swapped, rows_p, rows_q,
+               k_slabs, tiles_p, per, (int)total,
+               scale_sumsq, scale_parts, scale_ld, scale_sumsq ? 1.0f / (float)scale_width : 0.0f, scale_eps,
+               residual, gain, sumsq_out, ldr, sumsq_ld};
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
-        case 16: return launch<16, 10>(mp, mq, a, ctas, s);
+        case 16: return launch<16, 6>(mp, mq, a, ctas, s);
         case 32: return launch<32, 9>(mp, mq, a, ctas, s);
         case 64: return launch<64, 8>(mp, mq, a, ctas, s);
         case 128: return launch<128, 6>(mp, mq, a, ctas, s);
         default: return launch<256, 4>(mp, mq, a, ctas, s);
     }
+}
+
+VCB_EXPORT int vcb_gemm_bf16_tcgen05(const void* p, int rows_p, int ldp, const void* p_tiled, const void* q, int rows_q,
+                                     int ldq, int k, void* out, int ldc, int out_f32, int swapped, int bn,
+                                     int max_ctas, float* partial, int* tickets, int n_tickets, int* status,
+                                     void* stream) {
+    return vcb_gemm_bf16_tcgen05_fused(p, rows_p, ldp, p_tiled, q, rows_q, ldq, k, out, ldc, out_f32, swapped, bn,
+                                       max_ctas, partial, tickets, n_tickets, status, nullptr, 0, 0, 1, 0.0f,
+                                       nullptr, 0, nullptr, nullptr, 0, stream);
 }

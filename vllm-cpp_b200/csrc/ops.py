@@ -37,6 +37,8 @@ _SIGNATURES = {
     "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
+    "vcb_gemm_bf16_tcgen05_fused": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P,
+                                    _P, _I, _I, _I, _F, _P, _I, _P, _P, _I, _P],
     "vcb_tile_weights": [_P, _I, _I, _I, _P, _P],
     "vcb_repetition_penalty": [_P, _I, _P, _P, _P, _I, _I, _P],
     "vcb_sample": [_P, _I, _I, _P, _P, _P, _I, _P],
@@ -308,33 +310,66 @@ def tcgen05_plan(tokens: int, features: int, k: int):
 GEMM_MAX_TICKETS = 16384
 
 
-_tiled = {}
-
-
 def tile_weights(w: torch.Tensor) -> torch.Tensor:
     """The pre-tiled image of a weight matrix for decode products (see gemm_tcgen05.cu): made once,
-    kept beside the matrix, and used by ``linear`` whenever the weights sit on the 128-row side."""
-    key = (w.data_ptr(), tuple(w.shape), w.stride(0))
-    t = _tiled.get(key)
+    kept on the tensor object itself (so it lives and dies with the matrix), and used by ``linear``
+    whenever the weights sit on the 128-row side.  The matrix must not change afterwards."""
+    t = getattr(w, "_vcb_tiled", None)
     if t is None:
         _need(w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1, "tile_weights: a bfloat16 matrix")
         rows, k = w.shape
         nbytes = -(-rows // 128) * -(-k // 64) * 16384
         t = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
         _check(lib().vcb_tile_weights(w.data_ptr(), rows, k, w.stride(0), t.data_ptr(), _stream()), "tile_weights")
-        _tiled[key] = t
+        w._vcb_tiled = t
     return t
 
 
+def drop_tiled_weights(w: torch.Tensor) -> None:
+    if getattr(w, "_vcb_tiled", None) is not None:
+        w._vcb_tiled = None
+
+
 def tiled_weights_of(w: torch.Tensor) -> Optional[torch.Tensor]:
-    return _tiled.get((w.data_ptr(), tuple(w.shape), w.stride(0)))
+    return getattr(w, "_vcb_tiled", None)
+
+
+class RowScale:
+    """Says that the rows of a product's input still lack the factor of an RMSNorm:
+    row t is to be multiplied by rsqrt(sum(sumsq[:parts, t]) / width + eps).  ``sumsq`` holds
+    partial sums of squares of the un-normalised row, [parts, tokens] float32."""
+    __slots__ = ("sumsq", "parts", "width", "eps")
+
+    def __init__(self, sumsq: torch.Tensor, parts: int, width: int, eps: float):
+        self.sumsq, self.parts, self.width, self.eps = sumsq, parts, width, float(eps)
+
+
+class ResidualNorm:
+    """Asks a product to end a residual branch itself: residual (float32 [tokens, features]) += result;
+    out = bfloat16(residual * gain), the un-normalised input of the norm that follows; sumsq
+    ([sumsq_parts(features), tokens] float32) = partial sums of squares of the new residual rows.
+    ``scale()`` is the RowScale the next product needs."""
+    __slots__ = ("residual", "gain", "sumsq", "eps")
+
+    def __init__(self, residual: torch.Tensor, gain: torch.Tensor, sumsq: torch.Tensor, eps: float):
+        self.residual, self.gain, self.sumsq, self.eps = residual, gain, sumsq, float(eps)
+
+    def scale(self) -> RowScale:
+        return RowScale(self.sumsq, sumsq_parts(self.residual.shape[1]), self.residual.shape[1], self.eps)
+
+
+def sumsq_parts(features: int) -> int:
+    """Partial sums a ResidualNorm product leaves per token: one per epilogue warp of every 128-row tile."""
+    return 4 * (-(-features // 128))
 
 
 def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=None, max_ctas: int = SM_COUNT,
-                      use_tiled: bool = True) -> None:
+                      use_tiled: bool = True, x_scale: Optional[RowScale] = None,
+                      fuse: Optional[ResidualNorm] = None) -> None:
     """out = x @ w^T on tcgen05 tensor cores fed by TMA (see gemm_tcgen05.cu); out bfloat16 or float32.
     When the weights are the 128-row operand and tile_weights(w) has been made, the image is used
-    (``use_tiled`` False forces the tensor-map path)."""
+    (``use_tiled`` False forces the tensor-map path).  ``x_scale`` and ``fuse`` (up to 128 tokens):
+    see RowScale and ResidualNorm."""
     m, k = x.shape
     n = w.shape[0]
     _need(w.shape[1] == k and out.shape == (m, n), "gemm_bf16_tcgen05: shapes do not agree")
@@ -344,17 +379,34 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=
     _need(k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0,
           "gemm_bf16_tcgen05: TMA needs K and the row strides to be multiples of 8 and 16-byte aligned bases")
     swapped, bn = plan or tcgen05_plan(m, n, k)
+    sc = (None, 0, 0, 1, 0.0)
+    if x_scale is not None:
+        _need(swapped and m <= bn <= 128, "gemm_bf16_tcgen05: a row scale needs the few-token form")
+        _need(x_scale.sumsq.dtype == torch.float32 and x_scale.sumsq.dim() == 2 and x_scale.sumsq.stride(1) == 1
+              and x_scale.sumsq.shape[0] >= x_scale.parts and x_scale.sumsq.shape[1] >= m,
+              "gemm_bf16_tcgen05: sums of squares must be float32 [parts, tokens]")
+        sc = (x_scale.sumsq.data_ptr(), x_scale.parts, x_scale.sumsq.stride(0), x_scale.width, x_scale.eps)
+    fu = (None, 0, None, None, 0)
+    if fuse is not None:
+        _need(swapped and m <= bn <= 128 and out.dtype == torch.bfloat16,
+              "gemm_bf16_tcgen05: a fused residual needs the few-token form and a bfloat16 result")
+        r, g, ss = fuse.residual, fuse.gain, fuse.sumsq
+        _need(r.dtype == torch.float32 and r.shape == (m, n) and r.stride(1) == 1 and g.dtype == torch.float32
+              and g.shape == (n,) and g.is_contiguous(), "gemm_bf16_tcgen05: residual float32 [tokens, features], gain float32 [features]")
+        _need(ss.dtype == torch.float32 and ss.dim() == 2 and ss.stride(1) == 1 and ss.shape[0] >= sumsq_parts(n)
+              and ss.shape[1] >= m, "gemm_bf16_tcgen05: sums of squares must be float32 [sumsq_parts(features), tokens]")
+        fu = (r.data_ptr(), r.stride(0), g.data_ptr(), ss.data_ptr(), ss.stride(0))
     partial = scratch("gemm_partial", SM_COUNT * 2 * 256 * 128, out.device)
     tickets = zeroed_ints("gemm_tickets", GEMM_MAX_TICKETS, out.device)
     p, q = (w, x) if swapped else (x, w)
     tiled = tiled_weights_of(w) if (swapped and use_tiled) else None
-    _check(lib().vcb_gemm_bf16_tcgen05(p.data_ptr(), p.shape[0], p.stride(0),
-                                       None if tiled is None else tiled.data_ptr(),
-                                       q.data_ptr(), q.shape[0], q.stride(0), k,
-                                       out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0,
-                                       1 if swapped else 0, bn, min(max_ctas, SM_COUNT), partial.data_ptr(),
-                                       tickets.data_ptr(), GEMM_MAX_TICKETS, status_tensor(out.device).data_ptr(),
-                                       _stream()), "gemm_bf16_tcgen05")
+    _check(lib().vcb_gemm_bf16_tcgen05_fused(p.data_ptr(), p.shape[0], p.stride(0),
+                                             None if tiled is None else tiled.data_ptr(),
+                                             q.data_ptr(), q.shape[0], q.stride(0), k,
+                                             out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0,
+                                             1 if swapped else 0, bn, min(max_ctas, SM_COUNT), partial.data_ptr(),
+                                             tickets.data_ptr(), GEMM_MAX_TICKETS, status_tensor(out.device).data_ptr(),
+                                             *sc, *fu, _stream()), "gemm_bf16_tcgen05")
 
 
 TCGEN05_MAX_TOKENS = 128      # up to here the engine's own tcgen05 product may run; above, the library's
@@ -367,6 +419,16 @@ def set_tcgen05_linear(on: bool) -> None:
     """Allow this library's tcgen05 product for bfloat16 products with few tokens (default), or cuBLAS for all."""
     global _tcgen05_linear
     _tcgen05_linear = bool(on)
+
+
+_linear_tuning = True
+
+
+def set_linear_tuning(on: bool) -> None:
+    """With tuning off nothing is measured at load, so every product with few tokens runs this
+    library's tcgen05 kernel (tests use it to pin the path)."""
+    global _linear_tuning
+    _linear_tuning = bool(on)
 
 
 def token_bucket(m: int) -> int:
@@ -391,48 +453,111 @@ def _library_mm(x, w, out) -> None:
             out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))
 
 
-def tune_linear(weights, out_dtype=torch.bfloat16, reps: int = 6) -> None:
-    """Measure, for one shape of weight matrix and each bucket of token counts, whether the engine's
-    tcgen05 product or the library's is faster on this device, and remember the choice.
-    ``weights``: matrices of the same shape (the same projection of several layers), used in
-    rotation so that the L2 cache cannot serve them."""
+TOKEN_BUCKETS = ((16, 8), (32, 32), (64, 64), (128, 128))      # (bucket, token count it is measured at)
+
+
+def time_in_graph(fn, reps: int = 8) -> float:
+    """Microseconds per call of ``fn(i)``: ``reps`` calls are captured into a CUDA graph and the graph
+    is replayed, so that the host's launch cost stays out of the figure."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(2):
+            fn(i)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(reps):
+                fn(i)
+        graph.replay()
+        side.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        graph.replay()
+        e1.record()
+        side.synchronize()
+    torch.cuda.current_stream().wait_stream(side)
+    return e0.elapsed_time(e1) * 1e3 / (2 * reps)
+
+
+def measure_linear(weights, out_dtype=torch.bfloat16):
+    """{bucket: (microseconds of this library's tcgen05 product, of the library's)} for one shape of
+    weight matrix.  ``weights``: matrices of the same shape (the same projection of several layers),
+    used in rotation so that the L2 cache cannot serve them; their tiled images must exist.
+    Buckets the tcgen05 kernel cannot take are left out."""
     n, k = weights[0].shape
     dev_ = weights[0].device
-    for bucket, m in ((16, 8), (32, 32), (64, 64), (128, 128)):
+    out_times = {}
+    for bucket, m in TOKEN_BUCKETS:
         x = torch.randn(m, k, device=dev_).to(torch.bfloat16)
         out = torch.empty(m, n, dtype=out_dtype, device=dev_)
         if not _tcgen05_ok(x, weights[0], out):
             continue
-        times = []
-        for fn in (lambda w: gemm_bf16_tcgen05(x, w, out), lambda w: _library_mm(x, w, out)):
-            for i in range(2):
-                fn(weights[i % len(weights)])
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for i in range(reps):
-                fn(weights[i % len(weights)])
-            e1.record()
-            torch.cuda.synchronize()
-            times.append(e0.elapsed_time(e1))
-        _linear_choice[(n, k, bucket, out_dtype)] = times[0] <= times[1]
+        out_times[bucket] = (time_in_graph(lambda i: gemm_bf16_tcgen05(x, weights[i % len(weights)], out)),
+                             time_in_graph(lambda i: _library_mm(x, weights[i % len(weights)], out)))
     check_status()
+    return out_times
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+def measure_norm(hidden: int, dtype, device) -> dict:
+    """{bucket: microseconds of one residual-add + RMSNorm kernel} at the buckets' token counts."""
+    times = {}
+    gain = torch.ones(hidden, device=device)
+    for bucket, m in TOKEN_BUCKETS:
+        res = torch.zeros(m, hidden, device=device)
+        delta = torch.zeros(m, hidden, dtype=dtype, device=device)
+        out = torch.empty(m, hidden, dtype=dtype, device=device)
+        times[bucket] = time_in_graph(lambda i: add_rmsnorm(res, delta, gain, out, 1e-6))
+    return times
+
+
+def choose_linear(features: int, k: int, bucket: int, out_dtype, tcgen05: bool) -> None:
+    """Record which product ``linear`` runs for this shape and bucket of token counts."""
+    _linear_choice[(features, k, bucket, out_dtype)] = bool(tcgen05)
+
+
+def linear_tuning() -> bool:
+    return _linear_tuning
+
+
+_norm_fusion = True
+
+
+def set_norm_fusion(on: bool) -> None:
+    """Allow products to take over the norms around them (default), or run every norm as a kernel."""
+    global _norm_fusion
+    _norm_fusion = bool(on)
+
+
+def linear_fuses_norm(tokens: int, w: torch.Tensor, out_dtype=torch.bfloat16) -> bool:
+    """True if ``linear`` will run this library's tcgen05 product for ``tokens`` rows against ``w``
+    (taken contiguous and 16-byte aligned, as workspace buffers and loaded weights are): only then can
+    it apply a RowScale or a ResidualNorm."""
+    return (_norm_fusion and _tcgen05_linear and w.dtype == torch.bfloat16 and 0 < tokens <= TCGEN05_MAX_TOKENS
+            and w.shape[1] % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
+            and -(-w.shape[0] // 128) <= GEMM_MAX_TICKETS
+            and _linear_choice.get((w.shape[0], w.shape[1], token_bucket(tokens), out_dtype), True))
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_scale: Optional[RowScale] = None,
+           fuse: Optional[ResidualNorm] = None) -> None:
     """out = x @ w^T.  float32: the engine's own FMA kernel.  bfloat16 with up to TCGEN05_MAX_TOKENS
     rows (decode steps, short portions): the engine's tcgen05 + TMA kernel with the weights on the
-    128-row side of the tile, where ``tune_linear`` measured it faster than the library (and always
+    128-row side of the tile, where the measurement at load found it faster than the library (and always
     when nothing was measured); otherwise the library product (cuBLAS through torch.mm, float
-    accumulation).  out is bfloat16 or float32."""
+    accumulation).  out is bfloat16 or float32.  ``x_scale`` / ``fuse`` may be given only where
+    ``linear_fuses_norm`` said yes."""
     if x.dtype == torch.float32:
+        _need(x_scale is None and fuse is None, "linear: the float32 product fuses no norm")
         gemm_f32(x, w, out)
         return
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear: operands must both be bfloat16")
     if _tcgen05_linear and _tcgen05_ok(x, w, out) and \
             _linear_choice.get((w.shape[0], w.shape[1], token_bucket(x.shape[0]), out.dtype), True):
-        gemm_bf16_tcgen05(x, w, out)
+        gemm_bf16_tcgen05(x, w, out, x_scale=x_scale, fuse=fuse)
         return
+    _need(x_scale is None and fuse is None, "linear: the library product fuses no norm; ask linear_fuses_norm first")
     _library_mm(x, w, out)
 
 

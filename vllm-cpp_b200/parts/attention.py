@@ -80,11 +80,14 @@ class PagedAttention(Mixer):
         return PagedKVSpec(self.nkv, self.d, self.window)
 
     # -- run
-    def forward(self, x, out, step, cache, writes_cache, ws):
+    def fuses_norm(self, n_tokens):
+        return ops.linear_fuses_norm(n_tokens, self.w_qkv) and ops.linear_fuses_norm(n_tokens, self.w_o)
+
+    def forward(self, x, out, step, cache, writes_cache, ws, x_scale=None, fuse=None):
         n = x.shape[0]
         mark = ws.mark()
         qkv = ws.take((n, (self.nh + 2 * self.nkv) * self.d), self.dtype)
-        ops.linear(x, self.w_qkv, qkv)
+        ops.linear(x, self.w_qkv, qkv, x_scale=x_scale)
         q = ws.take((n, self.nh * self.d), self.dtype)
         block_table = step.block_tables[cache.group]
         fused = self.position.fused()
@@ -105,7 +108,7 @@ class PagedAttention(Mixer):
                              page_size=cache.page_size, write_kv=writes_cache)
         attn = ws.take((n, self.nh * self.d), self.dtype)
         self.attend(q, attn, step, cache, block_table)
-        ops.linear(attn, self.w_o, out)
+        ops.linear(attn, self.w_o, out, fuse=fuse)
         ws.release(mark)
 
     # -- work lists and kernel choice

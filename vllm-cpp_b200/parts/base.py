@@ -119,7 +119,7 @@ class Workspace:
         numel = 1
         for s in shape:
             numel *= int(s)
-        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        nbytes = numel * dtype.itemsize
         start = (self.offset + 255) // 256 * 256
         end = start + nbytes
         if end > self.buf.numel():
@@ -167,6 +167,12 @@ class Norm(Part):
         """residual += delta (float32, in place, unless rows are gathered); out = norm(residual)."""
         raise NotImplementedError
 
+    def split(self):
+        """(gain, eps) if the norm is y = x * rsqrt(mean(x^2) + eps) * gain with a float32 gain vector:
+        then the product before it may apply the gain and the product after it the per-row factor
+        (see ops.ResidualNorm, ops.RowScale), and no norm kernel runs.  None: the norm runs by itself."""
+        return None
+
 
 class Mixer(Part):
     """Mixes information between the tokens of a request (attention here)."""
@@ -175,6 +181,12 @@ class Mixer(Part):
         """PagedKVSpec, StateSpec or None."""
         return None
 
+    def fuses_norm(self, n_tokens: int) -> bool:
+        """True if, for a step of ``n_tokens``, ``forward`` accepts ``x_scale`` (an ops.RowScale its first
+        product applies to x) and ``fuse`` (an ops.ResidualNorm its last product performs instead of
+        writing ``out`` plainly).  The block passes those keywords only after a yes."""
+        return False
+
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext, cache, writes_cache: bool,
                 ws: Workspace) -> None:
         """x, out: [n_tokens, hidden] in the compute type."""
@@ -182,6 +194,10 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    def fuses_norm(self, n_tokens: int) -> bool:
+        """As Mixer.fuses_norm."""
+        return False
+
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext, ws: Workspace) -> None:
         raise NotImplementedError
 
@@ -193,10 +209,21 @@ class Block:
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
 
-    def forward(self, residual: torch.Tensor, delta: torch.Tensor, has_delta: bool, step: StepContext,
-                cache, writes_cache: bool, ws: Workspace) -> bool:
-        """Runs the layer.  ``delta`` holds a pending addition to ``residual`` when
-        ``has_delta``; on return it holds this layer's pending addition.  Returns True."""
+    def accepts_prenormed(self, n_tokens: int):
+        """(gain, eps) of the norm this block starts with if, for a step of ``n_tokens``, the block can
+        take its input as ``delta`` = residual * gain with the rows' factor still to be applied
+        (``pending`` an ops.RowScale); None if it wants the residual stream as it is."""
+        return None
+
+    def forward(self, residual: torch.Tensor, delta: torch.Tensor, pending, step: StepContext,
+                cache, writes_cache: bool, ws: Workspace, next_block: "Optional[Block]" = None,
+                carry: Optional[torch.Tensor] = None):
+        """Runs the layer.  ``pending`` says what ``delta`` holds: False nothing, True an addition to
+        ``residual`` that has not been made yet, an ops.RowScale the pre-normed input (see
+        accepts_prenormed; only given to a block that accepts it).  ``next_block`` runs after this
+        one (None: the model's final norm does); ``carry`` is float32 scratch
+        [2, ops.sumsq_parts(hidden), n_tokens] that lives for the whole step.  Returns the new
+        ``pending``."""
         raise NotImplementedError
 
 

@@ -96,25 +96,55 @@ class DecoderModel:
                                      for local in self.final_norm.param_specs()})
 
     def prepare_products(self, tune: bool = True) -> None:
-        """bfloat16 only: measure for every shape of weight matrix whether the engine's tcgen05
-        product or the library's is faster for few tokens, and make the pre-tiled images of the
-        matrices for which the engine's kernel was chosen (see csrc/gemm_tcgen05.cu)."""
+        """bfloat16 only: decide, for every shape of weight matrix and bucket of token counts, whether the
+        engine's tcgen05 product or the library's runs when a step has few tokens, and make the pre-tiled
+        images of the matrices the engine's kernel will read (see csrc/gemm_tcgen05.cu).  Both are
+        measured here, on this device, in CUDA graphs.  A layer whose products all run on the engine's
+        kernel needs no norm kernels (parts/block.py), so the layers' products are chosen together:
+        all on the engine's kernel if that, without the norm kernels, is faster than each on its own
+        best; the output product is chosen by itself."""
         if self.dtype != torch.bfloat16:
             return
-        by_shape = {}
+        layer_shapes, fusable_norms = {}, 0
         for blk in self.blocks:
             for part in (blk.mixer, blk.feed_forward):
                 for v in vars(part).values():
                     if isinstance(v, torch.Tensor) and v.dim() == 2 and v.dtype == torch.bfloat16:
-                        by_shape.setdefault((tuple(v.shape), torch.bfloat16), []).append(v)
-        by_shape.setdefault((tuple(self.lm_head.shape), torch.float32), []).append(self.lm_head)
-        for (shape, out_dtype), mats in by_shape.items():
-            if tune:
-                ops.tune_linear(mats[:8], out_dtype)
-            chosen = any(ops._linear_choice.get((shape[0], shape[1], b, out_dtype), True) for b in (16, 32, 64, 128))
-            if chosen and shape[1] % 8 == 0:
-                for m in mats:
+                        layer_shapes.setdefault(tuple(v.shape), []).append(v)
+        if self.blocks:
+            first = self.blocks[0]
+            fusable_norms = sum(1 for nrm in (first.mixer_norm, first.feed_forward_norm) if nrm.split() is not None)
+        tunable = {shape: mats for shape, mats in layer_shapes.items() if shape[1] % 8 == 0}
+        head_ok = self.lm_head.shape[1] % 8 == 0
+        measure = tune and ops.linear_tuning()
+        for mats in tunable.values():
+            for m in mats[:8]:                    # the kernel is measured as it will run: on the images
+                ops.tile_weights(m)
+        if head_ok:
+            ops.tile_weights(self.lm_head)
+        if measure:
+            times = {shape: ops.measure_linear(mats[:8]) for shape, mats in tunable.items()}
+            per_layer = {shape: len(mats) / max(1, len(self.blocks)) for shape, mats in tunable.items()}
+            norm_us = ops.measure_norm(self.hidden, self.dtype, self.device)
+            for bucket, _ in ops.TOKEN_BUCKETS:
+                have = [shape for shape in tunable if bucket in times[shape]]
+                ours = sum(times[shape][bucket][0] * per_layer[shape] for shape in have)
+                best = sum(min(times[shape][bucket]) * per_layer[shape] for shape in have)
+                together = len(have) == len(layer_shapes) and ours <= best + fusable_norms * norm_us[bucket]
+                for shape in have:
+                    t_ours, t_lib = times[shape][bucket]
+                    ops.choose_linear(shape[0], shape[1], bucket, torch.bfloat16, together or t_ours <= t_lib)
+            if head_ok:
+                for bucket, (t_ours, t_lib) in ops.measure_linear([self.lm_head], torch.float32).items():
+                    ops.choose_linear(self.lm_head.shape[0], self.lm_head.shape[1], bucket, torch.float32, t_ours <= t_lib)
+        for shape, mats in list(tunable.items()) + ([(tuple(self.lm_head.shape), [self.lm_head])] if head_ok else []):
+            out_dtype = torch.float32 if mats[0] is self.lm_head else torch.bfloat16
+            chosen = any(ops._linear_choice.get((shape[0], shape[1], b, out_dtype), True) for b, _ in ops.TOKEN_BUCKETS)
+            for m in mats:
+                if chosen:
                     ops.tile_weights(m)
+                else:
+                    ops.drop_tiled_weights(m)
 
     def weight_bytes(self) -> int:
         """Bytes of the matrices a decode step reads once (embedding rows excluded unless tied)."""
@@ -134,11 +164,15 @@ class DecoderModel:
         n = step.n_tokens
         residual = ws.take((n, self.hidden), torch.float32)
         delta = ws.take((n, self.hidden), self.dtype)
+        carry = ws.take((2, ops.sumsq_parts(self.hidden), n), torch.float32)
         ops.embedding(self.embed, step.token_ids, residual)
-        has_delta = False
-        for call in self.spec.run_order:
-            has_delta = self.blocks[call.layer].forward(residual, delta, has_delta, step, caches[call.cache],
-                                                        call.writes_cache, ws)
+        pending = False                 # what delta holds: see Block.forward
+        order = self.spec.run_order
+        for i, call in enumerate(order):
+            following = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
+            pending = self.blocks[call.layer].forward(residual, delta, pending, step, caches[call.cache],
+                                                      call.writes_cache, ws, next_block=following, carry=carry)
+        has_delta = bool(pending)
         m = step.n_logit_rows
         out = logits[:m]
         if m:

@@ -28,5 +28,8 @@ class RMSNorm(Norm):
     def load_params(self, tensors):
         self.weight = tensors["weight"]
 
+    def split(self):
+        return (self.weight, self.eps) if self.weight is not None and self.weight.dtype == torch.float32 else None
+
     def forward(self, residual, delta, out, row_index=None):
         ops.add_rmsnorm(residual, delta, self.weight, out, self.eps, row_index)
