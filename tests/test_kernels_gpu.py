@@ -97,7 +97,8 @@ def paged_layout(rng, n_reqs, max_len, page, n_pages):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nh,nkv,d,rot,pairing", [(4, 2, 16, 16, 0), (3, 1, 32, 32, 0), (7, 7, 48, 24, 0),
-                                                   (2, 1, 128, 128, 0), (5, 5, 80, 80, 1), (6, 3, 64, 0, 0)])
+                                                   (2, 1, 128, 128, 0), (5, 5, 80, 80, 1), (6, 3, 64, 0, 0),
+                                                   (28, 4, 128, 128, 0), (33, 3, 64, 64, 0), (9, 3, 16, 16, 0)])
 def test_rope_cache_write(ops, dtype, nh, nkv, d, rot, pairing):
     rng = np.random.default_rng(3)
     page, n_pages, n_reqs = 16, 12, 2

@@ -311,6 +311,65 @@ __global__ void rope_cache_kernel(RopeCacheArgs a, int heads_per_block) {
     dst[kv_row_pos(ib, slot, a.d, (int)sizeof(T))] = from_f32<T>(xb);
 }
 
+// The same for the common case (bfloat16, rotate-half pairing over the whole head, head size a
+// multiple of 16): 16-byte accesses, the angles' sines and cosines computed once per token and shared
+// by all heads.  One CTA per (token, group of heads); a thread owns chunk c of the first half of a
+// head and its partner chunk in the second half.
+__global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block) {
+    extern __shared__ float2 trig[];                    // [d / 2] (cos, sin)
+    pdl_start();
+    const int t = blockIdx.x;
+    const int nheads = a.nh + 2 * a.nkv;
+    const int half = a.d / 2, chunks = half / 8;
+    const int pos = a.positions[t];
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos / a.denom[j], &sn, &cs);
+        trig[j] = make_float2(cs, sn);
+    }
+    __syncthreads();
+    const int h = blockIdx.y * heads_per_block + threadIdx.x / chunks;
+    const int c = threadIdx.x % chunks;
+    if (h >= nheads || threadIdx.x >= heads_per_block * chunks) return;
+    const __nv_bfloat16* src = (const __nv_bfloat16*)a.qkv + ((size_t)t * nheads + h) * a.d;
+    const uint4 va = *reinterpret_cast<const uint4*>(src + c * 8);
+    const uint4 vb = *reinterpret_cast<const uint4*>(src + half + c * 8);
+    const __nv_bfloat16* pa = reinterpret_cast<const __nv_bfloat16*>(&va);
+    const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&vb);
+    __align__(16) __nv_bfloat16 oa[8], ob[8];
+    const bool rotate = h < a.nh + a.nkv;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        float xa = __bfloat162float(pa[e]), xb = __bfloat162float(pb[e]);
+        if (a.bias) { xa += a.bias[h * a.d + c * 8 + e]; xb += a.bias[h * a.d + half + c * 8 + e]; }
+        if (rotate) {
+            const float2 cs = trig[c * 8 + e];
+            const float ra = xa * cs.x - xb * cs.y;
+            const float rb = xa * cs.y + xb * cs.x;
+            xa = ra; xb = rb;
+        }
+        oa[e] = __float2bfloat16_rn(xa);
+        ob[e] = __float2bfloat16_rn(xb);
+    }
+    if (h < a.nh) {
+        __nv_bfloat16* dst = (__nv_bfloat16*)a.q_out + ((size_t)t * a.nh + h) * a.d;
+        *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(oa);
+        *reinterpret_cast<uint4*>(dst + half + c * 8) = *reinterpret_cast<const uint4*>(ob);
+        return;
+    }
+    if (!a.write_kv) return;
+    const int r = a.req_of_token[t];
+    const int pg = a.block_table[(size_t)r * a.bt_stride + pos / a.page];
+    const int slot = pos % a.page;
+    __nv_bfloat16* base = (__nv_bfloat16*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
+    const int kvh = h < a.nh + a.nkv ? h - a.nh : h - a.nh - a.nkv;
+    const size_t which = h < a.nh + a.nkv ? 0 : (size_t)a.nkv * a.page * a.d;
+    __nv_bfloat16* dst = base + which + ((size_t)kvh * a.page + slot) * a.d;
+    // whole 16-byte chunks move together in the rows' layout (kv_row_pos)
+    *reinterpret_cast<uint4*>(dst + kv_row_pos(c * 8, slot, a.d, 2)) = *reinterpret_cast<const uint4*>(oa);
+    *reinterpret_cast<uint4*>(dst + kv_row_pos(half + c * 8, slot, a.d, 2)) = *reinterpret_cast<const uint4*>(ob);
+}
+
 VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const int* positions,
                                     const int* req_of_token, const int* block_table, int bt_stride,
                                     const float* denom, void* q_out, void* cache, int n_tokens,
@@ -322,12 +381,21 @@ VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const in
     RopeCacheArgs a{qkv, bias, positions, req_of_token, block_table, denom, q_out, cache,
                     bt_stride, nh, nkv, d, rot, pairing, page, write_kv};
     const int half = d / 2, nheads = nh + 2 * nkv;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_BF16 && pairing == 0 && rot == d && d % 16 == 0 && denom &&
+        !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache) & 15)) {
+        const int chunks = half / 8;
+        const int groups = (nheads * chunks + 255) / 256;
+        const int per = (nheads + groups - 1) / groups;               // heads per CTA, at most 256 threads
+        const int threads = ((per * chunks + 31) / 32) * 32;
+        vcb_launch(rope_cache_vec_kernel, dim3(n_tokens, (nheads + per - 1) / per), threads, (size_t)half * sizeof(float2), s, a, per);
+        return vcb_last_error();
+    }
     int hpb = 128 / half;                      // heads per CTA: about 128 threads
     if (hpb < 1) hpb = 1;
     if (hpb > nheads) hpb = nheads;
     const int threads = ((hpb * half + 31) / 32) * 32;
     dim3 grid(n_tokens, (nheads + hpb - 1) / hpb);
-    cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VCB_F32) vcb_launch(rope_cache_kernel<float>, grid, threads, 0, s, a, hpb);
     else if (dtype == VCB_BF16) vcb_launch(rope_cache_kernel<__nv_bfloat16>, grid, threads, 0, s, a, hpb);
     else return VCB_ERR_BAD_ARG;
