@@ -454,6 +454,41 @@ def test_gemm_bf16_tcgen05_fused_norm(ops, m, n, k, ctas):
         assert np.abs(got_y - want_y).max() <= (4e-7 * np.sqrt(n) + 2e-6) * np.abs(want_y).max()
 
 
+@pytest.mark.parametrize("m,inter,k,ctas", [(8, 18944 // 4, 512, 148), (1, 64, 64, 148), (5, 200, 200, 3), (33, 176, 1024, 7),
+                                            (16, 1000, 576, 148), (100, 224, 96, 11), (128, 128, 64, 148)])
+@pytest.mark.parametrize("scaled", [False, True])
+def test_gemm_bf16_tcgen05_gated(ops, m, inter, k, ctas, scaled):
+    """The gate-and-up product with the activation in its epilogue against silu(x g^T) * (x u^T) done
+    plainly; feature counts that are no multiple of 64, tiles split between CTAs, with and without
+    the rows' factor of a norm."""
+    rng = np.random.default_rng(9)
+    x = as_stored(rng.standard_normal((m, k)), "bfloat16")
+    w = as_stored(rng.standard_normal((2 * inter, k)) * 0.1, "bfloat16")
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    ops.tile_weights(wd, inter)
+    factor = np.ones((m, 1))
+    scale = None
+    if scaled:
+        parts = 5
+        ss = rng.random((parts, m)).astype(np.float32) * 40
+        scale = ops.RowScale(dev(ss), parts, 96, 1e-5)
+        factor = 1.0 / np.sqrt(ss.astype(np.float64).sum(axis=0) / 96 + 1e-5)[:, None]
+    gu = (x.astype(np.float64) @ w.astype(np.float64).T) * factor
+    g, u = gu[:, :inter], gu[:, inter:]
+    want = g / (1 + np.exp(-g)) * u
+    full = torch.full((m, inter + 8), float("nan"), dtype=torch.bfloat16, device="cuda")
+    out = full[:, :inter]
+    for _ in range(2):
+        ops.gemm_bf16_tcgen05(xd, wd, out, None, ctas, x_scale=scale, gated=True)
+    torch.cuda.synchronize()
+    ops.check_status()
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    # bfloat16 output; float accumulation errors of gate and up multiply each other's values
+    assert np.abs(got - want).max() <= (4e-3 + 4e-6 * np.sqrt(k)) * np.abs(want).max()
+    assert torch.isnan(full[:, inter:]).all()                   # nothing written beyond the gate features
+
+
 def test_device_sampler_on_the_reference_samplers_golden_rows(ops):
     """The device sampler on the rows for which tests/golden holds the reference sampler's answers."""
     import json

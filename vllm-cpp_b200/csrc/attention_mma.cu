@@ -87,23 +87,57 @@ template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
 }
 
-// The producer warp's share of one tile of BN keys starting at key kb of kv head g: lanes 0-7
+// The request's block table as the producer warp sees it: a window of 64 consecutive entries in
+// two registers per lane, refilled 32 entries at a time, so that no tile waits for a load of its
+// page numbers (a dependent global load per tile is what would otherwise bound a CTA's rate).
+// Entries for pages wholly outside [lo, hi) may have been given back (window) or not exist yet:
+// the page of the last visible key, which always exists, is used in their place.
+struct PageWindow {
+    const int* bt;
+    int base, n_pages, last_pg, cur, nxt, lane;
+    __device__ __forceinline__ int fetch(int i) const { return i < n_pages ? __ldg(bt + i) : last_pg; }
+    __device__ __forceinline__ void init(const int* bt_, int first_page, int hi, int page, int lane_) {
+        bt = bt_; lane = lane_;
+        n_pages = (hi - 1) / page + 1;
+        last_pg = __ldg(bt + (hi - 1) / page);
+        base = first_page;
+        cur = fetch(base + lane);
+        nxt = fetch(base + 32 + lane);
+    }
+    // entry of logical page lp >= base; the same call sequence in all 32 lanes
+    __device__ __forceinline__ int get(int lp) {
+        while (__any_sync(0xffffffffu, lp >= base + 64)) {   // not reached by tiles of at most 32 pages' span in order
+            cur = nxt; base += 32; nxt = fetch(base + 32 + lane);
+        }
+        const int i = lp - base;
+        const int a = __shfl_sync(0xffffffffu, cur, i & 31), b = __shfl_sync(0xffffffffu, nxt, i & 31);
+        return i < 32 ? a : b;
+    }
+    // move on once every page below lp is done with
+    __device__ __forceinline__ void advance(int lp) {
+        if (lp >= base + 32) { cur = nxt; base += 32; nxt = fetch(base + 32 + lane); }
+    }
+};
+
+// The producer warp's share of one tile of TK keys starting at key kb of kv head g: lanes 0-7
 // each copy one page piece of K, lanes 8-15 the same pieces of V (a tile spans at most
-// BN / 16 + 1 pages).  Lane 0 has armed the stage's barrier with the tile's byte count.
+// TK / 16 + 1 pages).  Lane 0 has armed the stage's barrier with the tile's byte count.
 template <int D, int TK>
 __device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t bar, int kb, int lo, int hi,
-                                             const int* __restrict__ bt, const __nv_bfloat16* __restrict__ cache,
+                                             PageWindow& pw, const __nv_bfloat16* __restrict__ cache,
                                              int g, int page, int nkv, int lane) {
-    if (lane >= 16) return;
     const int piece = lane & 7;
     const int first_page = kb / page;
+    pw.advance(first_page);
     const int start = piece == 0 ? kb : (first_page + piece) * page;       // first key of the piece
-    if (start >= kb + TK) return;
-    const int end = min((start / page + 1) * page, kb + TK);
+    const bool active = lane < 16 && start < kb + TK;
     // the page itself if any of it is visible, else the page of the last visible key
-    const int lp = start / page;
+    const int lp = active ? start / page : first_page;
     const bool visible = lp * page < hi && (lp + 1) * page > lo;
-    const int pg = bt[visible ? lp : (hi - 1) / page];
+    const int got = pw.get(visible ? lp : first_page);                     // all lanes take part in the shuffles
+    if (!active) return;
+    const int pg = visible ? got : pw.last_pg;
+    const int end = min((start / page + 1) * page, kb + TK);
     const __nv_bfloat16* src = cache + (size_t)pg * ((size_t)2 * nkv * page * D) + ((size_t)g * page + (start % page)) * D;
     const uint32_t off = (uint32_t)(start - kb) * D * 2, bytes = (uint32_t)(end - start) * D * 2;
     if (lane < 8) cx_bulk_load(sk + off, src, bytes, bar);
@@ -218,6 +252,8 @@ attention_decode_kernel(MmaAttnArgs a) {
         float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;   // rows lane/4 and lane/4 + 8
 
         if (producer) {
+            PageWindow pw;
+            pw.init(bt, my0 * BN / a.page, hi, a.page, lane);
             for (int tile = my0; tile < my1; ++tile, ++it) {
                 const int st = it % STAGES;
                 if (!waited && (tile + 1) * BN > pos) { pdl_wait(); waited = true; }   // the tile with this step's row
@@ -225,7 +261,7 @@ attention_decode_kernel(MmaAttnArgs a) {
                 if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, 2 * TILE_BYTES);
                 __syncwarp();
                 produce_tile<D, BN>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
-                                    full0 + 8 * st, tile * BN, lo, hi, bt, a.cache, g, a.page, a.nkv, lane);
+                                    full0 + 8 * st, tile * BN, lo, hi, pw, a.cache, g, a.page, a.nkv, lane);
             }
         } else {
             uint32_t qf[D / 16][4];
@@ -239,33 +275,42 @@ attention_decode_kernel(MmaAttnArgs a) {
 #pragma unroll
                 for (int i = 0; i < 2; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
                 qk_product<D, 2>(s, qf, sk, warp * 16);
+                // only a tile that crosses lo or hi has keys to mask (the same for the whole CTA)
+                if (tile * BN < lo || tile * BN + BN > hi) {
 #pragma unroll
-                for (int nb = 0; nb < 2; ++nb)
+                    for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int j = kb + nb * 8 + (lane & 3) * 2 + (e & 1);
-                        s[nb][e] = (j >= lo && j < hi) ? s[nb][e] * sl2 : -INFINITY;
-                    }
+                        for (int e = 0; e < 4; ++e) {
+                            const int j = kb + nb * 8 + (lane & 3) * 2 + (e & 1);
+                            if (j < lo || j >= hi) s[nb][e] = -INFINITY;
+                        }
+                }
+                // raw scores from here on; 2^(s * sl2 - m * sl2) is one multiply-add and one ex2.
                 // all rows of a decode tile share the position, but keep the two row sets apart
                 float ta = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
                 float tb = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
                 ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 1)); ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 2));
                 tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 1)); tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 2));
                 const float na = fmaxf(m_a, ta), nb_ = fmaxf(m_b, tb);
-                const float sa = na == -INFINITY ? 0.0f : na, sb = nb_ == -INFINITY ? 0.0f : nb_;
-                const float ca = fast_exp2(m_a - sa), cb = fast_exp2(m_b - sb);   // m = -inf: 2^-inf = 0, sums are 0 anyway
-                m_a = na; m_b = nb_;
+                // the accumulators are rescaled only when some row's maximum rose (rare after the first tiles)
+                if (__any_sync(0xffffffffu, na != m_a || nb_ != m_b)) {
+                    const float ca = na == -INFINITY ? 1.0f : fast_exp2((m_a - na) * sl2);   // m = -inf: 2^-inf = 0, sums are 0 anyway
+                    const float cb = nb_ == -INFINITY ? 1.0f : fast_exp2((m_b - nb_) * sl2);
+                    m_a = na; m_b = nb_;
+                    l_a *= ca; l_b *= cb;
+#pragma unroll
+                    for (int i = 0; i < D / 8; ++i) { o[i][0] *= ca; o[i][1] *= ca; o[i][2] *= cb; o[i][3] *= cb; }
+                }
+                const float sa = m_a == -INFINITY ? 0.0f : m_a * sl2, sb = m_b == -INFINITY ? 0.0f : m_b * sl2;
                 uint32_t pf[1][4];
                 float p[2][4];
 #pragma unroll
                 for (int nb = 0; nb < 2; ++nb) {
-                    p[nb][0] = fast_exp2(s[nb][0] - sa); p[nb][1] = fast_exp2(s[nb][1] - sa);
-                    p[nb][2] = fast_exp2(s[nb][2] - sb); p[nb][3] = fast_exp2(s[nb][3] - sb);
+                    p[nb][0] = fast_exp2(fmaf(s[nb][0], sl2, -sa)); p[nb][1] = fast_exp2(fmaf(s[nb][1], sl2, -sa));
+                    p[nb][2] = fast_exp2(fmaf(s[nb][2], sl2, -sb)); p[nb][3] = fast_exp2(fmaf(s[nb][3], sl2, -sb));
                 }
-                l_a = l_a * ca + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
-                l_b = l_b * cb + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
-#pragma unroll
-                for (int i = 0; i < D / 8; ++i) { o[i][0] *= ca; o[i][1] *= ca; o[i][2] *= cb; o[i][3] *= cb; }
+                l_a += (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
+                l_b += (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
                 pf[0][0] = pack_bf16(p[0][0], p[0][1]); pf[0][1] = pack_bf16(p[0][2], p[0][3]);
                 pf[0][2] = pack_bf16(p[1][0], p[1][1]); pf[0][3] = pack_bf16(p[1][2], p[1][3]);
                 pv_product<D, 1>(o, pf, sv, warp * 16);
@@ -287,8 +332,9 @@ attention_decode_kernel(MmaAttnArgs a) {
                 pa[0] = o[nd][0]; pa[1] = o[nd][1]; pb[0] = o[nd][2]; pb[1] = o[nd][3];
             }
             if ((lane & 3) == 0) {
-                red_ml[(warp * 16 + ra) * 2] = m_a; red_ml[(warp * 16 + ra) * 2 + 1] = l_a;
-                red_ml[(warp * 16 + rb) * 2] = m_b; red_ml[(warp * 16 + rb) * 2 + 1] = l_b;
+                // maxima leave the loop in units of log2
+                red_ml[(warp * 16 + ra) * 2] = m_a * sl2; red_ml[(warp * 16 + ra) * 2 + 1] = l_a;
+                red_ml[(warp * 16 + rb) * 2] = m_b * sl2; red_ml[(warp * 16 + rb) * 2 + 1] = l_b;
             }
         }
         __syncthreads();
@@ -403,13 +449,15 @@ attention_prefill_kernel(MmaAttnArgs a) {
     bool gave_up = false;
 
     if (producer) {
+        PageWindow pw;
+        pw.init(bt, tile0 * TK / a.page, hi, a.page, lane);
         for (int tile = tile0, it = 0; tile < tile1; ++tile, ++it) {
             const int st = it % STAGES;
             if (!cx_mbar_wait(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) gave_up = true;
             if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, 2 * TILE_BYTES);
             __syncwarp();
             produce_tile<D, TK>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
-                                full0 + 8 * st, tile * TK, lo, hi, bt, a.cache, g, a.page, a.nkv, lane);
+                                full0 + 8 * st, tile * TK, lo, hi, pw, a.cache, g, a.page, a.nkv, lane);
         }
         if (gave_up && a.status) atomicCAS(a.status, 0, 6);
         return;

@@ -43,6 +43,12 @@
 // No norm kernel runs between the two.  The partials are summed in a fixed order: results do not
 // depend on the order in which CTAs finish.
 //
+// Fused SwiGLU (decode).  For the gate and up projections of a gated feed-forward the tile image can be
+// made so that every 128-row tile holds 64 gate rows and the 64 up rows of the same features
+// (vcb_tile_weights with gated > 0).  The epilogue then exchanges the two halves through shared
+// memory and stores silu(gate) * up: no activation kernel runs and the 2 x wider intermediate
+// never reaches memory.
+//
 // Replaces cublasGemmEx of the reference (src/layers/linear.cpp:70-77).
 #include "common.cuh"
 
@@ -73,6 +79,10 @@ struct GemmArgs {
     const float* gain;           // [rows_p]: out = bfloat16(residual * gain)
     float* sumsq_out;            // [tiles_p * 4][sumsq_ld]: sums of squares of the new residual, per epilogue warp
     int ldr, sumsq_ld;
+    // Gated feed-forward (swapped products on a gated tile image only): > 0 = the number of gate features.
+    // Tile t holds gate rows 64 t .. and, in its upper half, the matching up rows;
+    // out[token, 64 t + r] = silu(gate) * up.
+    int gated;
 };
 
 // The segments of one CTA's run of (tile, slab) units.
@@ -157,17 +167,33 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// One (tile, slab) unit after the other of a CTA's run.
+// One (tile, slab) unit after the other of a CTA's run, for the producer.  What a stage's loads need
+// is worked out once per segment, so that a step costs a few instructions: one thread issues every
+// load of the CTA, and its instruction latency bounds the CTA's rate.
 struct Units {
     Segments seg;
-    int tile, s0, s1, slab;
+    const GemmArgs& a;
+    int bn, slab, s1;
+    int p_row, q_row;            // first row of the tile's P and Q boxes
+    const uint8_t* p_image;      // the current slab's tile of a tiled P, or null
     bool ok;
-    __device__ Units(const GemmArgs& a, int cta) : seg(a, cta) { ok = seg.next(tile, s0, s1); slab = s0; }
-    __device__ void advance() {
-        if (++slab >= s1) { ok = seg.next(tile, s0, s1); slab = s0; }
+    __device__ Units(const GemmArgs& a_, int cta, int bn_) : seg(a_, cta), a(a_), bn(bn_), slab(0), s1(0), p_row(0), q_row(0),
+                                                             p_image(nullptr) { next_segment(); }
+    __device__ void next_segment() {
+        int tile, s0;
+        ok = seg.next(tile, s0, s1);
+        if (!ok) return;
+        const int tp = tile % a.tiles_p;
+        slab = s0;
+        p_row = tp * BM;
+        q_row = (tile / a.tiles_p) * bn;
+        p_image = a.p_tiled ? a.p_tiled + ((size_t)tp * a.k_slabs + s0) * P_BYTES : nullptr;
     }
-    __device__ int p0(const GemmArgs& a) const { return (tile % a.tiles_p) * BM; }
-    __device__ int q0(const GemmArgs& a, int bn) const { return (tile / a.tiles_p) * bn; }
+    __device__ __forceinline__ void advance() {
+        ++slab;
+        if (p_image) p_image += P_BYTES;
+        if (slab >= s1) next_segment();
+    }
 };
 
 template <int BN, int STAGES>
@@ -210,39 +236,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         // stages are requested before the previous kernel has finished: weights depend on
         // nothing.  The activations (Q) follow once griddepcontrol.wait has returned.
         if (lane == 0) {
-            Units ahead(a, cta), units(a, cta);
+            Units ahead(a, cta, BN), units(a, cta, BN);
             int it_p = 0, it_q = 0;
+            auto load_p = [&](const Units& u, uint32_t dst, uint32_t bar) {
+                if (u.p_image) bulk_load(dst, u.p_image, P_BYTES, bar);
+                else tma_load_2d(dst, &map_p, bar, u.slab * BK, u.p_row);
+            };
             if (a.swapped) {
                 for (; ahead.ok && it_p < STAGES; ++it_p, ahead.advance()) {
-                    const int s = it_p % STAGES;
-                    mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                    if (a.p_tiled)
-                        bulk_load(tiles0 + s * STAGE_BYTES,
-                                  a.p_tiled + ((size_t)(ahead.tile % a.tiles_p) * a.k_slabs + ahead.slab) * P_BYTES,
-                                  P_BYTES, full0 + 8 * s);
-                    else
-                        tma_load_2d(tiles0 + s * STAGE_BYTES, &map_p, full0 + 8 * s, ahead.slab * BK, ahead.p0(a));
+                    mbar_expect_tx(full0 + 8 * it_p, STAGE_BYTES);
+                    load_p(ahead, tiles0 + it_p * STAGE_BYTES, full0 + 8 * it_p);
                 }
             }
             pdl_wait();
-            for (; it_q < it_p; ++it_q, units.advance()) {
-                const int s = it_q % STAGES;
-                tma_load_2d(tiles0 + s * STAGE_BYTES + P_BYTES, &map_q, full0 + 8 * s, units.slab * BK, units.q0(a, BN));
-            }
-            for (; units.ok && !flags[0]; ++it_q, units.advance()) {
-                const int s = it_q % STAGES;
-                if (!mbar_wait(empty0 + 8 * s, ((it_q / STAGES) & 1) ^ 1)) {
+            for (; it_q < it_p; ++it_q, units.advance())
+                tma_load_2d(tiles0 + it_q * STAGE_BYTES + P_BYTES, &map_q, full0 + 8 * it_q, units.slab * BK, units.q_row);
+            int s = it_q % STAGES;
+            uint32_t parity = ((it_q / STAGES) & 1) ^ 1;
+            for (; units.ok && !flags[0]; units.advance()) {
+                if (!mbar_wait(empty0 + 8 * s, parity)) {
                     if (!flags[0]) { flags[0] = 1; atomicCAS(a.status, 0, 1); }
                     break;
                 }
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 const uint32_t dst = tiles0 + s * STAGE_BYTES;
-                if (a.p_tiled)
-                    bulk_load(dst, a.p_tiled + ((size_t)(units.tile % a.tiles_p) * a.k_slabs + units.slab) * P_BYTES,
-                              P_BYTES, full0 + 8 * s);
-                else
-                    tma_load_2d(dst, &map_p, full0 + 8 * s, units.slab * BK, units.p0(a));
-                tma_load_2d(dst + P_BYTES, &map_q, full0 + 8 * s, units.slab * BK, units.q0(a, BN));
+                load_p(units, dst, full0 + 8 * s);
+                tma_load_2d(dst + P_BYTES, &map_q, full0 + 8 * s, units.slab * BK, units.q_row);
+                if (++s == STAGES) { s = 0; parity ^= 1; }
             }
         }
     } else if (warp == 1) {
@@ -285,7 +305,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         Segments seg(a, cta);
         int tile, s0, s1, n = 0;
         pdl_wait();                                 // nothing is written before the previous kernel is done
-        float* rstd_s = reinterpret_cast<float*>(const_cast<int*>(flags + 2));      // [BN]
+        float* rstd_s = reinterpret_cast<float*>(const_cast<int*>(flags + 2));      // [min(BN, 128)]
+        float* xch = rstd_s + 128;                                                  // [64][8]: up halves
         if (a.scale_sumsq) {
             // the factor of every token: rsqrt(sum of the partials / width + eps); a warp per token,
             // a lane per partial, summed in a fixed order
@@ -302,6 +323,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         constexpr int PRE = BN <= 32 ? BN : 1;
         auto emit = [&](const auto& v, int c, int i, int q0, int tile_p, const float* pre) {
             constexpr int NE = (int)(sizeof(v) / sizeof(float));
+            if (a.gated) {                          // swapped: rows 0-63 gate, 64-127 up of features 64 tile_p + ..
+                const int feature = tile_p * 64 + (r & 63);
+#pragma unroll
+                for (int g8 = 0; g8 < NE; g8 += 8) {
+                    if (q0 + c + g8 >= a.rows_q) break;             // the same for all 128 threads
+                    if (r >= 64) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) xch[(r - 64) * 8 + e] = v[g8 + e];
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (r < 64 && feature < a.gated) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const int j = q0 + c + g8 + e;
+                            if (j >= a.rows_q) break;
+                            const float f = a.scale_sumsq ? rstd_s[j] : 1.0f;
+                            const float z = v[g8 + e] * f, u = xch[r * 8 + e] * f;
+                            reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)j * a.ldc + feature] =
+                                __float2bfloat16_rn(z / (1.0f + expf(-z)) * u);
+                        }
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");   // the halves are read before the next group overwrites them
+                }
+                return;
+            }
             const bool row_ok = i < a.rows_p;
             if (a.residual) {                       // swapped, one tile of tokens: j = c + e is the token
                 const float g = row_ok ? a.gain[i] : 0.0f;
@@ -454,7 +500,7 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int bo
 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int ctas, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * (P_BYTES + BN * BK * 2) + 1024 + 1024;
+    constexpr size_t smem = (size_t)STAGES * (P_BYTES + BN * BK * 2) + 1024 + 3072;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -471,16 +517,18 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int 
 // row-major matrix goes to chunk c ^ (r % 8) of row r of the tile, which is the 128-byte
 // swizzle of the TMA copy.  Rows beyond the matrix and columns beyond K are zero.
 __global__ void tile_weights_kernel(const __nv_bfloat16* __restrict__ w, int rows, int k, int ld, int k_slabs,
-                                    uint4* __restrict__ out, size_t n_chunks) {
+                                    uint4* __restrict__ out, size_t n_chunks, int gated) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n_chunks; idx += (size_t)gridDim.x * blockDim.x) {
         const int c = (int)(idx & 7), r = (int)((idx >> 3) & 127);
         const size_t tile = idx >> 10;
         const int slab = (int)(tile % k_slabs);
         const size_t tp = tile / k_slabs;
-        const size_t row = tp * BM + r;
+        // gated: tile tp = gate rows 64 tp .. 64 tp + 63, then the up rows (gated + the same) of a [2 gated, k] matrix
+        const size_t row = gated ? (size_t)(r < 64 ? 0 : gated) + tp * 64 + (r & 63) : tp * BM + r;
+        const bool row_ok = gated ? tp * 64 + (r & 63) < (size_t)gated : row < (size_t)rows;
         const int col = slab * BK + c * 8;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < (size_t)rows) {
+        if (row_ok) {
             if (col + 8 <= k && (ld % 8) == 0) {
                 v = *reinterpret_cast<const uint4*>(w + row * ld + col);
             } else {
@@ -493,20 +541,24 @@ __global__ void tile_weights_kernel(const __nv_bfloat16* __restrict__ w, int row
     }
 }
 
-// Bytes of the tiled image of a [rows, k] matrix.
-VCB_EXPORT long long vcb_tiled_weight_bytes(int rows, int k) {
-    return (long long)((rows + BM - 1) / BM) * ((k + BK - 1) / BK) * P_BYTES;
+// Bytes of the tiled image of a [rows, k] matrix (gated > 0: of a [2 gated, k] gate-and-up matrix).
+VCB_EXPORT long long vcb_tiled_weight_bytes(int rows, int k, int gated) {
+    const int tiles = gated > 0 ? (gated + 63) / 64 : (rows + BM - 1) / BM;
+    return (long long)tiles * ((k + BK - 1) / BK) * P_BYTES;
 }
 
-// out (vcb_tiled_weight_bytes(rows, k) bytes, 16-byte aligned) = the tiled image of w.
-VCB_EXPORT int vcb_tile_weights(const void* w, int rows, int k, int ld, void* out, void* stream) {
+// out (vcb_tiled_weight_bytes bytes, 16-byte aligned) = the tiled image of w.  gated > 0: w is
+// [2 gated, k], gate rows first; tile t of the image holds gate rows 64 t .. and the matching up rows.
+VCB_EXPORT int vcb_tile_weights(const void* w, int rows, int k, int ld, int gated, void* out, void* stream) {
     if (rows <= 0 || k <= 0 || ld < k || ((uintptr_t)out & 15) || ((uintptr_t)w & 15)) return VCB_ERR_BAD_ARG;
+    if (gated < 0 || (gated > 0 && rows != 2 * gated)) return VCB_ERR_BAD_ARG;
     const int k_slabs = (k + BK - 1) / BK;
-    const size_t n_chunks = (size_t)((rows + BM - 1) / BM) * k_slabs * 1024;
+    const int tiles = gated > 0 ? (gated + 63) / 64 : (rows + BM - 1) / BM;
+    const size_t n_chunks = (size_t)tiles * k_slabs * 1024;
     size_t blocks = (n_chunks + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
     tile_weights_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)w, rows, k, ld, k_slabs,
-                                                                       (uint4*)out, n_chunks);
+                                                                       (uint4*)out, n_chunks, gated);
     return vcb_last_error();
 }
 
@@ -524,18 +576,26 @@ VCB_EXPORT int vcb_tile_weights(const void* w, int rows, int k, int ld, void* ou
 //   residual [rows_q][ldr] float, gain [rows_p] float, sumsq_out [4 * ceil(rows_p / 128)][sumsq_ld]:
 //       residual += result; out (bfloat16) = residual * gain; sumsq_out = partial sums over the features
 //       of residual^2 for every token.
+//   gated > 0: p_tiled is a gated image (vcb_tile_weights) of a [2 gated, k] matrix, rows_p = 2 gated;
+//       out (bfloat16, [rows_q][>= gated]) = silu(gate) * up.
 VCB_EXPORT int vcb_gemm_bf16_tcgen05_fused(const void* p, int rows_p, int ldp, const void* p_tiled, const void* q,
                                            int rows_q, int ldq, int k, void* out, int ldc, int out_f32, int swapped,
                                            int bn, int max_ctas, float* partial, int* tickets, int n_tickets,
                                            int* status, const float* scale_sumsq, int scale_parts, int scale_ld,
                                            int scale_width, float scale_eps, float* residual, int ldr,
-                                           const float* gain, float* sumsq_out, int sumsq_ld, void* stream) {
+                                           const float* gain, float* sumsq_out, int sumsq_ld, int gated, void* stream) {
     if (rows_p <= 0 || rows_q <= 0) return 0;
     if (k <= 0 || max_ctas < 1 || !status || !partial || !tickets) return VCB_ERR_BAD_ARG;
     // TMA needs 16-byte aligned bases and row strides
     if ((k % 8) || (ldq % 8) || (((uintptr_t)q | (uintptr_t)p_tiled) & 15)) return VCB_ERR_UNSUPPORTED;
     if (!p_tiled && ((ldp % 8) || ((uintptr_t)p & 15))) return VCB_ERR_UNSUPPORTED;
     if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return VCB_ERR_BAD_ARG;
+    if (gated) {
+        if (gated < 0 || rows_p != 2 * gated || !p_tiled || !swapped || rows_q > bn || bn > 128 || out_f32 || residual ||
+            ldc < gated)
+            return VCB_ERR_BAD_ARG;
+        rows_p = 128 * ((gated + 63) / 64);       // rows of the image
+    }
     if (scale_sumsq || residual) {
         if (!swapped || rows_q > bn || bn > 128) return VCB_ERR_UNSUPPORTED;
         if (scale_sumsq && (scale_parts < 1 || scale_ld < rows_q || scale_width < 1)) return VCB_ERR_BAD_ARG;
@@ -557,7 +617,7 @@ VCB_EXPORT int vcb_gemm_bf16_tcgen05_fused(const void* p, int rows_p, int ldp, c
     GemmArgs a{out, partial, tickets, status, (const uint8_t*)p_tiled, ldc, out_f32, swapped, rows_p, rows_q,
                k_slabs, tiles_p, per, (int)total,
                scale_sumsq, scale_parts, scale_ld, scale_sumsq ? 1.0f / (float)scale_width : 0.0f, scale_eps,
-               residual, gain, sumsq_out, ldr, sumsq_ld};
+               residual, gain, sumsq_out, ldr, sumsq_ld, gated};
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
         case 16: return launch<16, 6>(mp, mq, a, ctas, s);
@@ -574,5 +634,5 @@ VCB_EXPORT int vcb_gemm_bf16_tcgen05(const void* p, int rows_p, int ldp, const v
                                      void* stream) {
     return vcb_gemm_bf16_tcgen05_fused(p, rows_p, ldp, p_tiled, q, rows_q, ldq, k, out, ldc, out_f32, swapped, bn,
                                        max_ctas, partial, tickets, n_tickets, status, nullptr, 0, 0, 1, 0.0f,
-                                       nullptr, 0, nullptr, nullptr, 0, stream);
+                                       nullptr, 0, nullptr, nullptr, 0, 0, stream);
 }

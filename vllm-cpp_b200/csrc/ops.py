@@ -38,8 +38,8 @@ _SIGNATURES = {
     "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
     "vcb_gemm_bf16_tcgen05_fused": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P,
-                                    _P, _I, _I, _I, _F, _P, _I, _P, _P, _I, _P],
-    "vcb_tile_weights": [_P, _I, _I, _I, _P, _P],
+                                    _P, _I, _I, _I, _F, _P, _I, _P, _P, _I, _I, _P],
+    "vcb_tile_weights": [_P, _I, _I, _I, _I, _P, _P],
     "vcb_repetition_penalty": [_P, _I, _P, _P, _P, _I, _I, _P],
     "vcb_sample": [_P, _I, _I, _P, _P, _P, _I, _P],
     "vcb_sample_filtered": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
@@ -310,28 +310,33 @@ def tcgen05_plan(tokens: int, features: int, k: int):
 GEMM_MAX_TICKETS = 16384
 
 
-def tile_weights(w: torch.Tensor) -> torch.Tensor:
+def tile_weights(w: torch.Tensor, gated: int = 0) -> torch.Tensor:
     """The pre-tiled image of a weight matrix for decode products (see gemm_tcgen05.cu): made once,
     kept on the tensor object itself (so it lives and dies with the matrix), and used by ``linear``
-    whenever the weights sit on the 128-row side.  The matrix must not change afterwards."""
-    t = getattr(w, "_vcb_tiled", None)
+    whenever the weights sit on the 128-row side.  The matrix must not change afterwards.
+    ``gated`` > 0: w is the [2 * gated, k] gate-and-up matrix of a gated feed-forward and the image
+    pairs gate and up rows in every tile, for ``linear_gated``."""
+    attr = "_vcb_tiled_gated" if gated else "_vcb_tiled"
+    t = getattr(w, attr, None)
     if t is None:
         _need(w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1, "tile_weights: a bfloat16 matrix")
         rows, k = w.shape
-        nbytes = -(-rows // 128) * -(-k // 64) * 16384
-        t = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
-        _check(lib().vcb_tile_weights(w.data_ptr(), rows, k, w.stride(0), t.data_ptr(), _stream()), "tile_weights")
-        w._vcb_tiled = t
+        _need(gated == 0 or rows == 2 * gated, "tile_weights: a gated matrix has 2 * gated rows")
+        tiles = -(-gated // 64) if gated else -(-rows // 128)
+        t = torch.empty(tiles * -(-k // 64) * 16384, dtype=torch.uint8, device=w.device)
+        _check(lib().vcb_tile_weights(w.data_ptr(), rows, k, w.stride(0), gated, t.data_ptr(), _stream()), "tile_weights")
+        setattr(w, attr, t)
     return t
 
 
 def drop_tiled_weights(w: torch.Tensor) -> None:
-    if getattr(w, "_vcb_tiled", None) is not None:
-        w._vcb_tiled = None
+    for attr in ("_vcb_tiled", "_vcb_tiled_gated"):
+        if getattr(w, attr, None) is not None:
+            setattr(w, attr, None)
 
 
-def tiled_weights_of(w: torch.Tensor) -> Optional[torch.Tensor]:
-    return getattr(w, "_vcb_tiled", None)
+def tiled_weights_of(w: torch.Tensor, gated: bool = False) -> Optional[torch.Tensor]:
+    return getattr(w, "_vcb_tiled_gated" if gated else "_vcb_tiled", None)
 
 
 class RowScale:
@@ -365,14 +370,15 @@ def sumsq_parts(features: int) -> int:
 
 def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=None, max_ctas: int = SM_COUNT,
                       use_tiled: bool = True, x_scale: Optional[RowScale] = None,
-                      fuse: Optional[ResidualNorm] = None) -> None:
+                      fuse: Optional[ResidualNorm] = None, gated: bool = False) -> None:
     """out = x @ w^T on tcgen05 tensor cores fed by TMA (see gemm_tcgen05.cu); out bfloat16 or float32.
     When the weights are the 128-row operand and tile_weights(w) has been made, the image is used
     (``use_tiled`` False forces the tensor-map path).  ``x_scale`` and ``fuse`` (up to 128 tokens):
-    see RowScale and ResidualNorm."""
+    see RowScale and ResidualNorm.  ``gated``: w is a gate-and-up matrix [2 * inter, k] with a gated
+    image (tile_weights(w, inter)) and out [tokens, inter] = silu(x gate^T) * (x up^T)."""
     m, k = x.shape
     n = w.shape[0]
-    _need(w.shape[1] == k and out.shape == (m, n), "gemm_bf16_tcgen05: shapes do not agree")
+    _need(w.shape[1] == k and out.shape == (m, n // 2 if gated else n), "gemm_bf16_tcgen05: shapes do not agree")
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "gemm_bf16_tcgen05: operands must be bfloat16")
     _need(out.dtype in (torch.bfloat16, torch.float32) and out.stride(1) == 1 and x.stride(1) == 1 and w.stride(1) == 1,
           "gemm_bf16_tcgen05: unit inner strides, out bfloat16 or float32")
@@ -396,17 +402,20 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=
         _need(ss.dtype == torch.float32 and ss.dim() == 2 and ss.stride(1) == 1 and ss.shape[0] >= sumsq_parts(n)
               and ss.shape[1] >= m, "gemm_bf16_tcgen05: sums of squares must be float32 [sumsq_parts(features), tokens]")
         fu = (r.data_ptr(), r.stride(0), g.data_ptr(), ss.data_ptr(), ss.stride(0))
+    p, q = (w, x) if swapped else (x, w)
+    tiled = tiled_weights_of(w, gated) if (swapped and use_tiled) else None
+    if gated:
+        _need(swapped and m <= bn <= 128 and tiled is not None and out.dtype == torch.bfloat16 and fuse is None,
+              "gemm_bf16_tcgen05: the gated form needs few tokens, a gated tile image and a bfloat16 result")
     partial = scratch("gemm_partial", SM_COUNT * 2 * 256 * 128, out.device)
     tickets = zeroed_ints("gemm_tickets", GEMM_MAX_TICKETS, out.device)
-    p, q = (w, x) if swapped else (x, w)
-    tiled = tiled_weights_of(w) if (swapped and use_tiled) else None
     _check(lib().vcb_gemm_bf16_tcgen05_fused(p.data_ptr(), p.shape[0], p.stride(0),
                                              None if tiled is None else tiled.data_ptr(),
                                              q.data_ptr(), q.shape[0], q.stride(0), k,
                                              out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0,
                                              1 if swapped else 0, bn, min(max_ctas, SM_COUNT), partial.data_ptr(),
                                              tickets.data_ptr(), GEMM_MAX_TICKETS, status_tensor(out.device).data_ptr(),
-                                             *sc, *fu, _stream()), "gemm_bf16_tcgen05")
+                                             *sc, *fu, n // 2 if gated else 0, _stream()), "gemm_bf16_tcgen05")
 
 
 TCGEN05_MAX_TOKENS = 128      # up to here the engine's own tcgen05 product may run; above, the library's
@@ -481,10 +490,12 @@ def time_in_graph(fn, reps: int = 8) -> float:
     return e0.elapsed_time(e1) * 1e3 / (2 * reps)
 
 
-def measure_linear(weights, out_dtype=torch.bfloat16):
+def measure_linear(weights, out_dtype=torch.bfloat16, gated: int = 0):
     """{bucket: (microseconds of this library's tcgen05 product, of the library's)} for one shape of
     weight matrix.  ``weights``: matrices of the same shape (the same projection of several layers),
     used in rotation so that the L2 cache cannot serve them; their tiled images must exist.
+    ``gated`` > 0: the matrices are gate-and-up matrices with gated images; this library's side is
+    ``linear_gated``, the library's side the product followed by the activation kernel.
     Buckets the tcgen05 kernel cannot take are left out."""
     n, k = weights[0].shape
     dev_ = weights[0].device
@@ -494,21 +505,64 @@ def measure_linear(weights, out_dtype=torch.bfloat16):
         out = torch.empty(m, n, dtype=out_dtype, device=dev_)
         if not _tcgen05_ok(x, weights[0], out):
             continue
-        out_times[bucket] = (time_in_graph(lambda i: gemm_bf16_tcgen05(x, weights[i % len(weights)], out)),
-                             time_in_graph(lambda i: _library_mm(x, weights[i % len(weights)], out)))
+        if gated:
+            act = torch.empty(m, gated, dtype=out_dtype, device=dev_)
+
+            def theirs(i):
+                _library_mm(x, weights[i % len(weights)], out)
+                silu_mul(out, act)
+            out_times[bucket] = (time_in_graph(lambda i: gemm_bf16_tcgen05(x, weights[i % len(weights)], act, gated=True)),
+                                 time_in_graph(theirs))
+        else:
+            out_times[bucket] = (time_in_graph(lambda i: gemm_bf16_tcgen05(x, weights[i % len(weights)], out)),
+                                 time_in_graph(lambda i: _library_mm(x, weights[i % len(weights)], out)))
     check_status()
     return out_times
 
 
-def measure_norm(hidden: int, dtype, device) -> dict:
-    """{bucket: microseconds of one residual-add + RMSNorm kernel} at the buckets' token counts."""
+def measure_layer(products, hidden: int, fusable_norms: int, dtype=torch.bfloat16) -> dict:
+    """{bucket: (microseconds of a layer's products as this library runs them, as the library would)}.
+    ``products``: for every product of a layer, in the order they run, (matrices of that product
+    across layers, gated) with tiled images made.  This library's side is its tcgen05 product for each
+    (with a norm's factor applied, as the blocks link them; the activation inside the gated ones);
+    the library's side is a product each, the activation kernel after a gated one and
+    ``fusable_norms`` norm kernels, which the other side does not need."""
+    dev_ = products[0][0][0].device
     times = {}
-    gain = torch.ones(hidden, device=device)
     for bucket, m in TOKEN_BUCKETS:
-        res = torch.zeros(m, hidden, device=device)
-        delta = torch.zeros(m, hidden, dtype=dtype, device=device)
-        out = torch.empty(m, hidden, dtype=dtype, device=device)
-        times[bucket] = time_in_graph(lambda i: add_rmsnorm(res, delta, gain, out, 1e-6))
+        xs, outs, acts, scales = {}, [], [], {}
+        ok = True
+        for mats, gated in products:
+            n, k = mats[0].shape
+            if k not in xs:
+                xs[k] = torch.randn(m, k, device=dev_).to(dtype)
+                scales[k] = RowScale(torch.ones(sumsq_parts(k), m, device=dev_), sumsq_parts(k), k, 1e-6)
+            outs.append(torch.empty(m, n, dtype=dtype, device=dev_))
+            acts.append(torch.empty(m, gated, dtype=dtype, device=dev_) if gated else None)
+            ok = ok and _tcgen05_ok(xs[k], mats[0], outs[-1])
+        if not ok:
+            continue
+        res = torch.zeros(m, hidden, device=dev_)
+        delta = torch.zeros(m, hidden, dtype=dtype, device=dev_)
+        normed = torch.empty(m, hidden, dtype=dtype, device=dev_)
+        gain = torch.ones(hidden, device=dev_)
+
+        def ours(i):
+            for j, (mats, gated) in enumerate(products):
+                w = mats[i % len(mats)]
+                gemm_bf16_tcgen05(xs[w.shape[1]], w, acts[j] if gated else outs[j], x_scale=scales[w.shape[1]], gated=bool(gated))
+
+        def theirs(i):
+            for j, (mats, gated) in enumerate(products):
+                w = mats[i % len(mats)]
+                _library_mm(xs[w.shape[1]], w, outs[j])
+                if gated:
+                    silu_mul(outs[j], acts[j])
+            for _ in range(fusable_norms):
+                add_rmsnorm(res, delta, gain, normed, 1e-6)
+
+        times[bucket] = (time_in_graph(ours), time_in_graph(theirs))
+    check_status()
     return times
 
 
@@ -559,6 +613,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_scale: Optiona
         return
     _need(x_scale is None and fuse is None, "linear: the library product fuses no norm; ask linear_fuses_norm first")
     _library_mm(x, w, out)
+
+
+def linear_gated_fuses(tokens: int, w: torch.Tensor) -> bool:
+    """True if ``linear_gated`` will run as one kernel (this library's tcgen05 product on a gated tile image)."""
+    return tiled_weights_of(w, gated=True) is not None and _tcgen05_linear and 0 < tokens <= TCGEN05_MAX_TOKENS \
+        and _linear_choice.get((w.shape[0], w.shape[1], token_bucket(tokens), torch.bfloat16), True)
+
+
+def linear_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_scale: Optional[RowScale] = None) -> None:
+    """out [tokens, inter] = silu(x gate^T) * (x up^T) for w = [gate; up] ([2 * inter, k]) in one kernel;
+    only where ``linear_gated_fuses`` said yes."""
+    _need(linear_gated_fuses(x.shape[0], w), "linear_gated: ask linear_gated_fuses first")
+    gemm_bf16_tcgen05(x, w, out, x_scale=x_scale, gated=True)
 
 
 def repetition_penalty(logits, ids, row_start, penalty) -> None:

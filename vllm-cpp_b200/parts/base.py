@@ -143,6 +143,12 @@ class Part:
     def load_params(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Receives the tensors of ``param_specs`` (on the device, roles' types applied)."""
 
+    def product_weights(self):
+        """The weight matrices of this part's products as (matrix, gated) pairs, for the model's
+        choice of kernels at load: ``gated`` is 0, or the number of gate features of a
+        gate-and-up matrix that the part multiplies with ops.linear_gated."""
+        return [(v, 0) for v in vars(self).values() if isinstance(v, torch.Tensor) and v.dim() == 2]
+
 
 class PositionEncoding(Part):
     """How positions enter a mixer.

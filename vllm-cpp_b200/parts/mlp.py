@@ -33,15 +33,21 @@ class GatedMLP(FeedForward):
         self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"].contiguous()
 
+    def product_weights(self):
+        return [(self.w_gate_up, self.inter), (self.w_down, 0)]
+
     def fuses_norm(self, n_tokens):
         return ops.linear_fuses_norm(n_tokens, self.w_gate_up) and ops.linear_fuses_norm(n_tokens, self.w_down)
 
     def forward(self, x, out, step, ws, x_scale=None, fuse=None):
         n = x.shape[0]
         mark = ws.mark()
-        gate_up = ws.take((n, 2 * self.inter), self.dtype)
-        ops.linear(x, self.w_gate_up, gate_up, x_scale=x_scale)
         act = ws.take((n, self.inter), self.dtype)
-        ops.silu_mul(gate_up, act)
+        if ops.linear_gated_fuses(n, self.w_gate_up):
+            ops.linear_gated(x, self.w_gate_up, act, x_scale=x_scale)       # product and activation in one kernel
+        else:
+            gate_up = ws.take((n, 2 * self.inter), self.dtype)
+            ops.linear(x, self.w_gate_up, gate_up, x_scale=x_scale)
+            ops.silu_mul(gate_up, act)
         ops.linear(act, self.w_down, out, fuse=fuse)
         ws.release(mark)

@@ -100,49 +100,56 @@ class DecoderModel:
         engine's tcgen05 product or the library's runs when a step has few tokens, and make the pre-tiled
         images of the matrices the engine's kernel will read (see csrc/gemm_tcgen05.cu).  Both are
         measured here, on this device, in CUDA graphs.  A layer whose products all run on the engine's
-        kernel needs no norm kernels (parts/block.py), so the layers' products are chosen together:
-        all on the engine's kernel if that, without the norm kernels, is faster than each on its own
-        best; the output product is chosen by itself."""
+        kernel needs no norm or activation kernels (parts/block.py), so the layers' products are
+        measured together first: all on the engine's kernel if that beats the library's products with
+        the kernels between them, else each product on its own merits; the output product is chosen
+        by itself."""
         if self.dtype != torch.bfloat16:
             return
-        layer_shapes, fusable_norms = {}, 0
+        layer_shapes, fusable_norms = {}, 0          # (shape, gated) -> matrices
         for blk in self.blocks:
             for part in (blk.mixer, blk.feed_forward):
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor) and v.dim() == 2 and v.dtype == torch.bfloat16:
-                        layer_shapes.setdefault(tuple(v.shape), []).append(v)
+                for v, gated in part.product_weights():
+                    if v.dtype == torch.bfloat16:
+                        layer_shapes.setdefault((tuple(v.shape), gated), []).append(v)
         if self.blocks:
             first = self.blocks[0]
             fusable_norms = sum(1 for nrm in (first.mixer_norm, first.feed_forward_norm) if nrm.split() is not None)
-        tunable = {shape: mats for shape, mats in layer_shapes.items() if shape[1] % 8 == 0}
+        tunable = {key: mats for key, mats in layer_shapes.items() if key[0][1] % 8 == 0}
         head_ok = self.lm_head.shape[1] % 8 == 0
         measure = tune and ops.linear_tuning()
-        for mats in tunable.values():
+        for (shape, gated), mats in tunable.items():
             for m in mats[:8]:                    # the kernel is measured as it will run: on the images
-                ops.tile_weights(m)
+                ops.tile_weights(m, gated)
         if head_ok:
             ops.tile_weights(self.lm_head)
         if measure:
-            times = {shape: ops.measure_linear(mats[:8]) for shape, mats in tunable.items()}
-            per_layer = {shape: len(mats) / max(1, len(self.blocks)) for shape, mats in tunable.items()}
-            norm_us = ops.measure_norm(self.hidden, self.dtype, self.device)
+            whole = {}
+            if len(tunable) == len(layer_shapes) and tunable:
+                whole = ops.measure_layer([(mats[:8], key[1]) for key, mats in tunable.items()], self.hidden,
+                                          fusable_norms, self.dtype)
+            times = None
             for bucket, _ in ops.TOKEN_BUCKETS:
-                have = [shape for shape in tunable if bucket in times[shape]]
-                ours = sum(times[shape][bucket][0] * per_layer[shape] for shape in have)
-                best = sum(min(times[shape][bucket]) * per_layer[shape] for shape in have)
-                together = len(have) == len(layer_shapes) and ours <= best + fusable_norms * norm_us[bucket]
-                for shape in have:
-                    t_ours, t_lib = times[shape][bucket]
-                    ops.choose_linear(shape[0], shape[1], bucket, torch.bfloat16, together or t_ours <= t_lib)
+                if bucket in whole and whole[bucket][0] <= whole[bucket][1]:
+                    for key in tunable:                   # the layer as a whole is faster on the engine's kernel
+                        ops.choose_linear(key[0][0], key[0][1], bucket, torch.bfloat16, True)
+                    continue
+                if times is None:
+                    times = {key: ops.measure_linear(mats[:8], gated=key[1]) for key, mats in tunable.items()}
+                for key in tunable:                       # each product on its own merits
+                    if bucket in times[key]:
+                        t_ours, t_lib = times[key][bucket]
+                        ops.choose_linear(key[0][0], key[0][1], bucket, torch.bfloat16, t_ours <= t_lib)
             if head_ok:
                 for bucket, (t_ours, t_lib) in ops.measure_linear([self.lm_head], torch.float32).items():
                     ops.choose_linear(self.lm_head.shape[0], self.lm_head.shape[1], bucket, torch.float32, t_ours <= t_lib)
-        for shape, mats in list(tunable.items()) + ([(tuple(self.lm_head.shape), [self.lm_head])] if head_ok else []):
+        todo = list(tunable.items()) + ([((tuple(self.lm_head.shape), 0), [self.lm_head])] if head_ok else [])
+        for (shape, gated), mats in todo:
             out_dtype = torch.float32 if mats[0] is self.lm_head else torch.bfloat16
             chosen = any(ops._linear_choice.get((shape[0], shape[1], b, out_dtype), True) for b, _ in ops.TOKEN_BUCKETS)
             for m in mats:
                 if chosen:
-                    ops.tile_weights(m)
+                    ops.tile_weights(m, gated)
                 else:
                     ops.drop_tiled_weights(m)
 
@@ -151,9 +158,8 @@ class DecoderModel:
         total = 0
         for blk in self.blocks:
             for part in (blk.mixer, blk.feed_forward):
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor) and v.dim() == 2:
-                        total += v.numel() * v.element_size()
+                for v, _ in part.product_weights():
+                    total += v.numel() * v.element_size()
         total += self.lm_head.numel() * self.lm_head.element_size()
         return total
 
