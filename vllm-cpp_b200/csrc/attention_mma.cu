@@ -119,29 +119,43 @@ struct PageWindow {
     }
 };
 
+// Division by the page size on the producer's path: a shift when the size is a power of two (the
+// producer warp issues every copy of its CTA, so its instruction count bounds the CTA's rate).
+struct PageDiv {
+    int page, shift;             // shift < 0: not a power of two
+    __device__ __forceinline__ explicit PageDiv(int page_) : page(page_), shift(-1) {
+        if ((page_ & (page_ - 1)) == 0) { shift = 0; while ((1 << shift) < page_) ++shift; }
+    }
+    __device__ __forceinline__ int div(int x) const { return shift >= 0 ? x >> shift : x / page; }
+    __device__ __forceinline__ int mul(int x) const { return shift >= 0 ? x << shift : x * page; }
+};
+
 // The producer warp's share of one tile of TK keys starting at key kb of kv head g: lanes 0-7
 // each copy one page piece of K, lanes 8-15 the same pieces of V (a tile spans at most
 // TK / 16 + 1 pages).  Lane 0 has armed the stage's barrier with the tile's byte count.
+// head_base: the kv head's offset inside a page's K block; page_stride, v_off: elements per page, K block to V block.
 template <int D, int TK>
 __device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t bar, int kb, int lo, int hi,
                                              PageWindow& pw, const __nv_bfloat16* __restrict__ cache,
-                                             int g, int page, int nkv, int lane) {
+                                             size_t head_base, size_t page_stride, size_t v_off, const PageDiv& pd, int lane) {
     const int piece = lane & 7;
-    const int first_page = kb / page;
+    const int first_page = pd.div(kb);
     pw.advance(first_page);
-    const int start = piece == 0 ? kb : (first_page + piece) * page;       // first key of the piece
+    const int lp_piece = first_page + piece;
+    const int start = piece == 0 ? kb : pd.mul(lp_piece);                   // first key of the piece
     const bool active = lane < 16 && start < kb + TK;
     // the page itself if any of it is visible, else the page of the last visible key
-    const int lp = active ? start / page : first_page;
-    const bool visible = lp * page < hi && (lp + 1) * page > lo;
+    const int lp = active ? lp_piece : first_page;
+    const int page_lo = pd.mul(lp);
+    const bool visible = page_lo < hi && page_lo + pd.page > lo;
     const int got = pw.get(visible ? lp : first_page);                     // all lanes take part in the shuffles
     if (!active) return;
     const int pg = visible ? got : pw.last_pg;
-    const int end = min((start / page + 1) * page, kb + TK);
-    const __nv_bfloat16* src = cache + (size_t)pg * ((size_t)2 * nkv * page * D) + ((size_t)g * page + (start % page)) * D;
+    const int end = min(page_lo + pd.page, kb + TK);
+    const __nv_bfloat16* src = cache + (size_t)pg * page_stride + head_base + (size_t)(start - page_lo) * D;
     const uint32_t off = (uint32_t)(start - kb) * D * 2, bytes = (uint32_t)(end - start) * D * 2;
     if (lane < 8) cx_bulk_load(sk + off, src, bytes, bar);
-    else cx_bulk_load(sv + off, src + (size_t)nkv * page * D, bytes, bar);
+    else cx_bulk_load(sv + off, src + v_off, bytes, bar);
 }
 
 // S[16 x 8*NB] += Q[16 x D] * K[keys key0 .. key0 + 8*NB)^T, K tile at sk.
@@ -192,14 +206,13 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[D / 16][4], uint32_t
 
 // ------------------------------------------------------------------ decode
 template <int D, int STAGES>
-__global__ void __launch_bounds__(BLOCK_THREADS)
+__global__ void __launch_bounds__(BLOCK_THREADS, 2)
 attention_decode_kernel(MmaAttnArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     constexpr int TILE_BYTES = BN * D * 2;
     // The step's index arrays were copied in before its first kernel, and every cache row below the
     // request's newest position was written by an earlier step: both are read before
     // griddepcontrol.wait, while the kernel that rotates and stores this step's row still runs.
-    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool producer = warp == 4;
     bool waited = false;                                 // producer: griddepcontrol.wait has been executed
@@ -253,7 +266,10 @@ attention_decode_kernel(MmaAttnArgs a) {
 
         if (producer) {
             PageWindow pw;
-            pw.init(bt, my0 * BN / a.page, hi, a.page, lane);
+            const PageDiv pd(a.page);
+            pw.init(bt, pd.div(my0 * BN), hi, a.page, lane);
+            const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
+                         v_off = (size_t)a.nkv * a.page * D;
             for (int tile = my0; tile < my1; ++tile, ++it) {
                 const int st = it % STAGES;
                 if (!waited && (tile + 1) * BN > pos) { pdl_wait(); waited = true; }   // the tile with this step's row
@@ -261,7 +277,7 @@ attention_decode_kernel(MmaAttnArgs a) {
                 if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, 2 * TILE_BYTES);
                 __syncwarp();
                 produce_tile<D, BN>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
-                                    full0 + 8 * st, tile * BN, lo, hi, pw, a.cache, g, a.page, a.nkv, lane);
+                                    full0 + 8 * st, tile * BN, lo, hi, pw, a.cache, head_base, page_stride, v_off, pd, lane);
             }
         } else {
             uint32_t qf[D / 16][4];
@@ -319,7 +335,12 @@ attention_decode_kernel(MmaAttnArgs a) {
             }
         }
         if (producer && !waited) { pdl_wait(); waited = true; }   // nothing is written before the previous kernel is done
+        // Only now may the next kernel's CTAs come: if they came earlier they would take the place of
+        // this kernel's own second CTA on the SM (they wait, holding shared memory), and the tiles
+        // of this kernel would be read in two rounds.
+        pdl_launch_dependents();
         __syncthreads();                                 // every copy has landed and been read: reuse the tiles
+        const int Gm = min(16, G - mt * 16);             // rows of this round that are heads
         if (!producer) {
             l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
             l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
@@ -327,9 +348,8 @@ attention_decode_kernel(MmaAttnArgs a) {
 #pragma unroll
             for (int nd = 0; nd < D / 8; ++nd) {
                 const int col = nd * 8 + (lane & 3) * 2;
-                float* pa = red_o + ((size_t)(warp * 16 + ra)) * D + col;
-                float* pb = red_o + ((size_t)(warp * 16 + rb)) * D + col;
-                pa[0] = o[nd][0]; pa[1] = o[nd][1]; pb[0] = o[nd][2]; pb[1] = o[nd][3];
+                if (ra < Gm) *reinterpret_cast<float2*>(red_o + ((size_t)(warp * 16 + ra)) * D + col) = make_float2(o[nd][0], o[nd][1]);
+                if (rb < Gm) *reinterpret_cast<float2*>(red_o + ((size_t)(warp * 16 + rb)) * D + col) = make_float2(o[nd][2], o[nd][3]);
             }
             if ((lane & 3) == 0) {
                 // maxima leave the loop in units of log2
@@ -338,28 +358,28 @@ attention_decode_kernel(MmaAttnArgs a) {
             }
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < 16 * D; idx += BLOCK_THREADS) {
-            const int row = idx / D, dim = idx % D;
-            const int hg = mt * 16 + row;
-            if (hg >= G) continue;
-            float mx = -INFINITY;
+        // the four warps' partials of a row: out = sum_w o_w 2^(m_w - m), four dimensions per thread
+        for (int item = threadIdx.x; item < Gm * (D / 4); item += BLOCK_THREADS) {
+            const int row = item / (D / 4), dim = (item % (D / 4)) * 4;
+            float mw[4], f[4], mx = -INFINITY, l = 0.0f;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) mx = fmaxf(mx, red_ml[(w * 16 + row) * 2]);
-            float acc = 0.0f, l = 0.0f;
+            for (int w = 0; w < 4; ++w) { mw[w] = red_ml[(w * 16 + row) * 2]; mx = fmaxf(mx, mw[w]); }
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                const float mw = red_ml[(w * 16 + row) * 2];
-                if (mw == -INFINITY) continue;
-                const float f = fast_exp2(mw - mx);
-                acc += red_o[((size_t)(w * 16 + row)) * D + dim] * f;
-                l += red_ml[(w * 16 + row) * 2 + 1] * f;
+                f[w] = mw[w] == -INFINITY ? 0.0f : fast_exp2(mw[w] - mx);
+                l += red_ml[(w * 16 + row) * 2 + 1] * f[w];
+                const float4 v = *reinterpret_cast<const float4*>(red_o + ((size_t)(w * 16 + row)) * D + dim);
+                acc.x += v.x * f[w]; acc.y += v.y * f[w]; acc.z += v.z * f[w]; acc.w += v.w * f[w];
             }
-            const int head = g * G + hg;
+            const int head = g * G + mt * 16 + row;
             if (nsplit == 1) {
-                a.out[((size_t)t * a.nh + head) * D + dim] = __float2bfloat16_rn(acc / l);
+                const float inv = 1.0f / l;
+                uint2 packed = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+                *reinterpret_cast<uint2*>(a.out + ((size_t)t * a.nh + head) * D + dim) = packed;
             } else {
                 const size_t pi = ((size_t)li * a.nh + head) * nsplit + split;
-                a.part_o[pi * D + dim] = acc;
+                *reinterpret_cast<float4*>(a.part_o + pi * D + dim) = acc;
                 if (dim == 0) { a.part_ml[pi * 2] = mx; a.part_ml[pi * 2 + 1] = l; }
             }
         }
@@ -377,26 +397,33 @@ attention_decode_kernel(MmaAttnArgs a) {
     __syncthreads();
     if (s_ticket != nsplit - 1) return;
     __threadfence();
-    // factors 2^(m_s - m) / sum per (head, split): one warp per head, one lane per split
-    float* fac = reinterpret_cast<float*>(smem);           // [G][32], the tiles are dead
-    for (int hg = warp; hg < G; hg += BLOCK_THREADS / 32) {
-        const size_t p0 = ((size_t)li * a.nh + g * G + hg) * nsplit;
-        float ms = -INFINITY, ls = 0.0f;
-        if (lane < nsplit) { ms = __ldcg(a.part_ml + (p0 + lane) * 2); ls = __ldcg(a.part_ml + (p0 + lane) * 2 + 1); }
-        const float mx = warp_max(ms);
-        const float f = ms == -INFINITY ? 0.0f : fast_exp2(ms - mx);
-        const float total = warp_sum(ls * f);
-        fac[hg * 32 + lane] = f / total;
+    // (max, sum) of every (head, split) into shared memory with one round of loads; the tiles are dead
+    float2* ml = reinterpret_cast<float2*>(smem);          // [G][nsplit]
+    for (int i = threadIdx.x; i < G * nsplit; i += BLOCK_THREADS) {
+        const int hg = i / nsplit, sp = i - hg * nsplit;
+        ml[i] = __ldcg(reinterpret_cast<const float2*>(a.part_ml) + ((size_t)li * a.nh + g * G + hg) * nsplit + sp);
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < G * D; idx += BLOCK_THREADS) {
-        const int hg = idx / D, dim = idx % D;
+    // four dimensions of one head per thread: all its loads of partial outputs are independent
+    for (int item = threadIdx.x; item < G * (D / 4); item += BLOCK_THREADS) {
+        const int hg = item / (D / 4), dim = (item % (D / 4)) * 4;
         const int head = g * G + hg;
+        const float2* mlh = ml + hg * nsplit;
+        float mx = -INFINITY, total = 0.0f;
+        for (int sp = 0; sp < nsplit; ++sp) mx = fmaxf(mx, mlh[sp].x);
         const float* po = a.part_o + ((size_t)li * a.nh + head) * nsplit * D + dim;
-        float acc = 0.0f;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 8
-        for (int sp = 0; sp < nsplit; ++sp) acc += __ldcg(po + (size_t)sp * D) * fac[hg * 32 + sp];
-        a.out[((size_t)t * a.nh + head) * D + dim] = __float2bfloat16_rn(acc);
+        for (int sp = 0; sp < nsplit; ++sp) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(po + (size_t)sp * D));
+            const float2 m_l = mlh[sp];
+            const float f = m_l.x == -INFINITY ? 0.0f : fast_exp2(m_l.x - mx);
+            total += m_l.y * f;
+            acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+        }
+        const float inv = 1.0f / total;
+        uint2 packed = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+        *reinterpret_cast<uint2*>(a.out + ((size_t)t * a.nh + head) * D + dim) = packed;
     }
     if (threadIdx.x == 0) a.counters[li * a.nkv + g] = 0;       // ready for the next launch
 }
@@ -450,14 +477,17 @@ attention_prefill_kernel(MmaAttnArgs a) {
 
     if (producer) {
         PageWindow pw;
-        pw.init(bt, tile0 * TK / a.page, hi, a.page, lane);
+        const PageDiv pd(a.page);
+        pw.init(bt, pd.div(tile0 * TK), hi, a.page, lane);
+        const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
+                     v_off = (size_t)a.nkv * a.page * D;
         for (int tile = tile0, it = 0; tile < tile1; ++tile, ++it) {
             const int st = it % STAGES;
             if (!cx_mbar_wait(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) gave_up = true;
             if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, 2 * TILE_BYTES);
             __syncwarp();
             produce_tile<D, TK>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
-                                full0 + 8 * st, tile * TK, lo, hi, pw, a.cache, g, a.page, a.nkv, lane);
+                                full0 + 8 * st, tile * TK, lo, hi, pw, a.cache, head_base, page_stride, v_off, pd, lane);
         }
         if (gave_up && a.status) atomicCAS(a.status, 0, 6);
         return;
