@@ -321,7 +321,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         }
         // Stores eight or sixteen finished columns c .. c + NE of row r (element (i, q0 + c + e)).
         constexpr int PRE = BN <= 32 ? BN : 1;
-        auto emit = [&](const auto& v, int c, int i, int q0, int tile_p, const float* pre) {
+        auto emit = [&](const auto& v, int c, int i, int q0, int tile_p, const float* pre, float g) {
             constexpr int NE = (int)(sizeof(v) / sizeof(float));
             if (a.gated) {                          // swapped: rows 0-63 gate, 64-127 up of features 64 tile_p + ..
                 const int feature = tile_p * 64 + (r & 63);
@@ -350,7 +350,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             }
             const bool row_ok = i < a.rows_p;
             if (a.residual) {                       // swapped, one tile of tokens: j = c + e is the token
-                const float g = row_ok ? a.gain[i] : 0.0f;
                 float x[NE];
 #pragma unroll
                 for (int e = 0; e < NE; ++e) {      // all loads first: the stores below would order them
@@ -392,6 +391,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             const int i = p0 + r;
             // narrow tiles: the residual values this tile may be added to are fetched while the MMAs run
             [[maybe_unused]] float res_pre[PRE];
+            const float gain_pre = (a.residual && i < a.rows_p) ? __ldg(a.gain + i) : 0.0f;
             if constexpr (PRE > 1) {
                 if (a.residual) {
 #pragma unroll
@@ -419,7 +419,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     float f[16];
 #pragma unroll
                     for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[e]);
-                    emit(f, c, i, q0, tile_p, res_pre);
+                    emit(f, c, i, q0, tile_p, res_pre, gain_pre);
                 }
             }
             // the accumulator has been read: hand it back to the MMA warp
@@ -445,13 +445,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 float acc[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
-                for (int sg = 0; sg < nseg; ++sg) {
-                    const int x = first_cta + sg;
-                    const float* src = a.partial + ((size_t)x * 2 + (x * U >= tile * S ? 0 : 1)) * BN * BM + r;
+                // eight segments' values are requested before the first is added (in order: the sum does
+                // not depend on which CTA finished when); a loop that adds as it loads would pay one trip
+                // to the L2 cache per segment
+                for (int sg0 = 0; sg0 < nseg; sg0 += 8) {
+                    float v[8][8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[e] += __ldcg(src + (c + e) * BM);
+                    for (int k = 0; k < 8; ++k) {
+                        const int x = first_cta + sg0 + k;
+                        const float* src = a.partial + ((size_t)x * 2 + (x * U >= tile * S ? 0 : 1)) * BN * BM + r;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[k][e] = sg0 + k < nseg ? __ldcg(src + (c + e) * BM) : 0.0f;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[e] += v[k][e];
                 }
-                emit(acc, c, i, q0, tile_p, res_pre);
+                emit(acc, c, i, q0, tile_p, res_pre, gain_pre);
             }
             if (threadIdx.x == 64) a.tickets[tile] = 0;       // ready for the next launch
         }
