@@ -41,6 +41,13 @@ def check_invariants(m: CacheManager):
         assert all(g.pool.ref_count(b) == 1 for b in held)
     slots = [rc.slot for rc in m.requests.values()]
     assert len(slots) == len(set(slots)) and len(slots) + len(m._free_slots) == m.max_num_seqs
+    # the tables as rows of one array (what the step function copies) say the same as the lists
+    for gi in range(len(m.paged)):
+        width = 1 + max([len(rc.tables[gi]) for rc in m.requests.values()] + [3])
+        rows = m.table_rows(gi, width if len(m.requests) % 2 else width + 2)      # widened now and then
+        for rc in m.requests.values():
+            t = rc.tables[gi]
+            assert list(rows[rc.slot, : len(t)]) == t and (rows[rc.slot, len(t):] == RELEASED).all()
 
 
 def test_groups_follow_the_layers_needs():

@@ -23,6 +23,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
+import numpy as np
 import torch
 
 from ..parts.base import PagedKVSpec, PagedKVView, StateSpec, StateView
@@ -93,6 +94,8 @@ class CacheManager:
                 raise TypeError(f"cache layer {layer}: unknown cache need {spec!r}")
         self._free_slots: List[int] = list(range(max_num_seqs - 1, -1, -1))
         self.requests: Dict[object, RequestCache] = {}
+        # every group's block tables as rows of one array (see table_rows); widened on demand
+        self._table_rows: List[np.ndarray] = [np.full((max_num_seqs, 0), RELEASED, dtype=np.int32) for _ in self.paged]
         if device is not None:
             self._allocate_device()
 
@@ -139,6 +142,8 @@ class CacheManager:
         slot = self._free_slots.pop()
         rc = RequestCache(tables=[[] for _ in self.paged], slot=slot, released=[0] * len(self.paged))
         self.requests[req_id] = rc
+        for t in self._table_rows:
+            t[slot, :] = RELEASED
         for g in self.state:
             if g.slots is not None:
                 g.slots[:, slot].zero_()
@@ -171,9 +176,12 @@ class CacheManager:
             if not g.pool.can_allocate(n):
                 raise OutOfPages(f"request {req_id!r} needs {n} more pages for {n_new} tokens; "
                                  f"{g.pool.num_free} of {self.num_pages} are free")
-        for g, table, n in zip(self.paged, rc.tables, need):
+        for gi, (g, table, n) in enumerate(zip(self.paged, rc.tables, need)):
             for _ in range(n):
-                table.append(g.pool.acquire())
+                page = g.pool.acquire()
+                if len(table) < self._table_rows[gi].shape[1]:
+                    self._table_rows[gi][rc.slot, len(table)] = page
+                table.append(page)
 
     def commit(self, req_id, n_new: int) -> None:
         """The request now holds ``n_new`` more tokens; give back what windows have passed."""
@@ -191,6 +199,8 @@ class CacheManager:
             for b in range(rc.released[gi], min(dead_blocks, len(table))):
                 g.pool.release(table[b])
                 table[b] = RELEASED
+                if b < self._table_rows[gi].shape[1]:
+                    self._table_rows[gi][rc.slot, b] = RELEASED
             rc.released[gi] = max(rc.released[gi], min(dead_blocks, len(table)))
 
     def free_request(self, req_id) -> None:
@@ -207,6 +217,19 @@ class CacheManager:
 
     def table(self, req_id, group: int) -> List[int]:
         return self.requests[req_id].tables[group]
+
+    def table_rows(self, group: int, width: int) -> np.ndarray:
+        """The block tables of the group as one int32 array [request slot, width], kept up to date
+        with every page handed out or given back (RELEASED where a request holds no page): the
+        step function copies rows of it instead of building tables from lists."""
+        rows = self._table_rows[group]
+        if rows.shape[1] < width:
+            wider = np.full((self.max_num_seqs, width), RELEASED, dtype=np.int32)
+            for rc in self.requests.values():
+                t = rc.tables[group][:width]
+                wider[rc.slot, : len(t)] = t
+            self._table_rows[group] = rows = wider
+        return rows
 
     def slot(self, req_id) -> int:
         return self.requests[req_id].slot

@@ -317,7 +317,10 @@ __global__ void rope_cache_kernel(RopeCacheArgs a, int heads_per_block) {
 // head and its partner chunk in the second half.
 __global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block) {
     extern __shared__ float2 trig[];                    // [d / 2] (cos, sin)
-    pdl_start();
+    // Positions, denominators and the block table belong to the step (copied in before its first
+    // kernel), not to the kernel before this one: the table of sines and cosines is made while that
+    // kernel still runs, and only qkv is read after griddepcontrol.wait.
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int nheads = a.nh + 2 * a.nkv;
     const int half = a.d / 2, chunks = half / 8;
@@ -327,10 +330,30 @@ __global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block) {
         sincosf((float)pos / a.denom[j], &sn, &cs);
         trig[j] = make_float2(cs, sn);
     }
-    __syncthreads();
     const int h = blockIdx.y * heads_per_block + threadIdx.x / chunks;
     const int c = threadIdx.x % chunks;
-    if (h >= nheads || threadIdx.x >= heads_per_block * chunks) return;
+    const bool mine = h < nheads && threadIdx.x < heads_per_block * chunks;
+    // where a k or v row goes
+    __nv_bfloat16* row_dst = nullptr;
+    int slot = 0;
+    if (mine && h >= a.nh && a.write_kv) {
+        const int r = a.req_of_token[t];
+        const int pg = a.block_table[(size_t)r * a.bt_stride + pos / a.page];
+        slot = pos % a.page;
+        __nv_bfloat16* base = (__nv_bfloat16*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
+        const int kvh = h < a.nh + a.nkv ? h - a.nh : h - a.nh - a.nkv;
+        const size_t which = h < a.nh + a.nkv ? 0 : (size_t)a.nkv * a.page * a.d;
+        row_dst = base + which + ((size_t)kvh * a.page + slot) * a.d;
+    }
+    float ba[8], bb[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        ba[e] = (mine && a.bias) ? a.bias[h * a.d + c * 8 + e] : 0.0f;
+        bb[e] = (mine && a.bias) ? a.bias[h * a.d + half + c * 8 + e] : 0.0f;
+    }
+    __syncthreads();
+    pdl_wait();
+    if (!mine) return;
     const __nv_bfloat16* src = (const __nv_bfloat16*)a.qkv + ((size_t)t * nheads + h) * a.d;
     const uint4 va = *reinterpret_cast<const uint4*>(src + c * 8);
     const uint4 vb = *reinterpret_cast<const uint4*>(src + half + c * 8);
@@ -340,8 +363,7 @@ __global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block) {
     const bool rotate = h < a.nh + a.nkv;
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-        float xa = __bfloat162float(pa[e]), xb = __bfloat162float(pb[e]);
-        if (a.bias) { xa += a.bias[h * a.d + c * 8 + e]; xb += a.bias[h * a.d + half + c * 8 + e]; }
+        float xa = __bfloat162float(pa[e]) + ba[e], xb = __bfloat162float(pb[e]) + bb[e];
         if (rotate) {
             const float2 cs = trig[c * 8 + e];
             const float ra = xa * cs.x - xb * cs.y;
@@ -357,14 +379,8 @@ __global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block) {
         *reinterpret_cast<uint4*>(dst + half + c * 8) = *reinterpret_cast<const uint4*>(ob);
         return;
     }
-    if (!a.write_kv) return;
-    const int r = a.req_of_token[t];
-    const int pg = a.block_table[(size_t)r * a.bt_stride + pos / a.page];
-    const int slot = pos % a.page;
-    __nv_bfloat16* base = (__nv_bfloat16*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
-    const int kvh = h < a.nh + a.nkv ? h - a.nh : h - a.nh - a.nkv;
-    const size_t which = h < a.nh + a.nkv ? 0 : (size_t)a.nkv * a.page * a.d;
-    __nv_bfloat16* dst = base + which + ((size_t)kvh * a.page + slot) * a.d;
+    if (!row_dst) return;
+    __nv_bfloat16* dst = row_dst;
     // whole 16-byte chunks move together in the rows' layout (kv_row_pos)
     *reinterpret_cast<uint4*>(dst + kv_row_pos(c * 8, slot, a.d, 2)) = *reinterpret_cast<const uint4*>(oa);
     *reinterpret_cast<uint4*>(dst + kv_row_pos(half + c * 8, slot, a.d, 2)) = *reinterpret_cast<const uint4*>(ob);

@@ -210,30 +210,43 @@ class ModelRunner:
         cl = section("ctx_lens", r)
         sl = section("state_slots", r)
         lr = section("logit_rows", m)
-        t0 = 0
-        mi = 0
-        qs[0] = 0
-        for i, e in enumerate(entries):
-            ql = q_lens[i]
-            ids = np.asarray(e.tokens, dtype=np.int64)
-            if ids.min() < 0 or ids.max() >= vocab:
-                raise StepError(f"request {e.req_id!r}: token id outside the vocabulary of {vocab}")
-            tok[t0: t0 + ql] = ids
-            pos[t0: t0 + ql] = np.arange(ctx_lens[i], ctx_lens[i] + ql)
-            rot[t0: t0 + ql] = i
-            for w in e.want:
-                lr[mi] = t0 + w
-                mi += 1
-            t0 += ql
-            qs[i + 1] = t0
+        decode_only = max(q_lens) == 1
+        if decode_only:
+            # one token per request: every section is a whole-array assignment
+            tok[:] = [e.tokens[0] for e in entries]
+            if tok.min() < 0 or tok.max() >= vocab:
+                raise StepError(f"a token id lies outside the vocabulary of {vocab}")
+            pos[:] = ctx_lens
+            rot[:] = np.arange(r, dtype=np.int32)
+            qs[:] = np.arange(r + 1, dtype=np.int32)
+            mi = 0
+            for i, e in enumerate(entries):
+                for w in e.want:
+                    lr[mi] = i + w
+                    mi += 1
+        else:
+            t0 = 0
+            mi = 0
+            qs[0] = 0
+            for i, e in enumerate(entries):
+                ql = q_lens[i]
+                ids = np.asarray(e.tokens, dtype=np.int64)
+                if ids.min() < 0 or ids.max() >= vocab:
+                    raise StepError(f"request {e.req_id!r}: token id outside the vocabulary of {vocab}")
+                tok[t0: t0 + ql] = ids
+                pos[t0: t0 + ql] = np.arange(ctx_lens[i], ctx_lens[i] + ql)
+                rot[t0: t0 + ql] = i
+                for w in e.want:
+                    lr[mi] = t0 + w
+                    mi += 1
+                t0 += ql
+                qs[i + 1] = t0
         cl[:] = ctx_lens
         sl[:] = slots
         for g in range(self.n_groups):
+            # rows of the manager's table array, picked by the requests' slots in one go
             bt = section(f"block_table{g}", r * self.max_blocks).reshape(r, self.max_blocks)
-            for i, e in enumerate(entries):
-                table = self.cache.table(e.req_id, g)
-                bt[i, : len(table)] = table
-                bt[i, len(table):] = -1
+            np.take(self.cache.table_rows(g, self.max_blocks)[:, : self.max_blocks], slots, axis=0, out=bt)
         for name, arr in extra.items():
             section("x:" + name, arr.size)[:] = arr.ravel()
         self.meta_dev[:off].copy_(self.meta_host[:off], non_blocking=True)
@@ -252,7 +265,7 @@ class ModelRunner:
             block_tables=[dev(f"block_table{g}", (r, self.max_blocks)) for g in range(self.n_groups)],
             state_slots=dev("state_slots"), logit_rows=dev("logit_rows"), n_logit_rows=m,
             h_q_start=[int(x) for x in qs], h_ctx_lens=list(ctx_lens), h_state_slots=list(slots),
-            decode_only=all(q == 1 for q in q_lens), max_q_len=max(q_lens),
+            decode_only=decode_only, max_q_len=max(q_lens),
             max_total_len=max(c + q for c, q in zip(ctx_lens, q_lens)),
             split_len=max(256, 1 << (max(c + q for c, q in zip(ctx_lens, q_lens)) - 1).bit_length()),
             extras={name: dev("x:" + name, arr.shape) for name, arr in extra.items()})
