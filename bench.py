@@ -96,6 +96,49 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
+def write_timeline(path, batch, runner, cache, rng, vocab):
+    """Kernel start and end times of one steady decode step, from the profiler's device-side records.
+    Under programmatic dependent launch a kernel starts (its CTAs become resident) long before the
+    kernel before it ends, so the column to read is how much later than its predecessor it ENDS."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from vllm_cpp_b200.engine.runner import StepEntry
+    ids = [f"t{i}" for i in range(batch)]
+    for r in ids:
+        cache.add_request(r)
+        cache.reserve(r, CONTEXT - 64)
+        cache.commit(r, CONTEXT - 64)
+
+    def one():
+        runner.step([StepEntry(r, [int(rng.integers(0, vocab))], [0]) for r in ids])
+
+    for _ in range(4):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(2):
+            one()
+        torch.cuda.synchronize()
+    tmp = path + ".trace.json"
+    prof.export_chrome_trace(tmp)
+    with open(tmp) as f:
+        ev = [e for e in json.load(f)["traceEvents"] if e.get("cat") == "kernel"]
+    os.remove(tmp)
+    for r in ids:
+        cache.free_request(r)
+    ev.sort(key=lambda e: e["ts"])
+    ev = ev[len(ev) // 2:]                          # the second step
+    t0 = ev[0]["ts"]
+    rows = sorted(((e["ts"] + e["dur"] - t0, e["ts"] - t0, e["name"]) for e in ev))
+    with open(path, "w") as f:
+        f.write(f"# one decode step, batch {batch}, contexts {CONTEXT - 60}: end, start (us from the step's first kernel), "
+                "end minus previous end, kernel\n")
+        prev = 0.0
+        for end, start, name in rows:
+            f.write(f"{end:9.2f} {start:9.2f} {end - prev:8.2f}  {name[:90]}\n")
+            prev = end
+
+
 def model_numbers(cfg):
     h, nh, nkv = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
     d = h // nh
@@ -119,6 +162,9 @@ def main() -> int:
                     help="run one part only (for profiling); the other fields of the line are null")
     ap.add_argument("--no-pdl", action="store_true", help="ordinary launches instead of programmatic dependent launch")
     ap.add_argument("--library-gemm", action="store_true", help="cuBLAS for every bfloat16 product (no tcgen05 kernel)")
+    ap.add_argument("--timeline", metavar="FILE", default=None,
+                    help="with --only decode: also write the device timeline of one decode step (every kernel's "
+                         "start and end as CUPTI reports them through torch.profiler) to FILE as text")
     ap.add_argument("--no-cuda-graphs", action="store_true",
                     help="launch every kernel of a decode step directly (for a profiler's launch list)")
     a = ap.parse_args()
@@ -257,6 +303,8 @@ def main() -> int:
     clocks.start()
     ms, launches, kv_bytes = time_decode(a.batch, steps, warmup)
     clock_info = clocks.stop()
+    if a.only == "decode" and a.timeline:
+        write_timeline(a.timeline, a.batch, runner, cache, rng, vocab)
     if a.only == "decode":
         print(json.dumps({"metric": METRIC, "only": "decode", "batch": a.batch, "ms_per_step": round(ms, 4),
                           "value": round(a.batch / (ms * 1e-3), 1), "unit": "tokens/s", "gpu_launches": launches,
