@@ -15,8 +15,9 @@
 // SM, so every SM streams the same number of bytes whatever the shape.  A CTA's run is a
 // sequence of segments (a tile and a range of its slabs).  A segment that covers all of K
 // is stored directly; the others leave float partial tiles in global scratch memory, take
-// a ticket of their tile, and the CTA that draws the tile's last ticket adds them up.  No
-// CTA ever waits for another.  The ring of stages runs on across segments, and two
+// a ticket of their tile, and the CTA that draws the tile's last ticket adds them up: no CTA
+// waits for another.  (Tiles of 32 columns and more share the merge among the tile's CTAs at the end
+// of their runs instead, see the epilogue.)  The ring of stages runs on across segments, and two
 // accumulators in tensor memory alternate, so loads and MMAs of the next segment overlap
 // the read-back of the last.
 //
@@ -147,6 +148,17 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
                    "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                  : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Bounded wait until *p >= target (a count that other CTAs of this launch raise).  False: gave up.
+__device__ __forceinline__ bool wait_count(const int* p, int target) {
+    for (uint32_t spin = 0; spin < (1u << 21); ++spin) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+        if (v >= target) return true;
+        __nanosleep(20);
+    }
+    return false;
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled
@@ -384,6 +396,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 else reinterpret_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16_rn(x);
             }
         };
+        [[maybe_unused]] int pending[2];       // wide tiles: this CTA's partial tiles, merged after the loop
+        [[maybe_unused]] int n_pending = 0;
         while (seg.next(tile, s0, s1)) {
             const int buf = n & 1;
             const int tile_p = tile % a.tiles_p;
@@ -428,6 +442,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
             ++n;
             if (!part) continue;
+            if constexpr (BN >= 32) {
+                // wide tiles: count this segment in; the tile's CTAs share its merge at the end of their runs
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) atomicAdd(&a.tickets[tile], 1);
+                pending[n_pending++] = tile;
+                continue;
+            }
             // partial tile: take a ticket; the last of the tile's segments to arrive adds them up
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -465,6 +487,65 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 emit(acc, c, i, q0, tile_p, res_pre, gain_pre);
             }
             if (threadIdx.x == 64) a.tickets[tile] = 0;       // ready for the next launch
+        }
+        // Wide tiles (32 columns and more): adding a tile's partials up is too much for one CTA at the
+        // end of the kernel, so every CTA that computed a segment of the tile merges a share of its
+        // columns.  That needs all segments to be there: the CTAs wait for the tile's count, here, after
+        // all their own segments are written (every CTA of the grid is resident by then: dependent
+        // kernels start only after all of them have, and nobody waits before this point).  Bounded.
+        if constexpr (BN >= 32) {
+            for (int k = 0; k < n_pending; ++k) {
+                const int tl = pending[k];
+                const int first_cta = (tl * S) / U;
+                const int nseg = ((tl + 1) * S - 1) / U - first_cta + 1;
+                if (threadIdx.x == 64 && !flags[0] && !wait_count(a.tickets + tl, nseg)) {
+                    flags[0] = 1;
+                    atomicCAS(a.status, 0, 8);
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (!flags[0]) {
+                    __threadfence();
+                    const int tile_p = tl % a.tiles_p;
+                    const int q0 = (tl / a.tiles_p) * BN, i = tile_p * BM + r;
+                    const int valid = min(BN, a.rows_q - q0);
+                    const int share = (((valid + nseg - 1) / nseg) + 7) & ~7;          // whole groups of eight columns
+                    const int c_begin = (cta - first_cta) * share, c_end = min(valid, c_begin + share);
+                    [[maybe_unused]] float res_pre[PRE];
+                    const float gain_pre = (a.residual && i < a.rows_p) ? __ldg(a.gain + i) : 0.0f;
+                    if constexpr (PRE > 1) {
+                        if (a.residual) {
+#pragma unroll
+                            for (int e = 0; e < PRE; ++e)
+                                res_pre[e] = (i < a.rows_p && q0 + e < a.rows_q) ? __ldcg(a.residual + (size_t)(q0 + e) * a.ldr + i) : 0.0f;
+                        }
+                    }
+#pragma unroll 1
+                    for (int c = c_begin; c < c_end; c += 8) {
+                        float acc[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+                        for (int sg0 = 0; sg0 < nseg; sg0 += 8) {
+                            float v[8][8];
+#pragma unroll
+                            for (int kk = 0; kk < 8; ++kk) {
+                                const int x = first_cta + sg0 + kk;
+                                const float* src = a.partial + ((size_t)x * 2 + (x * U >= tl * S ? 0 : 1)) * BN * BM + r;
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[kk][e] = sg0 + kk < nseg ? __ldcg(src + (c + e) * BM) : 0.0f;
+                            }
+#pragma unroll
+                            for (int kk = 0; kk < 8; ++kk)
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) acc[e] += v[kk][e];
+                        }
+                        emit(acc, c, i, q0, tile_p, res_pre, gain_pre);
+                    }
+                }
+                // the last of the tile's CTAs to be done with it clears the count for the next launch
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64 && atomicAdd(&a.tickets[tl], 1) == 2 * nseg - 1) a.tickets[tl] = 0;
+            }
         }
     }
     // An aborted CTA may still have copies in flight: give each armed stage a bounded chance to land.
@@ -632,7 +713,7 @@ VCB_EXPORT int vcb_gemm_bf16_tcgen05_fused(const void* p, int rows_p, int ldp, c
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
         case 16: return launch<16, 6>(mp, mq, a, ctas, s);
-        case 32: return launch<32, 9>(mp, mq, a, ctas, s);
+        case 32: return launch<32, 5>(mp, mq, a, ctas, s);
         case 64: return launch<64, 8>(mp, mq, a, ctas, s);
         case 128: return launch<128, 6>(mp, mq, a, ctas, s);
         default: return launch<256, 4>(mp, mq, a, ctas, s);
