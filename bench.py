@@ -341,7 +341,8 @@ def main() -> int:
                    "head_dim": nums["d"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
                    "global_batch": a.batch, "seq_len": CONTEXT, "kv_block": 16, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (a decode step reads %.1f GB)" % (step_bytes / 1e9),
-                   "cuda_graphs": bool(ecfg.use_cuda_graphs), "peaks": peaks["source"], "load_s": round(load_s, 1)},
+                   "cuda_graphs": bool(ecfg.use_cuda_graphs), "overlap_steps": bool(ecfg.overlap_decode_steps),
+                   "peaks": peaks["source"], "load_s": round(load_s, 1)},
         "clocks": clock_info,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,

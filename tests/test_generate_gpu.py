@@ -92,6 +92,48 @@ def test_stop_token_and_length(tmp_path):
         llm.generate([[]], SamplingParams(max_tokens=1))
 
 
+def test_steps_launched_ahead_give_the_same_tokens(tmp_path):
+    """With overlap_decode_steps the engine launches a step before it has read the step before it.
+    Requests that stop at different times (stop token, length), a request that arrives while others
+    decode and one that is aborted: the same tokens as with the option off, nothing left behind."""
+    from vllm_cpp_b200 import SamplingParams
+    cfg, _ = CONFIGS["B"]
+    prompts = [token_ids(cfg, n, 90 + n) for n in (3, 20, 41, 7)]
+    runs = {}
+    for overlap in (False, True):
+        _, _, llm = make_llm(tmp_path, "B", "float32", overlap_decode_steps=overlap)
+        eng = llm.engine
+        free = llm.generate(prompts[:1], SamplingParams(max_tokens=24, temperature=0.7, seed=5, ignore_eos=True))[0]
+        params = [SamplingParams(max_tokens=24, temperature=0.7, seed=5, stop_token_ids=[free[9]]),      # stops early
+                  SamplingParams(max_tokens=30, temperature=0.0, ignore_eos=True),
+                  SamplingParams(max_tokens=11, temperature=1.1, seed=9, top_k=20, ignore_eos=True),
+                  SamplingParams(max_tokens=16, temperature=0.0, ignore_eos=True)]
+        ids = [eng.add_request(p, sp) for p, sp in zip(prompts[:3], params[:3])]
+        got = {i: [] for i in ids}
+        aborted, steps, ahead_seen = None, 0, 0
+        while eng.has_pending_work():
+            for o in eng.step():
+                got[o.seq_id].extend(o.tokens)
+            steps += 1
+            ahead_seen += eng._ahead is not None
+            if steps == 6:                               # arrives while the others decode
+                late = eng.add_request(prompts[3], params[3])
+                got[late] = []
+            if steps == 14:
+                aborted = ids[1]
+                eng.abort_request(aborted)
+        assert -1 not in sum(got.values(), []), "a placeholder reached the caller"
+        assert (ahead_seen > 5) == overlap
+        assert eng.cache.num_free_pages() == 64 and not eng.cache.requests
+        runs[overlap] = [got[ids[0]], got[ids[1]], got[ids[2]], got[late]]
+    off, on = runs[False], runs[True]
+    # the aborted request (second) may have got a token more or less before the abort took hold
+    n = min(len(off[1]), len(on[1]))
+    assert off[1][:n] == on[1][:n] and abs(len(off[1]) - len(on[1])) <= 1
+    assert len(off[0]) == 10 and off[0] == on[0] and len(off[2]) == 11 and off[2] == on[2]
+    assert len(off[3]) == 16 and off[3] == on[3]
+
+
 def test_long_decoding_stays_on_the_plain_logits(tmp_path):
     """160 tokens decoded one by one after a 3-token prompt, replayed against the plain logits."""
     from vllm_cpp_b200.engine.runner import StepEntry

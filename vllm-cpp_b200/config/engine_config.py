@@ -71,6 +71,10 @@ class EngineConfig:
 
     # Capture pure-decode steps in CUDA graphs.
     use_cuda_graphs: bool = True
+    # While every running request decodes, launch the next step before this step's tokens
+    # have reached the host (they are fed to it on the device), so the GPU never waits for
+    # the host between steps.  The tokens are the same either way.
+    overlap_decode_steps: bool = True
 
     def __post_init__(self):
         self.validate()

@@ -10,6 +10,11 @@ One step (src/core/engine.cpp:106-127 is schedule -> prefill -> decode -> sample
 schedule -> one batch through ``ModelRunner.step`` with prompt portions beside
 decoded tokens -> sampling on the device for the rows that end a request's known
 tokens -> token ids to the host -> append, check stop, free finished requests.
+
+While every running request decodes, the step after is launched before this step's tokens
+are read (``overlap_decode_steps``): its metadata depends on lengths only, and the token
+ids reach it on the device.  ``step`` still returns one step's news per call, in order; a
+request that turns out to have ended leaves one unused row in the step launched ahead.
 """
 from __future__ import annotations
 
@@ -46,6 +51,16 @@ class StepStats:
     preemptions: int = 0
 
 
+@dataclass
+class _InFlight:
+    """A step that is on the device: what was scheduled, who gets a token, where in their outputs."""
+    items: list
+    sampled: List[Sequence]
+    slots: List[int]
+    handle: object
+    stats: StepStats
+
+
 class Engine:
     def __init__(self, config: EngineConfig):
         self.config = config
@@ -57,6 +72,7 @@ class Engine:
         self.sequences: Dict[int, Sequence] = {}
         self._next_id = 0
         self.last_stats = StepStats()
+        self._ahead: Optional[_InFlight] = None       # a step launched before the one before it was read
         self.initialized = True
 
     # ------------------------------------------------------------- requests
@@ -99,10 +115,10 @@ class Engine:
         return self.scheduler.has_pending_work()
 
     # ----------------------------------------------------------------- step
-    def step(self) -> List[GenerationOutput]:
-        items = self.scheduler.schedule()
-        if not items:
-            return []
+    PLACEHOLDER = -1          # stands in a request's outputs for a token that is still on the device
+
+    def _launch(self, items, token_source=None) -> "_InFlight":
+        """Send one scheduled batch to the device: model, sampling, copy of the ids; nothing is waited for."""
         entries, sampled = [], []
         stats = StepStats(num_requests=len(items))
         for it in items:
@@ -116,29 +132,80 @@ class Engine:
             if it.samples:
                 sampled.append(it.seq)
         with torch.no_grad():
-            logits = self.runner.step(entries)
+            logits = self.runner.step(entries, device_tokens=token_source)
             rows = [SamplingRow(s.params.temperature, s.params.top_p, s.params.top_k,
                                 s.params.repetition_penalty, s.output_tokens,
                                 uniform_for(s.params.seed, s.output_len)) for s in sampled]
-            tokens = self.sampler.sample(logits, rows)
+            handle = self.sampler.launch(logits, rows)
         for it in items:
             it.seq.num_processed_tokens += it.count
+        # the token each sampled request will get: known to the host at _collect
+        slots = []
+        for seq in sampled:
+            slots.append(seq.output_len)
+            seq.output_tokens.append(self.PLACEHOLDER)
+        return _InFlight(items, sampled, slots, handle, stats)
+
+    def _may_run_ahead(self, flight: "_InFlight") -> bool:
+        """True if the step after ``flight`` is known without its tokens: every running request took
+        part with one token and will go on (no length limit reached, no waiting request to admit,
+        no repetition penalty, which needs the ids on the host)."""
+        if not self.config.overlap_decode_steps or self.scheduler.waiting:
+            return False
+        if len(flight.items) != len(self.scheduler.running) or len(flight.sampled) != len(flight.items):
+            return False
+        for it in flight.items:
+            seq = it.seq
+            if it.count != 1 or seq.output_len >= seq.params.max_tokens or seq.params.repetition_penalty != 1.0:
+                return False
+        return True
+
+    def _collect(self, flight: "_InFlight") -> List[GenerationOutput]:
+        """Wait for the step's token ids, put them where the placeholders stand, check the stops."""
+        tokens = self.sampler.wait(flight.handle)
         outputs = []
-        for seq, tok in zip(sampled, tokens):
-            seq.output_tokens.append(tok)
+        for seq, slot, tok in zip(flight.sampled, flight.slots, tokens):
+            if seq.is_finished:
+                continue                  # ended (or was aborted) while this step was already on its way
+            seq.output_tokens[slot] = tok
             reason = None
             if not seq.params.ignore_eos and tok in seq.params.stop_token_ids:
                 reason = "stop"
-            elif seq.output_len >= seq.params.max_tokens:
+            elif slot + 1 >= seq.params.max_tokens:
                 reason = "length"
             if reason:
+                del seq.output_tokens[slot + 1:]          # a placeholder of a step launched ahead
                 self.scheduler.finish_sequence(seq, reason)
                 self.sequences.pop(seq.seq_id, None)
             outputs.append(GenerationOutput(seq.seq_id, [tok], reason is not None, reason))
-        stats.free_pages = self.cache.num_free_pages()
-        stats.preemptions = self.scheduler.num_preemptions
-        self.last_stats = stats
+        flight.stats.free_pages = self.cache.num_free_pages()
+        flight.stats.preemptions = self.scheduler.num_preemptions
+        self.last_stats = flight.stats
         return outputs
+
+    def step(self) -> List[GenerationOutput]:
+        flight, self._ahead = self._ahead, None
+        if flight is None:
+            items = self.scheduler.schedule()
+            if not items:
+                self.last_stats = StepStats()
+                return []
+            flight = self._launch(items)
+        if self._may_run_ahead(flight):
+            items = self.scheduler.schedule()
+            # only a plain continuation is sent ahead: the same requests, in the same order, one token each
+            if len(items) == len(flight.sampled) and all(
+                    it.seq is s and it.count == 1 and it.samples for it, s in zip(items, flight.sampled)):
+                self._ahead = self._launch(items, token_source=self.sampler.device_ids(flight.handle))
+            elif items:
+                # Not a plain continuation (pages ran short: somebody sits out or was preempted).  The
+                # batch is scheduled, so it runs, but only once this step's tokens are known.
+                outputs = self._collect(flight)
+                items = [it for it in items if not it.seq.is_finished]
+                if items:
+                    self._ahead = self._launch(items)
+                return outputs
+        return self._collect(flight)
 
     def run(self, callback: Optional[Callable[[GenerationOutput], None]] = None) -> None:
         """Step until nothing is pending (src/core/engine.cpp:129-136)."""

@@ -86,11 +86,18 @@ class ModelRunner:
                 + self.n_groups * _align(r * self.max_blocks))
 
     # ------------------------------------------------------------------ step
-    def step(self, entries: List[StepEntry]) -> torch.Tensor:
+    def step(self, entries: List[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one batch; returns float32 logits [number of wanted places, vocab] on the device,
         in the order of the entries and of each entry's ``want``.  The tensor is a
-        view of the runner's logits buffer and is overwritten by the next step."""
-        step = self._prepare(entries)
+        view of the runner's logits buffer and is overwritten by the next step.
+        ``device_tokens``: int32 ids on the device, one per entry of a step in which every entry
+        brings one token; they replace the entries' token ids (which are then not looked at) in
+        stream order, for a step launched before the ids it continues from have reached the host."""
+        step = self._prepare(entries, ids_on_device=device_tokens is not None)
+        if device_tokens is not None:
+            if not step.decode_only or device_tokens.numel() != step.n_tokens:
+                raise StepError("device_tokens needs one token per entry")
+            step.token_ids.copy_(device_tokens, non_blocking=True)
         if self.use_cuda_graphs and step.decode_only and step.n_logit_rows == step.n_reqs:
             out = self._run_decode_graph(step)
         else:
@@ -143,7 +150,7 @@ class ModelRunner:
         ops.add_launches(captured)
         return self.logits[: step.n_logit_rows]
 
-    def _prepare(self, entries: List[StepEntry]) -> StepContext:
+    def _prepare(self, entries: List[StepEntry], ids_on_device: bool = False) -> StepContext:
         if not entries:
             raise StepError("a step needs at least one entry")
         r = len(entries)
@@ -213,9 +220,12 @@ class ModelRunner:
         decode_only = max(q_lens) == 1
         if decode_only:
             # one token per request: every section is a whole-array assignment
-            tok[:] = [e.tokens[0] for e in entries]
-            if tok.min() < 0 or tok.max() >= vocab:
-                raise StepError(f"a token id lies outside the vocabulary of {vocab}")
+            if ids_on_device:
+                tok[:] = 0
+            else:
+                tok[:] = [e.tokens[0] for e in entries]
+                if tok.min() < 0 or tok.max() >= vocab:
+                    raise StepError(f"a token id lies outside the vocabulary of {vocab}")
             pos[:] = ctx_lens
             rot[:] = np.arange(r, dtype=np.int32)
             qs[:] = np.arange(r + 1, dtype=np.int32)
