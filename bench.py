@@ -33,6 +33,15 @@ QWEN25_7B = {
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "use_sliding_window": False,
     "max_position_embeddings": 32768, "hidden_act": "silu", "initializer_range": 0.02,
 }
+# further sizes of the same architecture, for --size (layers, hidden, heads, kv heads, intermediate, rms eps)
+SIZES = {
+    "7b": dict(num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+               intermediate_size=18944, rms_norm_eps=1e-6),
+    "14b": dict(num_hidden_layers=48, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                intermediate_size=13824, rms_norm_eps=1e-5),
+    "32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                intermediate_size=27648, rms_norm_eps=1e-6),
+}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 METRIC = "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen2.5-7B bf16)"
@@ -139,6 +148,45 @@ def write_timeline(path, batch, runner, cache, rng, vocab):
             prev = end
 
 
+def run_mix(cfg, a) -> int:
+    """Continuous batching through the engine's own API: requests of mixed lengths arrive at once, prompts
+    are read in portions of at most 2,048 tokens a step beside the tokens other requests decode."""
+    import numpy as np
+    import torch
+    from vllm_cpp_b200 import EngineConfig, SamplingParams
+    from vllm_cpp_b200.engine.llm_engine import Engine
+    n_req, gen, budget = 32, 256, 2048
+    rng = np.random.default_rng(3)
+    lens = rng.integers(128, 4097, size=n_req)
+    pages = int(sum(-(-(int(n) + gen) // 16) for n in lens)) + 64
+    ecfg = EngineConfig(load_format="random", model_config=cfg, seed=0, dtype="bfloat16", block_size=16,
+                        num_gpu_blocks=pages, max_num_seqs=n_req, max_model_len=4096 + gen,
+                        max_num_batched_tokens=budget, max_tokens_per_step=budget)
+    engine = Engine(ecfg)
+    sp = SamplingParams(max_tokens=gen, temperature=0.0, ignore_eos=True)
+
+    def run():
+        for n in lens:
+            engine.add_request(rng.integers(0, cfg["vocab_size"], size=int(n)).tolist(), sp)
+        torch.cuda.synchronize()
+        t, steps, out = time.perf_counter(), 0, 0
+        while engine.has_pending_work():
+            out += len(engine.step())
+            steps += 1
+        torch.cuda.synchronize()
+        return time.perf_counter() - t, steps, out
+
+    run()                                             # warm-up: sizes workspaces, captures graphs
+    dt, steps, out = run()
+    prompt = int(lens.sum())
+    print(json.dumps({"metric": "continuous batching: 32 requests, prompts 128-4096, 256 generated each, 2048 tokens a step",
+                      "value": round(out / dt, 1), "unit": "generated tokens/s", "seconds": round(dt, 3), "steps": steps,
+                      "prompt_tokens": prompt, "generated_tokens": out,
+                      "all_tokens_per_s": round((prompt + out) / dt, 1), "preemptions": engine.scheduler.num_preemptions,
+                      "config": {"model": f"Qwen2.5-{a.size.upper()} layer sizes", "layers": cfg["num_hidden_layers"]}}))
+    return 0
+
+
 def model_numbers(cfg):
     h, nh, nkv = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
     d = h // nh
@@ -157,6 +205,11 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=QWEN25_7B["num_hidden_layers"],
                     help="fewer layers than the 28 of the configuration (recorded in config)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--size", default="7b", choices=sorted(SIZES),
+                    help="layer sizes: Qwen2.5-7B (the benchmark's), 14B or 32B")
+    ap.add_argument("--mix", action="store_true",
+                    help="instead of the fixed-batch measurement: 32 requests with prompts of 128 to 4,096 tokens and "
+                         "256 generated tokens each through the engine, 2,048 tokens a step (continuous batching)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only (for profiling); the other fields of the line are null")
@@ -189,7 +242,11 @@ def main() -> int:
         ops.set_pdl(False)
     if a.library_gemm:
         ops.set_tcgen05_linear(False)
-    cfg = dict(QWEN25_7B, num_hidden_layers=a.layers)
+    cfg = dict(QWEN25_7B, **SIZES[a.size])
+    if a.size == "7b" or a.layers != QWEN25_7B["num_hidden_layers"]:
+        cfg["num_hidden_layers"] = a.layers
+    if a.mix:
+        return run_mix(cfg, a)
     nums = model_numbers(cfg)
     peaks = load_peaks()
     max_batch = max(64, a.batch)
@@ -335,8 +392,8 @@ def main() -> int:
         "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids",
-        "config": {"model": "Qwen2.5-7B layer sizes", "layers": cfg["num_hidden_layers"],
-                   "layers_of_configuration": QWEN25_7B["num_hidden_layers"], "hidden": cfg["hidden_size"],
+        "config": {"model": f"Qwen2.5-{a.size.upper()} layer sizes", "layers": cfg["num_hidden_layers"],
+                   "layers_of_configuration": SIZES[a.size]["num_hidden_layers"], "hidden": cfg["hidden_size"],
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": nums["d"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
                    "global_batch": a.batch, "seq_len": CONTEXT, "kv_block": 16, "parallelism": "single GPU",

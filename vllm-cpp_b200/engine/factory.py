@@ -58,7 +58,10 @@ def build(cfg: EngineConfig) -> Tuple[DecoderModel, CacheManager, ModelRunner]:
     torch.backends.cuda.matmul.allow_tf32 = False
     with torch.cuda.device(device), torch.no_grad():
         model = build_model(cfg, device)
-        model.prepare_products()
+        # the decode images of the weights may take a third of what the weights left free
+        free, total = torch.cuda.mem_get_info(device)
+        usable = int(total * cfg.gpu_memory_utilization / 100) - (total - free)
+        model.prepare_products(image_budget=max(0, usable // 3))
         specs = model.cache_specs()
         max_model_len = min(cfg.max_model_len, model.spec.max_position_embeddings)
         if cfg.num_gpu_blocks is not None:

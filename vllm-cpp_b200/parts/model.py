@@ -95,7 +95,7 @@ class DecoderModel:
         self.final_norm.load_params({local: tensors[s.final_norm_prefix + local]
                                      for local in self.final_norm.param_specs()})
 
-    def prepare_products(self, tune: bool = True) -> None:
+    def prepare_products(self, tune: bool = True, image_budget: Optional[int] = None) -> None:
         """bfloat16 only: decide, for every shape of weight matrix and bucket of token counts, whether the
         engine's tcgen05 product or the library's runs when a step has few tokens, and make the pre-tiled
         images of the matrices the engine's kernel will read (see csrc/gemm_tcgen05.cu).  Both are
@@ -103,7 +103,10 @@ class DecoderModel:
         kernel needs no norm or activation kernels (parts/block.py), so the layers' products are
         measured together first: all on the engine's kernel if that beats the library's products with
         the kernels between them, else each product on its own merits; the output product is chosen
-        by itself."""
+        by itself.
+        ``image_budget``: bytes the images may take (None: no limit).  Gated images come first (without
+        one the activation stays a kernel of its own), then the others by size; a matrix without an
+        image is read through a tensor map, a few percent slower."""
         if self.dtype != torch.bfloat16:
             return
         layer_shapes, fusable_norms = {}, 0          # (shape, gated) -> matrices
@@ -116,17 +119,33 @@ class DecoderModel:
             first = self.blocks[0]
             fusable_norms = sum(1 for nrm in (first.mixer_norm, first.feed_forward_norm) if nrm.split() is not None)
         tunable = {key: mats for key, mats in layer_shapes.items() if key[0][1] % 8 == 0}
+        head_key = (tuple(self.lm_head.shape), 0)
         head_ok = self.lm_head.shape[1] % 8 == 0
+        groups = dict(tunable)
+        if head_ok and head_key not in groups:
+            groups[head_key] = [self.lm_head]
+
+        def image_bytes(key, mats):
+            (rows, k), gated = key
+            tiles = -(-gated // 64) if gated else -(-rows // 128)
+            return len(mats) * tiles * -(-k // 64) * 16384
+
+        imaged, spent = set(), 0
+        for key in sorted(groups, key=lambda kk: (kk[1] == 0, -image_bytes(kk, groups[kk]))):
+            need = image_bytes(key, groups[key])
+            if image_budget is None or spent + need <= image_budget:
+                imaged.add(key)
+                spent += need
+        gated_of = {key: (key[1] if key in imaged else 0) for key in groups}     # a gated product only with its image
+
         measure = tune and ops.linear_tuning()
-        for (shape, gated), mats in tunable.items():
-            for m in mats[:8]:                    # the kernel is measured as it will run: on the images
-                ops.tile_weights(m, gated)
-        if head_ok:
-            ops.tile_weights(self.lm_head)
+        for key in imaged:
+            for m in groups[key][:8]:             # the kernel is measured as it will run: on the images
+                ops.tile_weights(m, key[1])
         if measure:
             whole = {}
             if len(tunable) == len(layer_shapes) and tunable:
-                whole = ops.measure_layer([(mats[:8], key[1]) for key, mats in tunable.items()], self.hidden,
+                whole = ops.measure_layer([(mats[:8], gated_of[key]) for key, mats in tunable.items()], self.hidden,
                                           fusable_norms, self.dtype)
             times = None
             for bucket, _ in ops.TOKEN_BUCKETS:
@@ -135,7 +154,7 @@ class DecoderModel:
                         ops.choose_linear(key[0][0], key[0][1], bucket, torch.bfloat16, True)
                     continue
                 if times is None:
-                    times = {key: ops.measure_linear(mats[:8], gated=key[1]) for key, mats in tunable.items()}
+                    times = {key: ops.measure_linear(mats[:8], gated=gated_of[key]) for key, mats in tunable.items()}
                 for key in tunable:                       # each product on its own merits
                     if bucket in times[key]:
                         t_ours, t_lib = times[key][bucket]
@@ -143,12 +162,12 @@ class DecoderModel:
             if head_ok:
                 for bucket, (t_ours, t_lib) in ops.measure_linear([self.lm_head], torch.float32).items():
                     ops.choose_linear(self.lm_head.shape[0], self.lm_head.shape[1], bucket, torch.float32, t_ours <= t_lib)
-        todo = list(tunable.items()) + ([((tuple(self.lm_head.shape), 0), [self.lm_head])] if head_ok else [])
-        for (shape, gated), mats in todo:
+        for key, mats in groups.items():
+            shape, gated = key
             out_dtype = torch.float32 if mats[0] is self.lm_head else torch.bfloat16
             chosen = any(ops._linear_choice.get((shape[0], shape[1], b, out_dtype), True) for b, _ in ops.TOKEN_BUCKETS)
             for m in mats:
-                if chosen:
+                if chosen and key in imaged:
                     ops.tile_weights(m, gated)
                 else:
                     ops.drop_tiled_weights(m)
