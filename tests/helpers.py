@@ -114,12 +114,14 @@ class Replayer:
         return np.stack([self.rows[(rid, p)] for p in positions])
 
 
-def kv_row_pos(d, esize, slot):
-    """Where the elements of a cache row are stored (the layout the engine documents in
-    csrc/common.cuh): rows that are a multiple of 128 bytes keep their 16-byte chunks XOR-swizzled
-    by the slot number; stored[pos[e]] = logical[e]."""
+def kv_pos(d, esize, slot, page):
+    """Where the elements of slot ``slot`` lie inside a (page, k|v, kv head) block of page * d elements
+    (the layout the engine documents in csrc/common.cuh): rows that are a multiple of 128 bytes are
+    stored in planes of 128-byte pieces, [plane][slot][piece], with the 16-byte chunks of a piece
+    XOR-swizzled by the slot number; other rows as they are.  block.ravel()[kv_pos(...)] = the row."""
     e = np.arange(d)
     if (d * esize) % 128:
-        return e
-    per = 16 // esize
-    return ((e // per) ^ (slot & 7)) * per + e % per
+        return slot * d + e
+    per_plane, per_chunk = 128 // esize, 16 // esize
+    plane, w = e // per_plane, e % per_plane
+    return plane * (page * per_plane) + slot * per_plane + ((w // per_chunk) ^ (slot & 7)) * per_chunk + w % per_chunk

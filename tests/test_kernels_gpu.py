@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_qwen2 as plain
-from helpers import kv_row_pos
+from helpers import kv_pos
 
 pytestmark = pytest.mark.gpu
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
@@ -114,7 +114,7 @@ def test_rope_cache_write(ops, dtype, nh, nkv, d, rot, pairing):
     if rot:
         j = np.arange(rot // 2, dtype=np.float32)
         denom = np.power(np.float32(theta), (np.float32(2) * j) / np.float32(rot)).astype(np.float32)
-    cache = torch.zeros((n_pages, 2, nkv, page, d), dtype=DT[dtype], device="cuda")
+    cache = torch.zeros((n_pages, 2, nkv, page * d), dtype=DT[dtype], device="cuda")
     q_out = torch.empty((n, nh * d), dtype=DT[dtype], device="cuda")
     ops.rope_cache_write(dev(qkv, DT[dtype]), dev(bias), dev(pos), dev(req), dev(bt), None if denom is None else dev(denom),
                          q_out, cache, num_heads=nh, num_kv_heads=nkv, head_dim=d, rotary_dim=rot, pairing=pairing,
@@ -135,17 +135,16 @@ def test_rope_cache_write(ops, dtype, nh, nkv, d, rot, pairing):
 
     q_ref, k_ref, v_ref = rotate(x[:, :nh]), rotate(x[:, nh:nh + nkv]), x[:, nh + nkv:]
     close(q_out.float().cpu().numpy().reshape(n, nh, d), q_ref, dtype, "q")
-    c = cache.float().cpu().numpy()
+    c = cache.float().cpu().numpy().reshape(n_pages, 2, nkv, page * d)        # blocks of page x d elements
     esize = 4 if dtype == "float32" else 2
+    owned = np.zeros(c.shape, dtype=bool)
     for t in range(n):
         pg, slot = bt[req[t], pos[t] // page], pos[t] % page
-        where = kv_row_pos(d, esize, slot)             # the row's chunks are stored swizzled by the slot
-        close(c[pg, 0, :, slot][:, where], k_ref[t], dtype, f"k of token {t}", scale=np.abs(k_ref).max())
-        close(c[pg, 1, :, slot][:, where], v_ref[t], dtype, f"v of token {t}", scale=np.abs(v_ref).max())
-    written = np.zeros((n_pages, page), dtype=bool)
-    for t in range(n):
-        written[bt[req[t], pos[t] // page], pos[t] % page] = True
-    assert not c.transpose(0, 3, 1, 2, 4)[~written].any(), "a slot that no token owns was written"
+        where = kv_pos(d, esize, slot, page)           # where the slot's elements lie in its block
+        close(c[pg, 0][:, where], k_ref[t], dtype, f"k of token {t}", scale=np.abs(k_ref).max())
+        close(c[pg, 1][:, where], v_ref[t], dtype, f"v of token {t}", scale=np.abs(v_ref).max())
+        owned[pg][:, :, where] = True
+    assert not c[~owned].any(), "a slot that no token owns was written"
     # write_kv off leaves the cache alone
     cache2 = torch.zeros_like(cache)
     ops.rope_cache_write(dev(qkv, DT[dtype]), dev(bias), dev(pos), dev(req), dev(bt), None if denom is None else dev(denom),
@@ -195,13 +194,13 @@ def attention_case(rng, dtype, nh, nkv, d, page, q_lens, ctx_lens, spike=True):
                 k[r][1] = as_stored(k[r][1] * 3.0, dtype)
                 q[t0 + ql - 1] = as_stored(np.repeat(k[r][1], nh // nkv, axis=0) * 0.7, dtype)
             t0 += ql
-    cache = np.zeros((n_pages, 2, nkv, page, d), dtype=np.float32)
+    cache = np.zeros((n_pages, 2, nkv, page * d), dtype=np.float32)
     esize = 4 if dtype == "float32" else 2
     for r, t in enumerate(total):
         for p in range(t):
-            where = kv_row_pos(d, esize, p % page)
-            cache[bt[r, p // page], 0, :, p % page][:, where] = k[r][p]
-            cache[bt[r, p // page], 1, :, p % page][:, where] = v[r][p]
+            where = kv_pos(d, esize, p % page, page)
+            cache[bt[r, p // page], 0][:, where] = k[r][p]
+            cache[bt[r, p // page], 1][:, where] = v[r][p]
     q_start = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
     pos = np.concatenate([np.arange(c, c + ql) for c, ql in zip(ctx_lens, q_lens)]).astype(np.int32)
     req = np.concatenate([np.full(ql, r) for r, ql in enumerate(q_lens)]).astype(np.int32)

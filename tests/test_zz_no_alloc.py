@@ -32,7 +32,7 @@ def _case(seed, n_req, nh, nkv, d, page, max_ctx):
     n_pages = n_req * blocks + 2
     bt = rng.permutation(n_pages)[: n_req * blocks].reshape(n_req, blocks).astype(np.int32)
     g = torch.Generator(device="cuda").manual_seed(seed)
-    cache = torch.randn((n_pages, 2, nkv, page, d), generator=g, device="cuda").to(torch.bfloat16)
+    cache = torch.randn((n_pages, 2, nkv, page * d), generator=g, device="cuda").to(torch.bfloat16)
     q = torch.randn((n_req, nh * d), generator=g, device="cuda").to(torch.bfloat16)
     q_start = torch.arange(n_req + 1, dtype=torch.int32, device="cuda")
     return q, cache, q_start, torch.from_numpy(ctx).cuda(), torch.from_numpy(bt).cuda()

@@ -41,7 +41,7 @@ class PagedGroup:
     spec: PagedKVSpec
     layers: List[int]                      # cache layer ids, in order
     pool: BlockPool
-    pages: Optional[torch.Tensor] = None   # [len(layers), num_pages, 2, kv_heads, page_size, head_dim]
+    pages: Optional[torch.Tensor] = None   # [len(layers), num_pages, 2, kv_heads, page_size * head_dim]: see csrc/common.cuh (kv_pos)
 
 
 @dataclass
@@ -110,7 +110,7 @@ class CacheManager:
     def _allocate_device(self) -> None:
         for g in self.paged:
             s = g.spec
-            g.pages = torch.zeros((len(g.layers), self.num_pages, 2, s.num_kv_heads, self.page_size, s.head_dim),
+            g.pages = torch.zeros((len(g.layers), self.num_pages, 2, s.num_kv_heads, self.page_size * s.head_dim),
                                   dtype=self.dtype, device=self.device)
         for g in self.state:
             g.slots = torch.zeros((len(g.layers), self.max_num_seqs) + tuple(g.spec.shape),

@@ -18,7 +18,7 @@
 // the plain kernel of attention_simt.cu uses expf).
 //
 // Loading.  The cache stores every row already in the XOR-swizzled chunk order that
-// ldmatrix wants (kv_row_pos in common.cuh), so a run of slots of a page is a ready-made
+// ldmatrix wants (kv_pos in common.cuh), so a run of slots of a page is a ready-made
 // piece of a shared-memory tile.  A fifth warp is the producer: for every tile of 64 keys
 // it issues one bulk copy (cp.async.bulk, the TMA unit, no tensor map, no multicast) per
 // page piece of K and of V into a ring of stages, completing on the stage's mbarrier; the
@@ -82,9 +82,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 #define LOG2E 1.4426950408889634f
 
-// Byte offset of element (row, 16-byte chunk) in a tile of rows of D bfloat16.
+// Byte offset of element (row, 16-byte chunk) in a tile of rows of D bfloat16 (the Q tile, which the
+// kernels write themselves).
 template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
+}
+// The same for a K or V tile of TK keys, which arrives from the cache in planes of 128-byte row
+// pieces (kv_pos in common.cuh): [plane][key][128 bytes], chunks swizzled inside a piece.
+template <int D, int TK> __device__ __forceinline__ uint32_t swz_kv(int key, int chunk) {
+    return (uint32_t)(((chunk >> 3) * TK + key) * 128 + (((chunk & 7) ^ (key & 7)) << 4));
 }
 
 // The request's block table as the producer warp sees it: a window of 64 consecutive entries in
@@ -130,20 +136,22 @@ struct PageDiv {
     __device__ __forceinline__ int mul(int x) const { return shift >= 0 ? x << shift : x * page; }
 };
 
-// The producer warp's share of one tile of TK keys starting at key kb of kv head g: lanes 0-7
-// each copy one page piece of K, lanes 8-15 the same pieces of V (a tile spans at most
-// TK / 16 + 1 pages).  Lane 0 has armed the stage's barrier with the tile's byte count.
-// head_base: the kv head's offset inside a page's K block; page_stride, v_off: elements per page, K block to V block.
+// The producer warp's share of one tile of TK keys starting at key kb of kv head g.  A tile spans at
+// most TK / 16 + 1 pages and D / 64 planes; lane = 16 * (K or V) + 8 * plane + page piece copies one run
+// of 128-byte row pieces.  Lane 0 has armed the stage's barrier with the tile's byte count.
+// head_base: the kv head's block inside a page's K half; page_stride, v_off: elements per page, K half to V half.
 template <int D, int TK>
 __device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t bar, int kb, int lo, int hi,
                                              PageWindow& pw, const __nv_bfloat16* __restrict__ cache,
                                              size_t head_base, size_t page_stride, size_t v_off, const PageDiv& pd, int lane) {
-    const int piece = lane & 7;
+    constexpr int PLANES = D / 64;
+    static_assert(PLANES == 1 || PLANES == 2, "head sizes 64 and 128");
+    const int piece = lane & 7, plane = (lane >> 3) & 1;
     const int first_page = pd.div(kb);
     pw.advance(first_page);
     const int lp_piece = first_page + piece;
     const int start = piece == 0 ? kb : pd.mul(lp_piece);                   // first key of the piece
-    const bool active = lane < 16 && start < kb + TK;
+    const bool active = plane < PLANES && start < kb + TK;
     // the page itself if any of it is visible, else the page of the last visible key
     const int lp = active ? lp_piece : first_page;
     const int page_lo = pd.mul(lp);
@@ -152,14 +160,15 @@ __device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t 
     if (!active) return;
     const int pg = visible ? got : pw.last_pg;
     const int end = min(page_lo + pd.page, kb + TK);
-    const __nv_bfloat16* src = cache + (size_t)pg * page_stride + head_base + (size_t)(start - page_lo) * D;
-    const uint32_t off = (uint32_t)(start - kb) * D * 2, bytes = (uint32_t)(end - start) * D * 2;
-    if (lane < 8) cx_bulk_load(sk + off, src, bytes, bar);
+    // plane `plane` of the head's block: pd.page rows of 64 elements
+    const __nv_bfloat16* src = cache + (size_t)pg * page_stride + head_base + ((size_t)plane * pd.page + (start - page_lo)) * 64;
+    const uint32_t off = (uint32_t)(plane * TK + (start - kb)) * 128, bytes = (uint32_t)(end - start) * 128;
+    if (lane < 16) cx_bulk_load(sk + off, src, bytes, bar);
     else cx_bulk_load(sv + off, src + v_off, bytes, bar);
 }
 
 // S[16 x 8*NB] += Q[16 x D] * K[keys key0 .. key0 + 8*NB)^T, K tile at sk.
-template <int D, int NB>
+template <int D, int TK, int NB>
 __device__ __forceinline__ void qk_product(float (&s)[NB][4], const uint32_t (&qf)[D / 16][4], uint32_t sk, int key0) {
     const int lane = threadIdx.x & 31;
     const int mi = lane >> 3, r8 = lane & 7;
@@ -169,7 +178,7 @@ __device__ __forceinline__ void qk_product(float (&s)[NB][4], const uint32_t (&q
         for (int nb = 0; nb < NB; nb += 2) {
             uint32_t b[4];
             const int key = key0 + (nb + (mi >> 1)) * 8 + r8;
-            ldmatrix_x4(b, sk + swz<D>(key, ks * 2 + (mi & 1)));
+            ldmatrix_x4(b, sk + swz_kv<D, TK>(key, ks * 2 + (mi & 1)));
             mma_bf16(s[nb], qf[ks], b[0], b[1]);
             mma_bf16(s[nb + 1], qf[ks], b[2], b[3]);
         }
@@ -177,7 +186,7 @@ __device__ __forceinline__ void qk_product(float (&s)[NB][4], const uint32_t (&q
 }
 
 // O[16 x D] += P[16 x 16*KK] * V[keys key0 .. key0 + 16*KK), V tile at sv.  pf[kk] is P's A fragment.
-template <int D, int KK>
+template <int D, int TK, int KK>
 __device__ __forceinline__ void pv_product(float (&o)[D / 8][4], const uint32_t (&pf)[KK][4], uint32_t sv, int key0) {
     const int lane = threadIdx.x & 31;
     const int mi = lane >> 3, r8 = lane & 7;
@@ -187,7 +196,7 @@ __device__ __forceinline__ void pv_product(float (&o)[D / 8][4], const uint32_t 
         for (int nd = 0; nd < D / 8; nd += 2) {
             uint32_t b[4];
             const int key = key0 + kk * 16 + (mi & 1) * 8 + r8;
-            ldmatrix_x4_trans(b, sv + swz<D>(key, nd + (mi >> 1)));
+            ldmatrix_x4_trans(b, sv + swz_kv<D, TK>(key, nd + (mi >> 1)));
             mma_bf16(o[nd], pf[kk], b[0], b[1]);
             mma_bf16(o[nd + 1], pf[kk], b[2], b[3]);
         }
@@ -290,7 +299,7 @@ attention_decode_kernel(MmaAttnArgs a) {
                 float s[2][4];
 #pragma unroll
                 for (int i = 0; i < 2; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
-                qk_product<D, 2>(s, qf, sk, warp * 16);
+                qk_product<D, BN, 2>(s, qf, sk, warp * 16);
                 // only a tile that crosses lo or hi has keys to mask (the same for the whole CTA)
                 if (tile * BN < lo || tile * BN + BN > hi) {
 #pragma unroll
@@ -329,7 +338,7 @@ attention_decode_kernel(MmaAttnArgs a) {
                 l_b += (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
                 pf[0][0] = pack_bf16(p[0][0], p[0][1]); pf[0][1] = pack_bf16(p[0][2], p[0][3]);
                 pf[0][2] = pack_bf16(p[1][0], p[1][1]); pf[0][3] = pack_bf16(p[1][2], p[1][3]);
-                pv_product<D, 1>(o, pf, sv, warp * 16);
+                pv_product<D, BN, 1>(o, pf, sv, warp * 16);
                 __syncwarp();
                 if (lane == 0) cx_mbar_arrive(empty0 + 8 * st);      // this warp is done with the stage
             }
@@ -516,7 +525,7 @@ attention_prefill_kernel(MmaAttnArgs a) {
         float s[TK / 8][4];
 #pragma unroll
         for (int i = 0; i < TK / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
-        qk_product<D, TK / 8>(s, qf, sk, 0);
+        qk_product<D, TK, TK / 8>(s, qf, sk, 0);
         const bool need_mask = (kb + TK - 1 > wpos_min) || (kb < wlo_max) || !live_b;
 #pragma unroll
         for (int nb = 0; nb < TK / 8; ++nb)
@@ -564,7 +573,7 @@ attention_prefill_kernel(MmaAttnArgs a) {
         l_b = l_b * cb + sum_b;
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) { o[i][0] *= ca; o[i][1] *= ca; o[i][2] *= cb; o[i][3] *= cb; }
-        pv_product<D, TK / 16>(o, pf, sv, 0);
+        pv_product<D, TK, TK / 16>(o, pf, sv, 0);
         __syncwarp();
         if (lane == 0) cx_mbar_arrive(empty0 + 8 * st);          // this warp is done with the stage
     }

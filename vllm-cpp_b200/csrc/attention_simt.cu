@@ -5,7 +5,7 @@
 // One warp per (query token, query head).  The query at position p of request r
 // attends keys j of the same request with  j <= p  and, when window > 0,
 // j > p - window;  key j lives in page block_table[r, j / page], slot j % page, its row in the
-// chunk order of kv_row_pos (common.cuh).
+// layout of kv_pos (common.cuh).
 // Scores, softmax and the output accumulation are float; softmax is computed
 // online over chunks of 32 keys (one key per lane).
 //
@@ -62,11 +62,11 @@ __global__ void attention_simt_kernel(AttnArgs a) {
         unsigned long long koff = 0;
         if (valid) {
             const int pg = bt[j / a.page];
-            koff = (unsigned long long)pg * page_elems + ((size_t)g * a.page + (j % a.page)) * a.d;
+            koff = (unsigned long long)pg * page_elems + (size_t)g * a.page * a.d;      // the head's block of the page
             const T* kr = cache + koff;
             const int slot = j % a.page;
             float acc = 0.0f;
-            for (int i = 0; i < a.d; ++i) acc += qs[i] * to_f32<T>(kr[kv_row_pos(i, slot, a.d, (int)sizeof(T))]);
+            for (int i = 0; i < a.d; ++i) acc += qs[i] * to_f32<T>(kr[kv_pos(i, slot, a.d, a.page, (int)sizeof(T))]);
             s = acc;
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -84,7 +84,7 @@ __global__ void attention_simt_kernel(AttnArgs a) {
 #pragma unroll
             for (int k = 0; k < ATT_MAX_D / 32; ++k) {
                 const int dim = lane + 32 * k;
-                if (dim < a.d) o[k] += pj * to_f32<T>(vr[kv_row_pos(dim, slot, a.d, (int)sizeof(T))]);
+                if (dim < a.d) o[k] += pj * to_f32<T>(vr[kv_pos(dim, slot, a.d, a.page, (int)sizeof(T))]);
             }
         }
         m = m_new;

@@ -73,17 +73,21 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 
 static inline int vcb_last_error() { return (int)cudaGetLastError(); }
 
-// ---- layout of a cache row
-// A page holds [k|v][kv head][slot][head dim].  When a row (one slot of one head) is a multiple
-// of 128 bytes, its 16-byte chunks are stored XOR-swizzled by the slot number: chunk c of slot s
-// lives at chunk c ^ (s & 7).  A run of slots of a page is then, byte for byte, the image that
-// the tensor-core attention kernels want in shared memory (conflict-free ldmatrix), and one
-// plain bulk copy brings it there.  Rows of other sizes are stored as they are.
-__host__ __device__ __forceinline__ int kv_row_pos(int elem, int slot, int d, int esize) {
-    if ((d * esize) & 127) return elem;
-    const int per_chunk = 16 / esize;
-    const int chunk = elem / per_chunk, within = elem - chunk * per_chunk;
-    return ((chunk ^ (slot & 7)) * per_chunk) + within;
+// ---- layout of the cache
+// A page holds [k|v][kv head] blocks of page * head_dim elements.  When a row (one slot of one head)
+// is a multiple of 128 bytes, a block is stored in planes of 128-byte row pieces,
+// [plane][slot][128 bytes], and inside a piece the 16-byte chunks are XOR-swizzled by the slot
+// number: chunk c of slot s lives at chunk c ^ (s & 7).  A run of slots of one plane is then, byte for
+// byte, a run of rows of the 128-byte-swizzled K-major (or MN-major) tile that the tensor cores read from
+// shared memory -- tcgen05.mma through its shared-memory descriptor, mma.sync through conflict-free
+// ldmatrix -- and one plain bulk copy brings it there.  Rows of other sizes are stored as they are,
+// [slot][head_dim].  kv_pos: offset of element `elem` of slot `slot` inside its block.
+__host__ __device__ __forceinline__ int kv_pos(int elem, int slot, int d, int page, int esize) {
+    if ((d * esize) & 127) return slot * d + elem;
+    const int per_plane = 128 / esize, per_chunk = 16 / esize;
+    const int plane = elem / per_plane, w = elem - plane * per_plane;
+    const int chunk = w / per_chunk, within = w - chunk * per_chunk;
+    return plane * (page * per_plane) + slot * per_plane + ((chunk ^ (slot & 7)) * per_chunk) + within;
 }
 
 // ---- mbarriers and bulk copies (shared by the kernels that stage memory asynchronously)

@@ -245,7 +245,7 @@ VCB_EXPORT int vcb_silu_mul(const void* gu, void* out, int n_tokens, int inter, 
 //   q, k, v get their bias (float); q and k heads are rotated over the first
 //   `rot` elements of each head; q goes to q_out [n_tokens, nh*d]; k and v go to
 //   page block_table[r, p / page] slot p % page of this layer's cache, laid out
-//   [page][k|v][kv_head][slot][d], each row in the chunk order of kv_row_pos (common.cuh).
+//   [page][k|v][kv_head] blocks of page x d elements in the layout of kv_pos (common.cuh).
 // Rotation (src/kernels/rotary_embedding.cu:18-33, table of src/model/qwen.cpp:119-128):
 //   angle = p / denom[j],  denom[j] = theta^(2j/rot)  (computed on the host in float)
 //   pairing 0 ("half"):        (a, b) = (x[j], x[j + rot/2])
@@ -302,13 +302,13 @@ __global__ void rope_cache_kernel(RopeCacheArgs a, int heads_per_block) {
     const int r = a.req_of_token[t];
     const int pg = a.block_table[(size_t)r * a.bt_stride + pos / a.page];
     const int slot = pos % a.page;
-    // [page][2][nkv][slot][d], rows in the layout of kv_row_pos
+    // [page][2][nkv] blocks in the layout of kv_pos
     T* base = (T*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
     const int kvh = h < a.nh + a.nkv ? h - a.nh : h - a.nh - a.nkv;
     const size_t which = h < a.nh + a.nkv ? 0 : (size_t)a.nkv * a.page * a.d;
-    T* dst = base + which + ((size_t)kvh * a.page + slot) * a.d;
-    dst[kv_row_pos(ia, slot, a.d, (int)sizeof(T))] = from_f32<T>(xa);
-    dst[kv_row_pos(ib, slot, a.d, (int)sizeof(T))] = from_f32<T>(xb);
+    T* dst = base + which + (size_t)kvh * a.page * a.d;
+    dst[kv_pos(ia, slot, a.d, a.page, (int)sizeof(T))] = from_f32<T>(xa);
+    dst[kv_pos(ib, slot, a.d, a.page, (int)sizeof(T))] = from_f32<T>(xb);
 }
 
 // The same for the common case (bfloat16, rotate-half pairing over the whole head, head size a
@@ -343,7 +343,7 @@ __global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block) {
         __nv_bfloat16* base = (__nv_bfloat16*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
         const int kvh = h < a.nh + a.nkv ? h - a.nh : h - a.nh - a.nkv;
         const size_t which = h < a.nh + a.nkv ? 0 : (size_t)a.nkv * a.page * a.d;
-        row_dst = base + which + ((size_t)kvh * a.page + slot) * a.d;
+        row_dst = base + which + (size_t)kvh * a.page * a.d;             // the head's block of the page
     }
     float ba[8], bb[8];
 #pragma unroll
@@ -381,9 +381,9 @@ __global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block) {
     }
     if (!row_dst) return;
     __nv_bfloat16* dst = row_dst;
-    // whole 16-byte chunks move together in the rows' layout (kv_row_pos)
-    *reinterpret_cast<uint4*>(dst + kv_row_pos(c * 8, slot, a.d, 2)) = *reinterpret_cast<const uint4*>(oa);
-    *reinterpret_cast<uint4*>(dst + kv_row_pos(half + c * 8, slot, a.d, 2)) = *reinterpret_cast<const uint4*>(ob);
+    // whole 16-byte chunks move together in the block's layout (kv_pos)
+    *reinterpret_cast<uint4*>(dst + kv_pos(c * 8, slot, a.d, a.page, 2)) = *reinterpret_cast<const uint4*>(oa);
+    *reinterpret_cast<uint4*>(dst + kv_pos(half + c * 8, slot, a.d, a.page, 2)) = *reinterpret_cast<const uint4*>(ob);
 }
 
 VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const int* positions,

@@ -51,7 +51,7 @@ class StateSpec:
 @dataclass
 class PagedKVView:
     """What a mixer sees of a paged cache layer."""
-    pages: torch.Tensor          # [num_pages, 2, num_kv_heads, page_size, head_dim]
+    pages: torch.Tensor          # [num_pages, 2, num_kv_heads, page_size * head_dim], a block laid out as csrc/common.cuh says (kv_pos)
     group: int                   # index into StepContext.block_tables
     page_size: int
 
