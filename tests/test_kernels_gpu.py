@@ -241,6 +241,31 @@ def test_attention_prefill_mma(ops, nh, nkv, d, page, window):
     close(out.float().cpu().numpy().reshape(c["n"], nh, d), want, "bfloat16", "attention_prefill_mma")
 
 
+@pytest.mark.parametrize("nh,nkv,page,window", [(28, 4, 16, 0), (8, 1, 16, 100), (40, 2, 64, 0), (3, 3, 32, 40), (16, 2, 16, 300)])
+def test_attention_prefill_tc(ops, nh, nkv, page, window):
+    """The tcgen05 prefill attention (head size 128) against the float64 reference: portions that start
+    and end inside tiles and pages, contexts before them, one far key that must dominate, windows."""
+    d = 128
+    rng = np.random.default_rng(6)
+    q_lens, ctx_lens = [70, 1, 2, 300, 5], [0, 500, 63, 64, 1000]
+    c = attention_case(rng, "bfloat16", nh, nkv, d, page, q_lens, ctx_lens)
+    group = nh // nkv
+    rows = ops.TC_ATTENTION_TILE_ROWS
+    tiles = [(r, k * rows) for r, ql in enumerate(q_lens) for k in range(-(-ql * group // rows))]
+    out = torch.full((c["n"], nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for _ in range(2):
+        ops.attention_prefill_tc(dev(c["q"].reshape(c["n"], -1), torch.bfloat16), dev(c["cache"], torch.bfloat16), out,
+                                 dev(c["q_start"]), dev(np.array(ctx_lens, dtype=np.int32)), dev(c["bt"]),
+                                 dev(np.array([t[0] for t in tiles], dtype=np.int32)),
+                                 dev(np.array([t[1] for t in tiles], dtype=np.int32)),
+                                 num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page, window=window,
+                                 scale=float(np.float32(1) / np.sqrt(np.float32(d))))
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = reference_attention(c["q"].astype(np.float64), c["k"], c["v"], q_lens, ctx_lens, nh, nkv, window)
+    close(out.float().cpu().numpy().reshape(c["n"], nh, d), want, "bfloat16", "attention_prefill_tc")
+
+
 @pytest.mark.parametrize("nsplit", [1, 3, 8])
 @pytest.mark.parametrize("nh,nkv,d,page,window", [(28, 4, 128, 16, 0), (6, 2, 64, 32, 0), (3, 3, 64, 16, 40),
                                                    (40, 2, 128, 16, 0), (16, 1, 128, 16, 200)])

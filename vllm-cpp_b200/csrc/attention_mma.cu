@@ -143,7 +143,8 @@ struct PageDiv {
 template <int D, int TK>
 __device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t bar, int kb, int lo, int hi,
                                              PageWindow& pw, const __nv_bfloat16* __restrict__ cache,
-                                             size_t head_base, size_t page_stride, size_t v_off, const PageDiv& pd, int lane) {
+                                             size_t head_base, size_t page_stride, size_t v_off, const PageDiv& pd, int lane,
+                                             uint32_t bar_v = 0) {
     constexpr int PLANES = D / 64;
     static_assert(PLANES == 1 || PLANES == 2, "head sizes 64 and 128");
     const int piece = lane & 7, plane = (lane >> 3) & 1;
@@ -164,7 +165,7 @@ __device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t 
     const __nv_bfloat16* src = cache + (size_t)pg * page_stride + head_base + ((size_t)plane * pd.page + (start - page_lo)) * 64;
     const uint32_t off = (uint32_t)(plane * TK + (start - kb)) * 128, bytes = (uint32_t)(end - start) * 128;
     if (lane < 16) cx_bulk_load(sk + off, src, bytes, bar);
-    else cx_bulk_load(sv + off, src + v_off, bytes, bar);
+    else cx_bulk_load(sv + off, src + v_off, bytes, bar_v ? bar_v : bar);
 }
 
 // S[16 x 8*NB] += Q[16 x D] * K[keys key0 .. key0 + 8*NB)^T, K tile at sk.
@@ -608,6 +609,318 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
     return vcb_last_error();
 }
 
+// ------------------------------------------------- prefill on tcgen05
+// The same work as attention_prefill_kernel for head size 128, on the fifth-generation tensor
+// cores.  A CTA owns 128 packed rows (token x head in group) of one kv head and walks the keys in tiles
+// of 128:
+//   S = Q K^T      tcgen05.mma, Q and K from shared memory (K-major, 128-byte swizzle: the cache's
+//                  planes are that layout already), S (128 x 128 float) in tensor memory, two buffers;
+//   softmax        four warps, one thread per row: tcgen05.ld of its row, mask, running maximum,
+//                  ex2.approx, running sum; P rounded to bfloat16 into shared memory (K-major);
+//   O_tile = P V   tcgen05.mma, V from shared memory as it lies in the cache (MN-major operand),
+//                  a fresh 128 x 128 float tile in tensor memory;
+//   O += O_tile    by the row's thread in registers, rescaled when the maximum rose.
+// Warp 0 copies K and V tiles (bulk copies from the pages, two stages each, separate barriers so a K
+// stage is free as soon as S is done), warp 1 issues the MMAs, warps 2-5 do the rest.  The MMA of
+// tile j + 1's scores is issued before tile j's P V, so the tensor cores work while tile j's softmax
+// runs.  Every wait is bounded; one that runs out sets *status and the CTA drains and leaves.
+namespace tc {
+constexpr int D = 128, BMT = 128, TKT = 128;
+constexpr int THREADS = 192;
+constexpr int Q_BYTES = BMT * D * 2, KV_BYTES = TKT * D * 2, P_BYTES = BMT * TKT * 2;
+constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256;
+
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// K-major operand, rows of 128 bytes, 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand (V: the head dimension runs along a row), 128-byte swizzle: planes of 64 elements
+// `plane_bytes` apart (leading offset), groups of 8 keys 1024 bytes apart (stride offset).
+__device__ __forceinline__ uint64_t desc_mn(uint32_t addr, uint32_t plane_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((plane_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// float accumulator, bfloat16 A and B, M = 128, N = 128; b_mn: B is MN-major
+__host__ __device__ constexpr uint32_t idesc(bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attention_prefill_tc_kernel(MmaAttnArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // No early release of the next kernel here: its CTAs would sit on this SM holding tensor memory
+    // while CTAs of this kernel, which want all 512 columns, still wait to be placed.
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = a.req_list[blockIdx.x];
+    const int row0 = a.tile_row0[blockIdx.x];
+    const int g = blockIdx.y;
+    const int G = a.nh / a.nkv;
+    const int q0 = a.q_start[r], q_len = a.q_start[r + 1] - q0, ctx = a.ctx_lens[r];
+    const int rows_total = q_len * G;
+    const int* bt = a.block_table + (size_t)r * a.bt_stride;
+    const float sl2 = a.scale * LOG2E;
+
+    // [Q][K0][K1][V0][V1][P][barriers]
+    const uint32_t sq = smem_u32(smem), sk0 = sq + Q_BYTES, sv0 = sk0 + 2 * KV_BYTES, sp = sv0 + 2 * KV_BYTES;
+    unsigned char* q_ptr = smem;
+    unsigned char* p_ptr = smem + Q_BYTES + 4 * KV_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_ptr + P_BYTES);
+    // 0,1 full_k  2,3 empty_k  4,5 full_v  6,7 empty_v  8,9 s_full  10,11 s_free  12 p_full  13 p_free  14 o_full  15 o_free  16 q_ready
+    const uint32_t b0 = cx_smem(bars);
+    auto B = [&](int i) { return b0 + 8 * i; };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) {
+            cx_mbar_init(B(0 + i), 1); cx_mbar_init(B(2 + i), 1); cx_mbar_init(B(4 + i), 1); cx_mbar_init(B(6 + i), 1);
+            cx_mbar_init(B(8 + i), 1); cx_mbar_init(B(10 + i), 4);
+        }
+        cx_mbar_init(B(12), 4); cx_mbar_init(B(13), 1); cx_mbar_init(B(14), 1); cx_mbar_init(B(15), 4); cx_mbar_init(B(16), 4);
+        *abort_flag = 0;
+        cx_mbar_init_fence();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tm_s0 = tmem, tm_o = tmem + 256;              // S buffers at columns 0 and 128, O tile at 256
+
+    // keys that any row of the tile can see
+    const int last_row = min(row0 + BMT, rows_total) - 1;
+    const int hi = ctx + last_row / G + 1;
+    const int lo = a.window > 0 ? max(0, ctx + row0 / G + 1 - a.window) : 0;
+    const int tile0 = lo / TKT, tile1 = (hi + TKT - 1) / TKT;
+    const int n_tiles = tile1 - tile0;
+
+    auto give_up = [&](int code) {
+        if (!*abort_flag) { *abort_flag = 1; if (a.status) atomicCAS(a.status, 0, code); }
+    };
+
+    if (warp == 0) {
+        // ---- producer: K and V tiles, two stages each
+        PageWindow pw;
+        const PageDiv pd(a.page);
+        pw.init(bt, pd.div(tile0 * TKT), hi, a.page, lane);
+        const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
+                     v_off = (size_t)a.nkv * a.page * D;
+        for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
+            const int st = j & 1;
+            const uint32_t ph = ((j >> 1) & 1) ^ 1;
+            if (!cx_mbar_wait(B(2 + st), ph) || !cx_mbar_wait(B(6 + st), ph)) { give_up(9); break; }
+            if (lane == 0) { cx_mbar_expect_tx(B(0 + st), KV_BYTES); cx_mbar_expect_tx(B(4 + st), KV_BYTES); }
+            __syncwarp();
+            produce_tile<D, TKT>(sk0 + st * KV_BYTES, sv0 + st * KV_BYTES, B(0 + st), (tile0 + j) * TKT, lo, hi, pw, a.cache,
+                                 head_base, page_stride, v_off, pd, lane, B(4 + st));
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t id_s = idesc(false), id_pv = idesc(true);
+            bool ok = cx_mbar_wait(B(16), 0);                 // Q tile written
+            if (!ok) give_up(9);
+            fence_after();
+            auto issue_pv = [&](int j) -> bool {                // O_tile = P_j V_j
+                const int st = j & 1;
+                if (!cx_mbar_wait(B(12), j & 1) || !cx_mbar_wait(B(4 + st), (j >> 1) & 1) ||
+                    !cx_mbar_wait(B(15), (j & 1) ^ 1))
+                    return false;
+                fence_after();
+                const uint32_t v_base = sv0 + st * KV_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < TKT / 16; ++kk)           // 16 keys a step: P plane kk / 4, V rows 16 kk ..
+                    mma(tm_o, desc_k(sp + (kk >> 2) * (BMT * 128) + (kk & 3) * 32), desc_mn(v_base + kk * 16 * 128, TKT * 128),
+                        id_pv, kk > 0 ? 1u : 0u);
+                commit(B(14));          // O tile complete
+                commit(B(6 + st));      // V stage free
+                commit(B(13));          // P free
+                return true;
+            };
+            for (int j = 0; j < n_tiles && ok && !*abort_flag; ++j) {
+                const int st = j & 1;
+                // S_j = Q K_j^T into S buffer j & 1 (free once the softmax of tile j - 2 has read it)
+                if (!cx_mbar_wait(B(0 + st), (j >> 1) & 1) || !cx_mbar_wait(B(10 + st), ((j >> 1) & 1) ^ 1)) { ok = false; break; }
+                fence_after();
+                const uint32_t k_base = sk0 + st * KV_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks)             // 16 dims a step: plane ks / 4
+                    mma(tm_s0 + st * 128, desc_k(sq + (ks >> 2) * (BMT * 128) + (ks & 3) * 32),
+                        desc_k(k_base + (ks >> 2) * (TKT * 128) + (ks & 3) * 32), id_s, ks > 0 ? 1u : 0u);
+                commit(B(8 + st));      // S complete
+                commit(B(2 + st));      // K stage free
+                if (j > 0 && !issue_pv(j - 1)) { ok = false; break; }
+            }
+            if (ok && n_tiles > 0 && !*abort_flag && !issue_pv(n_tiles - 1)) ok = false;
+            if (!ok) give_up(9);
+        }
+    } else {
+        // ---- softmax and output: thread i of warps 2..5 owns row 32 * (warp % 4) + lane (its tensor-memory lane)
+        const int lg = warp & 3;
+        const int row = lg * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
+        // Q tile: packed row -> (token, head in group); two planes of 128-byte pieces, chunks swizzled
+        for (int idx = threadIdx.x - 64; idx < BMT * (D / 8); idx += 128) {
+            const int rr = idx / (D / 8), c = idx % (D / 8);
+            const int pr = row0 + rr;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (pr < rows_total) {
+                const int tt = pr / G, hg = pr % G;
+                v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + tt) * a.nh + g * G + hg) * D + c * 8);
+            }
+            *reinterpret_cast<uint4*>(q_ptr + swz_kv<D, BMT>(rr, c)) = v;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) cx_mbar_arrive(B(16));
+
+        const int pr = row0 + row;
+        const bool row_ok = pr < rows_total;
+        const int pos = ctx + min(pr, rows_total - 1) / G;                 // the row's position
+        const int row_lo = a.window > 0 ? max(0, pos + 1 - a.window) : 0;
+        float o[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = 0.0f;
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
+            const int st = j & 1;
+            const int kb = (tile0 + j) * TKT;
+            if (!cx_mbar_wait(B(8 + st), (j >> 1) & 1)) { ok = false; break; }
+            fence_after();
+            const uint32_t s_addr = tm_s0 + st * 128 + lane_addr;
+            // does any row of the tile mask any key of this tile? (the first row sees the fewest late keys,
+            // the last row the fewest early ones)
+            const bool edge = kb + TKT - 1 > ctx + row0 / G || (a.window > 0 && kb < ctx + last_row / G + 1 - a.window);
+            // pass 1: the row's maximum over the tile
+            float mt = -INFINITY;
+#pragma unroll 1
+            for (int c0 = 0; c0 < TKT; c0 += 32) {
+                float s[32];
+                ld32(s_addr + c0, s);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int key = kb + c0 + i;
+                    if (!edge || (key >= row_lo && key <= pos)) mt = fmaxf(mt, s[i]);
+                }
+            }
+            const float m_new = fmaxf(m, mt);
+            const float base = m_new == -INFINITY ? 0.0f : m_new * sl2;
+            const float corr = m == -INFINITY ? 0.0f : fast_exp2(m * sl2 - base);
+            // P may be overwritten once the P V of the tile before has read it
+            if (!cx_mbar_wait(B(13), (j & 1) ^ 1)) { ok = false; break; }
+            // pass 2: probabilities, their sum, P into shared memory (row `row`, 16-byte chunks swizzled)
+            float lt = 0.0f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < TKT; c0 += 32) {
+                float s[32];
+                ld32(s_addr + c0, s);
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int key = kb + c0 + i;
+                    float p0 = fast_exp2(fmaf(s[i], sl2, -base)), p1 = fast_exp2(fmaf(s[i + 1], sl2, -base));
+                    if (edge) {
+                        if (!(key >= row_lo && key <= pos)) p0 = 0.0f;
+                        if (!(key + 1 >= row_lo && key + 1 <= pos)) p1 = 0.0f;
+                    }
+                    lt += p0 + p1;
+                    pk[i >> 1] = pack_bf16(p0, p1);
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {                   // four chunks of eight keys
+                    const int chunk = (c0 >> 3) + q4;              // 0..15 over the tile's 128 keys
+                    *reinterpret_cast<uint4*>(p_ptr + swz_kv<D, BMT>(row, chunk)) =
+                        make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+                }
+            }
+            // the S buffer has been read: the scores of tile j + 2 may overwrite it
+            fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) { cx_mbar_arrive(B(10 + st)); cx_mbar_arrive(B(12)); }
+            // O: add the tile before (computed with the maximum before this tile), then move to the new maximum
+            if (j > 0) {
+                if (!cx_mbar_wait(B(14), (j - 1) & 1)) { ok = false; break; }
+                fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {               // unrolled: o[] stays in registers
+                    float t[32];
+                    ld32(tm_o + lane_addr + c0, t);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c0 + i] = (o[c0 + i] + t[i]) * corr;
+                }
+                fence_before();
+                __syncwarp();
+                if (lane == 0) cx_mbar_arrive(B(15));
+            }
+            l = l * corr + lt;
+            m = m_new;
+        }
+        if (ok && n_tiles > 0 && !*abort_flag) {
+            if (!cx_mbar_wait(B(14), (n_tiles - 1) & 1)) ok = false;
+            fence_after();
+            if (ok) {
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+                __nv_bfloat16* dst = a.out + ((size_t)(q0 + min(pr, rows_total - 1) / G) * a.nh + g * G + min(pr, rows_total - 1) % G) * D;
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    float t[32];
+                    ld32(tm_o + lane_addr + c0, t);
+                    if (row_ok) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 w = make_uint4(pack_bf16((o[c0 + i] + t[i]) * inv, (o[c0 + i + 1] + t[i + 1]) * inv),
+                                                 pack_bf16((o[c0 + i + 2] + t[i + 2]) * inv, (o[c0 + i + 3] + t[i + 3]) * inv),
+                                                 pack_bf16((o[c0 + i + 4] + t[i + 4]) * inv, (o[c0 + i + 5] + t[i + 5]) * inv),
+                                                 pack_bf16((o[c0 + i + 6] + t[i + 6]) * inv, (o[c0 + i + 7] + t[i + 7]) * inv));
+                            *reinterpret_cast<uint4*>(dst + c0 + i) = w;
+                        }
+                    }
+                }
+            }
+        }
+        if (!ok) give_up(9);
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+}  // namespace tc
+
 template <int D, int TK, int STAGES, int MINB>
 static int launch_prefill_variant(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
     const size_t smem = (size_t)STAGES * 2 * TK * D * 2 + BM * D * 2 + 2 * STAGES * 8 + 64;     // tiles, Q, barriers
@@ -628,6 +941,18 @@ static int launch_prefill_variant(const MmaAttnArgs& a, int n_tiles, cudaStream_
 template <int D>
 static int launch_prefill(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
     return launch_prefill_variant<D, 32, 4, 2>(a, n_tiles, s);
+}
+
+static int launch_prefill_tc(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(tc::attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             tc::SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    vcb_launch(tc::attention_prefill_tc_kernel, dim3(n_tiles, a.nkv), tc::THREADS, (size_t)tc::SMEM_BYTES, s, a);
+    return vcb_last_error();
 }
 
 static int check_common(int nh, int nkv, int d, int page, int window) {
@@ -666,6 +991,21 @@ VCB_EXPORT int vcb_attention_prefill_mma(const void* q, const void* cache, void*
                   block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, bt_stride, nh, nkv, page, window, scale};
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_prefill<64>(a, n_tiles, s) : launch_prefill<128>(a, n_tiles, s);
+}
+
+// The same on tcgen05 tensor cores: head size 128 only; tiles (tile_req, tile_row0) of 128 packed rows.
+VCB_EXPORT int vcb_attention_prefill_tc(const void* q, const void* cache, void* out, const int* q_start,
+                                        const int* ctx_lens, const int* block_table, int bt_stride,
+                                        const int* tile_req, const int* tile_row0, int n_tiles, int nh,
+                                        int nkv, int d, int page, int window, float scale, int* status,
+                                        void* stream) {
+    if (n_tiles <= 0) return 0;
+    int c = check_common(nh, nkv, d, page, window);
+    if (c) return c;
+    if (d != 128 || page % 8) return VCB_ERR_UNSUPPORTED;
+    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
+                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, bt_stride, nh, nkv, page, window, scale};
+    return launch_prefill_tc(a, n_tiles, (cudaStream_t)stream);
 }
 
 // ------------------------------------------------ no-allocation entry point

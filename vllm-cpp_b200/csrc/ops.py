@@ -36,6 +36,7 @@ _SIGNATURES = {
     "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
+    "vcb_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
     "vcb_gemm_bf16_tcgen05_fused": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P,
                                     _P, _I, _I, _I, _F, _P, _I, _P, _P, _I, _I, _P],
@@ -263,6 +264,29 @@ def attention_prefill_mma(q, cache, out, q_start, ctx_lens, block_table, tile_re
         status_tensor(q.device).data_ptr(), _stream()), "attention_prefill_mma")
 
 
+TC_ATTENTION_HEAD_DIM = 128      # head size of the tcgen05 prefill attention kernel
+TC_ATTENTION_TILE_ROWS = 128     # packed rows per tile of its work list
+
+
+def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req, tile_row0, *,
+                         num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
+                         scale: float) -> None:
+    """Attention for portions of any length on tcgen05 tensor cores (scores and output tiles in tensor
+    memory); head size 128, bfloat16, tiles of 128 packed rows."""
+    _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attention_prefill_tc is a bfloat16 kernel")
+    _need(head_dim == TC_ATTENTION_HEAD_DIM and page_size % 8 == 0,
+          f"attention_prefill_tc takes head size {TC_ATTENTION_HEAD_DIM} and pages of a multiple of 8 slots")
+    n_tiles = tile_req.numel()
+    _need(tile_row0.numel() == n_tiles, "one first row per tile")
+    _check(lib().vcb_attention_prefill_tc(
+        _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
+        _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
+        block_table.shape[1], _dev(tile_req, "tile_req", torch.int32), _dev(tile_row0, "tile_row0", torch.int32),
+        n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale),
+        status_tensor(q.device).data_ptr(), _stream()), "attention_prefill_tc")
+
+
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M,N] = a[M,K] @ w[N,K]^T in true 32-bit arithmetic; rows may be strided."""
     m, k = a.shape
@@ -278,7 +302,9 @@ SM_COUNT = 148
 _status: Optional[torch.Tensor] = None
 STATUS_MEANING = {1: "the TMA producer waited too long for a free stage", 2: "the MMA issuer waited too long for a loaded stage",
                   3: "the epilogue waited too long for the accumulator", 4: "the MMA issuer waited too long for a free accumulator",
-                  5: "decode attention waited too long for a cache tile", 6: "prefill attention waited too long for a cache tile"}
+                  5: "decode attention waited too long for a cache tile", 6: "prefill attention waited too long for a cache tile",
+                  8: "a product's merge waited too long for the tile's other segments",
+                  9: "tcgen05 prefill attention waited too long on one of its barriers"}
 
 
 def status_tensor(device) -> torch.Tensor:

@@ -118,13 +118,20 @@ class PagedAttention(Mixer):
     def _tensor_core_path(self) -> bool:
         return self.dtype == torch.bfloat16 and self.d in ops.MMA_HEAD_DIMS
 
+    def _prefill_on_tcgen05(self) -> bool:
+        return self.d == ops.TC_ATTENTION_HEAD_DIM
+
+    def _tile_rows(self) -> int:
+        return ops.TC_ATTENTION_TILE_ROWS if self._prefill_on_tcgen05() else self.TILE_ROWS
+
     def step_arrays(self):
         """Work list of the prefill kernel: for every request that brings tokens, its tiles of
-        TILE_ROWS packed rows, as [2, n_tiles] = (request index, first row)."""
+        packed rows (128 for the tcgen05 kernel, TILE_ROWS for the mma.sync one), as
+        [2, n_tiles] = (request index, first row)."""
         if not self._tensor_core_path():
             return {}
         group = self.nh // self.nkv
-        rows = self.TILE_ROWS
+        rows = self._tile_rows()
 
         def tiles(host):
             if all(q == 1 for q in host.q_lens):
@@ -140,7 +147,7 @@ class PagedAttention(Mixer):
             order = np.argsort(-np.asarray(keys), kind="stable")
             return np.array([req, row0], dtype=np.int32)[:, order]
 
-        return {f"attn_tiles_g{group}": tiles}
+        return {f"attn_tiles_g{group}_r{rows}": tiles}
 
     def attend(self, q, attn, step, cache, block_table):
         if self._tensor_core_path():
@@ -164,9 +171,9 @@ class PagedAttention(Mixer):
                 ops.attention_decode_mma(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, None,
                                          step.n_reqs, nsplit, part_o, part_ml, counters, **kw)
             else:
-                tiles = step.extras[f"attn_tiles_g{self.nh // self.nkv}"]
-                ops.attention_prefill_mma(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table,
-                                          tiles[0], tiles[1], **kw)
+                tiles = step.extras[f"attn_tiles_g{self.nh // self.nkv}_r{self._tile_rows()}"]
+                kernel = ops.attention_prefill_tc if self._prefill_on_tcgen05() else ops.attention_prefill_mma
+                kernel(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, tiles[0], tiles[1], **kw)
             return
         ops.attention_simt(q, cache.pages, attn, step.positions, step.req_of_token, block_table,
                            num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d,
