@@ -36,7 +36,15 @@ TINY_D = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_
           "tie_word_embeddings": True, "use_sliding_window": False, "max_position_embeddings": 320,
           "hidden_act": "silu"}
 
-CONFIGS = {"A": (TINY_A, 16), "B": (TINY_B, 32), "C": (TINY_C, 16), "D": (TINY_D, 32)}   # name -> (config, page size)
+# head size 128 (the tcgen05 prefill attention and the widest decode tiles), one query group of two
+# heads, the second layer windowed
+TINY_E = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 88,
+          "num_hidden_layers": 2, "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 128,
+          "intermediate_size": 136, "vocab_size": 264, "rope_theta": 50000.0, "rms_norm_eps": 2e-6,
+          "tie_word_embeddings": False, "use_sliding_window": True, "sliding_window": 70,
+          "max_window_layers": 1, "max_position_embeddings": 400, "hidden_act": "silu"}
+
+CONFIGS = {"A": (TINY_A, 16), "B": (TINY_B, 32), "C": (TINY_C, 16), "D": (TINY_D, 32), "E": (TINY_E, 16)}   # name -> (config, page size)
 
 # |engine - plain| <= TOL * max|plain| over the compared rows
 TOL = {"float32": 1e-4, "bfloat16": 3e-2}

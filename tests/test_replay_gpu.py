@@ -33,7 +33,7 @@ def build(tmp_path, name, dtype, num_pages, seed=1, max_seqs=8):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole_prompts(tmp_path, name, dtype):
     cfg, weights, cache, runner = build(tmp_path, name, dtype, num_pages=40)
     rp = Replayer(runner, cache)
@@ -45,7 +45,7 @@ def test_whole_prompts(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_prefill_then_decode_last_32(tmp_path, name, dtype):
     cfg, weights, cache, runner = build(tmp_path, name, dtype, num_pages=40)
     rp = Replayer(runner, cache)
@@ -61,7 +61,7 @@ def test_prefill_then_decode_last_32(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_portions_of_changing_size(tmp_path, name, dtype):
     cfg, weights, cache, runner = build(tmp_path, name, dtype, num_pages=40)
     rp = Replayer(runner, cache)
@@ -124,7 +124,7 @@ def mixed_trace(cfg, seed, n_requests=7, live=4):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_mixed_requests_reusing_pages(tmp_path, name, dtype):
     cfg, page = CONFIGS[name]
     # four live requests of up to 120 tokens: just enough pages, so freed ones are reused at once
@@ -151,7 +151,7 @@ def pinned_tcgen05():
     ops._linear_choice.update(saved)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_norms_fused_into_products(tmp_path, pinned_tcgen05, name):
     """Steps of up to 128 tokens run no norm kernel between products: the product before a norm adds
     into the residual stream and applies the gain, the one after applies the rows' factor.  Portions,

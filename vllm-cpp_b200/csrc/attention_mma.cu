@@ -612,23 +612,30 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 // ------------------------------------------------- prefill on tcgen05
 // The same work as attention_prefill_kernel for head size 128, on the fifth-generation tensor
 // cores.  A CTA owns 128 packed rows (token x head in group) of one kv head and walks the keys in tiles
-// of 128:
+// of 64:
 //   S = Q K^T      tcgen05.mma, Q and K from shared memory (K-major, 128-byte swizzle: the cache's
-//                  planes are that layout already), S (128 x 128 float) in tensor memory, two buffers;
-//   softmax        four warps, one thread per row: tcgen05.ld of its row, mask, running maximum,
-//                  ex2.approx, running sum; P rounded to bfloat16 into shared memory (K-major);
-//   O_tile = P V   tcgen05.mma, V from shared memory as it lies in the cache (MN-major operand),
-//                  a fresh 128 x 128 float tile in tensor memory;
-//   O += O_tile    by the row's thread in registers, rescaled when the maximum rose.
+//                  planes are that layout already), S (128 x 64 float) in tensor memory, two buffers;
+//   softmax        four warps, one thread per row: tcgen05.ld of its row, mask, maximum, ex2.approx,
+//                  sum; P rounded to bfloat16 into shared memory (K-major);
+//   O += P V       tcgen05.mma, V from shared memory as it lies in the cache (MN-major operand),
+//                  accumulated in tensor memory (128 x 128 float) over all tiles.
+// The exponent's reference is not the running maximum but a value that follows it lazily: it moves
+// only when the maximum has risen by more than 8 (in units of log2), and then the row's thread
+// rescales its row of O in tensor memory and its sum.  Probabilities stay below 2^8, sums and O in
+// float; the rescaling is rare after the first tiles.
 // Warp 0 copies K and V tiles (bulk copies from the pages, two stages each, separate barriers so a K
 // stage is free as soon as S is done), warp 1 issues the MMAs, warps 2-5 do the rest.  The MMA of
 // tile j + 1's scores is issued before tile j's P V, so the tensor cores work while tile j's softmax
-// runs.  Every wait is bounded; one that runs out sets *status and the CTA drains and leaves.
+// runs, and two CTAs share an SM (256 columns of tensor memory and 112 KB of shared memory each), so
+// one CTA's softmax runs under the other's MMAs and waits.  Every wait is bounded; one that runs
+// out sets *status and the CTA drains and leaves.
 namespace tc {
-constexpr int D = 128, BMT = 128, TKT = 128;
+constexpr int D = 128, BMT = 128, TKT = 64;
 constexpr int THREADS = 192;
 constexpr int Q_BYTES = BMT * D * 2, KV_BYTES = TKT * D * 2, P_BYTES = BMT * TKT * 2;
-constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + 256;          // no slack: the base must be 1024-aligned
+constexpr int TMEM_COLS = 256;                                               // S0, S1 (64 each), O (128)
+constexpr float RESCALE_STEP = 8.0f;
 
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -655,6 +662,21 @@ __device__ __forceinline__ void ld32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr),
+                   "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                   "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+                   "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                   "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+                   "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+                   "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+                   "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+                   "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+                 : "memory");
+}
 // K-major operand, rows of 128 bytes, 128-byte swizzle: 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t desc_k(uint32_t addr) {
     return (uint64_t)((addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
@@ -665,17 +687,16 @@ __device__ __forceinline__ uint64_t desc_mn(uint32_t addr, uint32_t plane_bytes)
     return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((plane_bytes >> 4) & 0x3FFF) << 16) |
            ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
-// float accumulator, bfloat16 A and B, M = 128, N = 128; b_mn: B is MN-major
-__host__ __device__ constexpr uint32_t idesc(bool b_mn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+// float accumulator, bfloat16 A and B, M = 128, N = n; b_mn: B is MN-major
+__host__ __device__ constexpr uint32_t idesc(int n, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc_kernel(MmaAttnArgs a) {
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) unsigned char smem[];
     // No early release of the next kernel here: its CTAs would sit on this SM holding tensor memory
-    // while CTAs of this kernel, which want all 512 columns, still wait to be placed.
+    // while CTAs of this kernel still wait to be placed.
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = a.req_list[blockIdx.x];
@@ -692,10 +713,10 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
     unsigned char* q_ptr = smem;
     unsigned char* p_ptr = smem + Q_BYTES + 4 * KV_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(p_ptr + P_BYTES);
-    // 0,1 full_k  2,3 empty_k  4,5 full_v  6,7 empty_v  8,9 s_full  10,11 s_free  12 p_full  13 p_free  14 o_full  15 o_free  16 q_ready
+    // 0,1 full_k  2,3 empty_k  4,5 full_v  6,7 empty_v  8,9 s_full  10,11 s_free  12 p_full  13 pv_done  14 q_ready
     const uint32_t b0 = cx_smem(bars);
     auto B = [&](int i) { return b0 + 8 * i; };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if (threadIdx.x == 0) {
@@ -703,26 +724,28 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
             cx_mbar_init(B(0 + i), 1); cx_mbar_init(B(2 + i), 1); cx_mbar_init(B(4 + i), 1); cx_mbar_init(B(6 + i), 1);
             cx_mbar_init(B(8 + i), 1); cx_mbar_init(B(10 + i), 4);
         }
-        cx_mbar_init(B(12), 4); cx_mbar_init(B(13), 1); cx_mbar_init(B(14), 1); cx_mbar_init(B(15), 4); cx_mbar_init(B(16), 4);
-        *abort_flag = 0;
+        cx_mbar_init(B(12), 4); cx_mbar_init(B(13), 1); cx_mbar_init(B(14), 4);
+        // the tiles' swizzle is computed from shared-memory addresses: the base must be a multiple of 1024
+        *abort_flag = (sq & 1023) ? 1 : 0;
+        if ((sq & 1023) && a.status) atomicCAS(a.status, 0, 10);
         cx_mbar_init_fence();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     fence_before();
     __syncthreads();
     fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tm_s0 = tmem, tm_o = tmem + 256;              // S buffers at columns 0 and 128, O tile at 256
+    const uint32_t tm_s0 = tmem, tm_o = tmem + 2 * TKT;          // S buffers at columns 0 and 64, O at 128
 
     // keys that any row of the tile can see
     const int last_row = min(row0 + BMT, rows_total) - 1;
     const int hi = ctx + last_row / G + 1;
     const int lo = a.window > 0 ? max(0, ctx + row0 / G + 1 - a.window) : 0;
     const int tile0 = lo / TKT, tile1 = (hi + TKT - 1) / TKT;
-    const int n_tiles = tile1 - tile0;
+    const int n_tiles = *abort_flag ? 0 : tile1 - tile0;
 
     auto give_up = [&](int code) {
         if (!*abort_flag) { *abort_flag = 1; if (a.status) atomicCAS(a.status, 0, code); }
@@ -746,25 +769,20 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         }
     } else if (warp == 1) {
         // ---- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t id_s = idesc(false), id_pv = idesc(true);
-            bool ok = cx_mbar_wait(B(16), 0);                 // Q tile written
-            if (!ok) give_up(9);
+        if (lane == 0 && n_tiles > 0) {
+            constexpr uint32_t id_s = idesc(TKT, false), id_pv = idesc(D, true);
+            bool ok = cx_mbar_wait(B(14), 0);                 // Q tile written
             fence_after();
-            auto issue_pv = [&](int j) -> bool {                // O_tile = P_j V_j
+            auto issue_pv = [&](int j) -> bool {                // O += P_j V_j
                 const int st = j & 1;
-                if (!cx_mbar_wait(B(12), j & 1) || !cx_mbar_wait(B(4 + st), (j >> 1) & 1) ||
-                    !cx_mbar_wait(B(15), (j & 1) ^ 1))
-                    return false;
+                if (!cx_mbar_wait(B(12), j & 1) || !cx_mbar_wait(B(4 + st), (j >> 1) & 1)) return false;
                 fence_after();
                 const uint32_t v_base = sv0 + st * KV_BYTES;
 #pragma unroll
-                for (int kk = 0; kk < TKT / 16; ++kk)           // 16 keys a step: P plane kk / 4, V rows 16 kk ..
-                    mma(tm_o, desc_k(sp + (kk >> 2) * (BMT * 128) + (kk & 3) * 32), desc_mn(v_base + kk * 16 * 128, TKT * 128),
-                        id_pv, kk > 0 ? 1u : 0u);
-                commit(B(14));          // O tile complete
+                for (int kk = 0; kk < TKT / 16; ++kk)           // 16 keys a step
+                    mma(tm_o, desc_k(sp + kk * 32), desc_mn(v_base + kk * 16 * 128, TKT * 128), id_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                commit(B(13));          // P read, O updated
                 commit(B(6 + st));      // V stage free
-                commit(B(13));          // P free
                 return true;
             };
             for (int j = 0; j < n_tiles && ok && !*abort_flag; ++j) {
@@ -775,13 +793,13 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
                 const uint32_t k_base = sk0 + st * KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)             // 16 dims a step: plane ks / 4
-                    mma(tm_s0 + st * 128, desc_k(sq + (ks >> 2) * (BMT * 128) + (ks & 3) * 32),
+                    mma(tm_s0 + st * TKT, desc_k(sq + (ks >> 2) * (BMT * 128) + (ks & 3) * 32),
                         desc_k(k_base + (ks >> 2) * (TKT * 128) + (ks & 3) * 32), id_s, ks > 0 ? 1u : 0u);
                 commit(B(8 + st));      // S complete
                 commit(B(2 + st));      // K stage free
                 if (j > 0 && !issue_pv(j - 1)) { ok = false; break; }
             }
-            if (ok && n_tiles > 0 && !*abort_flag && !issue_pv(n_tiles - 1)) ok = false;
+            if (ok && !*abort_flag && !issue_pv(n_tiles - 1)) ok = false;
             if (!ok) give_up(9);
         }
     } else {
@@ -802,110 +820,102 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) cx_mbar_arrive(B(16));
+        if (lane == 0) cx_mbar_arrive(B(14));
 
         const int pr = row0 + row;
         const bool row_ok = pr < rows_total;
         const int pos = ctx + min(pr, rows_total - 1) / G;                 // the row's position
         const int row_lo = a.window > 0 ? max(0, pos + 1 - a.window) : 0;
-        float o[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.0f;
-        float m = -INFINITY, l = 0.0f;
+        float m_ref = -INFINITY, l = 0.0f;           // the exponent's reference (in raw score units) and the sum relative to it
         bool ok = true;
         for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
             const int st = j & 1;
             const int kb = (tile0 + j) * TKT;
             if (!cx_mbar_wait(B(8 + st), (j >> 1) & 1)) { ok = false; break; }
             fence_after();
-            const uint32_t s_addr = tm_s0 + st * 128 + lane_addr;
+            const uint32_t s_addr = tm_s0 + st * TKT + lane_addr;
             // does any row of the tile mask any key of this tile? (the first row sees the fewest late keys,
             // the last row the fewest early ones)
             const bool edge = kb + TKT - 1 > ctx + row0 / G || (a.window > 0 && kb < ctx + last_row / G + 1 - a.window);
-            // pass 1: the row's maximum over the tile
-            float mt = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < TKT; c0 += 32) {
-                float s[32];
-                ld32(s_addr + c0, s);
+            float s[TKT];
+            {
+                float t0[32], t1[32];
+                ld32(s_addr, t0);
+                ld32(s_addr + 32, t1);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = kb + c0 + i;
-                    if (!edge || (key >= row_lo && key <= pos)) mt = fmaxf(mt, s[i]);
-                }
-            }
-            const float m_new = fmaxf(m, mt);
-            const float base = m_new == -INFINITY ? 0.0f : m_new * sl2;
-            const float corr = m == -INFINITY ? 0.0f : fast_exp2(m * sl2 - base);
-            // P may be overwritten once the P V of the tile before has read it
-            if (!cx_mbar_wait(B(13), (j & 1) ^ 1)) { ok = false; break; }
-            // pass 2: probabilities, their sum, P into shared memory (row `row`, 16-byte chunks swizzled)
-            float lt = 0.0f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < TKT; c0 += 32) {
-                float s[32];
-                ld32(s_addr + c0, s);
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int key = kb + c0 + i;
-                    float p0 = fast_exp2(fmaf(s[i], sl2, -base)), p1 = fast_exp2(fmaf(s[i + 1], sl2, -base));
-                    if (edge) {
-                        if (!(key >= row_lo && key <= pos)) p0 = 0.0f;
-                        if (!(key + 1 >= row_lo && key + 1 <= pos)) p1 = 0.0f;
-                    }
-                    lt += p0 + p1;
-                    pk[i >> 1] = pack_bf16(p0, p1);
-                }
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {                   // four chunks of eight keys
-                    const int chunk = (c0 >> 3) + q4;              // 0..15 over the tile's 128 keys
-                    *reinterpret_cast<uint4*>(p_ptr + swz_kv<D, BMT>(row, chunk)) =
-                        make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-                }
+                for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; }
             }
             // the S buffer has been read: the scores of tile j + 2 may overwrite it
             fence_before();
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) { cx_mbar_arrive(B(10 + st)); cx_mbar_arrive(B(12)); }
-            // O: add the tile before (computed with the maximum before this tile), then move to the new maximum
-            if (j > 0) {
-                if (!cx_mbar_wait(B(14), (j - 1) & 1)) { ok = false; break; }
-                fence_after();
+            if (lane == 0) cx_mbar_arrive(B(10 + st));
+            float mt = -INFINITY;
+            if (edge) {
 #pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {               // unrolled: o[] stays in registers
+                for (int i = 0; i < TKT; ++i) {
+                    const int key = kb + i;
+                    if (!(key >= row_lo && key <= pos)) s[i] = -INFINITY;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < TKT; ++i) mt = fmaxf(mt, s[i]);
+            // move the reference only when the maximum has left it far behind
+            float factor = 1.0f;
+            if (mt > m_ref && (m_ref == -INFINITY || (mt - m_ref) * sl2 > RESCALE_STEP)) {
+                factor = m_ref == -INFINITY ? 0.0f : fast_exp2((m_ref - mt) * sl2);
+                m_ref = mt;
+            }
+            const float base = m_ref == -INFINITY ? 0.0f : m_ref * sl2;
+            uint32_t pk[TKT / 2];
+            float lt = 0.0f;
+#pragma unroll
+            for (int i = 0; i < TKT; i += 2) {
+                const float p0 = fast_exp2(fmaf(s[i], sl2, -base)), p1 = fast_exp2(fmaf(s[i + 1], sl2, -base));
+                lt += p0 + p1;
+                pk[i >> 1] = pack_bf16(p0, p1);
+            }
+            // P and O belong to the P V of the tile before until it is done
+            if (!cx_mbar_wait(B(13), (j & 1) ^ 1)) { ok = false; break; }
+            if (j > 0 && __any_sync(0xffffffffu, factor != 1.0f)) {
+                // somebody's reference moved: the warp rescales its rows of O (factor 1 where nothing moved)
+                fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
                     float t[32];
                     ld32(tm_o + lane_addr + c0, t);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c0 + i] = (o[c0 + i] + t[i]) * corr;
+                    for (int i = 0; i < 32; ++i) t[i] *= factor;
+                    st32(tm_o + lane_addr + c0, t);
                 }
-                fence_before();
-                __syncwarp();
-                if (lane == 0) cx_mbar_arrive(B(15));
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            l = l * corr + lt;
-            m = m_new;
+            l = l * factor + lt;
+#pragma unroll
+            for (int q8 = 0; q8 < TKT / 8; ++q8)                     // chunks of eight keys
+                *reinterpret_cast<uint4*>(p_ptr + swz_kv<D, BMT>(row, q8)) =
+                    make_uint4(pk[q8 * 4], pk[q8 * 4 + 1], pk[q8 * 4 + 2], pk[q8 * 4 + 3]);
+            fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) cx_mbar_arrive(B(12));
         }
         if (ok && n_tiles > 0 && !*abort_flag) {
-            if (!cx_mbar_wait(B(14), (n_tiles - 1) & 1)) ok = false;
+            if (!cx_mbar_wait(B(13), (n_tiles - 1) & 1)) ok = false;
             fence_after();
             if (ok) {
                 const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-                __nv_bfloat16* dst = a.out + ((size_t)(q0 + min(pr, rows_total - 1) / G) * a.nh + g * G + min(pr, rows_total - 1) % G) * D;
-#pragma unroll
+                const int prc = min(pr, rows_total - 1);
+                __nv_bfloat16* dst = a.out + ((size_t)(q0 + prc / G) * a.nh + g * G + prc % G) * D;
+#pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     float t[32];
                     ld32(tm_o + lane_addr + c0, t);
                     if (row_ok) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 w = make_uint4(pack_bf16((o[c0 + i] + t[i]) * inv, (o[c0 + i + 1] + t[i + 1]) * inv),
-                                                 pack_bf16((o[c0 + i + 2] + t[i + 2]) * inv, (o[c0 + i + 3] + t[i + 3]) * inv),
-                                                 pack_bf16((o[c0 + i + 4] + t[i + 4]) * inv, (o[c0 + i + 5] + t[i + 5]) * inv),
-                                                 pack_bf16((o[c0 + i + 6] + t[i + 6]) * inv, (o[c0 + i + 7] + t[i + 7]) * inv));
-                            *reinterpret_cast<uint4*>(dst + c0 + i) = w;
-                        }
+                        for (int i = 0; i < 32; i += 8)
+                            *reinterpret_cast<uint4*>(dst + c0 + i) =
+                                make_uint4(pack_bf16(t[i] * inv, t[i + 1] * inv), pack_bf16(t[i + 2] * inv, t[i + 3] * inv),
+                                           pack_bf16(t[i + 4] * inv, t[i + 5] * inv), pack_bf16(t[i + 6] * inv, t[i + 7] * inv));
                     }
                 }
             }
@@ -916,7 +926,7 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
     __syncthreads();
     if (warp == 1) {
         fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
 }
 }  // namespace tc

@@ -304,7 +304,8 @@ STATUS_MEANING = {1: "the TMA producer waited too long for a free stage", 2: "th
                   3: "the epilogue waited too long for the accumulator", 4: "the MMA issuer waited too long for a free accumulator",
                   5: "decode attention waited too long for a cache tile", 6: "prefill attention waited too long for a cache tile",
                   8: "a product's merge waited too long for the tile's other segments",
-                  9: "tcgen05 prefill attention waited too long on one of its barriers"}
+                  9: "tcgen05 prefill attention waited too long on one of its barriers",
+                  10: "tcgen05 prefill attention found its shared memory not aligned to 1024 bytes"}
 
 
 def status_tensor(device) -> torch.Tensor:
