@@ -144,7 +144,8 @@ template <int D, int TK>
 __device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t bar, int kb, int lo, int hi,
                                              PageWindow& pw, const __nv_bfloat16* __restrict__ cache,
                                              size_t head_base, size_t page_stride, size_t v_off, const PageDiv& pd, int lane,
-                                             uint32_t bar_v = 0) {
+                                             uint32_t bar_v = 0, int which = 0) {
+    // which: 0 K and V, 1 K only, 2 V only (a kernel that fetches them at different times)
     constexpr int PLANES = D / 64;
     static_assert(PLANES == 1 || PLANES == 2, "head sizes 64 and 128");
     const int piece = lane & 7, plane = (lane >> 3) & 1;
@@ -164,8 +165,8 @@ __device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t 
     // plane `plane` of the head's block: pd.page rows of 64 elements
     const __nv_bfloat16* src = cache + (size_t)pg * page_stride + head_base + ((size_t)plane * pd.page + (start - page_lo)) * 64;
     const uint32_t off = (uint32_t)(plane * TK + (start - kb)) * 128, bytes = (uint32_t)(end - start) * 128;
-    if (lane < 16) cx_bulk_load(sk + off, src, bytes, bar);
-    else cx_bulk_load(sv + off, src + v_off, bytes, bar_v ? bar_v : bar);
+    if (lane < 16) { if (which != 2) cx_bulk_load(sk + off, src, bytes, bar); }
+    else if (which != 1) cx_bulk_load(sv + off, src + v_off, bytes, bar_v ? bar_v : bar);
 }
 
 // S[16 x 8*NB] += Q[16 x D] * K[keys key0 .. key0 + 8*NB)^T, K tile at sk.
@@ -752,20 +753,32 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
     };
 
     if (warp == 0) {
-        // ---- producer: K and V tiles, two stages each
-        PageWindow pw;
+        // ---- producer: K and V tiles, two stages each.  K_j is wanted a tile earlier than V_j (the
+        // scores come first) and its stage is free earlier (once S_{j-2} is done), so the two are
+        // fetched apart: K_j, then V_{j-1}.
+        PageWindow pw_k, pw_v;
         const PageDiv pd(a.page);
-        pw.init(bt, pd.div(tile0 * TKT), hi, a.page, lane);
+        pw_k.init(bt, pd.div(tile0 * TKT), hi, a.page, lane);
+        pw_v.init(bt, pd.div(tile0 * TKT), hi, a.page, lane);
         const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
                      v_off = (size_t)a.nkv * a.page * D;
-        for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
-            const int st = j & 1;
-            const uint32_t ph = ((j >> 1) & 1) ^ 1;
-            if (!cx_mbar_wait(B(2 + st), ph) || !cx_mbar_wait(B(6 + st), ph)) { give_up(9); break; }
-            if (lane == 0) { cx_mbar_expect_tx(B(0 + st), KV_BYTES); cx_mbar_expect_tx(B(4 + st), KV_BYTES); }
-            __syncwarp();
-            produce_tile<D, TKT>(sk0 + st * KV_BYTES, sv0 + st * KV_BYTES, B(0 + st), (tile0 + j) * TKT, lo, hi, pw, a.cache,
-                                 head_base, page_stride, v_off, pd, lane, B(4 + st));
+        for (int j = 0; j <= n_tiles && !*abort_flag; ++j) {
+            if (j < n_tiles) {
+                const int st = j & 1;
+                if (!cx_mbar_wait(B(2 + st), ((j >> 1) & 1) ^ 1)) { give_up(9); break; }
+                if (lane == 0) cx_mbar_expect_tx(B(0 + st), KV_BYTES);
+                __syncwarp();
+                produce_tile<D, TKT>(sk0 + st * KV_BYTES, 0, B(0 + st), (tile0 + j) * TKT, lo, hi, pw_k, a.cache,
+                                     head_base, page_stride, v_off, pd, lane, 0, 1);
+            }
+            if (j > 0) {
+                const int jv = j - 1, st = jv & 1;
+                if (!cx_mbar_wait(B(6 + st), ((jv >> 1) & 1) ^ 1)) { give_up(9); break; }
+                if (lane == 0) cx_mbar_expect_tx(B(4 + st), KV_BYTES);
+                __syncwarp();
+                produce_tile<D, TKT>(0, sv0 + st * KV_BYTES, 0, (tile0 + jv) * TKT, lo, hi, pw_v, a.cache,
+                                     head_base, page_stride, v_off, pd, lane, B(4 + st), 2);
+            }
         }
     } else if (warp == 1) {
         // ---- MMA issuer
