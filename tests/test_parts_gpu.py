@@ -1,6 +1,7 @@
 """Each part of a layer alone against its plain formula, and the generality of the parts:
-a toy architecture defined in this file — a mixer with state of its own, a position
-encoding the fused kernel does not know, different mixers in different layers, a layer that
+a toy architecture defined in this file — a mixer with state of its own, a feed-forward that
+routes tokens to experts, a position encoding the fused kernel does not know, different mixers
+and feed-forwards in different layers, a layer that
 runs twice, a layer that reads another layer's cache — is registered, built, loaded and
 stepped through the unchanged framework, and compared with a plain model under different
 ways of cutting the work."""
@@ -132,14 +133,14 @@ def test_attention_part_whole_and_in_portions(dtype, nh, nkv, d, window):
 # --------------------------------------------------------------------------------------
 # A toy architecture, defined here and nowhere in the framework.
 TOY_CFG = {"architectures": ["ToyMixForCausalLM"], "hidden_size": 48, "vocab_size": 97, "heads": 3, "head_dim": 16,
-           "inter": 80, "eps": 1e-5, "max_position_embeddings": 200, "tie_word_embeddings": False}
+           "inter": 80, "experts": 3, "expert_inter": 24, "eps": 1e-5, "max_position_embeddings": 200, "tie_word_embeddings": False}
 
 
 def register_toy():
     from vllm_cpp_b200.config.model_spec import LayerCall, LayerSpec, ModelSpec, PartSpec
     from vllm_cpp_b200.config.registry import register_architecture
-    from vllm_cpp_b200.parts.base import (Mixer, ParamSpec, PositionEncoding, StateSpec, register_mixer,
-                                          register_position_encoding)
+    from vllm_cpp_b200.parts.base import (FeedForward, Mixer, ParamSpec, PositionEncoding, StateSpec,
+                                          register_feed_forward, register_mixer, register_position_encoding)
 
     @register_mixer("toy_running_mean")
     class RunningMean(Mixer):
@@ -168,6 +169,41 @@ def register_toy():
                     state[: self.h] = sums[-1]
                     state[self.h] = counts[-1]
 
+    @register_feed_forward("toy_relu_routed")
+    class ReluRouted(FeedForward):
+        """out = sum_e g_e(x) down_e(relu(up_e x)) with g = relu(router x) / (1 + sum relu(router x)), router
+        logits in 32-bit.  An expert runs only on the tokens that give it a weight above zero; the
+        weights fall to zero continuously, so rounding cannot flip a choice into a different result."""
+
+        def __init__(self, hidden_size, inter, experts, dtype, device):
+            self.h, self.inter, self.n, self.dtype = hidden_size, inter, experts, dtype
+
+        def param_specs(self):
+            specs = {"router.weight": ParamSpec((self.n, self.h), "bias")}        # held in float32
+            for e in range(self.n):
+                specs[f"experts.{e}.up.weight"] = ParamSpec((self.inter, self.h))
+                specs[f"experts.{e}.down.weight"] = ParamSpec((self.h, self.inter))
+            return specs
+
+        def load_params(self, tensors):
+            self.router = tensors["router.weight"]
+            self.up = [tensors[f"experts.{e}.up.weight"] for e in range(self.n)]
+            self.down = [tensors[f"experts.{e}.down.weight"] for e in range(self.n)]
+            self.tokens_per_expert = [0] * self.n
+
+        def forward(self, x, out, step, ws):
+            gate = torch.relu(x.float() @ self.router.t())
+            gate = gate / (1.0 + gate.sum(dim=1, keepdim=True))
+            acc = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for e in range(self.n):
+                rows = torch.nonzero(gate[:, e] > 0).flatten()
+                self.tokens_per_expert[e] += rows.numel()
+                if rows.numel() == 0:
+                    continue
+                hidden = torch.relu(x[rows] @ self.up[e].t())
+                acc.index_add_(0, rows, (hidden @ self.down[e].t()).float() * gate[rows, e, None])
+            out.copy_(acc)
+
     @register_position_encoding("toy_ramp")
     class Ramp(PositionEncoding):
         """Adds slope * position to the first element of every q and k head; not a rotation,
@@ -188,13 +224,14 @@ def register_toy():
         attn = lambda pos: PartSpec("attention", {"hidden_size": h, "num_heads": cfg["heads"], "num_kv_heads": 1,
                                                   "head_dim": cfg["head_dim"], "qkv_bias": False, "out_bias": False,
                                                   "window": 0, "position": pos})
-        kinds = [attn(PartSpec("rope", {"theta": 1e4, "rotary_dim": 8, "pairing": "interleaved"})),
-                 PartSpec("toy_running_mean", {"hidden_size": h}),
-                 attn(PartSpec("toy_ramp", {"slope": 0.01}))]
+        routed = PartSpec("toy_relu_routed", {"hidden_size": h, "inter": cfg["expert_inter"], "experts": cfg["experts"]})
+        kinds = [(attn(PartSpec("rope", {"theta": 1e4, "rotary_dim": 8, "pairing": "interleaved"})), ff()),
+                 (PartSpec("toy_running_mean", {"hidden_size": h}), routed),
+                 (attn(PartSpec("toy_ramp", {"slope": 0.01})), ff())]
         layers = []
-        for i, mixer in enumerate(kinds):
+        for i, (mixer, feed_forward) in enumerate(kinds):
             p = f"toy.{i}."
-            layers.append(LayerSpec(mixer=mixer, feed_forward=ff(), mixer_norm=norm(), feed_forward_norm=norm(),
+            layers.append(LayerSpec(mixer=mixer, feed_forward=feed_forward, mixer_norm=norm(), feed_forward_norm=norm(),
                                     names={"mixer": p + "mixer.", "feed_forward": p + "ff.", "mixer_norm": p + "n1.",
                                            "feed_forward_norm": p + "n2."}))
         # layer 0, the state layer, layer 2, then layer 0's weights once more on layer 0's cache
@@ -242,6 +279,14 @@ def toy_plain_forward(w, cfg, ids):
         return plain.linear(run, w[p + "mix.weight"])
 
     def ff(x, p):
+        if p + "router.weight" in w:               # the routed feed-forward: every expert on every token
+            gate = np.maximum(plain.linear(x, w[p + "router.weight"]), 0.0)
+            gate = gate / (1.0 + gate.sum(axis=1, keepdims=True))
+            y = np.zeros_like(x)
+            for e in range(cfg["experts"]):
+                hidden = np.maximum(plain.linear(x, w[p + f"experts.{e}.up.weight"]), 0.0)
+                y += gate[:, e:e + 1] * plain.linear(hidden, w[p + f"experts.{e}.down.weight"])
+            return y
         return plain.swiglu_mlp(x, w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"])
 
     x = plain.embedding(ids, w["toy.embed"])
@@ -309,3 +354,6 @@ def test_toy_architecture_with_state_runs_through_the_unchanged_framework(tmp_pa
     for r in "abcd":
         compare(rp.logits_of(r, range(len(ids[r]))), want[r], dtype, f"toy mixed {r}")
     assert cache.num_free_pages() == 24 and len(cache._free_slots) == 3
+    # the routed feed-forward did route: every expert got some tokens and none got all of them
+    seen = model.blocks[1].feed_forward.tokens_per_expert
+    assert all(0 < n < sum(seen) for n in seen), seen
