@@ -295,6 +295,18 @@ def test_attention_decode_mma(ops, nsplit, nh, nkv, d, page, window):
     got2 = out2.float().cpu().numpy().reshape(n, nh, d)
     close(got2[[5, 2]], want[[5, 2]], "bfloat16", "decode with a request list")
     assert not got2[[0, 1, 3, 4, 6]].any()
+    # splits of a fixed number of tiles: the long contexts take several grid columns, the short ones one;
+    # a number that would need more columns than the grid has falls back to equal parts
+    for tiles_per_split in (1, 5, 11, 1000):
+        out3 = torch.zeros_like(out)
+        ops.attention_decode_mma(dev(c["q"].reshape(n, -1), torch.bfloat16), dev(c["cache"], torch.bfloat16), out3,
+                                 dev(c["q_start"]), dev(np.array(ctx_lens, dtype=np.int32)), dev(c["bt"]), None, n, nsplit,
+                                 part_o, part_ml, counters, num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page,
+                                 window=window, scale=float(np.float32(1) / np.sqrt(np.float32(d))),
+                                 split_tiles=dev(np.array([tiles_per_split], dtype=np.int32)))
+        close(out3.float().cpu().numpy().reshape(n, nh, d), want, "bfloat16",
+              f"attention_decode_mma nsplit={nsplit}, {tiles_per_split} tiles a split")
+        assert not counters.any()
 
 
 def test_attention_refuses_what_it_cannot_do(ops):

@@ -50,6 +50,7 @@ struct MmaAttnArgs {
     float* part_ml;                // decode scratch: [n_list, nh, splits, 2]  (max in log2 units, sum)
     int* counters;                 // decode scratch: [n_list, nkv] tickets, zero between launches
     int* status;                   // nonzero after a bounded wait ran out (may be null)
+    const int* split_tiles;        // decode: key tiles per split, on the device (null: every request in gridDim.x equal parts)
     int bt_stride, nh, nkv, page, window;
     float scale;
 };
@@ -227,7 +228,7 @@ attention_decode_kernel(MmaAttnArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool producer = warp == 4;
     bool waited = false;                                 // producer: griddepcontrol.wait has been executed
-    const int split = blockIdx.x, nsplit = gridDim.x, g = blockIdx.y, li = blockIdx.z;
+    const int split = blockIdx.x, g = blockIdx.y, li = blockIdx.z;
     const int r = a.req_list ? a.req_list[li] : li;
     const int G = a.nh / a.nkv;
     const int t = a.q_start[r];
@@ -237,8 +238,20 @@ attention_decode_kernel(MmaAttnArgs a) {
     const int* bt = a.block_table + (size_t)r * a.bt_stride;
     const float sl2 = a.scale * LOG2E;                   // scores in units of log2
 
+    // The splits of a request.  With split_tiles no split of any request has more than that many tiles
+    // (a request's tiles are dealt evenly to the splits it needs), so a request with a long context gets
+    // more CTAs than one with a short context and the CTAs of a step with mixed contexts end together;
+    // the CTAs beyond a request's splits leave at once.
+    // (A number that would need more splits than the grid has falls back to equal parts.)
     const int tile0 = lo / BN, tile1 = (hi + BN - 1) / BN;
-    const int per = (tile1 - tile0 + nsplit - 1) / nsplit;
+    const int grid_splits = gridDim.x;
+    int per = (tile1 - tile0 + grid_splits - 1) / grid_splits, nsplit = grid_splits;
+    if (a.split_tiles) {
+        const int want = max(1, __ldg(a.split_tiles));
+        const int needs = (tile1 - tile0 + want - 1) / want;
+        if (needs <= grid_splits) { nsplit = max(1, needs); per = (tile1 - tile0 + nsplit - 1) / nsplit; }
+    }
+    if (split >= nsplit) return;
     const int my0 = tile0 + split * per, my1 = min(tile1, my0 + per);
 
     // [STAGES x (K, V) tiles][Q: 16 x D][barriers]; the merge buffers reuse the tiles
@@ -389,7 +402,7 @@ attention_decode_kernel(MmaAttnArgs a) {
                 uint2 packed = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
                 *reinterpret_cast<uint2*>(a.out + ((size_t)t * a.nh + head) * D + dim) = packed;
             } else {
-                const size_t pi = ((size_t)li * a.nh + head) * nsplit + split;
+                const size_t pi = ((size_t)li * a.nh + head) * grid_splits + split;
                 *reinterpret_cast<float4*>(a.part_o + pi * D + dim) = acc;
                 if (dim == 0) { a.part_ml[pi * 2] = mx; a.part_ml[pi * 2 + 1] = l; }
             }
@@ -412,7 +425,7 @@ attention_decode_kernel(MmaAttnArgs a) {
     float2* ml = reinterpret_cast<float2*>(smem);          // [G][nsplit]
     for (int i = threadIdx.x; i < G * nsplit; i += BLOCK_THREADS) {
         const int hg = i / nsplit, sp = i - hg * nsplit;
-        ml[i] = __ldcg(reinterpret_cast<const float2*>(a.part_ml) + ((size_t)li * a.nh + g * G + hg) * nsplit + sp);
+        ml[i] = __ldcg(reinterpret_cast<const float2*>(a.part_ml) + ((size_t)li * a.nh + g * G + hg) * grid_splits + sp);
     }
     __syncthreads();
     // four dimensions of one head per thread: all its loads of partial outputs are independent
@@ -422,7 +435,7 @@ attention_decode_kernel(MmaAttnArgs a) {
         const float2* mlh = ml + hg * nsplit;
         float mx = -INFINITY, total = 0.0f;
         for (int sp = 0; sp < nsplit; ++sp) mx = fmaxf(mx, mlh[sp].x);
-        const float* po = a.part_o + ((size_t)li * a.nh + head) * nsplit * D + dim;
+        const float* po = a.part_o + ((size_t)li * a.nh + head) * grid_splits * D + dim;
         float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 8
         for (int sp = 0; sp < nsplit; ++sp) {
@@ -984,20 +997,23 @@ static int check_common(int nh, int nkv, int d, int page, int window) {
     return 0;
 }
 
+// split_tiles (device, may be null): key tiles of 64 per split; a request then takes as many of the nsplit
+// grid columns as its context needs (see the kernel).
 // Scratch for the split-KV merge (nsplit > 1): part_o needs n_list*nh*nsplit*d floats, part_ml
 // n_list*nh*nsplit*2 floats, counters n_list*nkv ints that are zero when the kernel starts (it
 // leaves them zero).
 VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* out, const int* q_start,
                                         const int* ctx_lens, const int* block_table, int bt_stride,
                                         const int* req_list, int n_list, int nsplit, float* part_o,
-                                        float* part_ml, int* counters, int nh, int nkv, int d, int page,
-                                        int window, float scale, int* status, void* stream) {
+                                        float* part_ml, int* counters, const int* split_tiles, int nh, int nkv,
+                                        int d, int page, int window, float scale, int* status, void* stream) {
     if (n_list <= 0) return 0;
     int c = check_common(nh, nkv, d, page, window);
     if (c) return c;
     if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, req_list, nullptr, part_o, part_ml, counters, status, bt_stride, nh, nkv, page, window, scale};
+                  block_table, req_list, nullptr, part_o, part_ml, counters, status, split_tiles, bt_stride, nh, nkv,
+                  page, window, scale};
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
@@ -1011,7 +1027,8 @@ VCB_EXPORT int vcb_attention_prefill_mma(const void* q, const void* cache, void*
     int c = check_common(nh, nkv, d, page, window);
     if (c) return c;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, bt_stride, nh, nkv, page, window, scale};
+                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
+                  window, scale};
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_prefill<64>(a, n_tiles, s) : launch_prefill<128>(a, n_tiles, s);
 }
@@ -1027,7 +1044,8 @@ VCB_EXPORT int vcb_attention_prefill_tc(const void* q, const void* cache, void* 
     if (c) return c;
     if (d != 128 || page % 8) return VCB_ERR_UNSUPPORTED;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, bt_stride, nh, nkv, page, window, scale};
+                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
+                  window, scale};
     return launch_prefill_tc(a, n_tiles, (cudaStream_t)stream);
 }
 
@@ -1094,6 +1112,7 @@ VCB_EXPORT int vcb_attention_decode_mma_static(const void* q, const void* cache,
         if (e != cudaSuccess) return (int)e;
     }
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, req_list, nullptr, part_o, part_ml, counters, status, bt_stride, nh, nkv, page, window, scale};
+                  block_table, req_list, nullptr, part_o, part_ml, counters, status, nullptr, bt_stride, nh, nkv, page,
+                  window, scale};
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }

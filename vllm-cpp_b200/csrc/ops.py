@@ -34,7 +34,7 @@ _SIGNATURES = {
     "vcb_rope_cache_write": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "vcb_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+    "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "vcb_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
@@ -222,12 +222,17 @@ def attention_simt(q, cache, out, positions, req_of_token, block_table, *, num_h
 
 
 MMA_HEAD_DIMS = (64, 128)
+DECODE_KEY_TILE = 64          # keys per tile of the decode kernel
+DECODE_MAX_SPLITS = 32
 
 
 def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list, n_list: int, nsplit: int,
                          part_o, part_ml, counters, *, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
-                         window: int, scale: float) -> None:
-    """Split-KV tensor-core attention for requests that bring one token each (bfloat16)."""
+                         window: int, scale: float, split_tiles=None) -> None:
+    """Split-KV tensor-core attention for requests that bring one token each (bfloat16).  The grid has
+    ``nsplit`` columns; without ``split_tiles`` every request's keys are cut into that many equal parts,
+    with it (int32 [1] on the device: tiles of DECODE_KEY_TILE keys per split) a request takes as many
+    columns as its context needs, so that requests of different lengths keep all CTAs equally busy."""
     _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
           "attention_decode_mma is a bfloat16 kernel")
     _need(head_dim in MMA_HEAD_DIMS, f"attention_decode_mma takes head sizes {MMA_HEAD_DIMS}, got {head_dim}")
@@ -243,6 +248,7 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
         n_list, nsplit, None if part_o is None else _dev(part_o, "part_o", torch.float32),
         None if part_ml is None else _dev(part_ml, "part_ml", torch.float32),
         None if counters is None else _dev(counters, "counters", torch.int32),
+        None if split_tiles is None else _dev(split_tiles, "split_tiles", torch.int32),
         num_heads, num_kv_heads, head_dim, page_size, window, float(scale),
         status_tensor(q.device).data_ptr(), _stream()), "attention_decode_mma")
 

@@ -43,6 +43,9 @@ class HostStep:
     q_lens: List[int]
     ctx_lens: List[int]               # tokens in the cache before the step
     page_size: int
+    # launch shapes (grid sizes and the like) that a builder derives from the step: a captured step is
+    # replayed only for steps with the same shapes
+    shapes: Dict[str, int] = field(default_factory=dict)
 
 
 class StepError(ValueError):
@@ -118,7 +121,7 @@ class ModelRunner:
         step of a shape runs directly (it also sizes workspace and scratch), the second is
         captured, later ones replay.  The metadata copy and the sampling stay outside the graph."""
         from ..csrc import ops
-        key = (step.n_reqs, step.split_len)
+        key = (step.n_reqs, step.split_len, tuple(sorted(step.shapes.items())))
         sig = self._buffers_signature()
         if sig != self._graph_sig:
             self.graphs.clear()             # a buffer moved: recorded addresses are stale
@@ -278,4 +281,4 @@ class ModelRunner:
             decode_only=decode_only, max_q_len=max(q_lens),
             max_total_len=max(c + q for c, q in zip(ctx_lens, q_lens)),
             split_len=max(256, 1 << (max(c + q for c, q in zip(ctx_lens, q_lens)) - 1).bit_length()),
-            extras={name: dev("x:" + name, arr.shape) for name, arr in extra.items()})
+            extras={name: dev("x:" + name, arr.shape) for name, arr in extra.items()}, shapes=dict(host.shapes))

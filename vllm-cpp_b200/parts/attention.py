@@ -125,9 +125,10 @@ class PagedAttention(Mixer):
         return ops.TC_ATTENTION_TILE_ROWS if self._prefill_on_tcgen05() else self.TILE_ROWS
 
     def step_arrays(self):
-        """Work list of the prefill kernel: for every request that brings tokens, its tiles of
-        packed rows (128 for the tcgen05 kernel, TILE_ROWS for the mma.sync one), as
-        [2, n_tiles] = (request index, first row)."""
+        """What the kernels need per step beyond the common arrays, built on the host from the step's
+        lengths.  The prefill kernel's work list: for every request that brings tokens, its tiles of
+        packed rows (128 for the tcgen05 kernel, TILE_ROWS for the mma.sync one), as [2, n_tiles] =
+        (request index, first row).  The decode kernel's split length: see ``splits`` below."""
         if not self._tensor_core_path():
             return {}
         group = self.nh // self.nkv
@@ -147,21 +148,52 @@ class PagedAttention(Mixer):
             order = np.argsort(-np.asarray(keys), kind="stable")
             return np.array([req, row0], dtype=np.int32)[:, order]
 
-        return {f"attn_tiles_g{group}_r{rows}": tiles}
+        def splits(host):
+            """Decode-only steps: [most key tiles a split may have], and the grid's columns as a launch
+            shape.  A request gets as many splits as its context needs under that bound, so one with a
+            long context gets more CTAs than one with a short context.  The bound is the smallest with
+            which the splits of all requests fill the device once (two CTAs fit an SM; a second wave
+            would double the time).  Equal contexts come out as before: all requests in equal parts."""
+            if any(q != 1 for q in host.q_lens):
+                return np.zeros(1, dtype=np.int32)
+            tile, most = ops.DECODE_KEY_TILE, ops.DECODE_MAX_SPLITS
+            hi = np.asarray(host.ctx_lens, dtype=np.int64) + 1
+            lo = np.maximum(0, hi - self.window) if self.window > 0 else np.zeros_like(hi)
+            n = -(-hi // tile) - lo // tile                     # key tiles of every request
+            slots = max(len(n), 2 * self.SM_COUNT // self.nkv)  # splits per kv head that fill the device once
+            low, high = max(1, -(-int(n.sum()) // slots)), int(n.max())
+            while low < high:                                   # smallest count whose splits fit the slots
+                mid = (low + high) // 2
+                if int((-(-n // mid)).sum()) <= slots:
+                    high = mid
+                else:
+                    low = mid + 1
+            per = max(low, -(-int(n.max()) // most))
+            need = -(-int(n.max()) // per)
+            host.shapes[self._splits_key()] = 1 << (need - 1).bit_length()
+            return np.array([per], dtype=np.int32)
+
+        return {f"attn_tiles_g{group}_r{rows}": tiles, self._splits_key(): splits}
+
+    def _splits_key(self):
+        return f"attn_splits_kv{self.nkv}_w{self.window}"
 
     def attend(self, q, attn, step, cache, block_table):
         if self._tensor_core_path():
             kw = dict(num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d, page_size=cache.page_size,
                       window=self.window, scale=self.scale)
             if step.decode_only:
-                # the split count depends on the context only through its power-of-two bucket, so
-                # that a captured step stays valid while the contexts grow inside the bucket
-                longest = step.split_len or step.max_total_len
-                if self.window > 0:
-                    longest = min(longest, self.window + 64)
-                # as many splits as fill the GPU once: two CTAs fit an SM, a second wave would
-                # double the time
-                nsplit = max(1, min(-(-longest // 64), 2 * self.SM_COUNT // (step.n_reqs * self.nkv), 32))
+                nsplit = step.shapes.get(self._splits_key())
+                split_tiles = step.extras.get(self._splits_key())
+                if nsplit is None:
+                    # a step without the builder's arrays: every request in equal parts, as many as fill
+                    # the device once, from the longest context's power-of-two bucket
+                    longest = step.split_len or step.max_total_len
+                    if self.window > 0:
+                        longest = min(longest, self.window + 64)
+                    nsplit = max(1, min(-(-longest // 64), 2 * self.SM_COUNT // (step.n_reqs * self.nkv),
+                                        ops.DECODE_MAX_SPLITS))
+                    split_tiles = None
                 part_o = part_ml = counters = None
                 if nsplit > 1:
                     need = step.n_reqs * self.nh * nsplit
@@ -169,7 +201,7 @@ class PagedAttention(Mixer):
                     part_ml = ops.scratch("attn_part_ml", need * 2, q.device)
                     counters = ops.zeroed_ints("attn_tickets", step.n_reqs * self.nkv, q.device)
                 ops.attention_decode_mma(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, None,
-                                         step.n_reqs, nsplit, part_o, part_ml, counters, **kw)
+                                         step.n_reqs, nsplit, part_o, part_ml, counters, split_tiles=split_tiles, **kw)
             else:
                 tiles = step.extras[f"attn_tiles_g{self.nh // self.nkv}_r{self._tile_rows()}"]
                 kernel = ops.attention_prefill_tc if self._prefill_on_tcgen05() else ops.attention_prefill_mma

@@ -88,6 +88,7 @@ class StepContext:
     max_total_len: int                   # longest context after this step
     split_len: int = 0                   # max_total_len rounded up to a power of two (stable kernel shapes)
     extras: Dict[str, object] = field(default_factory=dict)   # per-step device arrays of kernels
+    shapes: Dict[str, int] = field(default_factory=dict)      # launch shapes the parts' builders chose for the step
 
 
 class Workspace:
