@@ -192,27 +192,46 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     }
 }
 
-// Eight elements per thread with 16-byte accesses (bfloat16, inter % 8 == 0).
+// Eight elements per vector with 16-byte accesses (bfloat16, inter % 8 == 0), four vectors per thread
+// and round so that eight loads are in flight before the first is used.  The result is rounded to
+// bfloat16, so the exponential and the division are the fast ones (a few units in the last place of a
+// float); the 32-bit path above uses expf and a true division.
+template <typename IDX>
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
-                                       int inter, size_t n_vec) {
+                                       int inter, IDX n_vec) {
     pdl_start();
-    const int vpr = inter >> 3;                       // vectors per row
-    for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = v / vpr;
-        const int i = (int)(v % vpr) << 3;
-        const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + i);
-        const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + inter + i);
-        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
-        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
-        uint4 o4;
-        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+    constexpr int U = 4;
+    const IDX vpr = (IDX)(inter >> 3);                // vectors per row
+    const IDX stride = (IDX)gridDim.x * blockDim.x * U;
+    for (IDX v0 = (IDX)blockIdx.x * blockDim.x * U + threadIdx.x; v0 < n_vec; v0 += stride) {
+        uint4 g4[U], u4[U];
+        size_t dst[U];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-            const float a = g.x / (1.0f + expf(-g.x)), b = g.y / (1.0f + expf(-g.y));
-            o2[k] = __floats2bfloat162_rn(a * u.x, b * u.y);
+        for (int k = 0; k < U; ++k) {
+            const IDX v = v0 + (IDX)k * blockDim.x;
+            if (v >= n_vec) { dst[k] = ~(size_t)0; g4[k] = u4[k] = make_uint4(0, 0, 0, 0); continue; }
+            const IDX t = v / vpr;
+            const size_t i = (size_t)(v - t * vpr) << 3;
+            const __nv_bfloat16* row = gu + (size_t)t * 2 * inter;
+            g4[k] = *reinterpret_cast<const uint4*>(row + i);
+            u4[k] = *reinterpret_cast<const uint4*>(row + inter + i);
+            dst[k] = (size_t)t * inter + i;
         }
-        *reinterpret_cast<uint4*>(out + t * inter + i) = o4;
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            if (dst[k] == ~(size_t)0) continue;
+            const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4[k]);
+            const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4[k]);
+            uint4 o4;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
+                const float a = __fdividef(g.x, 1.0f + __expf(-g.x)), b = __fdividef(g.y, 1.0f + __expf(-g.y));
+                o2[e] = __floats2bfloat162_rn(a * u.x, b * u.y);
+            }
+            *reinterpret_cast<uint4*>(out + dst[k]) = o4;
+        }
     }
 }
 
@@ -221,9 +240,14 @@ VCB_EXPORT int vcb_silu_mul(const void* gu, void* out, int n_tokens, int inter, 
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VCB_BF16 && inter % 8 == 0 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
         const size_t n_vec = (size_t)n_tokens * (inter >> 3);
-        size_t blocks = (n_vec + 255) / 256;
+        size_t blocks = (n_vec + 1023) / 1024;
         if (blocks > 148 * 16) blocks = 148 * 16;
-        vcb_launch(silu_mul_bf16x8_kernel, (int)blocks, 256, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, n_vec);
+        if (n_vec < (1u << 30))
+            vcb_launch(silu_mul_bf16x8_kernel<unsigned>, (int)blocks, 256, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+                       inter, (unsigned)n_vec);
+        else
+            vcb_launch(silu_mul_bf16x8_kernel<size_t>, (int)blocks, 256, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+                       inter, n_vec);
         return vcb_last_error();
     }
     const int threads = 256;
@@ -315,35 +339,50 @@ __global__ void rope_cache_kernel(RopeCacheArgs a, int heads_per_block) {
 // multiple of 16): 16-byte accesses, the angles' sines and cosines computed once per token and shared
 // by all heads.  One CTA per (token, group of heads); a thread owns chunk c of the first half of a
 // head and its partner chunk in the second half.
-__global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block) {
-    extern __shared__ float2 trig[];                    // [d / 2] (cos, sin)
+template <int TOK>
+__global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block, int n_tokens) {
+    extern __shared__ float2 trig[];                    // [TOK][d / 2] (cos, sin)
     // Positions, denominators and the block table belong to the step (copied in before its first
     // kernel), not to the kernel before this one: the table of sines and cosines is made while that
     // kernel still runs, and only qkv is read after griddepcontrol.wait.
+    // A CTA takes TOK tokens (one for the few tokens of a decode step, several for a prompt's portion:
+    // the biases are fetched once and the loads of all its tokens are in flight together).
     pdl_launch_dependents();
-    const int t = blockIdx.x;
+    const int t0 = blockIdx.x * TOK;
     const int nheads = a.nh + 2 * a.nkv;
     const int half = a.d / 2, chunks = half / 8;
-    const int pos = a.positions[t];
+    int pos[TOK];
+#pragma unroll
+    for (int k = 0; k < TOK; ++k) pos[k] = t0 + k < n_tokens ? a.positions[t0 + k] : 0;
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
-        float sn, cs;
-        sincosf((float)pos / a.denom[j], &sn, &cs);
-        trig[j] = make_float2(cs, sn);
+        const float den = a.denom[j];
+#pragma unroll
+        for (int k = 0; k < TOK; ++k) {
+            float sn, cs;
+            sincosf((float)pos[k] / den, &sn, &cs);
+            trig[k * half + j] = make_float2(cs, sn);
+        }
     }
     const int h = blockIdx.y * heads_per_block + threadIdx.x / chunks;
     const int c = threadIdx.x % chunks;
     const bool mine = h < nheads && threadIdx.x < heads_per_block * chunks;
+    const bool to_cache = mine && h >= a.nh;
     // where a k or v row goes
-    __nv_bfloat16* row_dst = nullptr;
-    int slot = 0;
-    if (mine && h >= a.nh && a.write_kv) {
-        const int r = a.req_of_token[t];
-        const int pg = a.block_table[(size_t)r * a.bt_stride + pos / a.page];
-        slot = pos % a.page;
-        __nv_bfloat16* base = (__nv_bfloat16*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
-        const int kvh = h < a.nh + a.nkv ? h - a.nh : h - a.nh - a.nkv;
-        const size_t which = h < a.nh + a.nkv ? 0 : (size_t)a.nkv * a.page * a.d;
-        row_dst = base + which + (size_t)kvh * a.page * a.d;             // the head's block of the page
+    __nv_bfloat16* row_dst[TOK];
+    int slot[TOK];
+#pragma unroll
+    for (int k = 0; k < TOK; ++k) {
+        row_dst[k] = nullptr;
+        slot[k] = 0;
+        if (to_cache && a.write_kv && t0 + k < n_tokens) {
+            const int r = a.req_of_token[t0 + k];
+            const int pg = a.block_table[(size_t)r * a.bt_stride + pos[k] / a.page];
+            slot[k] = pos[k] % a.page;
+            __nv_bfloat16* base = (__nv_bfloat16*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
+            const int kvh = h < a.nh + a.nkv ? h - a.nh : h - a.nh - a.nkv;
+            const size_t which = h < a.nh + a.nkv ? 0 : (size_t)a.nkv * a.page * a.d;
+            row_dst[k] = base + which + (size_t)kvh * a.page * a.d;      // the head's block of the page
+        }
     }
     float ba[8], bb[8];
 #pragma unroll
@@ -354,36 +393,44 @@ __global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block) {
     __syncthreads();
     pdl_wait();
     if (!mine) return;
-    const __nv_bfloat16* src = (const __nv_bfloat16*)a.qkv + ((size_t)t * nheads + h) * a.d;
-    const uint4 va = *reinterpret_cast<const uint4*>(src + c * 8);
-    const uint4 vb = *reinterpret_cast<const uint4*>(src + half + c * 8);
-    const __nv_bfloat16* pa = reinterpret_cast<const __nv_bfloat16*>(&va);
-    const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&vb);
-    __align__(16) __nv_bfloat16 oa[8], ob[8];
+    uint4 va[TOK], vb[TOK];
+#pragma unroll
+    for (int k = 0; k < TOK; ++k) {
+        if (t0 + k >= n_tokens) { va[k] = vb[k] = make_uint4(0, 0, 0, 0); continue; }
+        const __nv_bfloat16* src = (const __nv_bfloat16*)a.qkv + ((size_t)(t0 + k) * nheads + h) * a.d;
+        va[k] = *reinterpret_cast<const uint4*>(src + c * 8);
+        vb[k] = *reinterpret_cast<const uint4*>(src + half + c * 8);
+    }
     const bool rotate = h < a.nh + a.nkv;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        float xa = __bfloat162float(pa[e]) + ba[e], xb = __bfloat162float(pb[e]) + bb[e];
-        if (rotate) {
-            const float2 cs = trig[c * 8 + e];
-            const float ra = xa * cs.x - xb * cs.y;
-            const float rb = xa * cs.y + xb * cs.x;
-            xa = ra; xb = rb;
+    for (int k = 0; k < TOK; ++k) {
+        if (t0 + k >= n_tokens) break;
+        const __nv_bfloat16* pa = reinterpret_cast<const __nv_bfloat16*>(&va[k]);
+        const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&vb[k]);
+        __align__(16) __nv_bfloat16 oa[8], ob[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float xa = __bfloat162float(pa[e]) + ba[e], xb = __bfloat162float(pb[e]) + bb[e];
+            if (rotate) {
+                const float2 cs = trig[k * half + c * 8 + e];
+                const float ra = xa * cs.x - xb * cs.y;
+                const float rb = xa * cs.y + xb * cs.x;
+                xa = ra; xb = rb;
+            }
+            oa[e] = __float2bfloat16_rn(xa);
+            ob[e] = __float2bfloat16_rn(xb);
         }
-        oa[e] = __float2bfloat16_rn(xa);
-        ob[e] = __float2bfloat16_rn(xb);
+        if (h < a.nh) {
+            __nv_bfloat16* dst = (__nv_bfloat16*)a.q_out + ((size_t)(t0 + k) * a.nh + h) * a.d;
+            *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(oa);
+            *reinterpret_cast<uint4*>(dst + half + c * 8) = *reinterpret_cast<const uint4*>(ob);
+        } else if (row_dst[k]) {
+            // whole 16-byte chunks move together in the block's layout (kv_pos)
+            __nv_bfloat16* dst = row_dst[k];
+            *reinterpret_cast<uint4*>(dst + kv_pos(c * 8, slot[k], a.d, a.page, 2)) = *reinterpret_cast<const uint4*>(oa);
+            *reinterpret_cast<uint4*>(dst + kv_pos(half + c * 8, slot[k], a.d, a.page, 2)) = *reinterpret_cast<const uint4*>(ob);
+        }
     }
-    if (h < a.nh) {
-        __nv_bfloat16* dst = (__nv_bfloat16*)a.q_out + ((size_t)t * a.nh + h) * a.d;
-        *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(oa);
-        *reinterpret_cast<uint4*>(dst + half + c * 8) = *reinterpret_cast<const uint4*>(ob);
-        return;
-    }
-    if (!row_dst) return;
-    __nv_bfloat16* dst = row_dst;
-    // whole 16-byte chunks move together in the block's layout (kv_pos)
-    *reinterpret_cast<uint4*>(dst + kv_pos(c * 8, slot, a.d, a.page, 2)) = *reinterpret_cast<const uint4*>(oa);
-    *reinterpret_cast<uint4*>(dst + kv_pos(half + c * 8, slot, a.d, a.page, 2)) = *reinterpret_cast<const uint4*>(ob);
 }
 
 VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const int* positions,
@@ -404,7 +451,13 @@ VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const in
         const int groups = (nheads * chunks + 255) / 256;
         const int per = (nheads + groups - 1) / groups;               // heads per CTA, at most 256 threads
         const int threads = ((per * chunks + 31) / 32) * 32;
-        vcb_launch(rope_cache_vec_kernel, dim3(n_tokens, (nheads + per - 1) / per), threads, (size_t)half * sizeof(float2), s, a, per);
+        const dim3 grid_y((nheads + per - 1) / per);
+        if (n_tokens >= 512)
+            vcb_launch(rope_cache_vec_kernel<4>, dim3((n_tokens + 3) / 4, grid_y.x), threads, (size_t)4 * half * sizeof(float2),
+                       s, a, per, n_tokens);
+        else
+            vcb_launch(rope_cache_vec_kernel<1>, dim3(n_tokens, grid_y.x), threads, (size_t)half * sizeof(float2), s, a, per,
+                       n_tokens);
         return vcb_last_error();
     }
     int hpb = 128 / half;                      // heads per CTA: about 128 threads
