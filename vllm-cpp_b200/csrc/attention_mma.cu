@@ -624,7 +624,7 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 }
 
 // ------------------------------------------------- prefill on tcgen05
-// The same work as attention_prefill_kernel for head size 128, on the fifth-generation tensor
+// The same work as attention_prefill_kernel for head sizes 64 and 128, on the fifth-generation tensor
 // cores.  A CTA owns 128 packed rows (token x head in group) of one kv head and walks the keys in tiles
 // of 64:
 //   S = Q K^T      tcgen05.mma, Q and K from shared memory (K-major, 128-byte swizzle: the cache's
@@ -632,7 +632,7 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 //   softmax        four warps, one thread per row: tcgen05.ld of its row, mask, maximum, ex2.approx,
 //                  sum; P rounded to bfloat16 into shared memory (K-major);
 //   O += P V       tcgen05.mma, V from shared memory as it lies in the cache (MN-major operand),
-//                  accumulated in tensor memory (128 x 128 float) over all tiles.
+//                  accumulated in tensor memory (128 x head size, float) over all tiles.
 // The exponent's reference is not the running maximum but a value that follows it lazily: it moves
 // only when the maximum has risen by more than 8 (in units of log2), and then the row's thread
 // rescales its row of O in tensor memory and its sum.  Probabilities stay below 2^8, sums and O in
@@ -640,16 +640,18 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 // Warp 0 copies K and V tiles (bulk copies from the pages, two stages each, separate barriers so a K
 // stage is free as soon as S is done), warp 1 issues the MMAs, warps 2-5 do the rest.  The MMA of
 // tile j + 1's scores is issued before tile j's P V, so the tensor cores work while tile j's softmax
-// runs, and two CTAs share an SM (256 columns of tensor memory and 112 KB of shared memory each), so
+// runs, and two CTAs share an SM (256 columns of tensor memory and, at head size 128, 112 KB of shared
+// memory each), so
 // one CTA's softmax runs under the other's MMAs and waits.  Every wait is bounded; one that runs
 // out sets *status and the CTA drains and leaves.
 namespace tc {
-constexpr int D = 128, BMT = 128, TKT = 64;
+constexpr int BMT = 128, TKT = 64;
 constexpr int THREADS = 192;
-constexpr int Q_BYTES = BMT * D * 2, KV_BYTES = TKT * D * 2, P_BYTES = BMT * TKT * 2;
-constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + 256;          // no slack: the base must be 1024-aligned
-constexpr int TMEM_COLS = 256;                                               // S0, S1 (64 each), O (128)
+constexpr int P_BYTES = BMT * TKT * 2;
+constexpr int TMEM_COLS = 256;                                               // S0, S1 (64 each), O (head size)
 constexpr float RESCALE_STEP = 8.0f;
+// Q, two K and two V stages, P, barriers; no slack: the base must be 1024-aligned
+template <int D> constexpr int smem_bytes() { return BMT * D * 2 + 4 * TKT * D * 2 + P_BYTES + 256; }
 
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -706,8 +708,11 @@ __host__ __device__ constexpr uint32_t idesc(int n, bool b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+template <int D>
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc_kernel(MmaAttnArgs a) {
+    static_assert(D == 64 || D == 128, "one or two planes of 64 elements; S, S and O fit 256 columns");
+    constexpr int Q_BYTES = BMT * D * 2, KV_BYTES = TKT * D * 2;
     extern __shared__ __align__(1024) unsigned char smem[];
     // No early release of the next kernel here: its CTAs would sit on this SM holding tensor memory
     // while CTAs of this kernel still wait to be placed.
@@ -979,15 +984,16 @@ static int launch_prefill(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
     return launch_prefill_variant<D, 32, 4, 2>(a, n_tiles, s);
 }
 
+template <int D>
 static int launch_prefill_tc(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(tc::attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             tc::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(tc::attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             tc::smem_bytes<D>());
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    vcb_launch(tc::attention_prefill_tc_kernel, dim3(n_tiles, a.nkv), tc::THREADS, (size_t)tc::SMEM_BYTES, s, a);
+    vcb_launch(tc::attention_prefill_tc_kernel<D>, dim3(n_tiles, a.nkv), tc::THREADS, (size_t)tc::smem_bytes<D>(), s, a);
     return vcb_last_error();
 }
 
@@ -1033,7 +1039,8 @@ VCB_EXPORT int vcb_attention_prefill_mma(const void* q, const void* cache, void*
     return d == 64 ? launch_prefill<64>(a, n_tiles, s) : launch_prefill<128>(a, n_tiles, s);
 }
 
-// The same on tcgen05 tensor cores: head size 128 only; tiles (tile_req, tile_row0) of 128 packed rows.
+// The same on tcgen05 tensor cores (head sizes 64 and 128, pages of a multiple of 8 tokens); tiles
+// (tile_req, tile_row0) of 128 packed rows.
 VCB_EXPORT int vcb_attention_prefill_tc(const void* q, const void* cache, void* out, const int* q_start,
                                         const int* ctx_lens, const int* block_table, int bt_stride,
                                         const int* tile_req, const int* tile_row0, int n_tiles, int nh,
@@ -1042,11 +1049,11 @@ VCB_EXPORT int vcb_attention_prefill_tc(const void* q, const void* cache, void* 
     if (n_tiles <= 0) return 0;
     int c = check_common(nh, nkv, d, page, window);
     if (c) return c;
-    if (d != 128 || page % 8) return VCB_ERR_UNSUPPORTED;
+    if (page % 8) return VCB_ERR_UNSUPPORTED;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
                   window, scale};
-    return launch_prefill_tc(a, n_tiles, (cudaStream_t)stream);
+    return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
 }
 
 // ------------------------------------------------ no-allocation entry point

@@ -270,7 +270,7 @@ def attention_prefill_mma(q, cache, out, q_start, ctx_lens, block_table, tile_re
         status_tensor(q.device).data_ptr(), _stream()), "attention_prefill_mma")
 
 
-TC_ATTENTION_HEAD_DIM = 128      # head size of the tcgen05 prefill attention kernel
+TC_ATTENTION_HEAD_DIMS = (64, 128)      # head sizes of the tcgen05 prefill attention kernel
 TC_ATTENTION_TILE_ROWS = 128     # packed rows per tile of its work list
 
 
@@ -281,8 +281,8 @@ def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req
     memory); head size 128, bfloat16, tiles of 128 packed rows."""
     _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
           "attention_prefill_tc is a bfloat16 kernel")
-    _need(head_dim == TC_ATTENTION_HEAD_DIM and page_size % 8 == 0,
-          f"attention_prefill_tc takes head size {TC_ATTENTION_HEAD_DIM} and pages of a multiple of 8 slots")
+    _need(head_dim in TC_ATTENTION_HEAD_DIMS and page_size % 8 == 0,
+          f"attention_prefill_tc takes head sizes {TC_ATTENTION_HEAD_DIMS} and pages of a multiple of 8 slots")
     n_tiles = tile_req.numel()
     _need(tile_row0.numel() == n_tiles, "one first row per tile")
     _check(lib().vcb_attention_prefill_tc(

@@ -119,7 +119,7 @@ class PagedAttention(Mixer):
         return self.dtype == torch.bfloat16 and self.d in ops.MMA_HEAD_DIMS
 
     def _prefill_on_tcgen05(self) -> bool:
-        return self.d == ops.TC_ATTENTION_HEAD_DIM
+        return self.d in ops.TC_ATTENTION_HEAD_DIMS
 
     def _tile_rows(self) -> int:
         return ops.TC_ATTENTION_TILE_ROWS if self._prefill_on_tcgen05() else self.TILE_ROWS
