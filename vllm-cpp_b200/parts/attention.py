@@ -118,11 +118,11 @@ class PagedAttention(Mixer):
     def _tensor_core_path(self) -> bool:
         return self.dtype == torch.bfloat16 and self.d in ops.MMA_HEAD_DIMS
 
-    def _prefill_on_tcgen05(self) -> bool:
-        return self.d in ops.TC_ATTENTION_HEAD_DIMS
+    def _prefill_on_tcgen05(self, page_size: int) -> bool:
+        return self.d in ops.TC_ATTENTION_HEAD_DIMS and page_size % 8 == 0
 
-    def _tile_rows(self) -> int:
-        return ops.TC_ATTENTION_TILE_ROWS if self._prefill_on_tcgen05() else self.TILE_ROWS
+    def _tile_rows(self, page_size: int) -> int:
+        return ops.TC_ATTENTION_TILE_ROWS if self._prefill_on_tcgen05(page_size) else self.TILE_ROWS
 
     def step_arrays(self):
         """What the kernels need per step beyond the common arrays, built on the host from the step's
@@ -132,11 +132,11 @@ class PagedAttention(Mixer):
         if not self._tensor_core_path():
             return {}
         group = self.nh // self.nkv
-        rows = self._tile_rows()
 
         def tiles(host):
             if all(q == 1 for q in host.q_lens):
                 return np.zeros((2, 0), dtype=np.int32)         # decode-only steps use the split-KV kernel
+            rows = self._tile_rows(host.page_size)
             req, row0, keys = [], [], []
             for r, (q, ctx) in enumerate(zip(host.q_lens, host.ctx_lens)):
                 for k in range(-(-q * group // rows)):
@@ -173,7 +173,7 @@ class PagedAttention(Mixer):
             host.shapes[self._splits_key()] = 1 << (need - 1).bit_length()
             return np.array([per], dtype=np.int32)
 
-        return {f"attn_tiles_g{group}_r{rows}": tiles, self._splits_key(): splits}
+        return {f"attn_tiles_g{group}_d{self.d}": tiles, self._splits_key(): splits}
 
     def _splits_key(self):
         return f"attn_splits_kv{self.nkv}_w{self.window}"
@@ -203,8 +203,8 @@ class PagedAttention(Mixer):
                 ops.attention_decode_mma(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, None,
                                          step.n_reqs, nsplit, part_o, part_ml, counters, split_tiles=split_tiles, **kw)
             else:
-                tiles = step.extras[f"attn_tiles_g{self.nh // self.nkv}_r{self._tile_rows()}"]
-                kernel = ops.attention_prefill_tc if self._prefill_on_tcgen05() else ops.attention_prefill_mma
+                tiles = step.extras[f"attn_tiles_g{self.nh // self.nkv}_d{self.d}"]
+                kernel = ops.attention_prefill_tc if self._prefill_on_tcgen05(cache.page_size) else ops.attention_prefill_mma
                 kernel(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, tiles[0], tiles[1], **kw)
             return
         ops.attention_simt(q, cache.pages, attn, step.positions, step.req_of_token, block_table,
