@@ -630,15 +630,16 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 //   S = Q K^T      tcgen05.mma, Q and K from shared memory (K-major, 128-byte swizzle: the cache's
 //                  planes are that layout already), S (128 x 64 float) in tensor memory, two buffers;
 //   softmax        four warps, one thread per row: tcgen05.ld of its row, mask, maximum, ex2.approx,
-//                  sum; P rounded to bfloat16 into shared memory (K-major);
-//   O += P V       tcgen05.mma, V from shared memory as it lies in the cache (MN-major operand),
-//                  accumulated in tensor memory (128 x head size, float) over all tiles.
+//                  sum; P rounded to bfloat16 and stored (tcgen05.st) over the first half of the
+//                  row's own scores in tensor memory, two keys to a 32-bit column;
+//   O += P V       tcgen05.mma with P from tensor memory and V from shared memory as it lies in the
+//                  cache (MN-major operand), accumulated in tensor memory (128 x head size, float).
 // The exponent's reference is not the running maximum but a value that follows it lazily: it moves
 // only when the maximum has risen by more than 8 (in units of log2), and then the row's thread
 // rescales its row of O in tensor memory and its sum.  Probabilities stay below 2^8, sums and O in
 // float; the rescaling is rare after the first tiles.
-// Warp 0 copies K and V tiles (bulk copies from the pages, two stages each, separate barriers so a K
-// stage is free as soon as S is done), warp 1 issues the MMAs, warps 2-5 do the rest.  The MMA of
+// Warp 0 copies K and V tiles (bulk copies from the pages, three K stages and two V stages, separate
+// barriers so a K stage is free as soon as S is done), warp 1 issues the MMAs, warps 2-5 do the rest.  The MMA of
 // tile j + 1's scores is issued before tile j's P V, so the tensor cores work while tile j's softmax
 // runs, and two CTAs share an SM (256 columns of tensor memory and, at head size 128, 112 KB of shared
 // memory each), so
@@ -647,11 +648,11 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 namespace tc {
 constexpr int BMT = 128, TKT = 64;
 constexpr int THREADS = 192;
-constexpr int P_BYTES = BMT * TKT * 2;
+constexpr int K_STAGES = 3, V_STAGES = 2;
 constexpr int TMEM_COLS = 256;                                               // S0, S1 (64 each), O (head size)
 constexpr float RESCALE_STEP = 8.0f;
-// Q, two K and two V stages, P, barriers; no slack: the base must be 1024-aligned
-template <int D> constexpr int smem_bytes() { return BMT * D * 2 + 4 * TKT * D * 2 + P_BYTES + 256; }
+// Q, the K and V stages, barriers; no slack: the base must be 1024-aligned
+template <int D> constexpr int smem_bytes() { return BMT * D * 2 + (K_STAGES + V_STAGES) * TKT * D * 2 + 256; }
 
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -663,6 +664,36 @@ __device__ __forceinline__ void mma(uint32_t tmem_d, uint64_t desc_a, uint64_t d
                  "setp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Two floats to a 64-bit register and packed arithmetic on them (one instruction for two elements), a
+// maximum of three: the softmax warps are bound by the instructions they issue.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+// the same with A (128 x 16 bfloat16: row = lane, two elements of k to a column) in tensor memory
+__device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t r[32];
@@ -691,6 +722,17 @@ __device__ __forceinline__ void st32(uint32_t taddr, const float (&v)[32]) {
                    "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
                    "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
                    "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+                 : "memory");
+}
+__device__ __forceinline__ void st32u(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr),
+                   "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                   "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                   "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
                  : "memory");
 }
 // K-major operand, rows of 128 bytes, 128-byte swizzle: 8-row groups 1024 bytes apart.
@@ -727,23 +769,27 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
     const int* bt = a.block_table + (size_t)r * a.bt_stride;
     const float sl2 = a.scale * LOG2E;
 
-    // [Q][K0][K1][V0][V1][P][barriers]
-    const uint32_t sq = smem_u32(smem), sk0 = sq + Q_BYTES, sv0 = sk0 + 2 * KV_BYTES, sp = sv0 + 2 * KV_BYTES;
+    // [Q][K0][K1][K2][V0][V1][barriers]
+    const uint32_t sq = smem_u32(smem), sk0 = sq + Q_BYTES, sv0 = sk0 + K_STAGES * KV_BYTES;
     unsigned char* q_ptr = smem;
-    unsigned char* p_ptr = smem + Q_BYTES + 4 * KV_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_ptr + P_BYTES);
-    // 0,1 full_k  2,3 empty_k  4,5 full_v  6,7 empty_v  8,9 s_full  10,11 s_free  12 p_full  13 pv_done  14 q_ready
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_BYTES + (K_STAGES + V_STAGES) * KV_BYTES);
+    // 0-2 full_k  3-5 empty_k  6,7 full_v  8,9 empty_v  10,11 s_full  12,13 s_free  14 p_full  15 pv_done  16 q_ready
+    // 17 o_done (the last P V: a barrier of its own, because a parity tells one phase only and the
+    // softmax warps do not follow every phase of pv_done)
+    constexpr int FULL_K = 0, EMPTY_K = 3, FULL_V = 6, EMPTY_V = 8, S_FULL = 10, S_FREE = 12, P_FULL = 14, PV_DONE = 15,
+                  Q_READY = 16, O_DONE = 17, N_BARS = 18;
     const uint32_t b0 = cx_smem(bars);
     auto B = [&](int i) { return b0 + 8 * i; };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if (threadIdx.x == 0) {
+        for (int i = 0; i < K_STAGES; ++i) { cx_mbar_init(B(FULL_K + i), 1); cx_mbar_init(B(EMPTY_K + i), 1); }
         for (int i = 0; i < 2; ++i) {
-            cx_mbar_init(B(0 + i), 1); cx_mbar_init(B(2 + i), 1); cx_mbar_init(B(4 + i), 1); cx_mbar_init(B(6 + i), 1);
-            cx_mbar_init(B(8 + i), 1); cx_mbar_init(B(10 + i), 4);
+            cx_mbar_init(B(FULL_V + i), 1); cx_mbar_init(B(EMPTY_V + i), 1);
+            cx_mbar_init(B(S_FULL + i), 1); cx_mbar_init(B(S_FREE + i), 4);
         }
-        cx_mbar_init(B(12), 4); cx_mbar_init(B(13), 1); cx_mbar_init(B(14), 4);
+        cx_mbar_init(B(P_FULL), 4); cx_mbar_init(B(PV_DONE), 1); cx_mbar_init(B(Q_READY), 4); cx_mbar_init(B(O_DONE), 1);
         // the tiles' swizzle is computed from shared-memory addresses: the base must be a multiple of 1024
         *abort_flag = (sq & 1023) ? 1 : 0;
         if ((sq & 1023) && a.status) atomicCAS(a.status, 0, 10);
@@ -771,8 +817,8 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
     };
 
     if (warp == 0) {
-        // ---- producer: K and V tiles, two stages each.  K_j is wanted a tile earlier than V_j (the
-        // scores come first) and its stage is free earlier (once S_{j-2} is done), so the two are
+        // ---- producer: K tiles in three stages, V tiles in two.  K_j is wanted a tile earlier than V_j
+        // (the scores come first) and its stage is free earlier (once S_{j-3} is done), so the two are
         // fetched apart: K_j, then V_{j-1}.
         PageWindow pw_k, pw_v;
         const PageDiv pd(a.page);
@@ -780,58 +826,74 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         pw_v.init(bt, pd.div(tile0 * TKT), hi, a.page, lane);
         const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
                      v_off = (size_t)a.nkv * a.page * D;
+        int ks = 0, kphase = 1;                 // K stage of tile j and the parity its empty barrier is waited with
         for (int j = 0; j <= n_tiles && !*abort_flag; ++j) {
             if (j < n_tiles) {
-                const int st = j & 1;
-                if (!cx_mbar_wait(B(2 + st), ((j >> 1) & 1) ^ 1)) { give_up(9); break; }
-                if (lane == 0) cx_mbar_expect_tx(B(0 + st), KV_BYTES);
+                if (!cx_mbar_wait(B(EMPTY_K + ks), kphase)) { give_up(9); break; }
+                if (lane == 0) cx_mbar_expect_tx(B(FULL_K + ks), KV_BYTES);
                 __syncwarp();
-                produce_tile<D, TKT>(sk0 + st * KV_BYTES, 0, B(0 + st), (tile0 + j) * TKT, lo, hi, pw_k, a.cache,
+                produce_tile<D, TKT>(sk0 + ks * KV_BYTES, 0, B(FULL_K + ks), (tile0 + j) * TKT, lo, hi, pw_k, a.cache,
                                      head_base, page_stride, v_off, pd, lane, 0, 1);
+                if (++ks == K_STAGES) { ks = 0; kphase ^= 1; }
             }
             if (j > 0) {
                 const int jv = j - 1, st = jv & 1;
-                if (!cx_mbar_wait(B(6 + st), ((jv >> 1) & 1) ^ 1)) { give_up(9); break; }
-                if (lane == 0) cx_mbar_expect_tx(B(4 + st), KV_BYTES);
+                if (!cx_mbar_wait(B(EMPTY_V + st), ((jv >> 1) & 1) ^ 1)) { give_up(9); break; }
+                if (lane == 0) cx_mbar_expect_tx(B(FULL_V + st), KV_BYTES);
                 __syncwarp();
                 produce_tile<D, TKT>(0, sv0 + st * KV_BYTES, 0, (tile0 + jv) * TKT, lo, hi, pw_v, a.cache,
-                                     head_base, page_stride, v_off, pd, lane, B(4 + st), 2);
+                                     head_base, page_stride, v_off, pd, lane, B(FULL_V + st), 2);
             }
         }
     } else if (warp == 1) {
-        // ---- MMA issuer
-        if (lane == 0 && n_tiles > 0) {
+        // ---- MMA issuer.  The whole warp walks the loop and waits, one elected lane issues: addresses and
+        // descriptors are then the same in all lanes, which lets the compiler keep them in uniform
+        // registers, where tcgen05.mma wants them; a loop inside "if (lane == 0)" computes them in vector
+        // registers and moves every operand of every instruction across.
+        if (n_tiles > 0) {
             constexpr uint32_t id_s = idesc(TKT, false), id_pv = idesc(D, true);
-            bool ok = cx_mbar_wait(B(14), 0);                 // Q tile written
+            uint32_t leader;
+            asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(leader));
+            bool ok = cx_mbar_wait(B(Q_READY), 0);            // Q tile written
             fence_after();
-            auto issue_pv = [&](int j) -> bool {                // O += P_j V_j
+            auto issue_pv = [&](int j) -> bool {                // O += P_j V_j, P_j in the first half of S buffer j & 1
                 const int st = j & 1;
-                if (!cx_mbar_wait(B(12), j & 1) || !cx_mbar_wait(B(4 + st), (j >> 1) & 1)) return false;
+                if (!cx_mbar_wait(B(P_FULL), j & 1) || !cx_mbar_wait(B(FULL_V + st), (j >> 1) & 1)) return false;
                 fence_after();
-                const uint32_t v_base = sv0 + st * KV_BYTES;
+                const uint32_t v_base = sv0 + st * KV_BYTES, tm_p = tm_s0 + st * TKT;
+                if (leader) {
 #pragma unroll
-                for (int kk = 0; kk < TKT / 16; ++kk)           // 16 keys a step
-                    mma(tm_o, desc_k(sp + kk * 32), desc_mn(v_base + kk * 16 * 128, TKT * 128), id_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                commit(B(13));          // P read, O updated
-                commit(B(6 + st));      // V stage free
+                    for (int kk = 0; kk < TKT / 16; ++kk)       // 16 keys a step: eight columns of P
+                        mma_ts(tm_o, tm_p + kk * 8, desc_mn(v_base + kk * 16 * 128, TKT * 128), id_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    commit(B(PV_DONE));         // P read, O updated
+                    commit(B(EMPTY_V + st));    // V stage free
+                    if (j == n_tiles - 1) commit(B(O_DONE));
+                }
+                __syncwarp();
                 return true;
             };
+            int ks = 0, kphase = 0;
             for (int j = 0; j < n_tiles && ok && !*abort_flag; ++j) {
                 const int st = j & 1;
-                // S_j = Q K_j^T into S buffer j & 1 (free once the softmax of tile j - 2 has read it)
-                if (!cx_mbar_wait(B(0 + st), (j >> 1) & 1) || !cx_mbar_wait(B(10 + st), ((j >> 1) & 1) ^ 1)) { ok = false; break; }
+                // S_j = Q K_j^T into S buffer j & 1 (free once the softmax of tile j - 2 has read it; the P V
+                // of tile j - 2, which read P from the same columns, was issued before and runs before)
+                if (!cx_mbar_wait(B(FULL_K + ks), kphase) || !cx_mbar_wait(B(S_FREE + st), ((j >> 1) & 1) ^ 1)) { ok = false; break; }
                 fence_after();
-                const uint32_t k_base = sk0 + st * KV_BYTES;
+                const uint32_t k_base = sk0 + ks * KV_BYTES;
+                if (leader) {
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks)             // 16 dims a step: plane ks / 4
-                    mma(tm_s0 + st * TKT, desc_k(sq + (ks >> 2) * (BMT * 128) + (ks & 3) * 32),
-                        desc_k(k_base + (ks >> 2) * (TKT * 128) + (ks & 3) * 32), id_s, ks > 0 ? 1u : 0u);
-                commit(B(8 + st));      // S complete
-                commit(B(2 + st));      // K stage free
+                    for (int kd = 0; kd < D / 16; ++kd)         // 16 dims a step: plane kd / 4
+                        mma(tm_s0 + st * TKT, desc_k(sq + (kd >> 2) * (BMT * 128) + (kd & 3) * 32),
+                            desc_k(k_base + (kd >> 2) * (TKT * 128) + (kd & 3) * 32), id_s, kd > 0 ? 1u : 0u);
+                    commit(B(S_FULL + st));         // S complete
+                    commit(B(EMPTY_K + ks));        // K stage free
+                }
+                __syncwarp();
+                if (++ks == K_STAGES) { ks = 0; kphase ^= 1; }
                 if (j > 0 && !issue_pv(j - 1)) { ok = false; break; }
             }
             if (ok && !*abort_flag && !issue_pv(n_tiles - 1)) ok = false;
-            if (!ok) give_up(9);
+            if (!ok && lane == 0) give_up(9);
         }
     } else {
         // ---- softmax and output: thread i of warps 2..5 owns row 32 * (warp % 4) + lane (its tensor-memory lane)
@@ -851,7 +913,7 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) cx_mbar_arrive(B(14));
+        if (lane == 0) cx_mbar_arrive(B(Q_READY));
 
         const int pr = row0 + row;
         const bool row_ok = pr < rows_total;
@@ -862,7 +924,7 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
             const int st = j & 1;
             const int kb = (tile0 + j) * TKT;
-            if (!cx_mbar_wait(B(8 + st), (j >> 1) & 1)) { ok = false; break; }
+            if (!cx_mbar_wait(B(S_FULL + st), (j >> 1) & 1)) { ok = false; break; }
             fence_after();
             const uint32_t s_addr = tm_s0 + st * TKT + lane_addr;
             // does any row of the tile mask any key of this tile? (the first row sees the fewest late keys,
@@ -879,7 +941,7 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
             // the S buffer has been read: the scores of tile j + 2 may overwrite it
             fence_before();
             __syncwarp();
-            if (lane == 0) cx_mbar_arrive(B(10 + st));
+            if (lane == 0) cx_mbar_arrive(B(S_FREE + st));
             float mt = -INFINITY;
             if (edge) {
 #pragma unroll
@@ -888,8 +950,12 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
                     if (!(key >= row_lo && key <= pos)) s[i] = -INFINITY;
                 }
             }
+            {
+                float m2 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < TKT; ++i) mt = fmaxf(mt, s[i]);
+                for (int i = 0; i < TKT; i += 4) { mt = max3(mt, s[i], s[i + 1]); m2 = max3(m2, s[i + 2], s[i + 3]); }
+                mt = fmaxf(mt, m2);
+            }
             // move the reference only when the maximum has left it far behind
             float factor = 1.0f;
             if (mt > m_ref && (m_ref == -INFINITY || (mt - m_ref) * sl2 > RESCALE_STEP)) {
@@ -898,17 +964,29 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
             }
             const float base = m_ref == -INFINITY ? 0.0f : m_ref * sl2;
             uint32_t pk[TKT / 2];
-            float lt = 0.0f;
+            const uint64_t scale2 = pack2(sl2, sl2), minus_base2 = pack2(-base, -base);
+            uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
 #pragma unroll
             for (int i = 0; i < TKT; i += 2) {
-                const float p0 = fast_exp2(fmaf(s[i], sl2, -base)), p1 = fast_exp2(fmaf(s[i + 1], sl2, -base));
-                lt += p0 + p1;
+                float e0, e1;
+                unpack2(fma2(pack2(s[i], s[i + 1]), scale2, minus_base2), e0, e1);
+                const float p0 = fast_exp2(e0), p1 = fast_exp2(e1);
+                sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(p0, p1));
                 pk[i >> 1] = pack_bf16(p0, p1);
             }
-            // P and O belong to the P V of the tile before until it is done
-            if (!cx_mbar_wait(B(13), (j & 1) ^ 1)) { ok = false; break; }
+            float lt;
+            {
+                float a0, a1, b0, b1;
+                unpack2(sum2[0], a0, a1);
+                unpack2(sum2[1], b0, b1);
+                lt = (a0 + a1) + (b0 + b1);
+            }
             if (j > 0 && __any_sync(0xffffffffu, factor != 1.0f)) {
-                // somebody's reference moved: the warp rescales its rows of O (factor 1 where nothing moved)
+                // somebody's reference moved: the warp rescales its rows of O (factor 1 where nothing moved),
+                // once the P V of the tile before, which adds into them, is done.  (That of tile j - 2 is: the
+                // scores of this tile were computed after it.  So the barrier is one or no phase behind and
+                // its parity tells which.)
+                if (!cx_mbar_wait(B(PV_DONE), (j & 1) ^ 1)) { ok = false; break; }
                 fence_after();
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
@@ -918,20 +996,21 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
                     for (int i = 0; i < 32; ++i) t[i] *= factor;
                     st32(tm_o + lane_addr + c0, t);
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
             l = l * factor + lt;
-#pragma unroll
-            for (int q8 = 0; q8 < TKT / 8; ++q8)                     // chunks of eight keys
-                *reinterpret_cast<uint4*>(p_ptr + swz_kv<D, BMT>(row, q8)) =
-                    make_uint4(pk[q8 * 4], pk[q8 * 4 + 1], pk[q8 * 4 + 2], pk[q8 * 4 + 3]);
+            // P over the row's own scores (this thread has read them; the tensor cores write these columns
+            // again only with the scores of tile j + 2, after the P V that reads P)
+            st32u(s_addr, pk);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            // the four warps arrive on one barrier per tile: a warp that runs ahead must not count towards
+            // a tile that another warp has not finished
+            if (j > 0 && !cx_mbar_wait(B(P_FULL), (j - 1) & 1)) { ok = false; break; }
             fence_before();
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) cx_mbar_arrive(B(12));
+            if (lane == 0) cx_mbar_arrive(B(P_FULL));
         }
         if (ok && n_tiles > 0 && !*abort_flag) {
-            if (!cx_mbar_wait(B(13), (n_tiles - 1) & 1)) ok = false;
+            if (!cx_mbar_wait(B(O_DONE), 0)) ok = false;       // the last P V
             fence_after();
             if (ok) {
                 const float inv = l > 0.0f ? 1.0f / l : 0.0f;
