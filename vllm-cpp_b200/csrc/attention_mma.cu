@@ -638,8 +638,8 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 // only when the maximum has risen by more than 8 (in units of log2), and then the row's thread
 // rescales its row of O in tensor memory and its sum.  Probabilities stay below 2^8, sums and O in
 // float; the rescaling is rare after the first tiles.
-// Warp 0 copies K and V tiles (bulk copies from the pages, three K stages and two V stages, separate
-// barriers so a K stage is free as soon as S is done), warp 1 issues the MMAs, warps 2-5 do the rest.  The MMA of
+// Warp 0 copies K tiles and warp 1 V tiles (bulk copies from the pages, three K stages and two V stages,
+// separate barriers so a K stage is free as soon as S is done), warp 2 issues the MMAs, warps 3-6 do the rest.  The MMA of
 // tile j + 1's scores is issued before tile j's P V, so the tensor cores work while tile j's softmax
 // runs, and two CTAs share an SM (256 columns of tensor memory and, at head size 128, 112 KB of shared
 // memory each), so
@@ -647,7 +647,7 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 // out sets *status and the CTA drains and leaves.
 namespace tc {
 constexpr int BMT = 128, TKT = 64;
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;
 constexpr int K_STAGES = 3, V_STAGES = 2;
 constexpr int TMEM_COLS = 256;                                               // S0, S1 (64 each), O (head size)
 constexpr float RESCALE_STEP = 8.0f;
@@ -795,7 +795,7 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         if ((sq & 1023) && a.status) atomicCAS(a.status, 0, 10);
         cx_mbar_init_fence();
     }
-    if (warp == 1) {
+    if (warp == 2) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -816,36 +816,37 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         if (!*abort_flag) { *abort_flag = 1; if (a.status) atomicCAS(a.status, 0, code); }
     };
 
-    if (warp == 0) {
-        // ---- producer: K tiles in three stages, V tiles in two.  K_j is wanted a tile earlier than V_j
-        // (the scores come first) and its stage is free earlier (once S_{j-3} is done), so the two are
-        // fetched apart: K_j, then V_{j-1}.
-        PageWindow pw_k, pw_v;
+    if (warp == 0 || warp == 1) {
+        // ---- producers: warp 0 copies K tiles (three stages), warp 1 V tiles (two stages).  A tile's copies
+        // cost a warp some 0.6 us of address arithmetic and issue, so one warp for both would take longer
+        // than the softmax does for the tile.  K_j's stage is free once S_{j-3} is done, V_j's once the P V of
+        // tile j - 2 is.
+        PageWindow pw;
         const PageDiv pd(a.page);
-        pw_k.init(bt, pd.div(tile0 * TKT), hi, a.page, lane);
-        pw_v.init(bt, pd.div(tile0 * TKT), hi, a.page, lane);
+        pw.init(bt, pd.div(tile0 * TKT), hi, a.page, lane);
         const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
                      v_off = (size_t)a.nkv * a.page * D;
-        int ks = 0, kphase = 1;                 // K stage of tile j and the parity its empty barrier is waited with
-        for (int j = 0; j <= n_tiles && !*abort_flag; ++j) {
-            if (j < n_tiles) {
+        if (warp == 0) {
+            int ks = 0, kphase = 1;             // K stage of tile j and the parity its empty barrier is waited with
+            for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
                 if (!cx_mbar_wait(B(EMPTY_K + ks), kphase)) { give_up(9); break; }
                 if (lane == 0) cx_mbar_expect_tx(B(FULL_K + ks), KV_BYTES);
                 __syncwarp();
-                produce_tile<D, TKT>(sk0 + ks * KV_BYTES, 0, B(FULL_K + ks), (tile0 + j) * TKT, lo, hi, pw_k, a.cache,
+                produce_tile<D, TKT>(sk0 + ks * KV_BYTES, 0, B(FULL_K + ks), (tile0 + j) * TKT, lo, hi, pw, a.cache,
                                      head_base, page_stride, v_off, pd, lane, 0, 1);
                 if (++ks == K_STAGES) { ks = 0; kphase ^= 1; }
             }
-            if (j > 0) {
-                const int jv = j - 1, st = jv & 1;
-                if (!cx_mbar_wait(B(EMPTY_V + st), ((jv >> 1) & 1) ^ 1)) { give_up(9); break; }
+        } else {
+            for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
+                const int st = j & 1;
+                if (!cx_mbar_wait(B(EMPTY_V + st), ((j >> 1) & 1) ^ 1)) { give_up(9); break; }
                 if (lane == 0) cx_mbar_expect_tx(B(FULL_V + st), KV_BYTES);
                 __syncwarp();
-                produce_tile<D, TKT>(0, sv0 + st * KV_BYTES, 0, (tile0 + jv) * TKT, lo, hi, pw_v, a.cache,
+                produce_tile<D, TKT>(0, sv0 + st * KV_BYTES, 0, (tile0 + j) * TKT, lo, hi, pw, a.cache,
                                      head_base, page_stride, v_off, pd, lane, B(FULL_V + st), 2);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 2) {
         // ---- MMA issuer.  The whole warp walks the loop and waits, one elected lane issues: addresses and
         // descriptors are then the same in all lanes, which lets the compiler keep them in uniform
         // registers, where tcgen05.mma wants them; a loop inside "if (lane == 0)" computes them in vector
@@ -896,12 +897,12 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
             if (!ok && lane == 0) give_up(9);
         }
     } else {
-        // ---- softmax and output: thread i of warps 2..5 owns row 32 * (warp % 4) + lane (its tensor-memory lane)
+        // ---- softmax and output: thread i of warps 3..6 owns row 32 * (warp % 4) + lane (its tensor-memory lane)
         const int lg = warp & 3;
         const int row = lg * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
         // Q tile: packed row -> (token, head in group); two planes of 128-byte pieces, chunks swizzled
-        for (int idx = threadIdx.x - 64; idx < BMT * (D / 8); idx += 128) {
+        for (int idx = threadIdx.x - 96; idx < BMT * (D / 8); idx += 128) {
             const int rr = idx / (D / 8), c = idx % (D / 8);
             const int pr = row0 + rr;
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -1034,7 +1035,7 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
     }
     fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 2) {
         fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
