@@ -141,12 +141,16 @@ struct PageDiv {
 // most TK / 16 + 1 pages and D / 64 planes; lane = 16 * (K or V) + 8 * plane + page piece copies one run
 // of 128-byte row pieces.  Lane 0 has armed the stage's barrier with the tile's byte count.
 // head_base: the kv head's block inside a page's K half; page_stride, v_off: elements per page, K half to V half.
+struct TilePiece {
+    const __nv_bfloat16* src;    // K piece; the V piece lies v_off further
+    uint32_t off, bytes;         // where in the tile, how much
+    bool active;
+};
+// Where this lane's piece of the tile comes from: all the address arithmetic of a tile's copies, none of
+// which depends on the stage being free, so a producer can do it for the next tile while it waits.
 template <int D, int TK>
-__device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t bar, int kb, int lo, int hi,
-                                             PageWindow& pw, const __nv_bfloat16* __restrict__ cache,
-                                             size_t head_base, size_t page_stride, size_t v_off, const PageDiv& pd, int lane,
-                                             uint32_t bar_v = 0, int which = 0) {
-    // which: 0 K and V, 1 K only, 2 V only (a kernel that fetches them at different times)
+__device__ __forceinline__ TilePiece tile_piece(int kb, int lo, int hi, PageWindow& pw, const __nv_bfloat16* __restrict__ cache,
+                                                size_t head_base, size_t page_stride, const PageDiv& pd, int lane) {
     constexpr int PLANES = D / 64;
     static_assert(PLANES == 1 || PLANES == 2, "head sizes 64 and 128");
     const int piece = lane & 7, plane = (lane >> 3) & 1;
@@ -154,20 +158,34 @@ __device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t 
     pw.advance(first_page);
     const int lp_piece = first_page + piece;
     const int start = piece == 0 ? kb : pd.mul(lp_piece);                   // first key of the piece
-    const bool active = plane < PLANES && start < kb + TK;
+    TilePiece t;
+    t.active = plane < PLANES && start < kb + TK;
     // the page itself if any of it is visible, else the page of the last visible key
-    const int lp = active ? lp_piece : first_page;
+    const int lp = t.active ? lp_piece : first_page;
     const int page_lo = pd.mul(lp);
     const bool visible = page_lo < hi && page_lo + pd.page > lo;
     const int got = pw.get(visible ? lp : first_page);                     // all lanes take part in the shuffles
-    if (!active) return;
     const int pg = visible ? got : pw.last_pg;
     const int end = min(page_lo + pd.page, kb + TK);
     // plane `plane` of the head's block: pd.page rows of 64 elements
-    const __nv_bfloat16* src = cache + (size_t)pg * page_stride + head_base + ((size_t)plane * pd.page + (start - page_lo)) * 64;
-    const uint32_t off = (uint32_t)(plane * TK + (start - kb)) * 128, bytes = (uint32_t)(end - start) * 128;
-    if (lane < 16) { if (which != 2) cx_bulk_load(sk + off, src, bytes, bar); }
-    else if (which != 1) cx_bulk_load(sv + off, src + v_off, bytes, bar_v ? bar_v : bar);
+    t.src = cache + (size_t)pg * page_stride + head_base + ((size_t)plane * pd.page + (start - page_lo)) * 64;
+    t.off = (uint32_t)(plane * TK + (start - kb)) * 128;
+    t.bytes = (uint32_t)(end - start) * 128;
+    return t;
+}
+// which: 0 K and V, 1 K only, 2 V only (a kernel that fetches them at different times)
+__device__ __forceinline__ void issue_piece(const TilePiece& t, uint32_t sk, uint32_t sv, uint32_t bar, size_t v_off, int lane,
+                                            uint32_t bar_v = 0, int which = 0) {
+    if (!t.active) return;
+    if (lane < 16) { if (which != 2) cx_bulk_load(sk + t.off, t.src, t.bytes, bar); }
+    else if (which != 1) cx_bulk_load(sv + t.off, t.src + v_off, t.bytes, bar_v ? bar_v : bar);
+}
+template <int D, int TK>
+__device__ __forceinline__ void produce_tile(uint32_t sk, uint32_t sv, uint32_t bar, int kb, int lo, int hi,
+                                             PageWindow& pw, const __nv_bfloat16* __restrict__ cache,
+                                             size_t head_base, size_t page_stride, size_t v_off, const PageDiv& pd, int lane,
+                                             uint32_t bar_v = 0, int which = 0) {
+    issue_piece(tile_piece<D, TK>(kb, lo, hi, pw, cache, head_base, page_stride, pd, lane), sk, sv, bar, v_off, lane, bar_v, which);
 }
 
 // S[16 x 8*NB] += Q[16 x D] * K[keys key0 .. key0 + 8*NB)^T, K tile at sk.
@@ -648,7 +666,7 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 namespace tc {
 constexpr int BMT = 128, TKT = 64;
 constexpr int THREADS = 224;
-constexpr int K_STAGES = 3, V_STAGES = 2;
+constexpr int K_STAGES = 2, V_STAGES = 3;
 constexpr int TMEM_COLS = 256;                                               // S0, S1 (64 each), O (head size)
 constexpr float RESCALE_STEP = 8.0f;
 // Q, the K and V stages, barriers; no slack: the base must be 1024-aligned
@@ -769,15 +787,16 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
     const int* bt = a.block_table + (size_t)r * a.bt_stride;
     const float sl2 = a.scale * LOG2E;
 
-    // [Q][K0][K1][K2][V0][V1][barriers]
+    // [Q][K stages][V stages][barriers]
     const uint32_t sq = smem_u32(smem), sk0 = sq + Q_BYTES, sv0 = sk0 + K_STAGES * KV_BYTES;
     unsigned char* q_ptr = smem;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_BYTES + (K_STAGES + V_STAGES) * KV_BYTES);
-    // 0-2 full_k  3-5 empty_k  6,7 full_v  8,9 empty_v  10,11 s_full  12,13 s_free  14 p_full  15 pv_done  16 q_ready
-    // 17 o_done (the last P V: a barrier of its own, because a parity tells one phase only and the
-    // softmax warps do not follow every phase of pv_done)
-    constexpr int FULL_K = 0, EMPTY_K = 3, FULL_V = 6, EMPTY_V = 8, S_FULL = 10, S_FREE = 12, P_FULL = 14, PV_DONE = 15,
-                  Q_READY = 16, O_DONE = 17, N_BARS = 18;
+    // full and empty per K stage and per V stage, s_full and s_free per S buffer, p_full, pv_done, q_ready,
+    // o_done (the last P V: a barrier of its own, because a parity tells one phase only and the softmax
+    // warps do not follow every phase of pv_done)
+    constexpr int FULL_K = 0, EMPTY_K = FULL_K + K_STAGES, FULL_V = EMPTY_K + K_STAGES, EMPTY_V = FULL_V + V_STAGES,
+                  S_FULL = EMPTY_V + V_STAGES, S_FREE = S_FULL + 2, P_FULL = S_FREE + 2, PV_DONE = P_FULL + 1,
+                  Q_READY = PV_DONE + 1, O_DONE = Q_READY + 1, N_BARS = O_DONE + 1;
     const uint32_t b0 = cx_smem(bars);
     auto B = [&](int i) { return b0 + 8 * i; };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
@@ -785,10 +804,8 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < K_STAGES; ++i) { cx_mbar_init(B(FULL_K + i), 1); cx_mbar_init(B(EMPTY_K + i), 1); }
-        for (int i = 0; i < 2; ++i) {
-            cx_mbar_init(B(FULL_V + i), 1); cx_mbar_init(B(EMPTY_V + i), 1);
-            cx_mbar_init(B(S_FULL + i), 1); cx_mbar_init(B(S_FREE + i), 4);
-        }
+        for (int i = 0; i < V_STAGES; ++i) { cx_mbar_init(B(FULL_V + i), 1); cx_mbar_init(B(EMPTY_V + i), 1); }
+        for (int i = 0; i < 2; ++i) { cx_mbar_init(B(S_FULL + i), 1); cx_mbar_init(B(S_FREE + i), 4); }
         cx_mbar_init(B(P_FULL), 4); cx_mbar_init(B(PV_DONE), 1); cx_mbar_init(B(Q_READY), 4); cx_mbar_init(B(O_DONE), 1);
         // the tiles' swizzle is computed from shared-memory addresses: the base must be a multiple of 1024
         *abort_flag = (sq & 1023) ? 1 : 0;
@@ -826,24 +843,27 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         pw.init(bt, pd.div(tile0 * TKT), hi, a.page, lane);
         const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
                      v_off = (size_t)a.nkv * a.page * D;
+        // a tile's addresses are worked out before its stage is waited for
+        TilePiece pc = tile_piece<D, TKT>(tile0 * TKT, lo, hi, pw, a.cache, head_base, page_stride, pd, lane);
         if (warp == 0) {
             int ks = 0, kphase = 1;             // K stage of tile j and the parity its empty barrier is waited with
             for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
                 if (!cx_mbar_wait(B(EMPTY_K + ks), kphase)) { give_up(9); break; }
                 if (lane == 0) cx_mbar_expect_tx(B(FULL_K + ks), KV_BYTES);
                 __syncwarp();
-                produce_tile<D, TKT>(sk0 + ks * KV_BYTES, 0, B(FULL_K + ks), (tile0 + j) * TKT, lo, hi, pw, a.cache,
-                                     head_base, page_stride, v_off, pd, lane, 0, 1);
+                issue_piece(pc, sk0 + ks * KV_BYTES, 0, B(FULL_K + ks), v_off, lane, 0, 1);
                 if (++ks == K_STAGES) { ks = 0; kphase ^= 1; }
+                if (j + 1 < n_tiles) pc = tile_piece<D, TKT>((tile0 + j + 1) * TKT, lo, hi, pw, a.cache, head_base, page_stride, pd, lane);
             }
         } else {
+            int vs = 0, vphase = 1;
             for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
-                const int st = j & 1;
-                if (!cx_mbar_wait(B(EMPTY_V + st), ((j >> 1) & 1) ^ 1)) { give_up(9); break; }
-                if (lane == 0) cx_mbar_expect_tx(B(FULL_V + st), KV_BYTES);
+                if (!cx_mbar_wait(B(EMPTY_V + vs), vphase)) { give_up(9); break; }
+                if (lane == 0) cx_mbar_expect_tx(B(FULL_V + vs), KV_BYTES);
                 __syncwarp();
-                produce_tile<D, TKT>(0, sv0 + st * KV_BYTES, 0, (tile0 + j) * TKT, lo, hi, pw, a.cache,
-                                     head_base, page_stride, v_off, pd, lane, B(FULL_V + st), 2);
+                issue_piece(pc, 0, sv0 + vs * KV_BYTES, 0, v_off, lane, B(FULL_V + vs), 2);
+                if (++vs == V_STAGES) { vs = 0; vphase ^= 1; }
+                if (j + 1 < n_tiles) pc = tile_piece<D, TKT>((tile0 + j + 1) * TKT, lo, hi, pw, a.cache, head_base, page_stride, pd, lane);
             }
         }
     } else if (warp == 2) {
@@ -857,20 +877,22 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
             asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(leader));
             bool ok = cx_mbar_wait(B(Q_READY), 0);            // Q tile written
             fence_after();
+            int vs = 0, vphase = 0;
             auto issue_pv = [&](int j) -> bool {                // O += P_j V_j, P_j in the first half of S buffer j & 1
                 const int st = j & 1;
-                if (!cx_mbar_wait(B(P_FULL), j & 1) || !cx_mbar_wait(B(FULL_V + st), (j >> 1) & 1)) return false;
+                if (!cx_mbar_wait(B(P_FULL), j & 1) || !cx_mbar_wait(B(FULL_V + vs), vphase)) return false;
                 fence_after();
-                const uint32_t v_base = sv0 + st * KV_BYTES, tm_p = tm_s0 + st * TKT;
+                const uint32_t v_base = sv0 + vs * KV_BYTES, tm_p = tm_s0 + st * TKT;
                 if (leader) {
 #pragma unroll
                     for (int kk = 0; kk < TKT / 16; ++kk)       // 16 keys a step: eight columns of P
                         mma_ts(tm_o, tm_p + kk * 8, desc_mn(v_base + kk * 16 * 128, TKT * 128), id_pv, (j > 0 || kk > 0) ? 1u : 0u);
                     commit(B(PV_DONE));         // P read, O updated
-                    commit(B(EMPTY_V + st));    // V stage free
+                    commit(B(EMPTY_V + vs));    // V stage free
                     if (j == n_tiles - 1) commit(B(O_DONE));
                 }
                 __syncwarp();
+                if (++vs == V_STAGES) { vs = 0; vphase ^= 1; }
                 return true;
             };
             int ks = 0, kphase = 0;
