@@ -41,9 +41,9 @@ def test_mixed_contexts(seed):
     lo = np.maximum(0, hi - window) if window else 0 * hi
     tiles = -(-hi // ops.DECODE_KEY_TILE) - lo // ops.DECODE_KEY_TILE
     need = -(-tiles // per)
-    slots = max(len(ctx), 2 * att.SM_COUNT // nkv)
+    slots = att.decode_slots(len(ctx))
     # the grid holds every request's splits and is no larger than twice what the longest needs
-    assert need.max() <= grid <= ops.DECODE_MAX_SPLITS and grid < 2 * need.max() and grid & (grid - 1) == 0
+    assert need.max() <= grid <= ops.DECODE_MAX_SPLITS and 3 * grid <= 4 * need.max() + 3 and grid in att.SPLIT_GRIDS
     # one wave, unless the longest request alone needs the most splits a grid has
     assert need.sum() <= slots or per == -(-tiles.max() // ops.DECODE_MAX_SPLITS)
     # and no longer splits than that takes

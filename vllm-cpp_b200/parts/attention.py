@@ -152,15 +152,15 @@ class PagedAttention(Mixer):
             """Decode-only steps: [most key tiles a split may have], and the grid's columns as a launch
             shape.  A request gets as many splits as its context needs under that bound, so one with a
             long context gets more CTAs than one with a short context.  The bound is the smallest with
-            which the splits of all requests fill the device once (two CTAs fit an SM; a second wave
-            would double the time).  Equal contexts come out as before: all requests in equal parts."""
+            which the splits of all requests fit decode_slots() (one round of CTAs; a second would
+            double the time).  Equal contexts come out as before: all requests in equal parts."""
             if any(q != 1 for q in host.q_lens):
                 return np.zeros(1, dtype=np.int32)
             tile, most = ops.DECODE_KEY_TILE, ops.DECODE_MAX_SPLITS
             hi = np.asarray(host.ctx_lens, dtype=np.int64) + 1
             lo = np.maximum(0, hi - self.window) if self.window > 0 else np.zeros_like(hi)
             n = -(-hi // tile) - lo // tile                     # key tiles of every request
-            slots = max(len(n), 2 * self.SM_COUNT // self.nkv)  # splits per kv head that fill the device once
+            slots = self.decode_slots(len(n))
             low, high = max(1, -(-int(n.sum()) // slots)), int(n.max())
             while low < high:                                   # smallest count whose splits fit the slots
                 mid = (low + high) // 2
@@ -170,10 +170,20 @@ class PagedAttention(Mixer):
                     low = mid + 1
             per = max(low, -(-int(n.max()) // most))
             need = -(-int(n.max()) // per)
-            host.shapes[self._splits_key()] = 1 << (need - 1).bit_length()
+            # the grid's columns: the next size of a short ladder, so that few shapes are captured and at
+            # most a quarter of a request's CTAs find nothing to do (they cost a launch each)
+            host.shapes[self._splits_key()] = next(g for g in self.SPLIT_GRIDS if g >= need)
             return np.array([per], dtype=np.int32)
 
         return {f"attn_tiles_g{group}_d{self.d}": tiles, self._splits_key(): splits}
+
+    SPLIT_GRIDS = (1, 2, 3, 4, 5, 6, 8, 10, 12, 16, 20, 24, 32)
+
+    def decode_slots(self, n_reqs: int) -> int:
+        """Splits per kv head that a decode step may have in all: seven eighths of the places the device has
+        for the kernel's CTAs (two per SM).  Filling every place was measured slower: the CTAs of the
+        kernels before and after share the SMs, and a CTA that finds no place waits for a second round."""
+        return max(n_reqs, (2 * self.SM_COUNT * 7 // 8) // self.nkv)
 
     def _splits_key(self):
         return f"attn_splits_kv{self.nkv}_w{self.window}"
