@@ -1,6 +1,9 @@
 // Paged grouped-query attention on tensor cores for bfloat16, head sizes 64 and 128.
 //
-// Two kernels share the tile loader and the fragment code:
+// Prompt portions run on tc::attention_prefill_tc_kernel (tcgen05, further down, with its own
+// description), single tokens on attention_decode_kernel; attention_prefill_kernel is the prefill kernel
+// on the legacy tensor-core path, kept for pages whose size is no multiple of 8 and as a second reference.
+// The two mma.sync kernels share the tile loader and the fragment code:
 //   * attention_prefill_kernel: portions of prompts of any length (and, in mixed
 //     batches, single tokens).  The query heads that share one kv head are packed
 //     into the row dimension: row = token * G + head_in_group, G = heads / kv_heads,
@@ -656,13 +659,12 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 // only when the maximum has risen by more than 8 (in units of log2), and then the row's thread
 // rescales its row of O in tensor memory and its sum.  Probabilities stay below 2^8, sums and O in
 // float; the rescaling is rare after the first tiles.
-// Warp 0 copies K tiles and warp 1 V tiles (bulk copies from the pages, three K stages and two V stages,
-// separate barriers so a K stage is free as soon as S is done), warp 2 issues the MMAs, warps 3-6 do the rest.  The MMA of
-// tile j + 1's scores is issued before tile j's P V, so the tensor cores work while tile j's softmax
-// runs, and two CTAs share an SM (256 columns of tensor memory and, at head size 128, 112 KB of shared
-// memory each), so
-// one CTA's softmax runs under the other's MMAs and waits.  Every wait is bounded; one that runs
-// out sets *status and the CTA drains and leaves.
+// Warp 0 copies K tiles and warp 1 V tiles (bulk copies from the pages, two K stages and three V stages,
+// separate barriers so a K stage is free as soon as S is done), warp 2 issues the MMAs, warps 3-6 do the
+// rest.  The MMA of tile j + 1's scores is issued before tile j's P V, so the tensor cores work while
+// tile j's softmax runs, and two CTAs share an SM (256 columns of tensor memory and, at head size 128,
+// 112 KB of shared memory each), so one CTA's softmax runs under the other's MMAs and waits.  Every wait
+// is bounded; one that runs out sets *status and the CTA drains and leaves.
 namespace tc {
 constexpr int BMT = 128, TKT = 64;
 constexpr int THREADS = 224;

@@ -278,7 +278,7 @@ def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req
                          num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
                          scale: float) -> None:
     """Attention for portions of any length on tcgen05 tensor cores (scores and output tiles in tensor
-    memory); head size 128, bfloat16, tiles of 128 packed rows."""
+    memory); head sizes 64 and 128, bfloat16, pages of a multiple of 8 slots, tiles of 128 packed rows."""
     _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
           "attention_prefill_tc is a bfloat16 kernel")
     _need(head_dim in TC_ATTENTION_HEAD_DIMS and page_size % 8 == 0,
