@@ -134,6 +134,33 @@ def test_steps_launched_ahead_give_the_same_tokens(tmp_path):
     assert len(off[3]) == 16 and off[3] == on[3]
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_captured_steps_with_mixed_contexts_give_the_same_tokens(tmp_path, name):
+    """Requests whose contexts differ twentyfold decode together on the tensor-core kernels: the splits of
+    the decode attention follow the contexts and change the grid as they grow and as requests leave, and
+    every such shape is captured as a graph of its own.  Same tokens as with every kernel launched
+    directly, several shapes seen, nothing left behind."""
+    from vllm_cpp_b200 import SamplingParams
+    cfg, page = CONFIGS[name]
+    prompts = [token_ids(cfg, n, 30 + n) for n in (250, 12, 90, 3, 180)]
+    params = [SamplingParams(max_tokens=n, temperature=0.0, ignore_eos=True) for n in (40, 60, 25, 60, 33)]
+    runs, shapes = {}, set()
+    for graphs in (False, True):
+        _, _, llm = make_llm(tmp_path, name, "bfloat16", use_cuda_graphs=graphs, num_gpu_blocks=96)
+        eng = llm.engine
+        ids = [eng.add_request(p, sp) for p, sp in zip(prompts, params)]
+        got = {i: [] for i in ids}
+        while eng.has_pending_work():
+            for o in eng.step():
+                got[o.seq_id].extend(o.tokens)
+        runs[graphs] = [got[i] for i in ids]
+        if graphs:
+            shapes = set(eng.runner.graphs)
+        assert eng.cache.num_free_pages() == 96 and not eng.cache.requests
+    assert runs[False] == runs[True] and [len(t) for t in runs[True]] == [40, 60, 25, 60, 33]
+    assert len(shapes) >= 3, shapes
+
+
 def test_long_decoding_stays_on_the_plain_logits(tmp_path):
     """160 tokens decoded one by one after a 3-token prompt, replayed against the plain logits."""
     from vllm_cpp_b200.engine.runner import StepEntry
