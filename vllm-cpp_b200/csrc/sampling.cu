@@ -92,7 +92,21 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
     if ((((uintptr_t)l) & 15) == 0) {
         const int nvec = vocab >> 2;
         const float4* l4 = reinterpret_cast<const float4*>(l);
-        for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        // four loads in flight per thread: one at a time is a round trip to the L2 cache per 16 bytes
+        constexpr int U = 4;
+        int i = threadIdx.x;
+        for (; i + (U - 1) * (int)blockDim.x < nvec; i += U * blockDim.x) {
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) v[u] = l4[i + u * blockDim.x];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int id = 4 * (i + u * (int)blockDim.x);
+                argmax_combine(bv, bi, v[u].x, id); argmax_combine(bv, bi, v[u].y, id + 1);
+                argmax_combine(bv, bi, v[u].z, id + 2); argmax_combine(bv, bi, v[u].w, id + 3);
+            }
+        }
+        for (; i < nvec; i += blockDim.x) {
             const float4 v = l4[i];
             argmax_combine(bv, bi, v.x, 4 * i); argmax_combine(bv, bi, v.y, 4 * i + 1);
             argmax_combine(bv, bi, v.z, 4 * i + 2); argmax_combine(bv, bi, v.w, 4 * i + 3);
