@@ -346,7 +346,7 @@ def main() -> int:
         torch.cuda.synchronize()
         dt = time.perf_counter() - t
         assert produced == batch * n_steps
-        h2d = int(runner.last_meta_bytes) + 5 * 4 * batch
+        h2d = int(runner.last_meta_bytes) + 4 * 4 * batch        # step metadata + four floats of sampling options a row
         for i in ids:
             engine.abort_request(i)
         return produced / dt, h2d, 4 * batch

@@ -102,9 +102,12 @@ class Sampler:
             hf[2, i] = r.top_p
             hf[3, i] = r.repetition_penalty
             hi[0, i] = r.top_k
+        filtered = [i for i, r in enumerate(rows)
+                    if r.temperature > 0 and (r.top_p < 1.0 or r.top_k > 0)]
         d_float, d_int = self.d_float[slot], self.d_int[slot]
         d_float[:, :m].copy_(self.h_float[slot][:, :m], non_blocking=True)
-        d_int[:, :m].copy_(self.h_int[slot][:, :m], non_blocking=True)
+        if filtered:                                       # only the filtered draw reads top_k
+            d_int[:, :m].copy_(self.h_int[slot][:, :m], non_blocking=True)
         temperature, uniform = d_float[0, :m], d_float[1, :m]
 
         if any(r.repetition_penalty != 1.0 and len(r.generated) for r in rows):
@@ -117,8 +120,6 @@ class Sampler:
             d_start = torch.tensor(start, dtype=torch.int32, device=self.device)
             ops.repetition_penalty(logits, d_ids, d_start, d_float[3, :m].contiguous())
 
-        filtered = [i for i, r in enumerate(rows)
-                    if r.temperature > 0 and (r.top_p < 1.0 or r.top_k > 0)]
         out = self.d_out[slot][:m]
         ops.sample(logits, temperature.contiguous(), uniform.contiguous(), out)
         if filtered:
