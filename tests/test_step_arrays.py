@@ -23,7 +23,7 @@ def splits_of(att, ctx_lens):
     return per, host.shapes[att._splits_key()]
 
 
-@pytest.mark.parametrize("nh,nkv,batch,ctx,per,grid", [(28, 4, 8, 4095, 8, 8), (28, 4, 1, 4095, 2, 32), (28, 4, 64, 4095, 64, 1),
+@pytest.mark.parametrize("nh,nkv,batch,ctx,per,grid", [(28, 4, 8, 4095, 8, 8), (28, 4, 1, 4095, 4, 16), (28, 4, 64, 4095, 64, 1),
                                                        (28, 4, 32, 4095, 32, 2), (40, 8, 8, 100, 1, 2), (28, 4, 1, 0, 1, 1)])
 def test_equal_contexts_fill_the_device_once(nh, nkv, batch, ctx, per, grid):
     assert splits_of(part(nh, nkv), [ctx] * batch) == (per, grid)
@@ -44,10 +44,12 @@ def test_mixed_contexts(seed):
     slots = att.decode_slots(len(ctx))
     # the grid holds every request's splits and is no larger than twice what the longest needs
     assert need.max() <= grid <= ops.DECODE_MAX_SPLITS and 3 * grid <= 4 * need.max() + 3 and grid in att.SPLIT_GRIDS
-    # one wave, unless the longest request alone needs the most splits a grid has
-    assert need.sum() <= slots or per == -(-tiles.max() // ops.DECODE_MAX_SPLITS)
+    longest = int(tiles.max())
+    floor = max(-(-longest // ops.DECODE_MAX_SPLITS), min(4, -(-longest // 8)))     # the grid's limit; splits not too short
+    # one wave, unless the floor decides
+    assert need.sum() <= slots or per == floor
     # and no longer splits than that takes
-    if per > 1 and per > -(-tiles.max() // ops.DECODE_MAX_SPLITS):
+    if per > floor:
         assert (-(-tiles // (per - 1))).sum() > slots
 
 

@@ -168,8 +168,12 @@ class PagedAttention(Mixer):
                     high = mid
                 else:
                     low = mid + 1
-            per = max(low, -(-int(n.max()) // most))
-            need = -(-int(n.max()) // per)
+            longest = int(n.max())
+            # with few requests the slots would allow splits of one or two tiles, but below four tiles a
+            # split's start, its partials and a longer merge cost more than its share of the keys: at least
+            # four tiles a split, unless that leaves the longest request fewer than eight splits
+            per = max(low, -(-longest // most), min(4, -(-longest // 8)))
+            need = -(-longest // per)
             # the grid's columns: the next size of a short ladder, so that few shapes are captured and at
             # most a quarter of a request's CTAs find nothing to do (they cost a launch each)
             host.shapes[self._splits_key()] = next(g for g in self.SPLIT_GRIDS if g >= need)
