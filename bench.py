@@ -328,6 +328,7 @@ def main() -> int:
         steps start when every request decodes, and end before the first one finishes."""
         portions = -(-CONTEXT // PREFILL_TOKENS)
         slack = batch * portions + 2
+        n_warm = max(n_warm, 64)        # the prompts' steps leave reduced clocks behind: decode until they are back
         budget = n_steps + n_warm + slack
         prompt_len = CONTEXT - budget
         sp = SamplingParams(max_tokens=budget, temperature=0.0, ignore_eos=True)
