@@ -668,11 +668,13 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 namespace tc {
 constexpr int BMT = 128, TKT = 64;
 constexpr int THREADS = 224;
-constexpr int K_STAGES = 2, V_STAGES = 3;
+// stages of the K and of the V ring: what fits beside Q when two CTAs share an SM's shared memory
+template <int D> __host__ __device__ constexpr int k_stages() { return D == 64 ? 4 : 2; }
+template <int D> __host__ __device__ constexpr int v_stages() { return D == 64 ? 4 : 3; }
 constexpr int TMEM_COLS = 256;                                               // S0, S1 (64 each), O (head size)
 constexpr float RESCALE_STEP = 8.0f;
 // Q, the K and V stages, barriers; no slack: the base must be 1024-aligned
-template <int D> constexpr int smem_bytes() { return BMT * D * 2 + (K_STAGES + V_STAGES) * TKT * D * 2 + 256; }
+template <int D> constexpr int smem_bytes() { return BMT * D * 2 + (k_stages<D>() + v_stages<D>()) * TKT * D * 2 + 256; }
 
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -774,7 +776,7 @@ template <int D>
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc_kernel(MmaAttnArgs a) {
     static_assert(D == 64 || D == 128, "one or two planes of 64 elements; S, S and O fit 256 columns");
-    constexpr int Q_BYTES = BMT * D * 2, KV_BYTES = TKT * D * 2;
+    constexpr int Q_BYTES = BMT * D * 2, KV_BYTES = TKT * D * 2, K_STAGES = k_stages<D>(), V_STAGES = v_stages<D>();
     extern __shared__ __align__(1024) unsigned char smem[];
     // No early release of the next kernel here: its CTAs would sit on this SM holding tensor memory
     // while CTAs of this kernel still wait to be placed.
@@ -925,16 +927,28 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         const int lg = warp & 3;
         const int row = lg * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
-        // Q tile: packed row -> (token, head in group); two planes of 128-byte pieces, chunks swizzled
-        for (int idx = threadIdx.x - 96; idx < BMT * (D / 8); idx += 128) {
-            const int rr = idx / (D / 8), c = idx % (D / 8);
-            const int pr = row0 + rr;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (pr < rows_total) {
-                const int tt = pr / G, hg = pr % G;
-                v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + tt) * a.nh + g * G + hg) * D + c * 8);
+        // Q tile: packed row -> (token, head in group); two planes of 128-byte pieces, chunks swizzled.
+        // All of a thread's loads are issued before the first is stored: one at a time they cost a trip
+        // to the L2 cache each, 5 us for the tile.
+        {
+            constexpr int PER_THREAD = BMT * (D / 8) / 128;
+            uint4 v[PER_THREAD];
+#pragma unroll
+            for (int i = 0; i < PER_THREAD; ++i) {
+                const int idx = (int)threadIdx.x - 96 + i * 128;
+                const int rr = idx / (D / 8), c = idx % (D / 8);
+                const int pr = row0 + rr;
+                v[i] = make_uint4(0, 0, 0, 0);
+                if (pr < rows_total) {
+                    const int tt = pr / G, hg = pr % G;
+                    v[i] = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + tt) * a.nh + g * G + hg) * D + c * 8);
+                }
             }
-            *reinterpret_cast<uint4*>(q_ptr + swz_kv<D, BMT>(rr, c)) = v;
+#pragma unroll
+            for (int i = 0; i < PER_THREAD; ++i) {
+                const int idx = (int)threadIdx.x - 96 + i * 128;
+                *reinterpret_cast<uint4*>(q_ptr + swz_kv<D, BMT>(idx / (D / 8), idx % (D / 8))) = v[i];
+            }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
