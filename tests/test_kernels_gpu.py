@@ -76,10 +76,15 @@ def test_add_rmsnorm(ops, dtype, hidden):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_silu_mul_and_bias(ops, dtype):
     rng = np.random.default_rng(2)
-    gu = as_stored(3 * rng.standard_normal((5, 2 * 333)), dtype)
-    out = torch.empty((5, 333), dtype=DT[dtype], device="cuda")
-    ops.silu_mul(dev(gu, DT[dtype]), out)
-    close(out.float().cpu().numpy(), plain.silu(gu[:, :333].astype(np.float64)) * gu[:, 333:], dtype, "silu_mul")
+    # a width the 16-byte kernel cannot take, one it takes (several vectors a thread, a ragged end),
+    # values far out on both sides
+    for tokens, inter in ((5, 333), (70, 1000), (3, 8)):
+        gu = as_stored(3 * rng.standard_normal((tokens, 2 * inter)), dtype)
+        gu[0, :4] = [-200.0, -30.0, 40.0, 0.0]
+        out = torch.empty((tokens, inter), dtype=DT[dtype], device="cuda")
+        ops.silu_mul(dev(gu, DT[dtype]), out)
+        close(out.float().cpu().numpy(), plain.silu(gu[:, :inter].astype(np.float64)) * gu[:, inter:], dtype,
+              f"silu_mul {tokens} x {inter}")
     x = as_stored(rng.standard_normal((4, 77)), dtype)
     b = rng.standard_normal(77).astype(np.float32)
     xd = dev(x, DT[dtype])
@@ -100,11 +105,29 @@ def paged_layout(rng, n_reqs, max_len, page, n_pages):
                                                    (2, 1, 128, 128, 0), (5, 5, 80, 80, 1), (6, 3, 64, 0, 0),
                                                    (28, 4, 128, 128, 0), (33, 3, 64, 64, 0), (9, 3, 16, 16, 0)])
 def test_rope_cache_write(ops, dtype, nh, nkv, d, rot, pairing):
+    rope_cache_write_case(ops, dtype, nh, nkv, d, rot, pairing, many=False)
+
+
+@pytest.mark.parametrize("nh,nkv,d", [(28, 4, 128), (3, 1, 64), (5, 5, 16)])
+def test_rope_cache_write_of_a_long_portion(ops, nh, nkv, d):
+    """Hundreds of tokens in one call (the kernel then takes several tokens per CTA), a count that is no
+    multiple of that number, two requests."""
+    rope_cache_write_case(ops, "bfloat16", nh, nkv, d, d, 0, many=True)
+
+
+def rope_cache_write_case(ops, dtype, nh, nkv, d, rot, pairing, many):
     rng = np.random.default_rng(3)
-    page, n_pages, n_reqs = 16, 12, 2
-    bt = paged_layout(rng, n_reqs, 80, page, n_pages)
-    req = np.array([0] * 9 + [1] * 4, dtype=np.int32)
-    pos = np.concatenate([np.arange(30, 39), np.arange(61, 65)]).astype(np.int32)     # crosses page edges
+    page, n_reqs = 16, 2
+    if many:
+        n_pages = 48
+        bt = paged_layout(rng, n_reqs, 384, page, n_pages)
+        req = np.array([0] * 350 + [1] * 231, dtype=np.int32)
+        pos = np.concatenate([np.arange(7, 357), np.arange(100, 331)]).astype(np.int32)
+    else:
+        n_pages = 12
+        bt = paged_layout(rng, n_reqs, 80, page, n_pages)
+        req = np.array([0] * 9 + [1] * 4, dtype=np.int32)
+        pos = np.concatenate([np.arange(30, 39), np.arange(61, 65)]).astype(np.int32)     # crosses page edges
     n = len(pos)
     width = (nh + 2 * nkv) * d
     qkv = as_stored(rng.standard_normal((n, width)), dtype)
@@ -372,6 +395,25 @@ def test_sampling_greedy_and_temperature(ops):
     # u just below 1 gives the last id with any mass; u = 0 the first
     ops.sample(dev(logits), dev(temps), dev(np.zeros(rows, dtype=np.float32)), out)
     assert out.cpu().numpy()[3] == 0
+
+
+@pytest.mark.parametrize("vocab", [152064, 40003])
+def test_greedy_sampling_over_a_large_vocabulary(ops, vocab):
+    """The argmax pass with several loads in flight per thread: the maximum at the start, at the end, in the
+    ragged tail, a tie far apart (the lower id wins), rows of a wider buffer."""
+    rng = np.random.default_rng(10)
+    rows = 5
+    buf = rng.standard_normal((rows, vocab + 6)).astype(np.float32)
+    logits = buf[:, :vocab]
+    logits[0, 0] = 9.0
+    logits[1, vocab - 1] = 9.0
+    logits[2, vocab - 3] = 9.0
+    logits[3, 4097] = logits[3, vocab - 2] = 9.0
+    want = [0, vocab - 1, vocab - 3, 4097, int(np.argmax(logits[4]))]
+    full = dev(buf)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops.sample(full[:, :vocab], dev(np.zeros(rows, dtype=np.float32)), dev(np.zeros(rows, dtype=np.float32)), out)
+    assert out.cpu().numpy().tolist() == want
 
 
 def test_sampling_top_k_top_p_and_penalty(ops):
