@@ -289,6 +289,31 @@ def test_attention_prefill_tc(ops, nh, nkv, page, window, d):
     close(out.float().cpu().numpy().reshape(c["n"], nh, d), want, "bfloat16", "attention_prefill_tc")
 
 
+@pytest.mark.parametrize("d,window", [(128, 0), (64, 0), (128, 500)])
+def test_attention_prefill_tc_long(ops, d, window):
+    """Long portions: CTAs that walk dozens of key tiles, more CTAs than the device holds at once, the
+    warps of a CTA drifting apart.  (Two hazards between the kernel's barriers showed only at this size.)"""
+    rng = np.random.default_rng(16)
+    nh, nkv, page = 28, 4, 16
+    q_lens, ctx_lens = [1700, 300], [0, 1100]
+    c = attention_case(rng, "bfloat16", nh, nkv, d, page, q_lens, ctx_lens)
+    group = nh // nkv
+    rows = ops.TC_ATTENTION_TILE_ROWS
+    tiles = [(r, k * rows) for r, ql in enumerate(q_lens) for k in range(-(-ql * group // rows))]
+    tiles.sort(key=lambda t: -(ctx_lens[t[0]] + t[1] // group))
+    out = torch.full((c["n"], nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    args = (dev(c["q"].reshape(c["n"], -1), torch.bfloat16), dev(c["cache"], torch.bfloat16), out, dev(c["q_start"]),
+            dev(np.array(ctx_lens, dtype=np.int32)), dev(c["bt"]), dev(np.array([t[0] for t in tiles], dtype=np.int32)),
+            dev(np.array([t[1] for t in tiles], dtype=np.int32)))
+    for _ in range(5):
+        ops.attention_prefill_tc(*args, num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page, window=window,
+                                 scale=float(np.float32(1) / np.sqrt(np.float32(d))))
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = reference_attention(c["q"].astype(np.float64), c["k"], c["v"], q_lens, ctx_lens, nh, nkv, window)
+    close(out.float().cpu().numpy().reshape(c["n"], nh, d), want, "bfloat16", "attention_prefill_tc, long")
+
+
 @pytest.mark.parametrize("nsplit", [1, 3, 8])
 @pytest.mark.parametrize("nh,nkv,d,page,window", [(28, 4, 128, 16, 0), (6, 2, 64, 32, 0), (3, 3, 64, 16, 40),
                                                    (40, 2, 128, 16, 0), (16, 1, 128, 16, 200)])
