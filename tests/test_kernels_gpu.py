@@ -245,25 +245,6 @@ def test_attention_simt(ops, dtype, nh, nkv, d, page, window):
     close(out.float().cpu().numpy().reshape(c["n"], nh, d), want, dtype, "attention_simt")
 
 
-@pytest.mark.parametrize("nh,nkv,d,page,window", [(28, 4, 128, 16, 0), (6, 2, 64, 32, 0), (3, 3, 64, 16, 40),
-                                                   (8, 1, 128, 16, 100), (40, 2, 128, 64, 0)])
-def test_attention_prefill_mma(ops, nh, nkv, d, page, window):
-    rng = np.random.default_rng(5)
-    q_lens, ctx_lens = [70, 1, 2, 129, 5], [0, 500, 63, 64, 1000]      # tile and page edges on both sides
-    c = attention_case(rng, "bfloat16", nh, nkv, d, page, q_lens, ctx_lens)
-    group = nh // nkv
-    tiles = [(r, k * 64) for r, ql in enumerate(q_lens) for k in range(-(-ql * group // 64))]
-    out = torch.zeros((c["n"], nh * d), dtype=torch.bfloat16, device="cuda")
-    ops.attention_prefill_mma(dev(c["q"].reshape(c["n"], -1), torch.bfloat16), dev(c["cache"], torch.bfloat16), out,
-                              dev(c["q_start"]), dev(np.array(ctx_lens, dtype=np.int32)), dev(c["bt"]),
-                              dev(np.array([t[0] for t in tiles], dtype=np.int32)),
-                              dev(np.array([t[1] for t in tiles], dtype=np.int32)),
-                              num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page, window=window,
-                              scale=float(np.float32(1) / np.sqrt(np.float32(d))))
-    want = reference_attention(c["q"].astype(np.float64), c["k"], c["v"], q_lens, ctx_lens, nh, nkv, window)
-    close(out.float().cpu().numpy().reshape(c["n"], nh, d), want, "bfloat16", "attention_prefill_mma")
-
-
 @pytest.mark.parametrize("d", [128, 64])
 @pytest.mark.parametrize("nh,nkv,page,window", [(28, 4, 16, 0), (8, 1, 16, 100), (40, 2, 64, 0), (3, 3, 32, 40), (16, 2, 16, 300)])
 def test_attention_prefill_tc(ops, nh, nkv, page, window, d):
@@ -362,7 +343,7 @@ def test_attention_refuses_what_it_cannot_do(ops):
     z = torch.zeros(4, dtype=torch.int32, device="cuda")
     cache = torch.zeros((2, 2, 2, 16, 80), dtype=torch.bfloat16, device="cuda")
     with pytest.raises(ops.KernelError, match="head sizes"):
-        ops.attention_prefill_mma(q, cache, q, z, z, z.view(1, 4), z[:1], z[:1], num_heads=2, num_kv_heads=2,
+        ops.attention_prefill_tc(q, cache, q, z, z, z.view(1, 4), z[:1], z[:1], num_heads=2, num_kv_heads=2,
                                   head_dim=80, page_size=16, window=0, scale=1.0)
     with pytest.raises(ops.KernelError, match="256"):
         ops.attention_simt(torch.zeros((1, 272), dtype=torch.float32, device="cuda"), cache.float(), q.float(), z[:1],

@@ -1,20 +1,15 @@
 // Paged grouped-query attention on tensor cores for bfloat16, head sizes 64 and 128.
 //
-// Prompt portions run on tc::attention_prefill_tc_kernel (tcgen05, further down, with its own
-// description), single tokens on attention_decode_kernel; attention_prefill_kernel is the prefill kernel
-// on the legacy tensor-core path, kept for pages whose size is no multiple of 8 and as a second reference.
-// The two mma.sync kernels share the tile loader and the fragment code:
-//   * attention_prefill_kernel: portions of prompts of any length (and, in mixed
-//     batches, single tokens).  The query heads that share one kv head are packed
-//     into the row dimension: row = token * G + head_in_group, G = heads / kv_heads,
-//     so one K/V tile in shared memory serves all G heads.  A CTA of 4 warps owns
-//     64 such rows and walks the keys 0..p (or the window) in tiles of 64.
-//   * attention_decode_kernel: one query token per request.  Its G rows fill one
-//     16-row fragment; the context is split over gridDim.x CTAs, and inside a CTA
-//     each warp takes 16 of every 64 keys.  Partial (max, sum, output) triples are
-//     merged across warps in shared memory and across CTAs through scratch memory
-//     in global memory: every CTA of a (request, kv head) takes a ticket when its
-//     partials are written, and the one that draws the last ticket merges them.
+// Two kernels share the tile loader:
+//   * attention_decode_kernel (mma.sync): one query token per request.  The query heads that share one kv
+//     head are packed into the row dimension (row = head in group, G = heads / kv_heads), so one K/V
+//     tile in shared memory serves all G heads; the G rows fill one 16-row fragment.  The context is
+//     split over CTAs, and inside a CTA each warp takes 16 of every 64 keys.  Partial (max, sum, output)
+//     triples are merged across warps in shared memory and across CTAs through scratch memory in global
+//     memory: every CTA of a (request, kv head) takes a ticket when its partials are written, and the
+//     one that draws the last ticket merges them.
+//   * tc::attention_prefill_tc_kernel (tcgen05, further down, with its own description): portions of
+//     prompts of any length and, in mixed batches, single tokens; row = token * G + head in group.
 // Scores, softmax statistics and output accumulators are float; the probabilities
 // are rounded to bfloat16 for the P*V product, as K and V are stored.  Exponentials
 // are ex2.approx on scores pre-multiplied by log2(e) (this file is the bfloat16 path;
@@ -22,8 +17,8 @@
 //
 // Loading.  The cache stores every row already in the XOR-swizzled chunk order that
 // ldmatrix wants (kv_pos in common.cuh), so a run of slots of a page is a ready-made
-// piece of a shared-memory tile.  A fifth warp is the producer: for every tile of 64 keys
-// it issues one bulk copy (cp.async.bulk, the TMA unit, no tensor map, no multicast) per
+// piece of a shared-memory tile.  In the decode kernel a fifth warp is the producer: for every tile of
+// 64 keys it issues one bulk copy (cp.async.bulk, the TMA unit, no tensor map, no multicast) per
 // page piece of K and of V into a ring of stages, completing on the stage's mbarrier; the
 // four consumer warps wait on that barrier and hand the stage back on another.  No thread
 // that computes ever waits on a global load.  Pages wholly outside [lo, hi) may have been
@@ -36,7 +31,6 @@
 #include "common.cuh"
 
 #define BN 64            // keys per tile
-#define BM 64            // rows per CTA in the prefill kernel
 #define NTHREADS 128     // consumer threads (4 warps); warp 4 is the producer
 #define BLOCK_THREADS 160
 
@@ -473,160 +467,6 @@ attention_decode_kernel(MmaAttnArgs a) {
     if (threadIdx.x == 0) a.counters[li * a.nkv + g] = 0;       // ready for the next launch
 }
 
-// ----------------------------------------------------------------- prefill
-template <int D, int TK, int STAGES, int MINB>
-__global__ void __launch_bounds__(BLOCK_THREADS, MINB)
-attention_prefill_kernel(MmaAttnArgs a) {
-    extern __shared__ __align__(1024) unsigned char smem[];
-    constexpr int TILE_BYTES = TK * D * 2;
-    pdl_start();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool producer = warp == 4;
-    const int r = a.req_list[blockIdx.x];
-    const int row0 = a.tile_row0[blockIdx.x];
-    const int g = blockIdx.y;
-    const int G = a.nh / a.nkv;
-    const int q0 = a.q_start[r], q_len = a.q_start[r + 1] - q0, ctx = a.ctx_lens[r];
-    const int rows_total = q_len * G;
-    const int* bt = a.block_table + (size_t)r * a.bt_stride;
-    const float sl2 = a.scale * LOG2E;                   // scores in units of log2
-
-    // [STAGES x (K, V) tiles][Q: BM x D][barriers]
-    const uint32_t s_tiles = smem_u32(smem);
-    unsigned char* q_ptr = smem + (size_t)STAGES * 2 * TILE_BYTES;
-    const uint32_t sq = smem_u32(q_ptr);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(q_ptr + BM * D * 2);
-    const uint32_t full0 = cx_smem(bars), empty0 = cx_smem(bars + STAGES);
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { cx_mbar_init(full0 + 8 * s, 1); cx_mbar_init(empty0 + 8 * s, 4); }
-        cx_mbar_init_fence();
-    }
-    // Q tile: packed row -> (token, head in group)
-    for (int idx = threadIdx.x; idx < BM * (D / 8); idx += BLOCK_THREADS) {
-        const int row = idx / (D / 8), c = idx % (D / 8);
-        const int pr = row0 + row;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (pr < rows_total) {
-            const int tt = pr / G, hg = pr % G;
-            v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + tt) * a.nh + g * G + hg) * D + c * 8);
-        }
-        *reinterpret_cast<uint4*>(q_ptr + swz<D>(row, c)) = v;
-    }
-    // keys that any row of the tile can see
-    const int last_row = min(row0 + BM, rows_total) - 1;
-    const int hi = ctx + last_row / G + 1;
-    const int lo = a.window > 0 ? max(0, ctx + row0 / G + 1 - a.window) : 0;
-    const int tile0 = lo / TK, tile1 = (hi + TK - 1) / TK;
-    __syncthreads();                                     // barriers initialised, Q tile written
-    bool gave_up = false;
-
-    if (producer) {
-        PageWindow pw;
-        const PageDiv pd(a.page);
-        pw.init(bt, pd.div(tile0 * TK), hi, a.page, lane);
-        const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
-                     v_off = (size_t)a.nkv * a.page * D;
-        for (int tile = tile0, it = 0; tile < tile1; ++tile, ++it) {
-            const int st = it % STAGES;
-            if (!cx_mbar_wait(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) gave_up = true;
-            if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, 2 * TILE_BYTES);
-            __syncwarp();
-            produce_tile<D, TK>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
-                                full0 + 8 * st, tile * TK, lo, hi, pw, a.cache, head_base, page_stride, v_off, pd, lane);
-        }
-        if (gave_up && a.status) atomicCAS(a.status, 0, 6);
-        return;
-    }
-
-    // positions of this thread's two rows
-    const int pra = row0 + warp * 16 + (lane >> 2), prb = pra + 8;
-    const int pos_a = ctx + min(pra, rows_total - 1) / G, pos_b = ctx + min(prb, rows_total - 1) / G;
-    const bool live_a = pra < rows_total, live_b = prb < rows_total;
-    uint32_t qf[D / 16][4];
-    load_q_frags<D>(qf, sq, warp * 16);
-
-    float o[D / 8][4];
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
-    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
-    // the smallest position among this warp's rows: tiles wholly at or below it need no mask
-    const int wpos_min = ctx + min(row0 + warp * 16, rows_total - 1) / G;
-    const int wlo_max = a.window > 0 ? ctx + min(row0 + warp * 16 + 15, rows_total - 1) / G + 1 - a.window : 0;
-
-    for (int tile = tile0, it = 0; tile < tile1; ++tile, ++it) {
-        const int st = it % STAGES;
-        if (!cx_mbar_wait(full0 + 8 * st, (it / STAGES) & 1)) gave_up = true;
-        const uint32_t sk = s_tiles + st * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
-        const int kb = tile * TK;
-        float s[TK / 8][4];
-#pragma unroll
-        for (int i = 0; i < TK / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
-        qk_product<D, TK, TK / 8>(s, qf, sk, 0);
-        const bool need_mask = (kb + TK - 1 > wpos_min) || (kb < wlo_max) || !live_b;
-#pragma unroll
-        for (int nb = 0; nb < TK / 8; ++nb)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float v = s[nb][e] * sl2;
-                if (need_mask) {
-                    const int j = kb + nb * 8 + (lane & 3) * 2 + (e & 1);
-                    const int pos = (e < 2) ? pos_a : pos_b;
-                    const bool live = (e < 2) ? live_a : live_b;
-                    const bool ok = live && j <= pos && (a.window <= 0 || j > pos - a.window);
-                    if (!ok) v = -INFINITY;
-                }
-                s[nb][e] = v;
-            }
-        float ta = -INFINITY, tb = -INFINITY;
-#pragma unroll
-        for (int nb = 0; nb < TK / 8; ++nb) {
-            ta = fmaxf(ta, fmaxf(s[nb][0], s[nb][1]));
-            tb = fmaxf(tb, fmaxf(s[nb][2], s[nb][3]));
-        }
-        ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 1)); ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 2));
-        tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 1)); tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 2));
-        const float na = fmaxf(m_a, ta), nb_ = fmaxf(m_b, tb);
-        const float sa = na == -INFINITY ? 0.0f : na, sb = nb_ == -INFINITY ? 0.0f : nb_;
-        const float ca = fast_exp2(m_a - sa), cb = fast_exp2(m_b - sb);
-        m_a = na; m_b = nb_;
-        uint32_t pf[TK / 16][4];
-        float sum_a = 0.0f, sum_b = 0.0f;
-#pragma unroll
-        for (int kk = 0; kk < TK / 16; ++kk) {
-            float p[2][4];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int nb = kk * 2 + h;
-                p[h][0] = fast_exp2(s[nb][0] - sa); p[h][1] = fast_exp2(s[nb][1] - sa);
-                p[h][2] = fast_exp2(s[nb][2] - sb); p[h][3] = fast_exp2(s[nb][3] - sb);
-                sum_a += p[h][0] + p[h][1];
-                sum_b += p[h][2] + p[h][3];
-            }
-            pf[kk][0] = pack_bf16(p[0][0], p[0][1]); pf[kk][1] = pack_bf16(p[0][2], p[0][3]);
-            pf[kk][2] = pack_bf16(p[1][0], p[1][1]); pf[kk][3] = pack_bf16(p[1][2], p[1][3]);
-        }
-        l_a = l_a * ca + sum_a;
-        l_b = l_b * cb + sum_b;
-#pragma unroll
-        for (int i = 0; i < D / 8; ++i) { o[i][0] *= ca; o[i][1] *= ca; o[i][2] *= cb; o[i][3] *= cb; }
-        pv_product<D, TK, TK / 16>(o, pf, sv, 0);
-        __syncwarp();
-        if (lane == 0) cx_mbar_arrive(empty0 + 8 * st);          // this warp is done with the stage
-    }
-    if (gave_up && a.status) atomicCAS(a.status, 0, 6);
-    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
-    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-    const float ia = 1.0f / l_a, ib = 1.0f / l_b;
-    __nv_bfloat16* oa = live_a ? a.out + ((size_t)(q0 + pra / G) * a.nh + g * G + pra % G) * D : nullptr;
-    __nv_bfloat16* ob = live_b ? a.out + ((size_t)(q0 + prb / G) * a.nh + g * G + prb % G) * D : nullptr;
-#pragma unroll
-    for (int nd = 0; nd < D / 8; ++nd) {
-        const int col = nd * 8 + (lane & 3) * 2;
-        if (live_a) *reinterpret_cast<uint32_t*>(oa + col) = pack_bf16(o[nd][0] * ia, o[nd][1] * ia);
-        if (live_b) *reinterpret_cast<uint32_t*>(ob + col) = pack_bf16(o[nd][2] * ib, o[nd][3] * ib);
-    }
-}
-
 // ---------------------------------------------------------------- launchers
 template <int D>
 static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStream_t s) {
@@ -645,8 +485,7 @@ static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStrea
 }
 
 // ------------------------------------------------- prefill on tcgen05
-// The same work as attention_prefill_kernel for head sizes 64 and 128, on the fifth-generation tensor
-// cores.  A CTA owns 128 packed rows (token x head in group) of one kv head and walks the keys in tiles
+// Attention for prompt portions, head sizes 64 and 128, on the fifth-generation tensor cores.  A CTA owns 128 packed rows (token x head in group) of one kv head and walks the keys in tiles
 // of 64:
 //   S = Q K^T      tcgen05.mma, Q and K from shared memory (K-major, 128-byte swizzle: the cache's
 //                  planes are that layout already), S (128 x 64 float) in tensor memory, two buffers;
@@ -1080,28 +919,6 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
 }
 }  // namespace tc
 
-template <int D, int TK, int STAGES, int MINB>
-static int launch_prefill_variant(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
-    const size_t smem = (size_t)STAGES * 2 * TK * D * 2 + BM * D * 2 + 2 * STAGES * 8 + 64;     // tiles, Q, barriers
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D, TK, STAGES, MINB>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    dim3 grid(n_tiles, a.nkv);
-    vcb_launch(attention_prefill_kernel<D, TK, STAGES, MINB>, grid, BLOCK_THREADS, smem, s, a);
-    return vcb_last_error();
-}
-
-// 32-key tiles in a ring of four stages, two CTAs per SM: the best of the shapes tried
-// (64-key tiles with two or three stages, 32-key tiles with three CTAs per SM were within 2 %).
-template <int D>
-static int launch_prefill(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
-    return launch_prefill_variant<D, 32, 4, 2>(a, n_tiles, s);
-}
-
 template <int D>
 static int launch_prefill_tc(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
     static bool configured = false;
@@ -1142,23 +959,9 @@ VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* 
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
 
-VCB_EXPORT int vcb_attention_prefill_mma(const void* q, const void* cache, void* out, const int* q_start,
-                                         const int* ctx_lens, const int* block_table, int bt_stride,
-                                         const int* tile_req, const int* tile_row0, int n_tiles, int nh,
-                                         int nkv, int d, int page, int window, float scale, int* status,
-                                         void* stream) {
-    if (n_tiles <= 0) return 0;
-    int c = check_common(nh, nkv, d, page, window);
-    if (c) return c;
-    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
-                  window, scale};
-    cudaStream_t s = (cudaStream_t)stream;
-    return d == 64 ? launch_prefill<64>(a, n_tiles, s) : launch_prefill<128>(a, n_tiles, s);
-}
-
-// The same on tcgen05 tensor cores (head sizes 64 and 128, pages of a multiple of 8 tokens); tiles
-// (tile_req, tile_row0) of 128 packed rows.
+// Prompt portions (and, in mixed batches, single tokens) on tcgen05 tensor cores: head sizes 64 and 128,
+// pages of a multiple of 8 tokens; tiles (tile_req, tile_row0) of 128 packed rows, row = token * G + head
+// in group.
 VCB_EXPORT int vcb_attention_prefill_tc(const void* q, const void* cache, void* out, const int* q_start,
                                         const int* ctx_lens, const int* block_table, int bt_stride,
                                         const int* tile_req, const int* tile_row0, int n_tiles, int nh,

@@ -35,7 +35,6 @@ _SIGNATURES = {
     "vcb_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
-    "vcb_attention_prefill_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "vcb_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
     "vcb_gemm_bf16_tcgen05_fused": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P,
@@ -251,23 +250,6 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
         None if split_tiles is None else _dev(split_tiles, "split_tiles", torch.int32),
         num_heads, num_kv_heads, head_dim, page_size, window, float(scale),
         status_tensor(q.device).data_ptr(), _stream()), "attention_decode_mma")
-
-
-def attention_prefill_mma(q, cache, out, q_start, ctx_lens, block_table, tile_req, tile_row0, *,
-                          num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
-                          scale: float) -> None:
-    """Tensor-core attention for portions of any length; tiles of 64 packed rows (bfloat16)."""
-    _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
-          "attention_prefill_mma is a bfloat16 kernel")
-    _need(head_dim in MMA_HEAD_DIMS, f"attention_prefill_mma takes head sizes {MMA_HEAD_DIMS}, got {head_dim}")
-    n_tiles = tile_req.numel()
-    _need(tile_row0.numel() == n_tiles, "one first row per tile")
-    _check(lib().vcb_attention_prefill_mma(
-        _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
-        _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
-        block_table.shape[1], _dev(tile_req, "tile_req", torch.int32), _dev(tile_row0, "tile_row0", torch.int32),
-        n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale),
-        status_tensor(q.device).data_ptr(), _stream()), "attention_prefill_mma")
 
 
 TC_ATTENTION_HEAD_DIMS = (64, 128)      # head sizes of the tcgen05 prefill attention kernel

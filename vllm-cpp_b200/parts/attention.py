@@ -112,22 +112,16 @@ class PagedAttention(Mixer):
         ws.release(mark)
 
     # -- work lists and kernel choice
-    TILE_ROWS = 64           # packed rows (token x head in group) per CTA of the prefill kernel
     SM_COUNT = 148
 
     def _tensor_core_path(self) -> bool:
         return self.dtype == torch.bfloat16 and self.d in ops.MMA_HEAD_DIMS
 
-    def _prefill_on_tcgen05(self, page_size: int) -> bool:
-        return self.d in ops.TC_ATTENTION_HEAD_DIMS and page_size % 8 == 0
-
-    def _tile_rows(self, page_size: int) -> int:
-        return ops.TC_ATTENTION_TILE_ROWS if self._prefill_on_tcgen05(page_size) else self.TILE_ROWS
 
     def step_arrays(self):
         """What the kernels need per step beyond the common arrays, built on the host from the step's
         lengths.  The prefill kernel's work list: for every request that brings tokens, its tiles of
-        packed rows (128 for the tcgen05 kernel, TILE_ROWS for the mma.sync one), as [2, n_tiles] =
+        packed rows (token x head in group, ops.TC_ATTENTION_TILE_ROWS of them), as [2, n_tiles] =
         (request index, first row).  The decode kernel's split length: see ``splits`` below."""
         if not self._tensor_core_path():
             return {}
@@ -136,7 +130,7 @@ class PagedAttention(Mixer):
         def tiles(host):
             if all(q == 1 for q in host.q_lens):
                 return np.zeros((2, 0), dtype=np.int32)         # decode-only steps use the split-KV kernel
-            rows = self._tile_rows(host.page_size)
+            rows = ops.TC_ATTENTION_TILE_ROWS
             req, row0, keys = [], [], []
             for r, (q, ctx) in enumerate(zip(host.q_lens, host.ctx_lens)):
                 for k in range(-(-q * group // rows)):
@@ -179,7 +173,7 @@ class PagedAttention(Mixer):
             host.shapes[self._splits_key()] = next(g for g in self.SPLIT_GRIDS if g >= need)
             return np.array([per], dtype=np.int32)
 
-        return {f"attn_tiles_g{group}_d{self.d}": tiles, self._splits_key(): splits}
+        return {f"attn_tiles_g{group}": tiles, self._splits_key(): splits}
 
     SPLIT_GRIDS = (1, 2, 3, 4, 5, 6, 8, 10, 12, 16, 20, 24, 32)
 
@@ -217,9 +211,8 @@ class PagedAttention(Mixer):
                 ops.attention_decode_mma(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, None,
                                          step.n_reqs, nsplit, part_o, part_ml, counters, split_tiles=split_tiles, **kw)
             else:
-                tiles = step.extras[f"attn_tiles_g{self.nh // self.nkv}_d{self.d}"]
-                kernel = ops.attention_prefill_tc if self._prefill_on_tcgen05(cache.page_size) else ops.attention_prefill_mma
-                kernel(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, tiles[0], tiles[1], **kw)
+                tiles = step.extras[f"attn_tiles_g{self.nh // self.nkv}"]
+                ops.attention_prefill_tc(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, tiles[0], tiles[1], **kw)
             return
         ops.attention_simt(q, cache.pages, attn, step.positions, step.req_of_token, block_table,
                            num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d,
