@@ -77,15 +77,6 @@ def lib():
     return _lib
 
 
-def register_signature(name: str, sig) -> None:
-    """Declare one more exported launcher (used by kernel files added later)."""
-    _SIGNATURES[name] = sig
-    if _lib is not None:
-        fn = getattr(_lib, name)
-        fn.argtypes = sig
-        fn.restype = _I
-
-
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
