@@ -237,6 +237,3 @@ class CacheManager:
     def num_free_pages(self) -> int:
         """Free pages of the scarcest group."""
         return min((g.pool.num_free for g in self.paged), default=self.num_pages)
-
-    def max_blocks_per_request(self, max_len: int) -> int:
-        return cdiv(max_len, self.page_size)
