@@ -3,25 +3,33 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
-Prints one JSON line.  ``value`` is decoded tokens per second at batch 8 with
-contexts ending at 4,096 tokens, timed on the device with CUDA events around K
-decode steps of the engine's step function (random bfloat16 weights, random token
-ids, synthetic cache contents).  ``e2e`` is the same through the Python entry
-point's engine: every step copies its inputs from pinned host memory to the
-device and reads the sampled token ids back.  ``prefill`` times one 2,048-token
-prompt in one step; ``points`` holds decode at batch 1 and 64; ``roofline`` sets
-the decode step's bytes (every weight once, plus the cache of the live requests)
-against the memory bandwidth.  A decode step reads about 15 GB, far more than the
-126 MB of L2, so consecutive steps cannot serve each other from cache.
+Prints one JSON line.  ``value`` is decoded tokens per second at batch 8 while the contexts grow
+from 2,048 to 4,096 tokens: the K timed steps are taken in up to four runs of consecutive steps
+placed evenly along that growth (the first run starts at 2,048 tokens, the last ends at 4,096), on
+the device with CUDA events around the engine's step function (random bfloat16 weights, random
+token ids, synthetic cache contents); ``points`` holds the two ends and the same mean at batch 1
+and 64.  ``e2e`` is the same through the Python entry point's engine: requests with prompts of
+2,048 tokens generate up to 4,096, every step copies its inputs from pinned host memory to the
+device and reads the sampled token ids back, and the same runs of steps are timed by the wall
+clock.  ``prefill`` times one 2,048-token prompt in one step; ``roofline`` sets the decode steps'
+bytes (every weight once, plus the cache of the live requests) against the memory bandwidth.  A
+decode step reads about 15 GB, far more than the 126 MB of L2, so consecutive steps cannot serve
+each other from cache.
+
+``--impl reference`` runs the unmodified jiamumuzhao/vllm-cpp (built by baseline/build_reference.py
+into baseline/_ref) on the same configuration and the same runs of steps, through its own model
+interface as its engine drives it: one forward per token and sequence (baseline/ref_driver.cpp).
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import shutil
 import statistics
 import subprocess
 import sys
+import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -42,10 +50,12 @@ SIZES = {
     "32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
                 intermediate_size=27648, rms_norm_eps=1e-6),
 }
-CONTEXT = 4096
+CONTEXT_START = 2048          # the contexts of the decode measurement grow from here ...
+CONTEXT = 4096                # ... to here
+SLACK = 64                    # room beyond CONTEXT: requests that began a few steps earlier than others pass it
 PREFILL_TOKENS = 2048
 METRIC = "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen2.5-7B bf16)"
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
 def load_peaks():
@@ -54,55 +64,86 @@ def load_peaks():
         try:
             with open(path) as f:
                 p = json.load(f)
-            hbm = float(p.get("hbm_gbs"))
-            tf = float(p.get("bf16_tflops_sustained") or p.get("bf16_tflops"))
-            return {"hbm_gbs": hbm, "bf16_tflops": tf, "source": "measured"}
+            burst = float(p.get("bf16_tflops"))
+            return {"hbm_gbs": float(p.get("hbm_gbs")), "bf16_tflops": burst,
+                    "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained") or burst), "source": "measured"}
         except (ValueError, TypeError, json.JSONDecodeError):
             pass
     return dict(FALLBACK_PEAKS, source="fallback")
 
 
+def decode_runs(steps: int):
+    """[(context at the run's first step, steps)]: ``steps`` timed decode steps in up to four runs of
+    consecutive steps placed evenly along the growth of the contexts from CONTEXT_START to CONTEXT; the
+    last run ends with the contexts at CONTEXT."""
+    n = 4 if steps >= 8 else 2 if steps >= 2 else 1
+    sizes = [steps // n + (1 if i < steps % n else 0) for i in range(n)]
+    if n == 1:
+        return [(CONTEXT - sizes[0], sizes[0])]
+    last = CONTEXT - sizes[-1]
+    return [(CONTEXT_START + round(i * (last - CONTEXT_START) / (n - 1)), k) for i, k in enumerate(sizes)]
+
+
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    """Samples SM clocks and throttle reasons with nvidia-smi while the measurements run; ``mark`` names the
+    stretch of time that follows, so that every sample can be laid to the measurement it fell into."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self):
         self.proc = None
+        self.marks = []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
+    def mark(self, name):
+        self.marks.append((time.time(), name))
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.mark(None)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        mhz, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        by_region, mx, reasons = {}, None, {}
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 6:
+            if len(f) < 7:
                 continue
             try:
-                mhz.append(float(f[0]))
-                mx = float(f[1])
+                stamp = time.mktime(time.strptime(f[0][:19], "%Y/%m/%d %H:%M:%S")) + float("0" + f[0][19:])
+                mhz, mx = float(f[1]), float(f[2])
             except ValueError:
                 continue
-            for n, v in zip(names, f[2:6]):
+            region = None
+            for t, name in self.marks:
+                if stamp >= t:
+                    region = name
+            if region is None:
+                continue
+            by_region.setdefault(region, []).append(mhz)
+            for n, v in zip(self.NAMES, f[3:7]):
                 if v.lower().startswith("active"):
-                    reasons.add(n)
-        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx,
-                "reasons": sorted(reasons), "samples": len(mhz)}
+                    reasons.setdefault(region, set()).add(n)
+        decode = [m for r, v in by_region.items() if r != "prefill" for m in v]
+        info = {"sm_mhz": statistics.median(decode) if decode else None, "sm_max_mhz": mx,
+                "reasons": sorted(set().union(*[v for r, v in reasons.items() if r != "prefill"])) if reasons else [],
+                "samples": len(decode)}
+        if by_region.get("prefill"):
+            info["prefill_sm_mhz"] = statistics.median(by_region["prefill"])
+            info["prefill_reasons"] = sorted(reasons.get("prefill", ()))
+        return info
 
 
 def write_timeline(path, batch, runner, cache, rng, vocab):
@@ -150,7 +191,8 @@ def write_timeline(path, batch, runner, cache, rng, vocab):
 
 def run_mix(cfg, a) -> int:
     """Continuous batching through the engine's own API: requests of mixed lengths arrive at once, prompts
-    are read in portions of at most 2,048 tokens a step beside the tokens other requests decode."""
+    are read in portions of at most 2,048 tokens a step beside the tokens other requests decode.  Also
+    prints where a step's time goes (the engine's per-phase timers)."""
     import numpy as np
     import torch
     from vllm_cpp_b200 import EngineConfig, SamplingParams
@@ -161,7 +203,7 @@ def run_mix(cfg, a) -> int:
     pages = int(sum(-(-(int(n) + gen) // 16) for n in lens)) + 64
     ecfg = EngineConfig(load_format="random", model_config=cfg, seed=0, dtype="bfloat16", block_size=16,
                         num_gpu_blocks=pages, max_num_seqs=n_req, max_model_len=4096 + gen,
-                        max_num_batched_tokens=budget, max_tokens_per_step=budget)
+                        max_num_batched_tokens=budget, max_tokens_per_step=budget, time_phases=True)
     engine = Engine(ecfg)
     sp = SamplingParams(max_tokens=gen, temperature=0.0, ignore_eos=True)
 
@@ -170,19 +212,23 @@ def run_mix(cfg, a) -> int:
             engine.add_request(rng.integers(0, cfg["vocab_size"], size=int(n)).tolist(), sp)
         torch.cuda.synchronize()
         t, steps, out = time.perf_counter(), 0, 0
+        phases = {}
         while engine.has_pending_work():
             out += len(engine.step())
             steps += 1
+            for k, v in engine.last_stats.phase_ms.items():
+                phases[k] = phases.get(k, 0.0) + v
         torch.cuda.synchronize()
-        return time.perf_counter() - t, steps, out
+        return time.perf_counter() - t, steps, out, phases
 
     run()                                             # warm-up: sizes workspaces, captures graphs
-    dt, steps, out = run()
+    dt, steps, out, phases = run()
     prompt = int(lens.sum())
     print(json.dumps({"metric": "continuous batching: 32 requests, prompts 128-4096, 256 generated each, 2048 tokens a step",
                       "value": round(out / dt, 1), "unit": "generated tokens/s", "seconds": round(dt, 3), "steps": steps,
                       "prompt_tokens": prompt, "generated_tokens": out,
                       "all_tokens_per_s": round((prompt + out) / dt, 1), "preemptions": engine.scheduler.num_preemptions,
+                      "phase_ms_per_step": {k: round(v / steps, 4) for k, v in sorted(phases.items())},
                       "config": {"model": f"Qwen2.5-{a.size.upper()} layer sizes", "layers": cfg["num_hidden_layers"]}}))
     return 0
 
@@ -196,6 +242,123 @@ def model_numbers(cfg):
             "kv_bytes_per_token": layers * 2 * nkv * d * 2, "d": d}
 
 
+def flat_config(cfg, a, nums, extra):
+    out = {"model": f"Qwen2.5-{a.size.upper()} layer sizes", "layers": cfg["num_hidden_layers"],
+           "layers_of_configuration": SIZES[a.size]["num_hidden_layers"], "hidden": cfg["hidden_size"],
+           "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": nums["d"],
+           "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": a.batch,
+           "seq_len": CONTEXT, "decode_contexts": f"{CONTEXT_START} growing to {CONTEXT}", "kv_block": 16,
+           "parallelism": "single GPU"}
+    out.update(extra)
+    return out
+
+
+# ------------------------------------------------------------------------------------------ reference arm
+REFERENCE_NOTES = ("the reference's own faults at these sizes, none of which changes the work of a step: an untied lm_head is "
+                   "copied over the embedding table (src/model/qwen.cpp:279-281); the bias area of 3*1024 floats a layer "
+                   "(qwen.cpp:67,113-114,179-181) is overrun by 7B's 4,608 and the surplus lands, inside the same pool, on "
+                   "layer 0's rotation table below position 336")
+
+
+def unavailable(why: str) -> int:
+    print(json.dumps({"impl": "reference", "unavailable": " ".join(str(why).split())[:600]}))
+    return 0
+
+
+def run_reference(cfg, a) -> int:
+    """The reference's own speed on the same configuration: write the model folder, run baseline/_ref/ref_driver."""
+    if a.gpus != 1:
+        return unavailable("jiamumuzhao/vllm-cpp has no multi-GPU path")
+    try:
+        from baseline.build_reference import driver_env, driver_path
+        driver = driver_path()
+    except Exception as e:                                # the build's own message is the reason
+        return unavailable(f"the reference could not be built here: {e}")
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device")
+        from vllm_cpp_b200.weights.random_init import write_random_model
+    except Exception as e:
+        return unavailable(f"cannot prepare the model folder: {e}")
+    nums = model_numbers(cfg)
+    params = nums["matrix_params"] + cfg["vocab_size"] * cfg["hidden_size"]          # with the embedding table
+    need_file = params * 2 + (64 << 20)
+    # the reference's loader keeps every tensor as host float32 (src/model/model_loader.cpp:61,100) beside the file
+    need_ram = params * 4 + need_file + (8 << 30)
+    with open("/proc/meminfo") as f:
+        avail = next(int(l.split()[1]) * 1024 for l in f if l.startswith("MemAvailable"))
+    where = next((d for d in ("/dev/shm", tempfile.gettempdir()) if os.path.isdir(d)
+                  and shutil.disk_usage(d).free > need_file + (4 << 30)), None)
+    if where is None:
+        return unavailable(f"no room for the {need_file >> 30} GB model folder in /dev/shm or the temporary folder")
+    if avail < need_ram:
+        return unavailable(f"the reference's loader needs about {need_ram >> 30} GB of host memory "
+                           f"(float32 copies of all tensors), {avail >> 30} GB are available")
+    runs = decode_runs(max(1, a.steps))
+    per_run = min(k for _, k in runs)
+    runs = [(c, per_run) for c, _ in runs]                # the driver takes one length for all runs
+    warm = max(3, a.warmup)
+    folder = tempfile.mkdtemp(prefix="vcb_ref_model_", dir=where)
+    try:
+        t0 = time.time()
+        write_random_model(folder, cfg, seed=0, dtype="bfloat16", device="cuda")
+        torch.cuda.empty_cache()
+        write_s = time.time() - t0
+        print(f"[bench] model folder written in {write_s:.0f} s", file=sys.stderr, flush=True)
+        # batch 64 is left out unless asked for: one forward of the reference at these contexts takes a
+        # good part of a second, and a step of 64 sequences is 64 of them
+        batches = [a.batch] + ([] if a.skip_points else [b for b in ((1, 64) if a.reference_b64 else (1,)) if b != a.batch])
+        cmd = [driver, "bench", "--model", folder, "--batches", ",".join(map(str, batches)),
+               "--contexts", ",".join(str(c) for c, _ in runs), "--steps-per-context", str(per_run),
+               "--warmup", str(warm), "--prefill", str(PREFILL_TOKENS), "--max-model-len", str(CONTEXT + 16),
+               "--block-size", "16", "--budget-s", str(a.reference_budget_s)]
+        p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=None, text=True, env=driver_env())
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    lines = [l for l in p.stdout.strip().splitlines() if l.startswith("{")]
+    if p.returncode != 0 or not lines:
+        tail = p.stdout.strip().splitlines()[-3:]
+        return unavailable(f"the reference's run ended with code {p.returncode}: {' | '.join(tail)}")
+    res = json.loads(lines[-1])
+    if "error" in res:
+        return unavailable(f"the reference's run stopped: {res['error']}")
+    by_batch = {r["batch"]: r["decode"] for r in res["runs"]}
+    main = by_batch[a.batch]
+    steps = per_run * len(main)
+    ms = sum(d["device_ms_per_step"] for d in main) / len(main)
+    e2e_ms = sum(d["e2e_ms_per_step"] for d in main) / len(main)
+    points = {f"decode_b{a.batch}_ctx{main[0]['context']}": round(a.batch / (main[0]["device_ms_per_step"] * 1e-3), 2),
+              f"decode_b{a.batch}_ctx{main[-1]['context'] + per_run}": round(a.batch / (main[-1]["device_ms_per_step"] * 1e-3), 2)}
+    for b, dec in by_batch.items():
+        if b != a.batch:
+            points[f"decode_b{b}"] = round(b / (sum(d["device_ms_per_step"] for d in dec) / len(dec) * 1e-3), 2)
+    blocks = res["blocks_per_seq"]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(a.batch / (ms * 1e-3), 2), "unit": "tokens/s", "n_gpus": 1,
+        "steps": steps, "warmup": warm, "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16 operands, fp32 accumulation, activations and cache (the reference's only mode)",
+        "data": "synthetic: the same random weights N(0,0.02) as the other arm, written as a bfloat16 model folder; random token ids",
+        "config": flat_config(cfg, a, nums, {
+            "how": "QwenModel::forward, one call per token and sequence, as Engine::decode and Engine::prefill call it",
+            "cache": "zeros as the reference's pool is cleared to, plus what the steps write",
+            "load_s": res["load_s"], "write_model_s": round(write_s, 1), "notes": REFERENCE_NOTES}),
+        "e2e": {"value": round(a.batch / (e2e_ms * 1e-3), 2), "unit": "tokens/s",
+                # per sequence: the token id, and per layer the block table and the context length; the logits back
+                "h2d_bytes_per_step": a.batch * (4 + res["layers"] * 4 * (blocks + 1)),
+                "d2h_bytes_per_step": a.batch * 4 * res["vocab"]},
+        "gpu_launches": None,
+        "prefill": ({"value": round(res["prefill"]["tokens"] / (res["prefill"]["ms"] * 1e-3), 1), "tokens": res["prefill"]["tokens"],
+                     "ms": round(res["prefill"]["ms"], 1), "how": "one forward per token",
+                     # a prompt cut short by the time budget is not the 2,048-token prompt of the metric
+                     "same_config": res["prefill"]["tokens"] == PREFILL_TOKENS} if res["prefill"]["tokens"] else None),
+        "points": points, "seconds": res["seconds"],
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------ our arm
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -220,13 +383,18 @@ def main() -> int:
                          "start and end as CUPTI reports them through torch.profiler) to FILE as text")
     ap.add_argument("--no-cuda-graphs", action="store_true",
                     help="launch every kernel of a decode step directly (for a profiler's launch list)")
+    ap.add_argument("--utilization", type=int, default=0, metavar="PERCENT",
+                    help="let the engine size its own cache from this share of the device's memory "
+                         "(gpu_memory_utilization) instead of a fixed number of pages")
+    ap.add_argument("--reference-budget-s", type=float, default=1300.0,
+                    help="--impl reference: begin no further measurement after this many seconds")
+    ap.add_argument("--reference-b64", action="store_true", help="--impl reference: measure batch 64 too (many minutes)")
     a = ap.parse_args()
+    cfg = dict(QWEN25_7B, **SIZES[a.size])
+    if a.size == "7b" or a.layers != QWEN25_7B["num_hidden_layers"]:
+        cfg["num_hidden_layers"] = a.layers
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "jiamumuzhao/vllm-cpp is a CMake C++ project with no setup.py or pyproject.toml, so the "
-                          "offline pip install refuses it; its engine also forwards one token per call and "
-                          "overwrites the embedding with an untied lm_head, so it cannot run this 7B workload"}))
-        return 0
+        return run_reference(cfg, a)
     if a.gpus != 1:
         print(f"bench.py measures one GPU (N=1); this engine has no multi-GPU path, --gpus {a.gpus} is not run")
         return 2
@@ -242,17 +410,15 @@ def main() -> int:
         ops.set_pdl(False)
     if a.library_gemm:
         ops.set_tcgen05_linear(False)
-    cfg = dict(QWEN25_7B, **SIZES[a.size])
-    if a.size == "7b" or a.layers != QWEN25_7B["num_hidden_layers"]:
-        cfg["num_hidden_layers"] = a.layers
     if a.mix:
         return run_mix(cfg, a)
     nums = model_numbers(cfg)
     peaks = load_peaks()
     max_batch = max(64, a.batch)
-    pages = max_batch * (CONTEXT // 16 + 2) + PREFILL_TOKENS // 16 + 16
+    pages = max_batch * ((CONTEXT + SLACK) // 16 + 1) + PREFILL_TOKENS // 16 + 16
     ecfg = EngineConfig(load_format="random", model_config=cfg, seed=0, dtype="bfloat16", block_size=16,
-                        num_gpu_blocks=pages, max_num_seqs=max_batch, max_model_len=CONTEXT + 16,
+                        num_gpu_blocks=None if a.utilization else pages,
+                        gpu_memory_utilization=a.utilization or 90, max_num_seqs=max_batch, max_model_len=CONTEXT + SLACK,
                         max_num_batched_tokens=PREFILL_TOKENS, max_tokens_per_step=PREFILL_TOKENS,
                         use_cuda_graphs=not a.no_cuda_graphs)
     t0 = time.time()
@@ -265,42 +431,60 @@ def main() -> int:
         g.pages.normal_(0.0, 0.5, generator=gen)
     vocab = cfg["vocab_size"]
     rng = __import__("numpy").random.default_rng(0)
+    runs = decode_runs(steps)
 
-    def time_decode(batch, n_steps, n_warm):
-        """Device time of n_steps decode steps at ``batch`` requests whose contexts end at CONTEXT."""
-        start_ctx = CONTEXT - n_steps - n_warm
-        ids = [f"d{batch}_{i}" for i in range(batch)]
-        for r in ids:
-            cache.add_request(r)
-            cache.reserve(r, start_ctx)
-            cache.commit(r, start_ctx)
-        toks = rng.integers(0, vocab, size=(n_steps + n_warm, batch))
+    def time_decode(batch, n_warm):
+        """Device time of the timed runs of decode steps at ``batch`` requests: [(context, steps, ms)], launches."""
         temperature = torch.zeros(batch, device="cuda")
         uniform = torch.zeros(batch, device="cuda")
         out = torch.empty(batch, dtype=torch.int32, device="cuda")
+        results, launches = [], 0
+        for ctx0, k in runs:
+            toks = rng.integers(0, vocab, size=(max(k, n_warm), batch))
 
-        def one(k):
-            logits = runner.step([StepEntry(r, [int(toks[k, i])], [0]) for i, r in enumerate(ids)])
-            ops.sample(logits, temperature, uniform, out)
+            def requests(tag):                  # requests whose caches hold ctx0 tokens (synthetic contents)
+                ids = [f"d{batch}_{ctx0}_{tag}{i}" for i in range(batch)]
+                for r in ids:
+                    cache.add_request(r)
+                    cache.reserve(r, ctx0)
+                    cache.commit(r, ctx0)
+                return ids
 
-        for k in range(n_warm):
-            one(k)
-        torch.cuda.synchronize()
-        launches0 = ops.launch_count()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.nvtx.range_push("timed_decode")
-        e0.record()
-        for k in range(n_warm, n_warm + n_steps):
-            one(k)
-        e1.record()
-        torch.cuda.synchronize()
-        torch.cuda.nvtx.range_pop()
-        ms = e0.elapsed_time(e1) / n_steps
-        launches = ops.launch_count() - launches0
-        kv_bytes = batch * (CONTEXT - n_steps / 2) * nums["kv_bytes_per_token"]
-        for r in ids:
-            cache.free_request(r)
-        return ms, launches, kv_bytes
+            def one(ids, j):
+                logits = runner.step([StepEntry(r, [int(toks[j, i])], [0]) for i, r in enumerate(ids)])
+                ops.sample(logits, temperature, uniform, out)
+
+            # warm-up: the run itself once over, with requests of its own, so that the timed steps find
+            # their launch shapes captured (a step whose longest context enters a new power-of-two bucket,
+            # as 2,048 -> 2,049 does, is otherwise launched directly once and captured once)
+            ids = requests("w")
+            for j in range(max(k, n_warm)):
+                one(ids, j)
+            for r in ids:
+                cache.free_request(r)
+            ids = requests("t")
+            torch.cuda.synchronize()
+            before = ops.launch_count()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.nvtx.range_push("timed_decode")
+            e0.record()
+            for j in range(k):
+                one(ids, j)
+            e1.record()
+            torch.cuda.synchronize()
+            torch.cuda.nvtx.range_pop()
+            results.append((ctx0, k, e0.elapsed_time(e1)))
+            launches += ops.launch_count() - before
+            for r in ids:
+                cache.free_request(r)
+        return results, launches
+
+    def summary(batch, results):
+        """tokens/s over all runs, ms per step, bytes the steps had to read."""
+        total_ms = sum(ms for _, _, ms in results)
+        n = sum(k for _, k, _ in results)
+        kv = sum(batch * (c + (k - 1) / 2 + 1) * nums["kv_bytes_per_token"] * k for c, k, _ in results)
+        return batch * n / (total_ms * 1e-3), total_ms / n, nums["matrix_params"] * 2 * n + kv
 
     def time_prefill(reps, n_warm):
         times = []
@@ -322,35 +506,35 @@ def main() -> int:
                 times.append(e0.elapsed_time(e1))
         return statistics.median(times)
 
-    def time_e2e(batch, n_steps, n_warm):
-        """Wall time of engine.step() in steady decode: pinned inputs in, sampled ids out, every step.
-        Prompts are fed first (in portions, some requests already decoding beside them); the timed
-        steps start when every request decodes, and end before the first one finishes."""
-        portions = -(-CONTEXT // PREFILL_TOKENS)
-        slack = batch * portions + 2
-        n_warm = max(n_warm, 64)        # the prompts' steps leave reduced clocks behind: decode until they are back
-        budget = n_steps + n_warm + slack
-        prompt_len = CONTEXT - budget
-        sp = SamplingParams(max_tokens=budget, temperature=0.0, ignore_eos=True)
+    def time_e2e(batch):
+        """Wall time of engine.step() over the same runs of steps: requests with prompts just short of
+        CONTEXT_START tokens generate until their contexts reach CONTEXT; pinned inputs in, sampled ids out, every
+        step.  A run is timed between two synchronisations; the steps between the runs are not timed."""
+        lead = 64                               # steps before the first run: the prompts' steps leave reduced clocks behind
+        prompt_len = CONTEXT_START - lead
+        sp = SamplingParams(max_tokens=CONTEXT + SLACK - prompt_len, temperature=0.0, ignore_eos=True)
         ids = [engine.add_request(rng.integers(0, vocab, size=prompt_len).tolist(), sp) for _ in range(batch)]
         seqs = [engine.sequences[i] for i in ids]
         while engine.scheduler.waiting or any(s.remaining > 1 or s.output_len == 0 for s in seqs):
             engine.step()
-        for _ in range(n_warm):
-            engine.step()
-        assert all(s.output_len + n_steps <= budget for s in seqs) and len(engine.scheduler.running) == batch
-        torch.cuda.synchronize()
-        t = time.perf_counter()
-        produced = 0
-        for _ in range(n_steps):
-            produced += len(engine.step())
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - t
-        assert produced == batch * n_steps
+        produced, seconds = 0, 0.0
+        for ctx0, k in runs:
+            while min(s.num_processed_tokens for s in seqs) < ctx0:
+                engine.step()
+            assert len(engine.scheduler.running) == batch
+            torch.cuda.synchronize()
+            t = time.perf_counter()
+            got = 0
+            for _ in range(k):
+                got += len(engine.step())
+            torch.cuda.synchronize()
+            seconds += time.perf_counter() - t
+            assert got == batch * k, (got, batch, k)
+            produced += got
         h2d = int(runner.last_meta_bytes) + 4 * 4 * batch        # step metadata + four floats of sampling options a row
         for i in ids:
             engine.abort_request(i)
-        return produced / dt, h2d, 4 * batch
+        return produced / seconds, h2d, 4 * batch
 
     if a.only == "prefill":
         ms = time_prefill(max(1, min(steps, 3)), 2)
@@ -359,51 +543,53 @@ def main() -> int:
         return 0
     clocks = ClockSampler()
     clocks.start()
-    ms, launches, kv_bytes = time_decode(a.batch, steps, warmup)
-    clock_info = clocks.stop()
-    if a.only == "decode" and a.timeline:
-        write_timeline(a.timeline, a.batch, runner, cache, rng, vocab)
+    clocks.mark("decode")
+    results, launches = time_decode(a.batch, warmup)
+    value, ms, step_bytes = summary(a.batch, results)
     if a.only == "decode":
+        clock_info = clocks.stop()
+        if a.timeline:
+            write_timeline(a.timeline, a.batch, runner, cache, rng, vocab)
         print(json.dumps({"metric": METRIC, "only": "decode", "batch": a.batch, "ms_per_step": round(ms, 4),
-                          "value": round(a.batch / (ms * 1e-3), 1), "unit": "tokens/s", "gpu_launches": launches,
+                          "value": round(value, 1), "unit": "tokens/s", "gpu_launches": launches,
+                          "runs": [[c, k, round(t / k, 4)] for c, k, t in results],
                           "cuda_graphs": not a.no_cuda_graphs, "clocks": clock_info}))
         return 0
-
-    weight_bytes = nums["matrix_params"] * 2
-    step_bytes = weight_bytes + kv_bytes
-    achieved = step_bytes / (ms * 1e-3) / 1e9
-    value = a.batch / (ms * 1e-3)
+    n_timed = sum(k for _, k, _ in results)
+    achieved = step_bytes / (ms * n_timed * 1e-3) / 1e9
 
     # The decode figures first, the prefill last: the prefill steps run at the power limit, and what is
-    # measured right after them runs at the reduced clocks they leave behind for a while (batch 1 read
-    # 3.15-3.26 ms a step after them against 3.08 ms before).
-    points = {}
+    # measured right after them runs at the reduced clocks they leave behind for a while.
+    (c_first, k_first, t_first), (c_last, k_last, t_last) = results[0], results[-1]
+    points = {f"decode_b{a.batch}_ctx{c_first}": round(a.batch * k_first / (t_first * 1e-3), 1),
+              f"decode_b{a.batch}_ctx{c_last + k_last}": round(a.batch * k_last / (t_last * 1e-3), 1)}
     if not a.skip_points:
         for b in (1, 64):
-            pms, _, _ = time_decode(b, max(8, steps // 2), 3)
-            points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
-    e2e_value, h2d, d2h = time_e2e(a.batch, steps, warmup)
-
+            if b != a.batch:
+                res_b, _ = time_decode(b, 3)
+                points[f"decode_b{b}"] = round(summary(b, res_b)[0], 1)
+    clocks.mark("e2e")
+    e2e_value, h2d, d2h = time_e2e(a.batch)
+    clocks.mark("prefill")
     prefill_ms = time_prefill(3, 2)
+    clock_info = clocks.stop()
     t = PREFILL_TOKENS
     flops = 2.0 * (nums["matrix_params"] - vocab * cfg["hidden_size"]) * t + 2.0 * vocab * cfg["hidden_size"] \
         + cfg["num_hidden_layers"] * 4.0 * cfg["num_attention_heads"] * nums["d"] * (t * (t + 1) / 2)
+    tflops = flops / (prefill_ms * 1e-3) / 1e12
     prefill = {"value": round(t / (prefill_ms * 1e-3), 1), "tokens": t, "ms": round(prefill_ms, 3),
-               "frac": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
-               "tflops": round(flops / (prefill_ms * 1e-3) / 1e12, 1)}
+               # one step timed alone between synchronisations: the burst peak is its denominator
+               "frac": round(tflops / peaks["bf16_tflops"], 4),
+               "frac_of_sustained_peak": round(tflops / peaks["bf16_tflops_sustained"], 4), "tflops": round(tflops, 1)}
 
     line = {
-        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": n_timed,
         "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids",
-        "config": {"model": f"Qwen2.5-{a.size.upper()} layer sizes", "layers": cfg["num_hidden_layers"],
-                   "layers_of_configuration": SIZES[a.size]["num_hidden_layers"], "hidden": cfg["hidden_size"],
-                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
-                   "head_dim": nums["d"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
-                   "global_batch": a.batch, "seq_len": CONTEXT, "kv_block": 16, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (a decode step reads %.1f GB)" % (step_bytes / 1e9),
-                   "cuda_graphs": bool(ecfg.use_cuda_graphs), "overlap_steps": bool(ecfg.overlap_decode_steps),
-                   "peaks": peaks["source"], "load_s": round(load_s, 1)},
+        "config": flat_config(cfg, a, nums, {
+            "l2": "inputs larger than L2 (a decode step reads %.1f GB)" % (step_bytes / n_timed / 1e9),
+            "cuda_graphs": bool(ecfg.use_cuda_graphs), "overlap_steps": bool(ecfg.overlap_decode_steps),
+            "peaks": peaks["source"], "load_s": round(load_s, 1), "kv_pages": cache.num_pages}),
         "clocks": clock_info,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,

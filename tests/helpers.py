@@ -44,6 +44,12 @@ TINY_E = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_
           "tie_word_embeddings": False, "use_sliding_window": True, "sliding_window": 70,
           "max_window_layers": 1, "max_position_embeddings": 400, "hidden_act": "silu"}
 
+# The models whose logits the reference itself can anchor (tests/golden/make_reference_logits.py): tied
+# embeddings and eps 1e-6 only.  The second has the sizes of B: three heads on one kv head, widths that are
+# no power of two, another theta.
+GOLDEN_CONFIGS = {"A": TINY_A, "B_tied": dict(TINY_B, tie_word_embeddings=True, rms_norm_eps=1e-6)}
+GOLDEN_PROMPTS = (5, 17, 33)
+
 CONFIGS = {"A": (TINY_A, 16), "B": (TINY_B, 32), "C": (TINY_C, 16), "D": (TINY_D, 32), "E": (TINY_E, 16)}   # name -> (config, page size)
 
 # |engine - plain| <= TOL * max|plain| over the compared rows

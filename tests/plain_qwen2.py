@@ -5,12 +5,14 @@ with the engine: it has its own safetensors reader and writer, its own rotation
 table, its own sampler.  Every function is written from the formulas of
 jiamumuzhao/vllm-cpp and cites the file and lines it follows.
 
-It rests on the formulas, not on running the reference: the reference's model
-code (src/model/qwen.cpp, src/layers/*.cpp) calls the CUDA runtime and cuBLAS in
-every layer and has no CPU forward, so it cannot be compiled into something that
-runs on a CPU-only machine.  Its host-only sampler helpers can; the outputs of
-those for a few small inputs are kept under tests/golden/ with the program that
-made them.
+It is written from the formulas.  The reference's model code (src/model/qwen.cpp,
+src/layers/*.cpp) calls the CUDA runtime and cuBLAS in every layer and has no CPU
+forward, so it cannot run on a CPU-only machine; built on a GPU machine it gave the
+logits of two tiny tied models token by token, and those are kept under tests/golden/
+(reference_logits.npz, made by make_reference_logits.py) and compared with
+``forward`` here in tests/test_plain.py.  Its host-only sampler helpers run anywhere;
+their outputs for a few small inputs are kept there too, with the program that made
+them.
 
 Arithmetic is float64 unless ``dtype`` says otherwise, so that it judges the
 engine's float32 path as well as its bfloat16 path.  One thing is kept in float32
@@ -50,9 +52,18 @@ def rms_norm(x, weight, eps):
     return (x * r) * weight
 
 
+# The type the operands of every product are rounded through, or None.  The reference rounds both the
+# weights (src/layers/linear.cpp:38-42) and the inputs (:67, launch_f32_to_fp16) to half precision and
+# accumulates in float; ``forward(..., operand=np.float16)`` restates that, for the comparison with
+# logits the reference itself produced (tests/golden/).
+_OPERAND = None
+
+
 def linear(x, weight, bias=None):
     """out[t, o] = sum_i W[o, i] x[t, i] (+ bias[o]); W is [out, in]
     (src/layers/linear.cpp:70-77 computes it through cuBLAS, :84-86 adds the bias)."""
+    if _OPERAND is not None:
+        x, weight = x.astype(_OPERAND).astype(x.dtype), weight.astype(_OPERAND).astype(weight.dtype)
     y = x @ weight.T
     return y if bias is None else y + bias
 
@@ -134,10 +145,24 @@ def layer_window(cfg, layer):
     return 0
 
 
-def forward(weights, cfg, ids, dtype=np.float64):
+def forward(weights, cfg, ids, dtype=np.float64, operand=None):
     """Logits [T, vocab] of a whole sequence  (src/model/qwen.cpp:291-328):
-    embedding, then per layer  x += attn(norm(x));  x += mlp(norm(x)),  final norm, lm_head."""
+    embedding, then per layer  x += attn(norm(x));  x += mlp(norm(x)),  final norm, lm_head.
+    ``operand``: see _OPERAND above (the embedding table is stored in that type too,
+    src/layers/embedding.cpp:27-31)."""
+    global _OPERAND
+    _OPERAND = operand
+    try:
+        return _forward(weights, cfg, ids, dtype, operand)
+    finally:
+        _OPERAND = None
+
+
+def _forward(weights, cfg, ids, dtype, operand):
     w = {k: np.asarray(v, dtype=dtype) for k, v in weights.items()}
+    if operand is not None:
+        e = "model.embed_tokens.weight"
+        w[e] = w[e].astype(operand).astype(dtype)
     eps = cfg.get("rms_norm_eps", 1e-6)
     positions = np.arange(len(ids))
     x = embedding(ids, w["model.embed_tokens.weight"])

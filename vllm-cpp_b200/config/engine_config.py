@@ -75,6 +75,10 @@ class EngineConfig:
     # have reached the host (they are fed to it on the device), so the GPU never waits for
     # the host between steps.  The tokens are the same either way.
     overlap_decode_steps: bool = True
+    # Time the phases of every step (schedule, pack, launch, sample, wait on the host; forward and
+    # sampling on the device with CUDA events) into StepStats.phase_ms.  The reference has a scoped
+    # host timer for this (include/vllm/utils/profiler.hpp:15-53).
+    time_phases: bool = False
 
     def __post_init__(self):
         self.validate()

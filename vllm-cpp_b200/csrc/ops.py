@@ -43,6 +43,7 @@ _SIGNATURES = {
     "vcb_repetition_penalty": [_P, _I, _P, _P, _P, _I, _I, _P],
     "vcb_sample": [_P, _I, _I, _P, _P, _P, _I, _P],
     "vcb_sample_filtered": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
+    "vcb_random_normal": [_P, ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_ulonglong, _F, _F, _I, _P],
 }
 
 
@@ -632,6 +633,13 @@ def linear_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_scale: O
     only where ``linear_gated_fuses`` said yes."""
     _need(linear_gated_fuses(x.shape[0], w), "linear_gated: ask linear_gated_fuses first")
     gemm_bf16_tcgen05(x, w, out, x_scale=x_scale, gated=True)
+
+
+def random_normal(out: torch.Tensor, key: int, mean: float, std: float, first: int = 0) -> None:
+    """out.flatten()[i] = mean + std * normal(key, first + i), rounded to out's type: the counter-based
+    generator of the random-weights mode (csrc/random_init.cu; weights/random_init.py has it in numpy)."""
+    _check(lib().vcb_random_normal(_dev(out, "out"), out.numel(), int(first), int(key) & ((1 << 64) - 1),
+                                   float(mean), float(std), dtype_code(out.dtype), _stream()), "random_normal")
 
 
 def repetition_penalty(logits, ids, row_start, penalty) -> None:

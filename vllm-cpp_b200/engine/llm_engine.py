@@ -18,6 +18,7 @@ request that turns out to have ended leaves one unused row in the step launched 
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence as Seq
 
@@ -49,6 +50,11 @@ class StepStats:
     num_requests: int = 0
     free_pages: int = 0
     preemptions: int = 0
+    # with EngineConfig.time_phases: milliseconds of this step's phases.  Host time: "schedule", "pack"
+    # (metadata into the pinned buffer and its copy enqueued), "launch" (the model's kernels enqueued),
+    # "sample" (sampling and the read-back enqueued), "wait" (blocked until the token ids arrived).
+    # Device time, between CUDA events: "device_forward", "device_sample".
+    phase_ms: Dict[str, float] = field(default_factory=dict)
 
 
 @dataclass
@@ -59,6 +65,7 @@ class _InFlight:
     slots: List[int]
     handle: object
     stats: StepStats
+    events: Optional[tuple] = None        # (before the forward, after it, after the sampling) when phases are timed
 
 
 class Engine:
@@ -131,12 +138,24 @@ class Engine:
                 stats.num_prompt_tokens += it.count
             if it.samples:
                 sampled.append(it.seq)
+        timers = {} if self.config.time_phases else None
+        events = None
         with torch.no_grad():
-            logits = self.runner.step(entries, device_tokens=token_source)
+            logits = self.runner.step(entries, device_tokens=token_source, timers=timers)
+            if timers is not None:
+                after_forward = torch.cuda.Event(enable_timing=True)
+                after_forward.record()
+                t0 = time.perf_counter()
             rows = [SamplingRow(s.params.temperature, s.params.top_p, s.params.top_k,
                                 s.params.repetition_penalty, s.output_tokens,
                                 uniform_for(s.params.seed, s.output_len)) for s in sampled]
             handle = self.sampler.launch(logits, rows)
+            if timers is not None:
+                after_sample = torch.cuda.Event(enable_timing=True)
+                after_sample.record()
+                events = (timers["forward_start"], after_forward, after_sample)
+                stats.phase_ms.update(pack=timers["pack"] * 1e3, launch=timers["launch"] * 1e3,
+                                      sample=(time.perf_counter() - t0) * 1e3)
         for it in items:
             it.seq.num_processed_tokens += it.count
         # the token each sampled request will get: known to the host at _collect
@@ -144,7 +163,7 @@ class Engine:
         for seq in sampled:
             slots.append(seq.output_len)
             seq.output_tokens.append(self.PLACEHOLDER)
-        return _InFlight(items, sampled, slots, handle, stats)
+        return _InFlight(items, sampled, slots, handle, stats, events)
 
     def _may_run_ahead(self, flight: "_InFlight") -> bool:
         """True if the step after ``flight`` is known without its tokens: every running request took
@@ -162,7 +181,14 @@ class Engine:
 
     def _collect(self, flight: "_InFlight") -> List[GenerationOutput]:
         """Wait for the step's token ids, put them where the placeholders stand, check the stops."""
+        t0 = time.perf_counter()
         tokens = self.sampler.wait(flight.handle)
+        if flight.events is not None:
+            before, after_forward, after_sample = flight.events
+            after_sample.synchronize()
+            flight.stats.phase_ms.update(wait=(time.perf_counter() - t0) * 1e3,
+                                         device_forward=before.elapsed_time(after_forward),
+                                         device_sample=after_forward.elapsed_time(after_sample))
         outputs = []
         for seq, slot, tok in zip(flight.sampled, flight.slots, tokens):
             if seq.is_finished:
@@ -186,17 +212,25 @@ class Engine:
     def step(self) -> List[GenerationOutput]:
         flight, self._ahead = self._ahead, None
         if flight is None:
+            t0 = time.perf_counter()
             items = self.scheduler.schedule()
             if not items:
                 self.last_stats = StepStats()
                 return []
+            scheduled_ms = (time.perf_counter() - t0) * 1e3
             flight = self._launch(items)
+            if self.config.time_phases:
+                flight.stats.phase_ms["schedule"] = scheduled_ms
         if self._may_run_ahead(flight):
+            t0 = time.perf_counter()
             items = self.scheduler.schedule()
+            scheduled_ms = (time.perf_counter() - t0) * 1e3
             # only a plain continuation is sent ahead: the same requests, in the same order, one token each
             if len(items) == len(flight.sampled) and all(
                     it.seq is s and it.count == 1 and it.samples for it, s in zip(items, flight.sampled)):
                 self._ahead = self._launch(items, token_source=self.sampler.device_ids(flight.handle))
+                if self.config.time_phases:
+                    self._ahead.stats.phase_ms["schedule"] = scheduled_ms
             elif items:
                 # Not a plain continuation (pages ran short: somebody sits out or was preempted).  The
                 # batch is scheduled, so it runs, but only once this step's tokens are known.

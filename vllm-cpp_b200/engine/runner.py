@@ -23,6 +23,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence
 
+import time
+
 import numpy as np
 import torch
 
@@ -89,14 +91,24 @@ class ModelRunner:
                 + self.n_groups * _align(r * self.max_blocks))
 
     # ------------------------------------------------------------------ step
-    def step(self, entries: List[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def step(self, entries: List[StepEntry], device_tokens: Optional[torch.Tensor] = None,
+             timers: Optional[dict] = None) -> torch.Tensor:
         """Run one batch; returns float32 logits [number of wanted places, vocab] on the device,
         in the order of the entries and of each entry's ``want``.  The tensor is a
         view of the runner's logits buffer and is overwritten by the next step.
         ``device_tokens``: int32 ids on the device, one per entry of a step in which every entry
         brings one token; they replace the entries' token ids (which are then not looked at) in
-        stream order, for a step launched before the ids it continues from have reached the host."""
+        stream order, for a step launched before the ids it continues from have reached the host.
+        ``timers``: a dict that receives the host seconds of packing the metadata ("pack") and of
+        enqueuing the model's kernels ("launch"), and a CUDA event recorded before the first of them
+        ("forward_start")."""
+        t0 = time.perf_counter() if timers is not None else 0.0
         step = self._prepare(entries, ids_on_device=device_tokens is not None)
+        if timers is not None:
+            t1 = time.perf_counter()
+            timers["pack"] = t1 - t0
+            timers["forward_start"] = torch.cuda.Event(enable_timing=True)
+            timers["forward_start"].record()
         if device_tokens is not None:
             if not step.decode_only or device_tokens.numel() != step.n_tokens:
                 raise StepError("device_tokens needs one token per entry")
@@ -108,6 +120,8 @@ class ModelRunner:
             out = self.model.forward(step, self.views, self.ws, self.logits)
         for e in entries:
             self.cache.commit(e.req_id, len(e.tokens))
+        if timers is not None:
+            timers["launch"] = time.perf_counter() - t1
         return out
 
     # ---------------------------------------------------------- CUDA graphs
