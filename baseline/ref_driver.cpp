@@ -29,6 +29,7 @@
 // max_position_embeddings (the rotation table's length, qwen.cpp:115-128).
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -41,6 +42,7 @@
 #include "vllm/core/config.hpp"
 #include "vllm/model/qwen.hpp"
 #include "vllm/sampler/sampler.hpp"
+#include "vllm/utils/json_utils.hpp"
 
 namespace {
 
@@ -97,6 +99,42 @@ double now_s() {
     return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
 
+// QwenModel::load_weights sizes one pool from an estimate (src/model/qwen.cpp:58-80,104) and then hands out
+// slices that add up to something else (:108-161): the estimate counts one matrix where q and o (and k
+// and v) are two, and 2 of the 3 feed-forward work buffers.  What the estimate lacks comes out of the
+// cache's share, which is taken last; the cache's own constructor falls back to a cudaMalloc of its own
+// when its slice is missing (src/memory/kv_cache.cpp:20-26, the "[POOL] OOM" line on stderr).  A slice
+// BEFORE the cache that did not fit would come back as a null pointer, unchecked, and reach a kernel.
+// This repeats both sums on the host and refuses such a configuration before anything is loaded.
+void check_pool_arithmetic(const std::string& model_dir, const vllm::EngineConfig& cfg) {
+    auto j = vllm::json::parse_file(model_dir + "/config.json");
+    auto geti = [&](const char* k, long long dflt) { return j.contains(k) ? static_cast<long long>(j[k].get_int()) : dflt; };
+    const size_t H = geti("hidden_size", 896), L = geti("num_hidden_layers", 24), nh = geti("num_attention_heads", 14),
+                 nkv = geti("num_key_value_heads", 2), I = geti("intermediate_size", 4864),
+                 P = geti("max_position_embeddings", 32768), V = geti("vocab_size", 151936);
+    if (!H || !L || !nh || !nkv || !I || !P || !V || H % nh) die("config.json lacks a size the reference needs");
+    const size_t d = H / nh, qkv = nh * d, kv = nkv * d, S = cfg.max_num_seqs, bs = cfg.block_size;
+    const size_t blocks_per_seq = (cfg.max_model_len + bs - 1) / bs;
+    size_t estimate = V * H * 2 + L * (H * qkv * 2 + H * kv * 2 + H * I * 3 * 2) + L * 3 * 4 * 1024 + L * P * d * 4 +
+                      2 * S * H * 4 + 2 * L * I * 4 + L * (3 * I + 3 * qkv + 2 * kv + 2 * H) * 4 + H * 4 + (64u << 20) +
+                      64 * 4 + 64 * V * 4 + L * (blocks_per_seq + 1) * 4;
+    const size_t per_block = 2 * bs * nkv * d * 4 * L;
+    size_t free_b = 0, total_b = 0;
+    cuda_ok(cudaMemGetInfo(&free_b, &total_b), "cudaMemGetInfo");
+    const size_t budget = static_cast<size_t>(static_cast<double>(free_b) * cfg.gpu_memory_utilization / 100.0);
+    if (budget <= estimate) die("the device has too little free memory for the reference's pool");
+    const size_t kv_blocks = std::min(blocks_per_seq * S, (budget - estimate) / per_block);
+    const size_t pool = estimate + kv_blocks * per_block;
+    const size_t before_cache = (V * H + L * (2 * H * qkv + 2 * H * kv + 3 * H * I)) * 2 + L * 3 * 1024 * 4 + L * P * d * 4 +
+                                3 * L * I * 4 + L * (2 * qkv + 2 * kv) * 4 + L * qkv * 4 + L * (blocks_per_seq + 1) * 4 +
+                                (2 * L + 1) * H * 4 + 2 * S * H * 4 + 16 * 256 /* alignment of the slices */;
+    const size_t engine = 64 * 4 + V * 4 + 2 * 256;
+    std::fprintf(stderr, "ref_driver: the reference's pool will be %zu bytes; its slices before the cache need %zu\n", pool, before_cache);
+    if (before_cache + engine > pool)
+        die("the reference's pool (src/model/qwen.cpp:58-104) is smaller than the slices it takes before the cache "
+            "(:108-161) at these sizes; a null slice would reach a kernel, so this configuration is not run");
+}
+
 // The reference's model with the buffers its engine would hold (src/core/engine.cpp:68-76).
 struct Reference {
     vllm::EngineConfig cfg;
@@ -115,8 +153,7 @@ struct Reference {
         cfg.max_model_len = max_model_len;
         cfg.gpu_memory_utilization = 90;
         blocks_per_seq = (max_model_len + cfg.block_size - 1) / cfg.block_size;
-        size_t free_b = 0, total_b = 0;
-        cuda_ok(cudaMemGetInfo(&free_b, &total_b), "cudaMemGetInfo");
+        check_pool_arithmetic(a.model, cfg);
         const double t0 = now_s();
         model = std::make_unique<vllm::QwenModel>(cfg);
         if (!model->load_weights(a.model)) die("QwenModel::load_weights returned false");

@@ -145,21 +145,22 @@ def layer_window(cfg, layer):
     return 0
 
 
-def forward(weights, cfg, ids, dtype=np.float64, operand=None):
+def forward(weights, cfg, ids, dtype=np.float64, operand=None, rows=None):
     """Logits [T, vocab] of a whole sequence  (src/model/qwen.cpp:291-328):
     embedding, then per layer  x += attn(norm(x));  x += mlp(norm(x)),  final norm, lm_head.
     ``operand``: see _OPERAND above (the embedding table is stored in that type too,
-    src/layers/embedding.cpp:27-31)."""
+    src/layers/embedding.cpp:27-31).  ``rows``: positions whose logits are returned ([len(rows), vocab];
+    with a vocabulary of 150,000 the output product of every position is most of the work)."""
     global _OPERAND
     _OPERAND = operand
     try:
-        return _forward(weights, cfg, ids, dtype, operand)
+        return _forward(weights, cfg, ids, dtype, operand, rows)
     finally:
         _OPERAND = None
 
 
-def _forward(weights, cfg, ids, dtype, operand):
-    w = {k: np.asarray(v, dtype=dtype) for k, v in weights.items()}
+def _forward(weights, cfg, ids, dtype, operand, rows=None):
+    w = {k: (v if isinstance(v, np.ndarray) and v.dtype == dtype else np.asarray(v, dtype=dtype)) for k, v in weights.items()}
     if operand is not None:
         e = "model.embed_tokens.weight"
         w[e] = w[e].astype(operand).astype(dtype)
@@ -173,6 +174,8 @@ def _forward(weights, cfg, ids, dtype, operand):
         h = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
         x = x + swiglu_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                            w[p + "mlp.down_proj.weight"])
+    if rows is not None:
+        x = x[np.asarray(rows, dtype=np.int64)]
     x = rms_norm(x, w["model.norm.weight"], eps)
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return linear(x, head)

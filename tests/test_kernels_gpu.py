@@ -194,7 +194,11 @@ def reference_attention(q, k, v, q_lens, ctx_lens, nh, nkv, window):
     return out
 
 
-def attention_case(rng, dtype, nh, nkv, d, page, q_lens, ctx_lens, spike=True):
+def attention_case(rng, dtype, nh, nkv, d, page, q_lens, ctx_lens, spike=True, window=0):
+    """A batch for the attention kernels.  With a window, the pages that the cache manager would have given
+    back by now (every key at or below ctx - window: no query of the step reads them) are gone from the
+    table (-1), and what they held is overwritten with large values, as a page's next owner might leave
+    it: a kernel that still reads them shows it in its output or in the status word."""
     n_reqs = len(q_lens)
     total = [c + q for c, q in zip(ctx_lens, q_lens)]
     n_pages = sum(-(-t // page) for t in total) + 3
@@ -224,6 +228,11 @@ def attention_case(rng, dtype, nh, nkv, d, page, q_lens, ctx_lens, spike=True):
             where = kv_pos(d, esize, p % page, page)
             cache[bt[r, p // page], 0][:, where] = k[r][p]
             cache[bt[r, p // page], 1][:, where] = v[r][p]
+    if window > 0:
+        for r, ctx in enumerate(ctx_lens):
+            for b in range(max(0, (ctx - window + 1) // page)):
+                cache[bt[r, b]] = 3.0e4
+                bt[r, b] = -1
     q_start = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
     pos = np.concatenate([np.arange(c, c + ql) for c, ql in zip(ctx_lens, q_lens)]).astype(np.int32)
     req = np.concatenate([np.full(ql, r) for r, ql in enumerate(q_lens)]).astype(np.int32)
@@ -236,11 +245,12 @@ def attention_case(rng, dtype, nh, nkv, d, page, q_lens, ctx_lens, spike=True):
 def test_attention_simt(ops, dtype, nh, nkv, d, page, window):
     rng = np.random.default_rng(4)
     q_lens, ctx_lens = [1, 33, 2, 1], [300, 17, 0, 63]
-    c = attention_case(rng, dtype, nh, nkv, d, page, q_lens, ctx_lens)
+    c = attention_case(rng, dtype, nh, nkv, d, page, q_lens, ctx_lens, window=window)
     out = torch.empty((c["n"], nh * d), dtype=DT[dtype], device="cuda")
     ops.attention_simt(dev(c["q"].reshape(c["n"], -1), DT[dtype]), dev(c["cache"], DT[dtype]), out, dev(c["pos"]),
                        dev(c["req"]), dev(c["bt"]), num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page,
                        window=window, scale=float(np.float32(1) / np.sqrt(np.float32(d))))
+    ops.check_status()
     want = reference_attention(c["q"].astype(np.float64), c["k"], c["v"], q_lens, ctx_lens, nh, nkv, window)
     close(out.float().cpu().numpy().reshape(c["n"], nh, d), want, dtype, "attention_simt")
 
@@ -252,7 +262,7 @@ def test_attention_prefill_tc(ops, nh, nkv, page, window, d):
     start and end inside tiles and pages, contexts before them, one far key that must dominate, windows."""
     rng = np.random.default_rng(6)
     q_lens, ctx_lens = [70, 1, 2, 300, 5], [0, 500, 63, 64, 1000]
-    c = attention_case(rng, "bfloat16", nh, nkv, d, page, q_lens, ctx_lens)
+    c = attention_case(rng, "bfloat16", nh, nkv, d, page, q_lens, ctx_lens, window=window)
     group = nh // nkv
     rows = ops.TC_ATTENTION_TILE_ROWS
     tiles = [(r, k * rows) for r, ql in enumerate(q_lens) for k in range(-(-ql * group // rows))]
@@ -277,7 +287,9 @@ def test_attention_prefill_tc_long(ops, d, window):
     rng = np.random.default_rng(16)
     nh, nkv, page = 28, 4, 16
     q_lens, ctx_lens = [1700, 300], [0, 1100]
-    c = attention_case(rng, "bfloat16", nh, nkv, d, page, q_lens, ctx_lens)
+    if window:
+        q_lens, ctx_lens = [1700, 300], [0, 2400]      # 150 pages before the second portion, most of them given back
+    c = attention_case(rng, "bfloat16", nh, nkv, d, page, q_lens, ctx_lens, window=window)
     group = nh // nkv
     rows = ops.TC_ATTENTION_TILE_ROWS
     tiles = [(r, k * rows) for r, ql in enumerate(q_lens) for k in range(-(-ql * group // rows))]
@@ -297,12 +309,14 @@ def test_attention_prefill_tc_long(ops, d, window):
 
 @pytest.mark.parametrize("nsplit", [1, 3, 8])
 @pytest.mark.parametrize("nh,nkv,d,page,window", [(28, 4, 128, 16, 0), (6, 2, 64, 32, 0), (3, 3, 64, 16, 40),
-                                                   (40, 2, 128, 16, 0), (16, 1, 128, 16, 200)])
+                                                   (40, 2, 128, 16, 0), (16, 1, 128, 16, 200), (8, 2, 128, 8, 0)])
 def test_attention_decode_mma(ops, nsplit, nh, nkv, d, page, window):
     rng = np.random.default_rng(6)
     ctx_lens = [0, 1, 63, 64, 65, 777, 2000]
+    if window:
+        ctx_lens = [0, 1, 63, 64, 65, 777, 3000]       # 188 pages of 16, of which a window of 200 keeps 13
     q_lens = [1] * len(ctx_lens)
-    c = attention_case(rng, "bfloat16", nh, nkv, d, page, q_lens, ctx_lens)
+    c = attention_case(rng, "bfloat16", nh, nkv, d, page, q_lens, ctx_lens, window=window)
     n = c["n"]
     out = torch.zeros((n, nh * d), dtype=torch.bfloat16, device="cuda")
     part_o = torch.empty(n * nh * nsplit * d, dtype=torch.float32, device="cuda")
@@ -312,6 +326,7 @@ def test_attention_decode_mma(ops, nsplit, nh, nkv, d, page, window):
                              dev(c["q_start"]), dev(np.array(ctx_lens, dtype=np.int32)), dev(c["bt"]), None, n, nsplit,
                              part_o, part_ml, counters, num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page,
                              window=window, scale=float(np.float32(1) / np.sqrt(np.float32(d))))
+    ops.check_status()
     want = reference_attention(c["q"].astype(np.float64), c["k"], c["v"], q_lens, ctx_lens, nh, nkv, window)
     close(out.float().cpu().numpy().reshape(n, nh, d), want, "bfloat16", f"attention_decode_mma nsplit={nsplit}")
     # a request list picks and reorders requests
@@ -594,3 +609,68 @@ def test_device_sampler_on_the_reference_samplers_golden_rows(ops):
         assert abs(order.index(int(got[i])) - order.index(cases[i]["token"])) == 1 or \
             abs(int(got[i]) - cases[i]["token"]) == 1, (i, got[i], cases[i]["token"])
     assert len(wrong) <= 2
+
+
+def test_a_page_that_is_not_there_is_reported_not_followed(ops):
+    """A block table with an entry that names no page of the cache (what the cache manager stores for a
+    page it took back is -1): the cache write leaves every byte alone (rows beside the cache tensor
+    included), the attention kernels read page 0 in its place, and all of them leave a note that
+    ops.check_status() raises on.  Nothing traps."""
+    rng = np.random.default_rng(8)
+    nh, nkv, d, page, n_pages = 4, 2, 128, 16, 6
+    ops.check_status()
+    whole = torch.full((n_pages + 2, 2, nkv, page * d), 7.0, dtype=torch.bfloat16, device="cuda")
+    cache = whole[1:-1]                                   # canary pages before and after the cache
+    bt = np.array([[2, -1, 3], [4, 77, 5]], dtype=np.int32)
+    pos = np.array([15, 16, 17, 20], dtype=np.int32)      # request 0: slot 15 of page 2, then its missing second page
+    req = np.array([0, 0, 0, 1], dtype=np.int32)          # request 1: its second entry lies beyond the cache
+    qkv = rng.standard_normal((4, (nh + 2 * nkv) * d)).astype(np.float32)
+    denom = np.power(np.float32(1e4), np.arange(d // 2, dtype=np.float32) * 2 / d).astype(np.float32)
+    for dtype in (torch.bfloat16, torch.float32):
+        w = whole.to(dtype)
+        c = w[1:-1]
+        q_out = torch.empty((4, nh * d), dtype=dtype, device="cuda")
+        ops.rope_cache_write(dev(qkv, dtype), None, dev(pos), dev(req), dev(bt), dev(denom), q_out, c, num_heads=nh,
+                             num_kv_heads=nkv, head_dim=d, rotary_dim=d, pairing=0, page_size=page, write_kv=True)
+        with pytest.raises(ops.KernelError, match="names a page|named a page"):
+            ops.check_status()
+        changed = (w != 7.0).flatten(1).any(dim=1).cpu().numpy()
+        assert changed.tolist() == [False, False, False, True, False, False, False, False], changed   # page 2 only
+        ops.check_status()                                # the note was cleared
+    # the readers: a decode step and a portion whose visible pages include the missing one
+    q = dev(rng.standard_normal((2, nh * d)), torch.bfloat16)
+    q_start, ctx = dev(np.array([0, 1, 2], dtype=np.int32)), dev(np.array([20, 20], dtype=np.int32))
+    out = torch.zeros_like(q)
+    scale = float(1 / np.sqrt(np.float32(d)))
+    ops.attention_decode_mma(q, cache, out, q_start, ctx, dev(bt), None, 2, 1, None, None, None, num_heads=nh,
+                             num_kv_heads=nkv, head_dim=d, page_size=page, window=0, scale=scale)
+    with pytest.raises(ops.KernelError, match="named a page"):
+        ops.check_status()
+    ops.attention_prefill_tc(q, cache, out, q_start, ctx, dev(bt), dev(np.array([0, 1], dtype=np.int32)),
+                             dev(np.array([0, 0], dtype=np.int32)), num_heads=nh, num_kv_heads=nkv, head_dim=d,
+                             page_size=page, window=0, scale=scale)
+    with pytest.raises(ops.KernelError, match="named a page"):
+        ops.check_status()
+    ops.attention_simt(q, cache, out, dev(np.array([20, 20], dtype=np.int32)), dev(np.array([0, 1], dtype=np.int32)), dev(bt),
+                       num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page, window=0, scale=scale)
+    with pytest.raises(ops.KernelError, match="named a page"):
+        ops.check_status()
+    assert torch.isfinite(out.float()).all()
+
+
+def test_decode_attention_refuses_pages_it_cannot_copy(ops):
+    """Pages of fewer than 8 slots (or no multiple of 8) cannot be copied as the kernel copies a tile: refused,
+    nothing launched."""
+    q = torch.zeros((1, 2 * 64), dtype=torch.bfloat16, device="cuda")
+    out = torch.full_like(q, 5.0)
+    cache = torch.zeros((4, 2, 2, 4 * 64), dtype=torch.bfloat16, device="cuda")
+    z = torch.zeros(4, dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.attention_decode_mma(q, cache, out, z[:2], z[:1], z.view(1, 4), None, 1, 1, None, None, None, num_heads=2,
+                                 num_kv_heads=2, head_dim=64, page_size=4, window=0, scale=0.125)
+    rc = ops.lib().vcb_attention_decode_mma(q.data_ptr(), cache.data_ptr(), out.data_ptr(), z.data_ptr(), z.data_ptr(),
+                                            z.data_ptr(), 4, None, 1, 1, None, None, None, None, 2, 2, 64, 4, 0, 0.125, 4,
+                                            None, None)
+    assert rc == 10002
+    torch.cuda.synchronize()
+    assert (out == 5.0).all()

@@ -32,7 +32,7 @@ def part_harness(mixer, page=16, pages=32, max_len=256, max_seqs=4):
     from vllm_cpp_b200.cache.manager import CacheManager
     from vllm_cpp_b200.engine.runner import ModelRunner
     cache = CacheManager([mixer.cache_spec()], page, pages, max_seqs, mixer.dtype, "cuda")
-    fake = types.SimpleNamespace(vocab=1000, blocks=[types.SimpleNamespace(mixer=mixer, feed_forward=None)],
+    fake = types.SimpleNamespace(vocab=1000, blocks=[types.SimpleNamespace(parts={"mixer": mixer})], final_norm=None,
                                  spec=types.SimpleNamespace(max_position_embeddings=max_len))
     return cache, ModelRunner(fake, cache, 512, max_seqs, max_len, torch.device("cuda", 0))
 
@@ -139,8 +139,11 @@ TOY_CFG = {"architectures": ["ToyMixForCausalLM"], "hidden_size": 48, "vocab_siz
 def register_toy():
     from vllm_cpp_b200.config.model_spec import LayerCall, LayerSpec, ModelSpec, PartSpec
     from vllm_cpp_b200.config.registry import register_architecture
-    from vllm_cpp_b200.parts.base import (FeedForward, Mixer, ParamSpec, PositionEncoding, StateSpec,
-                                          register_feed_forward, register_mixer, register_position_encoding)
+    from vllm_cpp_b200.parts.base import (Block, FeedForward, Mixer, ParamSpec, PositionEncoding, StateSpec,
+                                          register_block, register_feed_forward, register_mixer, register_norm,
+                                          register_position_encoding)
+    from vllm_cpp_b200.parts.model import DecoderModel, register_model_class
+    from vllm_cpp_b200.parts.norm import RMSNorm
 
     @register_mixer("toy_running_mean")
     class RunningMean(Mixer):
@@ -216,6 +219,55 @@ def register_toy():
             q[:, :, 0] += (self.slope * positions.float()).to(q.dtype)[:, None]
             k[:, :, 0] += (self.slope * positions.float()).to(k.dtype)[:, None]
 
+    @register_norm("toy_first_token_norm")
+    class FirstTokenNorm(RMSNorm):
+        """An RMSNorm whose output row is doubled for the token at position 0 of a request.  Which rows
+        those are it learns from a work list of its own, built on the host for every step."""
+
+        def step_arrays(self):
+            def first_rows(host):
+                flags, t = np.zeros(sum(host.q_lens), dtype=np.int32), 0
+                for q, ctx in zip(host.q_lens, host.ctx_lens):
+                    flags[t] = 1 if ctx == 0 else 0
+                    t += q
+                return flags
+            return {"toy_first_rows": first_rows}
+
+        def forward_branch(self, x, out, step):
+            """out = norm(x) for a branch's output x (not the residual stream), rows of first tokens doubled."""
+            self.forward(x.float(), None, out)
+            out.mul_((1 + step.extras["toy_first_rows"]).to(out.dtype)[:, None])
+
+    @register_block("toy_sandwich")
+    class Sandwich(Block):
+        """x += post(mixer(norm_a(x)));  x += feed_forward(norm_b(x)): a third norm on the mixer's output."""
+        SLOTS = dict(Block.SLOTS, post_mixer_norm="norm")
+
+        def forward(self, residual, delta, pending, step, cache, writes_cache, ws, next_block=None, carry=None):
+            mark = ws.mark()
+            n, hidden = residual.shape
+            h, mixed, normed = (ws.take((n, hidden), delta.dtype) for _ in range(3))
+            self.mixer_norm.forward(residual, delta if pending else None, h)
+            self.mixer.forward(h, mixed, step, cache, writes_cache, ws)
+            self.post_mixer_norm.forward_branch(mixed, normed, step)
+            self.feed_forward_norm.forward(residual, normed, h)
+            self.feed_forward.forward(h, delta, step, ws)
+            ws.release(mark)
+            return True
+
+    @register_model_class("toy_scaled")
+    class ScaledModel(DecoderModel):
+        """Embeddings times sqrt(hidden), logits capped smoothly at +-cap: the two hooks of the model class."""
+        CAP = 3.0
+
+        def embed_tokens(self, step, residual):
+            super().embed_tokens(step, residual)
+            residual.mul_(float(np.sqrt(np.float32(self.hidden))))
+
+        def head(self, normed, out):
+            super().head(normed, out)
+            out.copy_(self.CAP * torch.tanh(out / self.CAP))
+
     @register_architecture("ToyMixForCausalLM")
     def build(cfg):
         h = cfg["hidden_size"]
@@ -231,9 +283,12 @@ def register_toy():
         layers = []
         for i, (mixer, feed_forward) in enumerate(kinds):
             p = f"toy.{i}."
-            layers.append(LayerSpec(mixer=mixer, feed_forward=feed_forward, mixer_norm=norm(), feed_forward_norm=norm(),
-                                    names={"mixer": p + "mixer.", "feed_forward": p + "ff.", "mixer_norm": p + "n1.",
-                                           "feed_forward_norm": p + "n2."}))
+            parts = {"mixer": mixer, "feed_forward": feed_forward, "mixer_norm": norm(), "feed_forward_norm": norm()}
+            names = {"mixer": p + "mixer.", "feed_forward": p + "ff.", "mixer_norm": p + "n1.", "feed_forward_norm": p + "n2."}
+            if i == 2:                      # the last layer has three norms, one of them with a work list of its own
+                parts["post_mixer_norm"] = PartSpec("toy_first_token_norm", {"size": h, "eps": cfg["eps"]})
+                names["post_mixer_norm"] = p + "n3."
+            layers.append(LayerSpec(parts, block="toy_sandwich" if i == 2 else "prenorm", names=names))
         # layer 0, the state layer, layer 2, then layer 0's weights once more on layer 0's cache
         # (read only), then the state layer again with a cache of its own
         order = [LayerCall(0, 0), LayerCall(1, 1), LayerCall(2, 2), LayerCall(0, 0, writes_cache=False),
@@ -241,7 +296,7 @@ def register_toy():
         spec = ModelSpec(architecture="ToyMixForCausalLM", hidden_size=h, vocab_size=cfg["vocab_size"], layers=layers,
                          run_order=order, final_norm=norm(), tie_word_embeddings=False,
                          max_position_embeddings=cfg["max_position_embeddings"], embed_name="toy.embed",
-                         final_norm_prefix="toy.final.", lm_head_name="toy.head")
+                         final_norm_prefix="toy.final.", lm_head_name="toy.head", model_class="toy_scaled")
         return cfg, spec
 
 
@@ -289,7 +344,7 @@ def toy_plain_forward(w, cfg, ids):
             return y
         return plain.swiglu_mlp(x, w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"])
 
-    x = plain.embedding(ids, w["toy.embed"])
+    x = plain.embedding(ids, w["toy.embed"]) * np.float64(np.sqrt(np.float32(h)))
     kv0 = None
     for layer, kind in [(0, "rope"), (1, "mean"), (2, "ramp"), (0, "rope-shared"), (1, "mean")]:
         p = f"toy.{layer}."
@@ -302,9 +357,13 @@ def toy_plain_forward(w, cfg, ids):
             o, kv = attn(hdn, p + "mixer.", kind)
             if layer == 0:
                 kv0 = kv
+            if layer == 2:                             # the third norm, on the branch; the first token's row doubled
+                o = plain.rms_norm(o, w[p + "n3.weight"], eps)
+                o[0] *= 2.0
             x = x + o
         x = x + ff(plain.rms_norm(x, w[p + "n2.weight"], eps), p + "ff.")
-    return plain.linear(plain.rms_norm(x, w["toy.final.weight"], eps), w["toy.head"])
+    logits = plain.linear(plain.rms_norm(x, w["toy.final.weight"], eps), w["toy.head"])
+    return 3.0 * np.tanh(logits / 3.0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -317,12 +376,14 @@ def test_toy_architecture_with_state_runs_through_the_unchanged_framework(tmp_pa
     from vllm_cpp_b200.parts.model import DecoderModel
 
     _, spec = resolve_architecture(TOY_CFG)
-    shapes = {k: v.shape for k, v in DecoderModel(spec, torch.float32, "meta").param_specs().items()}
+    from vllm_cpp_b200.parts.model import build_model
+    shapes = {k: v.shape for k, v in build_model(spec, torch.float32, "meta").param_specs().items()}
+    assert "toy.2.n3.weight" in shapes and type(build_model(spec, torch.float32, "meta")).__name__ == "ScaledModel"
     rng = np.random.default_rng(7)
     w = {}
     for name, shape in shapes.items():
         x = rng.standard_normal(shape).astype(np.float32)
-        w[name] = (1 + 0.1 * x) if name.endswith(("n1.weight", "n2.weight", "final.weight")) else 0.15 * x
+        w[name] = (1 + 0.1 * x) if name.endswith(("n1.weight", "n2.weight", "n3.weight", "final.weight")) else 0.15 * x
         w[name] = w[name].astype(np.float32)
     if dtype == "bfloat16":
         w = plain.round_to_bf16(w)

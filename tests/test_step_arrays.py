@@ -11,6 +11,12 @@ import vllm_cpp_b200.parts.model  # noqa: F401  (registers the parts)
 from vllm_cpp_b200.parts.attention import PagedAttention
 
 
+@pytest.fixture(autouse=True)
+def b200_sm_count(monkeypatch):
+    """These tests run without a device: the work lists are sized for a B200's 148 SMs."""
+    monkeypatch.setattr(ops, "_sm_count", 148)
+
+
 def part(nh, nkv, window=0):
     return PagedAttention(hidden_size=nh * 128, num_heads=nh, num_kv_heads=nkv, head_dim=128, qkv_bias=True,
                           out_bias=False, window=window, position=PartSpec("rope", {"theta": 1e6, "rotary_dim": 128, "pairing": "half"}),

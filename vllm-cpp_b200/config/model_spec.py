@@ -23,17 +23,32 @@ class PartSpec:
     params: Dict[str, Any] = field(default_factory=dict)
 
 
-@dataclass
 class LayerSpec:
-    mixer: PartSpec
-    feed_forward: PartSpec
-    # Norm before the mixer and before the feed-forward (pre-norm arrangement).
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    block: str = "prenorm"
-    # Checkpoint name prefixes for each part's tensors, e.g.
-    # {"mixer": "model.layers.3.self_attn.", "mixer_norm": "model.layers.3.input_layernorm."}
-    names: Dict[str, str] = field(default_factory=dict)
+    """One layer: a block arrangement and the parts that fill its slots.
+
+    ``block`` names a registered arrangement; the arrangement declares its slots and which family
+    of part each takes (``Block.SLOTS`` in parts/base.py).  "prenorm" has ``mixer``,
+    ``feed_forward``, ``mixer_norm`` (before the mixer) and ``feed_forward_norm`` (before the
+    feed-forward); another arrangement may have other slots, e.g. a third norm.  ``parts`` maps slot
+    names to PartSpecs (slots may also be given as keyword arguments); ``names`` maps the same slot
+    names to the checkpoint prefixes of the parts' tensors, e.g.
+    {"mixer": "model.layers.3.self_attn.", "mixer_norm": "model.layers.3.input_layernorm."}.
+    """
+
+    def __init__(self, parts: Optional[Dict[str, PartSpec]] = None, block: str = "prenorm",
+                 names: Optional[Dict[str, str]] = None, **slots: PartSpec):
+        self.parts: Dict[str, PartSpec] = dict(parts or {}, **slots)
+        self.block = block
+        self.names: Dict[str, str] = dict(names or {})
+
+    def __getattr__(self, slot):                  # spec.mixer_norm reads spec.parts["mixer_norm"]
+        parts = self.__dict__.get("parts", {})
+        if slot in parts:
+            return parts[slot]
+        raise AttributeError(slot)
+
+    def __repr__(self):
+        return f"LayerSpec(block={self.block!r}, parts={self.parts!r}, names={self.names!r})"
 
 
 @dataclass
@@ -71,6 +86,10 @@ class ModelSpec:
     # Standard deviations of the random-weights mode.
     init_std: float = 0.02
     init_gain_std: float = 0.02
+    # The registered model class that is built from this spec (parts/model.py MODEL_CLASSES).  "decoder" is
+    # embedding -> layers -> final norm -> output product; an architecture that scales its embeddings,
+    # caps its logits or adds an output bias registers a subclass that overrides embed() or head().
+    model_class: str = "decoder"
 
     def validate(self) -> None:
         n_cache = 1 + max((c.cache for c in self.run_order), default=-1)

@@ -50,6 +50,8 @@ struct MmaAttnArgs {
     const int* split_tiles;        // decode: key tiles per split, on the device (null: every request in gridDim.x equal parts)
     int bt_stride, nh, nkv, page, window;
     float scale;
+    int num_pages;                 // pages of the cache: a table entry outside [0, num_pages) is read as page 0
+                                   // and VCB_STATUS_BAD_PAGE goes to the status word
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -99,9 +101,15 @@ template <int D, int TK> __device__ __forceinline__ uint32_t swz_kv(int key, int
 struct PageWindow {
     const int* bt;
     int base, n_pages, last_pg, cur, nxt, lane;
+    int n_phys;                  // pages of the cache
+    bool bad;                    // a page number outside [0, n_phys) was met (and replaced by page 0)
     __device__ __forceinline__ int fetch(int i) const { return i < n_pages ? __ldg(bt + i) : last_pg; }
-    __device__ __forceinline__ void init(const int* bt_, int first_page, int hi, int page, int lane_) {
-        bt = bt_; lane = lane_;
+    __device__ __forceinline__ int checked(int pg) {
+        if ((unsigned)pg >= (unsigned)n_phys) { bad = true; return 0; }
+        return pg;
+    }
+    __device__ __forceinline__ void init(const int* bt_, int first_page, int hi, int page, int lane_, int n_phys_) {
+        bt = bt_; lane = lane_; n_phys = n_phys_; bad = false;
         n_pages = (hi - 1) / page + 1;
         last_pg = __ldg(bt + (hi - 1) / page);
         base = first_page;
@@ -162,7 +170,7 @@ __device__ __forceinline__ TilePiece tile_piece(int kb, int lo, int hi, PageWind
     const int page_lo = pd.mul(lp);
     const bool visible = page_lo < hi && page_lo + pd.page > lo;
     const int got = pw.get(visible ? lp : first_page);                     // all lanes take part in the shuffles
-    const int pg = visible ? got : pw.last_pg;
+    const int pg = pw.checked(visible ? got : pw.last_pg);
     const int end = min(page_lo + pd.page, kb + TK);
     // plane `plane` of the head's block: pd.page rows of 64 elements
     t.src = cache + (size_t)pg * page_stride + head_base + ((size_t)plane * pd.page + (start - page_lo)) * 64;
@@ -306,7 +314,7 @@ attention_decode_kernel(MmaAttnArgs a) {
         if (producer) {
             PageWindow pw;
             const PageDiv pd(a.page);
-            pw.init(bt, pd.div(my0 * BN), hi, a.page, lane);
+            pw.init(bt, pd.div(my0 * BN), hi, a.page, lane, a.num_pages);
             const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
                          v_off = (size_t)a.nkv * a.page * D;
             for (int tile = my0; tile < my1; ++tile, ++it) {
@@ -318,6 +326,7 @@ attention_decode_kernel(MmaAttnArgs a) {
                 produce_tile<D, BN>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
                                     full0 + 8 * st, tile * BN, lo, hi, pw, a.cache, head_base, page_stride, v_off, pd, lane);
             }
+            if (pw.bad && a.status) atomicCAS(a.status, 0, VCB_STATUS_BAD_PAGE);
         } else {
             uint32_t qf[D / 16][4];
             load_q_frags<D>(qf, sq, 0);
@@ -472,13 +481,8 @@ template <int D>
 static int launch_decode(const MmaAttnArgs& a, int n_list, int nsplit, cudaStream_t s) {
     constexpr int STAGES = 3;
     const size_t smem = (size_t)STAGES * 2 * BN * D * 2 + 16 * D * 2 + 2 * STAGES * 8 + 64;   // tiles, Q, barriers
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static unsigned long long configured = 0;
+    if (int e = vcb_allow_dynamic_smem(attention_decode_kernel<D, STAGES>, (int)smem, &configured)) return e;
     dim3 grid(nsplit, a.nkv, n_list);
     vcb_launch(attention_decode_kernel<D, STAGES>, grid, BLOCK_THREADS, smem, s, a);
     return vcb_last_error();
@@ -683,7 +687,7 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         // tile j - 2 is.
         PageWindow pw;
         const PageDiv pd(a.page);
-        pw.init(bt, pd.div(tile0 * TKT), hi, a.page, lane);
+        pw.init(bt, pd.div(tile0 * TKT), hi, a.page, lane, a.num_pages);
         const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
                      v_off = (size_t)a.nkv * a.page * D;
         // a tile's addresses are worked out before its stage is waited for
@@ -709,6 +713,7 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
                 if (j + 1 < n_tiles) pc = tile_piece<D, TKT>((tile0 + j + 1) * TKT, lo, hi, pw, a.cache, head_base, page_stride, pd, lane);
             }
         }
+        if (pw.bad && a.status) atomicCAS(a.status, 0, VCB_STATUS_BAD_PAGE);
     } else if (warp == 2) {
         // ---- MMA issuer.  The whole warp walks the loop and waits, one elected lane issues: addresses and
         // descriptors are then the same in all lanes, which lets the compiler keep them in uniform
@@ -921,20 +926,19 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
 
 template <int D>
 static int launch_prefill_tc(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(tc::attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             tc::smem_bytes<D>());
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static unsigned long long configured = 0;
+    if (int e = vcb_allow_dynamic_smem(tc::attention_prefill_tc_kernel<D>, tc::smem_bytes<D>(), &configured)) return e;
     vcb_launch(tc::attention_prefill_tc_kernel<D>, dim3(n_tiles, a.nkv), tc::THREADS, (size_t)tc::smem_bytes<D>(), s, a);
     return vcb_last_error();
 }
 
-static int check_common(int nh, int nkv, int d, int page, int window) {
-    if (nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || window < 0) return VCB_ERR_BAD_ARG;
+// Both kernels copy a tile of 64 keys as at most eight runs of whole pages' rows (tile_piece: one lane
+// per run), so a page holds a multiple of 8 slots; with smaller pages a tile's byte count would never
+// arrive and every wait would run to its limit.
+static int check_common(int nh, int nkv, int d, int page, int window, int num_pages) {
+    if (nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || window < 0 || num_pages <= 0) return VCB_ERR_BAD_ARG;
     if (d != 64 && d != 128) return VCB_ERR_UNSUPPORTED;
+    if (page % 8) return VCB_ERR_UNSUPPORTED;
     return 0;
 }
 
@@ -947,14 +951,15 @@ VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* 
                                         const int* ctx_lens, const int* block_table, int bt_stride,
                                         const int* req_list, int n_list, int nsplit, float* part_o,
                                         float* part_ml, int* counters, const int* split_tiles, int nh, int nkv,
-                                        int d, int page, int window, float scale, int* status, void* stream) {
+                                        int d, int page, int window, float scale, int num_pages, int* status,
+                                        void* stream) {
     if (n_list <= 0) return 0;
-    int c = check_common(nh, nkv, d, page, window);
+    int c = check_common(nh, nkv, d, page, window, num_pages);
     if (c) return c;
     if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, req_list, nullptr, part_o, part_ml, counters, status, split_tiles, bt_stride, nh, nkv,
-                  page, window, scale};
+                  page, window, scale, num_pages};
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
@@ -965,15 +970,14 @@ VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* 
 VCB_EXPORT int vcb_attention_prefill_tc(const void* q, const void* cache, void* out, const int* q_start,
                                         const int* ctx_lens, const int* block_table, int bt_stride,
                                         const int* tile_req, const int* tile_row0, int n_tiles, int nh,
-                                        int nkv, int d, int page, int window, float scale, int* status,
-                                        void* stream) {
+                                        int nkv, int d, int page, int window, float scale, int num_pages,
+                                        int* status, void* stream) {
     if (n_tiles <= 0) return 0;
-    int c = check_common(nh, nkv, d, page, window);
+    int c = check_common(nh, nkv, d, page, window, num_pages);
     if (c) return c;
-    if (page % 8) return VCB_ERR_UNSUPPORTED;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
-                  window, scale};
+                  window, scale, num_pages};
     return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
 }
 
@@ -989,50 +993,62 @@ static __device__ __align__(256) float vcb_static_scratch[VCB_STATIC_SCRATCH_ROW
 // Tickets of the split merge, one per (request, kv head); cleared before every launch.
 static __device__ __align__(256) int vcb_static_counters[VCB_STATIC_SCRATCH_ROWS];
 
+// Where the kernel notes that it gave up on a bounded wait or met a page number outside the cache;
+// vcb_attention_decode_mma_static_status reads and clears it.
+static __device__ int vcb_static_status_word;
+
 #define VCB_MAX_DEVICES 64
 static float* vcb_static_scratch_addr[VCB_MAX_DEVICES];
 static int* vcb_static_counters_addr[VCB_MAX_DEVICES];
+static int* vcb_static_status_addr[VCB_MAX_DEVICES];
 
-// The array's address on the current device, looked up once per device.
-static int static_scratch_address(float** addr, int** counters) {
+// The arrays' addresses on the current device, looked up once per device.
+static int static_scratch_address(float** addr, int** counters, int** status) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= VCB_MAX_DEVICES) return VCB_ERR_BAD_ARG;
-    if (vcb_static_scratch_addr[dev] == nullptr || vcb_static_counters_addr[dev] == nullptr) {
+    if (vcb_static_scratch_addr[dev] == nullptr || vcb_static_counters_addr[dev] == nullptr ||
+        vcb_static_status_addr[dev] == nullptr) {
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, vcb_static_scratch);
         if (e != cudaSuccess) return (int)e;
         void* pc = nullptr;
         e = cudaGetSymbolAddress(&pc, vcb_static_counters);
         if (e != cudaSuccess) return (int)e;
+        void* ps = nullptr;
+        e = cudaGetSymbolAddress(&ps, vcb_static_status_word);
+        if (e != cudaSuccess) return (int)e;
         vcb_static_scratch_addr[dev] = static_cast<float*>(p);
         vcb_static_counters_addr[dev] = static_cast<int*>(pc);
+        vcb_static_status_addr[dev] = static_cast<int*>(ps);
     }
     *addr = vcb_static_scratch_addr[dev];
     *counters = vcb_static_counters_addr[dev];
+    *status = vcb_static_status_addr[dev];
     return 0;
 }
 
 VCB_EXPORT int vcb_attention_decode_mma_static(const void* q, const void* cache, void* out, const int* q_start,
                                                const int* ctx_lens, const int* block_table, int bt_stride,
                                                const int* req_list, int n_list, int nsplit, int nh, int nkv,
-                                               int d, int page, int window, float scale, void* stream) {
+                                               int d, int page, int window, float scale, int num_pages,
+                                               void* stream) {
     if (n_list <= 0) return 0;
-    int c = check_common(nh, nkv, d, page, window);
+    int c = check_common(nh, nkv, d, page, window, num_pages);
     if (c) return c;
     if (nsplit < 1 || nsplit > 32) return VCB_ERR_BAD_ARG;
+    const long long rows = nsplit > 1 ? (long long)n_list * nh * nsplit : 0;
+    if (rows > VCB_STATIC_SCRATCH_ROWS || d > VCB_STATIC_SCRATCH_DIM) return VCB_ERR_SCRATCH_TOO_SMALL;
     float* part_o = nullptr;
     float* part_ml = nullptr;
+    float* base = nullptr;
     int* counters = nullptr;
-    int* status = nullptr;                  // a wait that runs out only ends the kernel early here
+    int* status = nullptr;
     cudaStream_t s = (cudaStream_t)stream;
+    c = static_scratch_address(&base, &counters, &status);
+    if (c) return c;
     if (nsplit > 1) {
-        const long long rows = (long long)n_list * nh * nsplit;
-        if (rows > VCB_STATIC_SCRATCH_ROWS || d > VCB_STATIC_SCRATCH_DIM) return VCB_ERR_SCRATCH_TOO_SMALL;
-        float* base = nullptr;
-        c = static_scratch_address(&base, &counters);
-        if (c) return c;
         part_o = base;
         part_ml = base + (size_t)VCB_STATIC_SCRATCH_ROWS * VCB_STATIC_SCRATCH_DIM;
         // the tickets must start at zero whatever an earlier call left behind
@@ -1040,7 +1056,24 @@ VCB_EXPORT int vcb_attention_decode_mma_static(const void* q, const void* cache,
         if (e != cudaSuccess) return (int)e;
     }
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, req_list, nullptr, part_o, part_ml, counters, status, nullptr, bt_stride, nh, nkv, page,
-                  window, scale};
+                  block_table, req_list, nullptr, nsplit > 1 ? part_o : nullptr, part_ml, nsplit > 1 ? counters : nullptr,
+                  status, nullptr, bt_stride, nh, nkv, page, window, scale, num_pages};
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
+}
+
+VCB_EXPORT int vcb_attention_decode_mma_static_status(int* code) {
+    float* base = nullptr;
+    int* counters = nullptr;
+    int* status = nullptr;
+    int c = static_scratch_address(&base, &counters, &status);
+    if (c) return c;
+    int seen = 0;
+    cudaError_t e = cudaMemcpy(&seen, status, sizeof(int), cudaMemcpyDeviceToHost);     // waits for the device
+    if (e != cudaSuccess) return (int)e;
+    if (seen) {
+        e = cudaMemset(status, 0, sizeof(int));
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (code) *code = seen;
+    return 0;
 }

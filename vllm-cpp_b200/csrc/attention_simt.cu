@@ -27,6 +27,8 @@ struct AttnArgs {
     const int* block_table;
     int bt_stride, n_tokens, nh, nkv, d, page, window;
     float scale;
+    int num_pages;              // a table entry outside [0, num_pages) is not read through: the key is left
+    int* status;                // out and VCB_STATUS_BAD_PAGE is recorded here (may be null)
 };
 
 template <typename T>
@@ -57,11 +59,19 @@ __global__ void attention_simt_kernel(AttnArgs a) {
 
     for (int kb = kstart; kb <= pos; kb += 32) {
         const int j = kb + lane;
-        const bool valid = j <= pos;
+        bool valid = j <= pos;
         float s = -INFINITY;
         unsigned long long koff = 0;
+        int pg = 0;
         if (valid) {
-            const int pg = bt[j / a.page];
+            const int lp = j / a.page;
+            pg = lp < a.bt_stride ? bt[lp] : -1;
+            if ((unsigned)pg >= (unsigned)a.num_pages) {
+                if (a.status) atomicCAS(a.status, 0, VCB_STATUS_BAD_PAGE);
+                valid = false;
+            }
+        }
+        if (valid) {
             koff = (unsigned long long)pg * page_elems + (size_t)g * a.page * a.d;      // the head's block of the page
             const T* kr = cache + koff;
             const int slot = j % a.page;
@@ -101,12 +111,12 @@ __global__ void attention_simt_kernel(AttnArgs a) {
 VCB_EXPORT int vcb_attention_simt(const void* q, const void* cache, void* out, const int* positions,
                                   const int* req_of_token, const int* block_table, int bt_stride,
                                   int n_tokens, int nh, int nkv, int d, int page, int window,
-                                  float scale, int dtype, void* stream) {
+                                  float scale, int num_pages, int* status, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
-    if (d <= 0 || d > ATT_MAX_D || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || window < 0)
+    if (d <= 0 || d > ATT_MAX_D || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || window < 0 || num_pages < 0)
         return VCB_ERR_BAD_ARG;
     AttnArgs a{q, cache, out, positions, req_of_token, block_table, bt_stride, n_tokens, nh, nkv, d,
-               page, window, scale};
+               page, window, scale, num_pages, status};
     const long long items = (long long)n_tokens * nh;
     const int blocks = (int)((items + ATT_WARPS - 1) / ATT_WARPS);
     const size_t smem = (size_t)ATT_WARPS * d * sizeof(float);

@@ -19,6 +19,9 @@ enum { VCB_F32 = 0, VCB_BF16 = 1 };
 // Return codes of the exported launchers beyond cudaError_t values.
 enum { VCB_ERR_BAD_ARG = 10001, VCB_ERR_UNSUPPORTED = 10002 };
 
+// Codes that kernels leave in the device status word (csrc/ops.py STATUS_MEANING names them all).
+enum { VCB_STATUS_BAD_PAGE = 11 };
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -72,6 +75,35 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 static inline int vcb_last_error() { return (int)cudaGetLastError(); }
+
+// Streaming multiprocessors of the current device, asked once per device (a cap for grid-stride grids).
+static inline int vcb_sm_count() {
+    static int count[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 128;
+    if (count[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 128;
+        count[dev] = n;
+    }
+    return count[dev];
+}
+
+// A kernel's cap on dynamic shared memory belongs to the (kernel, device) pair.  `done` is the calling
+// launcher's own word, one bit per device: the attribute is set at the first launch on each device.
+// (Two host threads that race here both set the same value.)
+template <typename K>
+static inline int vcb_allow_dynamic_smem(K kernel, int bytes, unsigned long long* done) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (dev < 64 && (__atomic_load_n(done, __ATOMIC_RELAXED) & bit)) return 0;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 64) __atomic_fetch_or(done, bit, __ATOMIC_RELAXED);
+    return 0;
+}
 
 // ---- layout of the cache
 // A page holds [k|v][kv head] blocks of page * head_dim elements.  When a row (one slot of one head)

@@ -241,7 +241,7 @@ VCB_EXPORT int vcb_silu_mul(const void* gu, void* out, int n_tokens, int inter, 
     if (dtype == VCB_BF16 && inter % 8 == 0 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
         const size_t n_vec = (size_t)n_tokens * (inter >> 3);
         size_t blocks = (n_vec + 1023) / 1024;
-        if (blocks > 148 * 16) blocks = 148 * 16;
+        if (blocks > vcb_sm_count() * 16) blocks = vcb_sm_count() * 16;
         if (n_vec < (1u << 30))
             vcb_launch(silu_mul_bf16x8_kernel<unsigned>, (int)blocks, 256, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
                        inter, (unsigned)n_vec);
@@ -285,7 +285,23 @@ struct RopeCacheArgs {
     void* q_out;
     void* cache;                // this layer's pages
     int bt_stride, nh, nkv, d, rot, pairing, page, write_kv;
+    int num_pages;              // pages of the cache: a table entry outside [0, num_pages) is not written through
+    int* status;                // receives VCB_STATUS_BAD_PAGE then (may be null)
 };
+
+// The page a token's k and v rows go to, or -1 (and a note in the status word) if the request's table
+// has no valid page there: a position beyond the table's width, an entry that was given back (-1) or one
+// that is no page of this cache.  Nothing is written then; the step's results are wrong and
+// ops.check_status() says why.
+__device__ __forceinline__ int checked_page(const RopeCacheArgs& a, int r, int pos) {
+    const int lp = pos / a.page;
+    const int pg = lp < a.bt_stride ? a.block_table[(size_t)r * a.bt_stride + lp] : -1;
+    if ((unsigned)pg >= (unsigned)a.num_pages) {
+        if (a.status) atomicCAS(a.status, 0, VCB_STATUS_BAD_PAGE);
+        return -1;
+    }
+    return pg;
+}
 
 template <typename T>
 __global__ void rope_cache_kernel(RopeCacheArgs a, int heads_per_block) {
@@ -323,8 +339,8 @@ __global__ void rope_cache_kernel(RopeCacheArgs a, int heads_per_block) {
         return;
     }
     if (!a.write_kv) return;
-    const int r = a.req_of_token[t];
-    const int pg = a.block_table[(size_t)r * a.bt_stride + pos / a.page];
+    const int pg = checked_page(a, a.req_of_token[t], pos);
+    if (pg < 0) return;
     const int slot = pos % a.page;
     // [page][2][nkv] blocks in the layout of kv_pos
     T* base = (T*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
@@ -375,8 +391,8 @@ __global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block, int 
         row_dst[k] = nullptr;
         slot[k] = 0;
         if (to_cache && a.write_kv && t0 + k < n_tokens) {
-            const int r = a.req_of_token[t0 + k];
-            const int pg = a.block_table[(size_t)r * a.bt_stride + pos[k] / a.page];
+            const int pg = checked_page(a, a.req_of_token[t0 + k], pos[k]);
+            if (pg < 0) continue;
             slot[k] = pos[k] % a.page;
             __nv_bfloat16* base = (__nv_bfloat16*)a.cache + (size_t)pg * 2 * a.nkv * a.page * a.d;
             const int kvh = h < a.nh + a.nkv ? h - a.nh : h - a.nh - a.nkv;
@@ -437,12 +453,12 @@ VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const in
                                     const int* req_of_token, const int* block_table, int bt_stride,
                                     const float* denom, void* q_out, void* cache, int n_tokens,
                                     int nh, int nkv, int d, int rot, int pairing, int page,
-                                    int write_kv, int dtype, void* stream) {
+                                    int write_kv, int num_pages, int* status, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
-    if (d <= 0 || (d & 1) || rot < 0 || rot > d || (rot & 1) || page <= 0 || nh <= 0 || nkv < 0)
+    if (d <= 0 || (d & 1) || rot < 0 || rot > d || (rot & 1) || page <= 0 || nh <= 0 || nkv < 0 || num_pages < 0)
         return VCB_ERR_BAD_ARG;
     RopeCacheArgs a{qkv, bias, positions, req_of_token, block_table, denom, q_out, cache,
-                    bt_stride, nh, nkv, d, rot, pairing, page, write_kv};
+                    bt_stride, nh, nkv, d, rot, pairing, page, write_kv, num_pages, status};
     const int half = d / 2, nheads = nh + 2 * nkv;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VCB_BF16 && pairing == 0 && rot == d && d % 16 == 0 && denom &&

@@ -593,12 +593,8 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int bo
 template <int BN, int STAGES>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int ctas, cudaStream_t s) {
     constexpr size_t smem = (size_t)STAGES * (P_BYTES + BN * BK * 2) + 1024 + 3072;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static unsigned long long configured = 0;
+    if (int e = vcb_allow_dynamic_smem(gemm_tcgen05_kernel<BN, STAGES>, (int)smem, &configured)) return e;
     vcb_launch(gemm_tcgen05_kernel<BN, STAGES>, ctas, GEMM_THREADS, smem, s, mp, mq, a);
     return vcb_last_error();
 }
@@ -648,7 +644,7 @@ VCB_EXPORT int vcb_tile_weights(const void* w, int rows, int k, int ld, int gate
     const int tiles = gated > 0 ? (gated + 63) / 64 : (rows + BM - 1) / BM;
     const size_t n_chunks = (size_t)tiles * k_slabs * 1024;
     size_t blocks = (n_chunks + 255) / 256;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > vcb_sm_count() * 32) blocks = vcb_sm_count() * 32;
     tile_weights_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)w, rows, k, ld, k_slabs,
                                                                        (uint4*)out, n_chunks, gated);
     return vcb_last_error();

@@ -35,6 +35,15 @@
 // kv head) find out who merges must start at zero; the entry point clears them on the
 // caller's stream before each launch.  Two calls that overlap on the GPU (different
 // streams) race on the array; run them on one stream or order them yourself.
+//
+// When the kernel cannot finish.  Every wait inside the kernel is bounded, and every page number it
+// reads from a block table is checked against num_pages.  A wait that runs out ends the CTA's loop
+// early; a page number outside [0, num_pages) is read as page 0.  Either way the call itself still
+// returns 0 (it only launches) and `out` is wrong.  The kernel notes what happened in a word beside
+// the array: vcb_attention_decode_mma_static_status waits for the device, hands the note back (0:
+// nothing happened; 5: a wait for a cache tile ran out; 11: a page number outside the cache) and
+// clears it.  Call it whenever a wrong result would matter, e.g. once every few hundred steps; it
+// allocates nothing either.
 #pragma once
 
 #ifdef __cplusplus
@@ -49,12 +58,18 @@ extern "C" {
 //   q, out: [n_tokens, nh * d] bfloat16; cache: [pages][2][nkv][page][d] bfloat16;
 //   q_start [n_reqs + 1], ctx_lens [n_reqs], block_table [n_reqs, bt_stride]: int32 on the device;
 //   req_list: n_list request indices on the device, or null for 0..n_list-1;
-//   nsplit: context splits per (request, kv head); stream: a cudaStream_t.
-// Returns 0, a cudaError_t value, or one of the VCB_ERR_* codes.
+//   nsplit: context splits per (request, kv head); page: slots per page, a multiple of 8;
+//   num_pages: pages the cache holds; stream: a cudaStream_t.
+// Returns 0, a cudaError_t value, or one of the VCB_ERR_* codes (10001 bad argument, 10002 a head
+// size other than 64 or 128 or a page size that is no multiple of 8; nothing is launched then).
 int vcb_attention_decode_mma_static(const void* q, const void* cache, void* out, const int* q_start,
                                     const int* ctx_lens, const int* block_table, int bt_stride,
                                     const int* req_list, int n_list, int nsplit, int nh, int nkv, int d,
-                                    int page, int window, float scale, void* stream);
+                                    int page, int window, float scale, int num_pages, void* stream);
+
+// *code = what the kernel noted since the last call of this function (see above); synchronises with the
+// device.  Returns 0 or a cudaError_t value.
+int vcb_attention_decode_mma_static_status(int* code);
 
 #ifdef __cplusplus
 }

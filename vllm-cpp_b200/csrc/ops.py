@@ -31,11 +31,11 @@ _SIGNATURES = {
     "vcb_add_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _P],
     "vcb_silu_mul": [_P, _P, _I, _I, _I, _P],
     "vcb_add_bias": [_P, _P, _I, _I, _I, _P],
-    "vcb_rope_cache_write": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
-    "vcb_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "vcb_rope_cache_write": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P],
+    "vcb_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
     "vcb_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
-    "vcb_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
+    "vcb_attention_decode_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "vcb_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "vcb_gemm_bf16_tcgen05": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
     "vcb_gemm_bf16_tcgen05_fused": [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P,
                                     _P, _I, _I, _I, _F, _P, _I, _P, _P, _I, _I, _P],
@@ -195,7 +195,8 @@ def rope_cache_write(qkv, bias, positions, req_of_token, block_table, denom, q_o
         _dev(block_table, "block_table", torch.int32), block_table.shape[1],
         None if denom is None else _dev(denom, "denom", torch.float32), _dev(q_out, "q_out"),
         _dev(cache, "cache"), n, num_heads, num_kv_heads, head_dim, rotary_dim, pairing, page_size,
-        1 if write_kv else 0, dtype_code(qkv.dtype), _stream()), "rope_cache_write")
+        1 if write_kv else 0, cache.shape[0], status_tensor(qkv.device).data_ptr(), dtype_code(qkv.dtype), _stream()),
+        "rope_cache_write")
 
 
 def attention_simt(q, cache, out, positions, req_of_token, block_table, *, num_heads: int,
@@ -209,7 +210,7 @@ def attention_simt(q, cache, out, positions, req_of_token, block_table, *, num_h
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(positions, "positions", torch.int32),
         _dev(req_of_token, "req_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], n, num_heads, num_kv_heads, head_dim, page_size, window, float(scale),
-        dtype_code(q.dtype), _stream()), "attention_simt")
+        cache.shape[0], status_tensor(q.device).data_ptr(), dtype_code(q.dtype), _stream()), "attention_simt")
 
 
 MMA_HEAD_DIMS = (64, 128)
@@ -226,7 +227,8 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
     columns as its context needs, so that requests of different lengths keep all CTAs equally busy."""
     _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
           "attention_decode_mma is a bfloat16 kernel")
-    _need(head_dim in MMA_HEAD_DIMS, f"attention_decode_mma takes head sizes {MMA_HEAD_DIMS}, got {head_dim}")
+    _need(head_dim in MMA_HEAD_DIMS and page_size % 8 == 0,
+          f"attention_decode_mma takes head sizes {MMA_HEAD_DIMS} and pages of a multiple of 8 slots, got {head_dim} and {page_size}")
     if nsplit > 1:
         need = n_list * num_heads * nsplit
         _need(part_o is not None and part_o.numel() >= need * head_dim and part_ml.numel() >= need * 2
@@ -240,7 +242,7 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
         None if part_ml is None else _dev(part_ml, "part_ml", torch.float32),
         None if counters is None else _dev(counters, "counters", torch.int32),
         None if split_tiles is None else _dev(split_tiles, "split_tiles", torch.int32),
-        num_heads, num_kv_heads, head_dim, page_size, window, float(scale),
+        num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
         status_tensor(q.device).data_ptr(), _stream()), "attention_decode_mma")
 
 
@@ -263,7 +265,7 @@ def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
         _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], _dev(tile_req, "tile_req", torch.int32), _dev(tile_row0, "tile_row0", torch.int32),
-        n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale),
+        n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
         status_tensor(q.device).data_ptr(), _stream()), "attention_prefill_tc")
 
 
@@ -278,14 +280,28 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                               a.stride(0), w.stride(0), out.stride(0), _stream()), "gemm_f32")
 
 
-SM_COUNT = 148
+_sm_count: Optional[int] = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the device the engine runs on, asked once (148 on a B200): the
+    most CTAs of a persistent kernel, and what the parts size their work lists by."""
+    global _sm_count
+    if _sm_count is None:
+        _need(torch.cuda.is_available(), "no CUDA device")
+        _sm_count = int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+    return _sm_count
+
+
 _status: Optional[torch.Tensor] = None
 STATUS_MEANING = {1: "the TMA producer waited too long for a free stage", 2: "the MMA issuer waited too long for a loaded stage",
                   3: "the epilogue waited too long for the accumulator", 4: "the MMA issuer waited too long for a free accumulator",
                   5: "decode attention waited too long for a cache tile", 6: "prefill attention waited too long for a cache tile",
                   8: "a product's merge waited too long for the tile's other segments",
                   9: "tcgen05 prefill attention waited too long on one of its barriers",
-                  10: "tcgen05 prefill attention found its shared memory not aligned to 1024 bytes"}
+                  10: "tcgen05 prefill attention found its shared memory not aligned to 1024 bytes",
+                  11: "a block table named a page that the cache does not have (a released or missing entry); "
+                      "nothing was written through it and attention read page 0 in its place"}
 
 
 def status_tensor(device) -> torch.Tensor:
@@ -375,7 +391,7 @@ def sumsq_parts(features: int) -> int:
     return 4 * (-(-features // 128))
 
 
-def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=None, max_ctas: int = SM_COUNT,
+def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=None, max_ctas: Optional[int] = None,
                       use_tiled: bool = True, x_scale: Optional[RowScale] = None,
                       fuse: Optional[ResidualNorm] = None, gated: bool = False) -> None:
     """out = x @ w^T on tcgen05 tensor cores fed by TMA (see gemm_tcgen05.cu); out bfloat16 or float32.
@@ -414,13 +430,14 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=
     if gated:
         _need(swapped and m <= bn <= 128 and tiled is not None and out.dtype == torch.bfloat16 and fuse is None,
               "gemm_bf16_tcgen05: the gated form needs few tokens, a gated tile image and a bfloat16 result")
-    partial = scratch("gemm_partial", SM_COUNT * 2 * 256 * 128, out.device)
+    sms = sm_count()
+    partial = scratch("gemm_partial", sms * 2 * 256 * 128, out.device)
     tickets = zeroed_ints("gemm_tickets", GEMM_MAX_TICKETS, out.device)
     _check(lib().vcb_gemm_bf16_tcgen05_fused(p.data_ptr(), p.shape[0], p.stride(0),
                                              None if tiled is None else tiled.data_ptr(),
                                              q.data_ptr(), q.shape[0], q.stride(0), k,
                                              out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0,
-                                             1 if swapped else 0, bn, min(max_ctas, SM_COUNT), partial.data_ptr(),
+                                             1 if swapped else 0, bn, min(max_ctas or sms, sms), partial.data_ptr(),
                                              tickets.data_ptr(), GEMM_MAX_TICKETS, status_tensor(out.device).data_ptr(),
                                              *sc, *fu, n // 2 if gated else 0, _stream()), "gemm_bf16_tcgen05")
 

@@ -16,9 +16,10 @@ import torch
 from ..cache.manager import CacheManager, cdiv
 from ..config.engine_config import ConfigError, EngineConfig
 from ..config.registry import read_config_json, resolve_architecture
-from ..parts.model import TORCH_DTYPES, DecoderModel
+from ..parts.model import TORCH_DTYPES, DecoderModel, build_model as build_from_spec
 from ..weights.loader import load_checkpoint
 from ..weights.random_init import init_random_on_device
+from .memory_plan import plan_for_model
 from .runner import ModelRunner
 
 
@@ -40,7 +41,7 @@ def build_model(cfg: EngineConfig, device) -> DecoderModel:
             raise ConfigError("model_path is empty")
         config_json = read_config_json(cfg.model_path)
     typed, spec = resolve_architecture(config_json, cfg.model_arch)
-    model = DecoderModel(spec, TORCH_DTYPES[cfg.dtype], device)
+    model = build_from_spec(spec, TORCH_DTYPES[cfg.dtype], device)
     model.typed_config = typed
     if cfg.load_format == "random":
         init_random_on_device(model, cfg.seed)
@@ -59,33 +60,32 @@ def build(cfg: EngineConfig) -> Tuple[DecoderModel, CacheManager, ModelRunner]:
     with torch.cuda.device(device), torch.no_grad():
         model = build_model(cfg, device)
         # the decode images of the weights may take a third of what the weights left free
+        torch.cuda.empty_cache()
         free, total = torch.cuda.mem_get_info(device)
         usable = int(total * cfg.gpu_memory_utilization / 100) - (total - free)
         model.prepare_products(image_budget=max(0, usable // 3))
-        specs = model.cache_specs()
         max_model_len = min(cfg.max_model_len, model.spec.max_position_embeddings)
+        # Every slice besides the pages is counted (engine/memory_plan.py); the workspace is allocated at the
+        # size the plan gives it.  With an explicit num_gpu_blocks the plan only sizes the workspace.
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()                  # what loading left cached goes back, so that "free" is exact
+        free, total = torch.cuda.mem_get_info(device)
+        from ..csrc import ops
+        try:
+            planned = plan_for_model(cfg, model, total, total - free, max_model_len, ops.sm_count())
+        except ConfigError:
+            if cfg.num_gpu_blocks is None:
+                raise
+            planned = None
+        specs = model.cache_specs()
         if cfg.num_gpu_blocks is not None:
             num_pages = cfg.num_gpu_blocks
         else:
-            # What the device still has after the weights, less a reserve for the
-            # step's work buffers and logits, split over the pages' cost; never more
-            # than every request at full length needs.  (src/model/qwen.cpp:86-99)
-            free, total = torch.cuda.mem_get_info(device)
-            budget = int(total * cfg.gpu_memory_utilization / 100) - (total - free)
-            el = 4 if cfg.dtype == "float32" else 2
-            widest = 1
-            for blk in model.blocks:
-                widest = max(widest, 4 * getattr(blk.feed_forward, "inter", model.hidden))
-            reserve = cfg.max_num_batched_tokens * (widest * el + 3 * model.hidden * 4) \
-                + cfg.max_num_seqs * model.vocab * 4 + (256 << 20)
-            per_page = max(1, CacheManager.bytes_per_page(specs, cfg.block_size, model.dtype))
-            want = cdiv(max_model_len, cfg.block_size) * cfg.max_num_seqs
-            num_pages = min(want, (budget - reserve) // per_page)
-            if num_pages < cdiv(max_model_len, cfg.block_size):
-                raise ConfigError(
-                    f"not enough device memory for one request of max_model_len {max_model_len}: "
-                    f"{num_pages} pages fit, {cdiv(max_model_len, cfg.block_size)} are needed")
+            num_pages = planned.num_pages
+            print("[vllm_cpp_b200] " + planned.table().replace("\n", "\n[vllm_cpp_b200] "), file=sys.stderr, flush=True)
         cache = CacheManager(specs, cfg.block_size, int(num_pages), cfg.max_num_seqs, model.dtype, device)
         runner = ModelRunner(model, cache, cfg.max_num_batched_tokens, cfg.max_num_seqs, max_model_len,
-                             device, use_cuda_graphs=cfg.use_cuda_graphs)
+                             device, use_cuda_graphs=cfg.use_cuda_graphs,
+                             workspace_bytes=planned.workspace_bytes if planned is not None else 0)
+        runner.memory_plan = planned
     return model, cache, runner

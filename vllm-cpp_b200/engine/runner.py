@@ -60,21 +60,21 @@ def _align(n: int, a: int = 4) -> int:
 
 class ModelRunner:
     def __init__(self, model, cache: CacheManager, max_num_batched_tokens: int, max_num_seqs: int,
-                 max_model_len: int, device, use_cuda_graphs: bool = False):
+                 max_model_len: int, device, use_cuda_graphs: bool = False, workspace_bytes: int = 0):
         self.model, self.cache, self.device = model, cache, device
         self.max_tokens, self.max_seqs, self.max_model_len = max_num_batched_tokens, max_num_seqs, max_model_len
         self.max_blocks = cdiv(max_model_len, cache.page_size)
         self.n_groups = len(cache.paged)
         self.views = cache.views()
-        self.ws = Workspace(device)
+        self.ws = Workspace(device, workspace_bytes)      # at its planned size it never grows
+        self.memory_plan = None
         self.logits = torch.empty((max(1, max_num_seqs), model.vocab), dtype=torch.float32, device=device)
         # work lists that parts ask for: name -> builder(HostStep) -> int32 numpy array
         self.array_builders: Dict[str, Callable[[HostStep], np.ndarray]] = {}
-        for blk in model.blocks:
-            for part in (blk.mixer, blk.feed_forward):
-                builders = getattr(part, "step_arrays", None)
-                if builders:
-                    self.array_builders.update(builders())
+        for owner in [p for blk in model.blocks for p in (blk, *blk.parts.values())] + [model.final_norm]:
+            builders = getattr(owner, "step_arrays", None)
+            if builders:
+                self.array_builders.update(builders())
         cap = self._meta_ints(self.max_tokens, self.max_seqs, self.max_tokens) + 64 * 1024
         self.meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
         self.meta_dev = torch.empty(cap, dtype=torch.int32, device=device)

@@ -14,6 +14,7 @@ restricts that to the last ``window`` keys, the query's own included.
 """
 from __future__ import annotations
 
+import sys
 from typing import Dict
 
 import numpy as np
@@ -21,9 +22,10 @@ import torch
 
 from ..config.model_spec import PartSpec
 from ..csrc import ops
-from .base import (POSITION_ENCODINGS, Mixer, PagedKVSpec, ParamSpec, build_part, register_mixer)
+from .base import (POSITION_ENCODINGS, Mixer, PagedKVSpec, ParamSpec, build_part, register_mixer, workspace_piece)
 
 MAX_HEAD_DIM = 256
+_warned_head_dims = set()
 
 
 @register_mixer("attention")
@@ -75,9 +77,19 @@ class PagedAttention(Mixer):
         self.position.load_params({k[len("position."):]: v for k, v in tensors.items()
                                    if k.startswith("position.")})
 
+        if self.dtype == torch.bfloat16 and self.d not in ops.MMA_HEAD_DIMS and self.d not in _warned_head_dims:
+            _warned_head_dims.add(self.d)
+            print(f"[vllm_cpp_b200] warning: head size {self.d} has no tensor-core attention kernel "
+                  f"(those take {ops.MMA_HEAD_DIMS}); bfloat16 attention runs the plain kernel, one warp per "
+                  "token and head, many times slower", file=sys.stderr, flush=True)
+
     # -- cache
     def cache_spec(self):
         return PagedKVSpec(self.nkv, self.d, self.window)
+
+    def workspace_bytes(self, n_tokens, n_reqs):
+        q = self.nh * self.d
+        return workspace_piece((n_tokens, q + 2 * self.nkv * self.d), self.dtype) + 2 * workspace_piece((n_tokens, q), self.dtype)
 
     # -- run
     def fuses_norm(self, n_tokens):
@@ -112,8 +124,6 @@ class PagedAttention(Mixer):
         ws.release(mark)
 
     # -- work lists and kernel choice
-    SM_COUNT = 148
-
     def _tensor_core_path(self) -> bool:
         return self.dtype == torch.bfloat16 and self.d in ops.MMA_HEAD_DIMS
 
@@ -181,7 +191,7 @@ class PagedAttention(Mixer):
         """Splits per kv head that a decode step may have in all: seven eighths of the places the device has
         for the kernel's CTAs (two per SM).  Filling every place was measured slower: the CTAs of the
         kernels before and after share the SMs, and a CTA that finds no place waits for a second round."""
-        return max(n_reqs, (2 * self.SM_COUNT * 7 // 8) // self.nkv)
+        return max(n_reqs, (2 * ops.sm_count() * 7 // 8) // self.nkv)
 
     def _splits_key(self):
         return f"attn_splits_kv{self.nkv}_w{self.window}"
@@ -199,7 +209,7 @@ class PagedAttention(Mixer):
                     longest = step.split_len or step.max_total_len
                     if self.window > 0:
                         longest = min(longest, self.window + 64)
-                    nsplit = max(1, min(-(-longest // 64), 2 * self.SM_COUNT // (step.n_reqs * self.nkv),
+                    nsplit = max(1, min(-(-longest // 64), 2 * ops.sm_count() // (step.n_reqs * self.nkv),
                                         ops.DECODE_MAX_SPLITS))
                     split_tiles = None
                 part_o = part_ml = counters = None

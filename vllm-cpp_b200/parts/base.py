@@ -67,7 +67,11 @@ class StepContext:
     """One batch as the parts see it: device arrays plus host copies of the small ones.
 
     Tokens are laid out request by request; request r owns rows
-    ``q_start[r] : q_start[r + 1]`` at positions ``ctx_lens[r] + 0, 1, …``.
+    ``q_start[r] : q_start[r + 1]`` at positions ``ctx_lens[r] + 0, 1, …``.  A kernel that keeps state
+    per request finds everything it needs on the device: token t belongs to request
+    ``req_of_token[t]``, whose state lives in slot ``state_slots[r]``; it is the first token the
+    request ever brought iff ``positions[t] == 0`` (the slot is zeroed at admission), and the first of
+    this step iff ``t == q_start[r]``.
     """
     n_tokens: int
     n_reqs: int
@@ -144,11 +148,34 @@ class Part:
     def load_params(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Receives the tensors of ``param_specs`` (on the device, roles' types applied)."""
 
+    def tensors(self) -> List[torch.Tensor]:
+        """Every device tensor the part holds (its own attributes and those of parts inside it)."""
+        out = []
+        for v in vars(self).values():
+            if isinstance(v, torch.Tensor):
+                out.append(v)
+            elif isinstance(v, Part):
+                out.extend(v.tensors())
+        return out
+
     def product_weights(self):
         """The weight matrices of this part's products as (matrix, gated) pairs, for the model's
         choice of kernels at load: ``gated`` is 0, or the number of gate features of a
         gate-and-up matrix that the part multiplies with ops.linear_gated."""
         return [(v, 0) for v in vars(self).values() if isinstance(v, torch.Tensor) and v.dim() == 2]
+
+    def step_arrays(self):
+        """Work lists the part wants built on the host for every step: name -> builder(HostStep) -> int32
+        numpy array.  The step function builds each once per step, uploads it with the step's other
+        arrays and hands it over as ``StepContext.extras[name]``; a builder may record a launch shape
+        it derived in ``HostStep.shapes`` (it reaches the part as ``StepContext.shapes`` and is part
+        of the key under which a decode step is captured).  Any part of any family may have some."""
+        return {}
+
+    def workspace_bytes(self, n_tokens: int, n_reqs: int) -> int:
+        """Most bytes of step workspace (Workspace.take) this part takes at once for a step of
+        ``n_tokens`` tokens of ``n_reqs`` requests; the engine sizes its memory plan with it."""
+        return 0
 
 
 class PositionEncoding(Part):
@@ -210,11 +237,44 @@ class FeedForward(Part):
 
 
 class Block:
-    """Arrangement of a layer's parts around the residual stream."""
+    """Arrangement of a layer's parts around the residual stream.
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
-        self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+    ``SLOTS`` names the arrangement's slots and the family of part each takes ("mixer",
+    "feed_forward" or "norm"); the model builds one part per slot from the layer's spec and hands
+    them over by name.  They are kept as attributes (``self.mixer`` ...) and, in the order of
+    ``SLOTS``, in ``self.parts``.  The model, the loader and the step function walk ``self.parts``;
+    none of them knows the slots' names.  An arrangement with other parts (a third norm, two
+    feed-forwards) declares them in its own ``SLOTS``."""
+
+    SLOTS: Dict[str, str] = {"mixer": "mixer", "feed_forward": "feed_forward",
+                             "mixer_norm": "norm", "feed_forward_norm": "norm"}
+
+    def __init__(self, **parts):
+        missing = [n for n in self.SLOTS if n not in parts]
+        extra = [n for n in parts if n not in self.SLOTS]
+        if missing or extra:
+            raise ValueError(f"{type(self).__name__} takes the parts {sorted(self.SLOTS)}; "
+                             f"missing {missing}, not known {extra}")
+        self.parts: Dict[str, Part] = {n: parts[n] for n in self.SLOTS}
+        for name, part in self.parts.items():
+            setattr(self, name, part)
+
+    def cache_spec(self):
+        """The cache need of the layer: that of its one part of the mixer family."""
+        mixers = [p for n, p in self.parts.items() if self.SLOTS[n] == "mixer"]
+        if len(mixers) != 1:
+            raise ValueError(f"{type(self).__name__} has {len(mixers)} mixers; it must say itself what its cache is")
+        return mixers[0].cache_spec()
+
+    def step_arrays(self):
+        """Per-step work lists of the arrangement itself, as Part.step_arrays (its parts are asked apart)."""
+        return {}
+
+    def workspace_bytes(self, n_tokens: int, n_reqs: int, hidden: int, dtype: torch.dtype) -> int:
+        """Most bytes of step workspace the layer holds at once in a model of width ``hidden`` computing in
+        ``dtype``.  Here: what its greediest part takes (the parts run one after the other and give back
+        what they took); an arrangement adds its own buffers."""
+        return max((p.workspace_bytes(n_tokens, n_reqs) for p in self.parts.values()), default=0)
 
     def accepts_prenormed(self, n_tokens: int):
         """(gain, eps) of the norm this block starts with if, for a step of ``n_tokens``, the block can
@@ -240,6 +300,8 @@ FEED_FORWARDS: Dict[str, Callable] = {}
 NORMS: Dict[str, Callable] = {}
 POSITION_ENCODINGS: Dict[str, Callable] = {}
 BLOCKS: Dict[str, Callable] = {}
+# family name (the values of Block.SLOTS) -> registry of the parts of that family
+FAMILIES: Dict[str, Dict[str, Callable]] = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}
 
 
 def _register(table, name):
@@ -254,6 +316,14 @@ def register_feed_forward(name): return _register(FEED_FORWARDS, name)
 def register_norm(name): return _register(NORMS, name)
 def register_position_encoding(name): return _register(POSITION_ENCODINGS, name)
 def register_block(name): return _register(BLOCKS, name)
+
+
+def workspace_piece(shape, dtype: torch.dtype) -> int:
+    """Bytes one Workspace.take of this shape and type advances the workspace by."""
+    n = dtype.itemsize
+    for d in shape:
+        n *= int(d)
+    return (n + 255) // 256 * 256
 
 
 def build_part(table: Dict[str, Callable], what: str, spec, **context):

@@ -16,13 +16,18 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Block, register_block
+from .base import Block, register_block, workspace_piece
 
 
 @register_block("prenorm")
 class PreNormBlock(Block):
     def accepts_prenormed(self, n_tokens):
         return self.mixer_norm.split() if self.mixer.fuses_norm(n_tokens) else None
+
+    def workspace_bytes(self, n_tokens, n_reqs, hidden, dtype):
+        own = 2 * workspace_piece((n_tokens, hidden), dtype) \
+            + workspace_piece((ops.sumsq_parts(hidden), n_tokens), torch.float32)
+        return own + super().workspace_bytes(n_tokens, n_reqs, hidden, dtype)
 
     def forward(self, residual, delta, pending, step, cache, writes_cache, ws, next_block=None, carry=None):
         mark = ws.mark()

@@ -11,7 +11,7 @@ from typing import Dict
 import torch
 
 from ..csrc import ops
-from .base import FeedForward, ParamSpec, register_feed_forward
+from .base import FeedForward, ParamSpec, register_feed_forward, workspace_piece
 
 
 @register_feed_forward("gated_mlp")
@@ -38,6 +38,10 @@ class GatedMLP(FeedForward):
 
     def fuses_norm(self, n_tokens):
         return ops.linear_fuses_norm(n_tokens, self.w_gate_up) and ops.linear_fuses_norm(n_tokens, self.w_down)
+
+    def workspace_bytes(self, n_tokens, n_reqs):
+        # the activations, and the gate-and-up product where the activation is a kernel of its own
+        return workspace_piece((n_tokens, self.inter), self.dtype) + workspace_piece((n_tokens, 2 * self.inter), self.dtype)
 
     def forward(self, x, out, step, ws, x_scale=None, fuse=None):
         n = x.shape[0]

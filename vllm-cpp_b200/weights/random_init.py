@@ -150,11 +150,11 @@ def write_random_model(path: str, config: dict, seed: int = 0, dtype: str = "bfl
     ``device``: where the values are computed ("cuda" is much faster for a large
     model; the file is the same).
     """
-    from ..parts.model import TORCH_DTYPES, DecoderModel
+    from ..parts.model import TORCH_DTYPES, build_model
     if dtype not in TORCH_DTYPES:
         raise ValueError(f"dtype must be one of {sorted(TORCH_DTYPES)}")
     _, spec = resolve_architecture(config, model_arch)
-    model = DecoderModel(spec, TORCH_DTYPES[dtype], "meta")
+    model = build_model(spec, TORCH_DTYPES[dtype], "meta")
     std = spec.init_std if std is None else std
     gain_std = spec.init_gain_std if gain_std is None else gain_std
     tensors = {}
