@@ -625,9 +625,12 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
     // while CTAs of this kernel still wait to be placed.
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = a.req_list[blockIdx.x];
-    const int row0 = a.tile_row0[blockIdx.x];
-    const int g = blockIdx.y;
+    // CTAs start in the order of their index: tile-major, so that the work list's first tiles (those with
+    // the most keys) start first for every kv head.  Head-major, a head's long tiles would start after the
+    // heads before it had started all of theirs, short ones included, and the kernel would end with them.
+    const int tile = blockIdx.x / a.nkv, g = blockIdx.x % a.nkv;
+    const int r = a.req_list[tile];
+    const int row0 = a.tile_row0[tile];
     const int G = a.nh / a.nkv;
     const int q0 = a.q_start[r], q_len = a.q_start[r + 1] - q0, ctx = a.ctx_lens[r];
     const int rows_total = q_len * G;
@@ -928,7 +931,7 @@ template <int D>
 static int launch_prefill_tc(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
     static unsigned long long configured = 0;
     if (int e = vcb_allow_dynamic_smem(tc::attention_prefill_tc_kernel<D>, tc::smem_bytes<D>(), &configured)) return e;
-    vcb_launch(tc::attention_prefill_tc_kernel<D>, dim3(n_tiles, a.nkv), tc::THREADS, (size_t)tc::smem_bytes<D>(), s, a);
+    vcb_launch(tc::attention_prefill_tc_kernel<D>, dim3((unsigned)n_tiles * a.nkv), tc::THREADS, (size_t)tc::smem_bytes<D>(), s, a);
     return vcb_last_error();
 }
 

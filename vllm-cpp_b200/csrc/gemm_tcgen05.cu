@@ -710,7 +710,7 @@ VCB_EXPORT int vcb_gemm_bf16_tcgen05_fused(const void* p, int rows_p, int ldp, c
     switch (bn) {
         case 16: return launch<16, 6>(mp, mq, a, ctas, s);
         case 32: return launch<32, 5>(mp, mq, a, ctas, s);
-        case 64: return launch<64, 8>(mp, mq, a, ctas, s);
+        case 64: return max_ctas > vcb_sm_count() ? launch<64, 4>(mp, mq, a, ctas, s) : launch<64, 8>(mp, mq, a, ctas, s);
         case 128: return launch<128, 6>(mp, mq, a, ctas, s);
         default: return launch<256, 4>(mp, mq, a, ctas, s);
     }

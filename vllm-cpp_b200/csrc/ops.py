@@ -431,13 +431,19 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=
         _need(swapped and m <= bn <= 128 and tiled is not None and out.dtype == torch.bfloat16 and fuse is None,
               "gemm_bf16_tcgen05: the gated form needs few tokens, a gated tile image and a bfloat16 result")
     sms = sm_count()
+    if max_ctas is None:
+        # Tiles of 32 and 64 columns: two CTAs of the product on every SM (its ring is then four or five
+        # stages deep each).  A stage carries the tokens' operand beside the weights', half as much again at
+        # 64 tokens, and one CTA's ring does not hold enough bytes in flight for the memory's rate
+        # (measured at 64 tokens, 7B sizes: gate-and-up 49.9 -> 44.6 us, qkv 14.8 -> 12.8; at 128 it is slower).
+        max_ctas = 2 * sms if bn in (32, 64) else sms
     partial = scratch("gemm_partial", sms * 2 * 256 * 128, out.device)
     tickets = zeroed_ints("gemm_tickets", GEMM_MAX_TICKETS, out.device)
     _check(lib().vcb_gemm_bf16_tcgen05_fused(p.data_ptr(), p.shape[0], p.stride(0),
                                              None if tiled is None else tiled.data_ptr(),
                                              q.data_ptr(), q.shape[0], q.stride(0), k,
                                              out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0,
-                                             1 if swapped else 0, bn, min(max_ctas or sms, sms), partial.data_ptr(),
+                                             1 if swapped else 0, bn, min(max_ctas, 2 * sms), partial.data_ptr(),
                                              tickets.data_ptr(), GEMM_MAX_TICKETS, status_tensor(out.device).data_ptr(),
                                              *sc, *fu, n // 2 if gated else 0, _stream()), "gemm_bf16_tcgen05")
 
