@@ -175,3 +175,37 @@ def test_long_decoding_stays_on_the_plain_logits(tmp_path):
         eng.cache.free_request("long")
         from helpers import compare
         compare(np.concatenate(rows), plain.forward(weights, cfg, ids), dtype, f"{name} long decode")
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_preemption_under_captured_steps_in_bfloat16(tmp_path, name):
+    """bfloat16, CUDA graphs, steps launched ahead, and so few pages that running requests are preempted
+    and recomputed while others decode: every generated token is the plain implementation's choice given
+    the tokens before it (or within rounding of it), every request gets its full length, nothing is left
+    behind, and the requests that were never preempted get the tokens they get with plenty of pages."""
+    from vllm_cpp_b200 import SamplingParams
+    cfg, page = CONFIGS[name]
+    prompts = [token_ids(cfg, n, 60 + n) for n in (70, 9, 45, 120, 30)]
+    sp = SamplingParams(max_tokens=48, temperature=0.0, ignore_eos=True)
+    need = [-(-(len(p) + 48) // page) for p in prompts]
+    _, weights, roomy = make_llm(tmp_path, name, "bfloat16", use_cuda_graphs=True, num_gpu_blocks=sum(need) + 2)
+    plenty = roomy.generate(prompts, sp)
+    assert roomy.engine.scheduler.num_preemptions == 0
+    # room for all the prompts and one page more: every request is admitted, and as they grow the newest are
+    # preempted and recomputed
+    _, _, tight = make_llm(tmp_path, name, "bfloat16", use_cuda_graphs=True,
+                           num_gpu_blocks=sum(-(-len(p) // page) for p in prompts) + 1)
+    eng = tight.engine
+    ids = [eng.add_request(p, sp) for p in prompts]
+    got = {i: [] for i in ids}
+    while eng.has_pending_work():
+        for o in eng.step():
+            got[o.seq_id].extend(o.tokens)
+    assert eng.scheduler.num_preemptions > 0 and eng.runner.graphs, "the run must preempt and must replay graphs"
+    assert not eng.cache.requests and eng.cache.num_free_pages() == eng.cache.num_pages
+    for i, p, ref in zip(ids, prompts, plenty):
+        assert len(got[i]) == 48
+        check_greedy(weights, cfg, p, got[i], "bfloat16")
+        # same tokens as with plenty of pages up to the first near tie that rounding decided otherwise
+        same = next((k for k, (x, y) in enumerate(zip(got[i], ref)) if x != y), 48)
+        assert same >= 8, f"request {i} leaves the roomy run's tokens after {same}"

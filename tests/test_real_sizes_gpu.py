@@ -215,3 +215,28 @@ def test_decode_under_cuda_graphs(engine, batch):
     for i in sorted({0, 1, batch // 2, batch - 1}):
         rows = list(range(lens[i], lens[i] + steps))
         check(got["g"], size, f"g{batch}_{i}", reqs[i], rows, f"{mode} graphs batch {batch} request {i}")
+
+
+def test_a_step_of_2048_tokens_with_portions_and_decoded_tokens(engine):
+    """The shape the continuous-batching benchmark runs: a step at the token budget of 2,048 that holds two
+    decoding requests, the end of one long prompt and the middle of another (what serving runs: the tuned
+    products only)."""
+    from vllm_cpp_b200.cache.manager import CacheManager
+    from vllm_cpp_b200.engine.runner import ModelRunner
+    size, mode, _, runner, _ = engine
+    if mode != "tuned" or size != "7b":
+        pytest.skip("one configuration is enough for this shape")
+    pages, max_len = 4 * 130, 2048
+    cache = CacheManager(runner.model.cache_specs(), PAGE, pages, 4, runner.model.dtype, runner.device)
+    big = ModelRunner(runner.model, cache, 2048, 4, max_len, runner.device)
+    reqs = {"a": ids_of(50, 71), "b": ids_of(33, 72), "c": ids_of(1400, 73), "d": ids_of(1700, 74)}
+    rp = Replayer(big, cache)
+    rp.step([("a", reqs["a"][:49], []), ("b", reqs["b"][:32], []), ("c", reqs["c"][:300], []), ("d", reqs["d"][:600], [])])
+    # 1 + 1 + 1100 + 946 = 2048 tokens
+    rp.step([("a", reqs["a"][49:], [0]), ("c", reqs["c"][300:], [0, 555, 1099]), ("b", reqs["b"][32:], [0]),
+             ("d", reqs["d"][600:1546], [0, 400, 945])], end=["a", "b", "c", "d"])
+    assert cache.num_free_pages() == pages
+    check(rp, size, "a", reqs["a"], [49], "2048-token step a")
+    check(rp, size, "b", reqs["b"], [32], "2048-token step b")
+    check(rp, size, "c", reqs["c"], [300, 855, 1399], "2048-token step c")
+    check(rp, size, "d", reqs["d"][:1546], [600, 1000, 1545], "2048-token step d")
