@@ -253,6 +253,132 @@ def flat_config(cfg, a, nums, extra):
     return out
 
 
+# ---------------------------------------------------------------------------------------- kernels one by one
+def run_kernels(cfg) -> int:
+    """Every kernel of the step alone at the benchmark's layer sizes: microseconds (CUDA events around a CUDA
+    graph of several launches on rotating buffers, so that neither the host nor the L2 cache flatters them) and
+    what that is in GB/s of the bytes the kernel must move or in TFLOP/s.  One text table."""
+    import numpy as np
+    import torch
+    from vllm_cpp_b200.csrc import ops
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    h, nh, nkv, inter, vocab = (cfg[k] for k in ("hidden_size", "num_attention_heads", "num_key_value_heads",
+                                                 "intermediate_size", "vocab_size"))
+    d, page, bf = h // nh, 16, torch.bfloat16
+    dev = "cuda"
+    rows = []
+
+    def rnd(*shape, dtype=bf, scale=1.0):
+        return (torch.randn(*shape, device=dev) * scale).to(dtype)
+
+    def add(name, fn, n_copies, bytes_=0, flops=0):
+        us = ops.time_in_graph(fn, reps=max(4, n_copies))
+        rows.append((name, us, bytes_ / us / 1e3 if bytes_ else None, flops / us / 1e6 if flops else None))
+
+    for t in (8, 2048):
+        copies = 6 if t == 8 else 3
+        ids = torch.randint(0, vocab, (t,), dtype=torch.int32, device=dev)
+        table = rnd(vocab, h, scale=0.02)
+        res = [torch.zeros(t, h, device=dev) for _ in range(copies)]
+        add(f"embedding, {t} tokens", lambda i: ops.embedding(table, ids, res[i % copies]), copies, bytes_=t * h * 6)
+        delta, normed = [rnd(t, h) for _ in range(copies)], [torch.empty(t, h, dtype=bf, device=dev) for _ in range(copies)]
+        gain = torch.ones(h, device=dev)
+        add(f"residual add + RMSNorm, {t} tokens",
+            lambda i: ops.add_rmsnorm(res[i % copies], delta[i % copies], gain, normed[i % copies], 1e-6), copies, bytes_=t * h * 12)
+        del table
+        # bias + rotation + cache write
+        width = (nh + 2 * nkv) * d
+        qkv, q_out = [rnd(t, width) for _ in range(copies)], torch.empty(t, nh * d, dtype=bf, device=dev)
+        cache = torch.zeros(t // page + 2, 2, nkv, page * d, dtype=bf, device=dev)
+        pos = torch.arange(t, dtype=torch.int32, device=dev)
+        req = torch.zeros(t, dtype=torch.int32, device=dev)
+        bt = torch.arange(t // page + 2, dtype=torch.int32, device=dev).view(1, -1)
+        denom = torch.from_numpy(np.power(np.float32(1e6), np.arange(d // 2, dtype=np.float32) * 2 / d).astype(np.float32)).to(dev)
+        bias = torch.zeros(width, device=dev)
+        add(f"q/k/v bias + rotation + cache write, {t} tokens",
+            lambda i: ops.rope_cache_write(qkv[i % copies], bias, pos, req, bt, denom, q_out, cache, num_heads=nh, num_kv_heads=nkv,
+                                           head_dim=d, rotary_dim=d, pairing=0, page_size=page, write_kv=True),
+            copies, bytes_=t * width * 4)
+    # SwiGLU on the library's gate-and-up product (prefill)
+    t = 2048
+    gu, act = [rnd(t, 2 * inter) for _ in range(2)], torch.empty(t, inter, dtype=bf, device=dev)
+    add("silu(gate) * up, 2,048 tokens", lambda i: ops.silu_mul(gu[i % 2], act), 2, bytes_=t * inter * 6)
+    del gu, act
+    # products: the engine's kernel at 8 tokens (plain epilogue; the fused ones are in the decode timeline), the library's at 2,048
+    shapes = [("qkv", (nh + 2 * nkv) * d, h), ("output projection", h, nh * d), ("gate and up", 2 * inter, h), ("down", h, inter)]
+    for name, n, k in shapes:
+        copies = 6 if n * k < 1e8 else 3
+        ws = [rnd(n, k, scale=0.02) for _ in range(copies)]
+        for w in ws:
+            ops.tile_weights(w)
+        x8, o8 = rnd(8, k), torch.empty(8, n, dtype=bf, device=dev)
+        add(f"product {name} [{n} x {k}], 8 tokens (tcgen05)", lambda i: ops.gemm_bf16_tcgen05(x8, ws[i % copies], o8), copies,
+            bytes_=n * k * 2)
+        x, o = rnd(2048, k), torch.empty(2048, n, dtype=bf, device=dev)
+        add(f"product {name}, 2,048 tokens (cuBLAS)", lambda i: ops._library_mm(x, ws[i % copies], o), copies, flops=2.0 * 2048 * n * k)
+        del ws
+    head = rnd(vocab, h, scale=0.02)
+    ops.tile_weights(head)
+    x8, logits = rnd(8, h), torch.empty(8, vocab, device=dev)
+    add(f"output product [{vocab} x {h}], 8 rows, float32 logits", lambda i: ops.gemm_bf16_tcgen05(x8, head, logits), 4, bytes_=vocab * h * 2)
+    del head
+    # attention
+    for t in (2048, 8192):
+        n_pages = t // page + 2
+        cache = rnd(n_pages, 2, nkv, page * d, scale=0.5)
+        q, out = rnd(t, nh * d), torch.empty(t, nh * d, dtype=bf, device=dev)
+        bt = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+        q_start = torch.tensor([0, t], dtype=torch.int32, device=dev)
+        ctx = torch.zeros(1, dtype=torch.int32, device=dev)
+        g = nh // nkv
+        n_tiles = -(-t * g // ops.TC_ATTENTION_TILE_ROWS)
+        order = np.argsort(-np.arange(n_tiles), kind="stable")          # the tiles with the most keys first
+        tile_req = torch.zeros(n_tiles, dtype=torch.int32, device=dev)
+        tile_row0 = torch.from_numpy((np.arange(n_tiles, dtype=np.int32) * ops.TC_ATTENTION_TILE_ROWS)[order].copy()).to(dev)
+        add(f"prefill attention, one prompt of {t}", lambda i: ops.attention_prefill_tc(
+            q, cache, out, q_start, ctx, bt, tile_req, tile_row0, num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page,
+            window=0, scale=d ** -0.5), 4, flops=4.0 * nh * d * t * (t + 1) / 2)
+    from vllm_cpp_b200.config.model_spec import PartSpec
+    from vllm_cpp_b200.engine.runner import HostStep
+    from vllm_cpp_b200.parts.attention import PagedAttention
+    part = PagedAttention(h, nh, nkv, d, True, False, 0, PartSpec("none"), bf, dev)
+    for batch in (8, 64):
+        c = CONTEXT - 1
+        blocks = CONTEXT // page
+        cache = rnd(batch * blocks + 1, 2, nkv, page * d, scale=0.5)
+        q, out = rnd(batch, nh * d), torch.empty(batch, nh * d, dtype=bf, device=dev)
+        bt = torch.arange(batch * blocks, dtype=torch.int32, device=dev).view(batch, blocks)
+        q_start = torch.arange(batch + 1, dtype=torch.int32, device=dev)
+        ctx = torch.full((batch,), c, dtype=torch.int32, device=dev)
+        host = HostStep([1] * batch, [c] * batch, page)
+        per = part.step_arrays()[part._splits_key()](host)
+        nsplit = host.shapes[part._splits_key()]
+        split_tiles = torch.from_numpy(per).to(dev)
+        need = batch * nh * nsplit
+        po, pml = torch.empty(need * d, device=dev), torch.empty(need * 2, device=dev)
+        tickets = torch.zeros(batch * nkv, dtype=torch.int32, device=dev)
+        add(f"decode attention, batch {batch}, contexts of {CONTEXT}", lambda i: ops.attention_decode_mma(
+            q, cache, out, q_start, ctx, bt, None, batch, nsplit, po, pml, tickets, num_heads=nh, num_kv_heads=nkv, head_dim=d,
+            page_size=page, window=0, scale=d ** -0.5, split_tiles=split_tiles), 4, bytes_=batch * CONTEXT * 2 * nkv * d * 2)
+        del cache
+    logits = rnd(64, vocab, dtype=torch.float32)
+    temp, uni, ids = torch.zeros(64, device=dev), torch.zeros(64, device=dev), torch.empty(64, dtype=torch.int32, device=dev)
+    add("sampling (greedy), 64 rows", lambda i: ops.sample(logits, temp, uni, ids), 4, bytes_=64 * vocab * 4)
+    temp.fill_(0.8)
+    add("sampling (temperature), 64 rows", lambda i: ops.sample(logits, temp, uni, ids), 4, bytes_=64 * vocab * 4)
+    w = torch.empty(2 * inter, h, dtype=bf, device=dev)
+    add("random weights, one gate-and-up matrix", lambda i: ops.random_normal(w, 12345 + i, 0.0, 0.02), 4, bytes_=w.numel() * 2)
+    ops.check_status()
+    peaks = load_peaks()
+    print(f"# kernels alone, Qwen2.5-7B layer sizes, bfloat16; peaks ({peaks['source']}): {peaks['hbm_gbs']:.0f} GB/s, "
+          f"{peaks['bf16_tflops']:.0f} TFLOP/s (burst)")
+    print(f"{'kernel':<62s} {'us':>9s} {'GB/s':>8s} {'TFLOP/s':>8s} {'of peak':>8s}")
+    for name, us, gbs, tf in rows:
+        frac = gbs / peaks["hbm_gbs"] if gbs else tf / peaks["bf16_tflops"]
+        print(f"{name:<62s} {us:9.1f} {gbs if gbs else float('nan'):8.0f} {tf if tf else float('nan'):8.1f} {frac:8.2f}")
+    return 0
+
+
 # ------------------------------------------------------------------------------------------ reference arm
 REFERENCE_NOTES = ("the reference's own faults at these sizes, none of which changes the work of a step: an untied lm_head is "
                    "copied over the embedding table (src/model/qwen.cpp:279-281); the bias area of 3*1024 floats a layer "
@@ -373,6 +499,9 @@ def main() -> int:
     ap.add_argument("--mix", action="store_true",
                     help="instead of the fixed-batch measurement: 32 requests with prompts of 128 to 4,096 tokens and "
                          "256 generated tokens each through the engine, 2,048 tokens a step (continuous batching)")
+    ap.add_argument("--kernels", action="store_true",
+                    help="instead of the step: every kernel alone at these layer sizes, a text table of microseconds "
+                         "and achieved GB/s or TFLOP/s")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only (for profiling); the other fields of the line are null")
@@ -412,6 +541,8 @@ def main() -> int:
         ops.set_tcgen05_linear(False)
     if a.mix:
         return run_mix(cfg, a)
+    if a.kernels:
+        return run_kernels(cfg)
     nums = model_numbers(cfg)
     peaks = load_peaks()
     max_batch = max(64, a.batch)
