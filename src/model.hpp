@@ -1,0 +1,60 @@
+// The Qwen2 model of the C++ host (see model.cpp).
+#pragma once
+
+#include <fstream>
+
+#include "host.hpp"
+
+namespace vllm {
+namespace host {
+
+class Qwen2Model {
+  public:
+    Qwen2Model(const EngineConfig& cfg, const Qwen2Config& mc, bool bf16);
+    ~Qwen2Model();
+
+    // Sizes, known from the configuration alone, from which the engine sizes the one pool.
+    size_t weight_bytes() const;
+    size_t step_bytes() const;                  // buffers of a step at the token budget, logits, kernels' scratch
+    size_t bytes_per_page() const;              // one page id over all layers
+    size_t max_logit_rows() const { return std::max<size_t>(cfg_.max_num_seqs, std::min<size_t>(cfg_.max_num_batched_tokens, 1024)); }
+    const std::vector<int>& group_windows() const { return group_windows_; }
+    const Qwen2Config& config() const { return mc_; }
+
+    void place(DevicePool& pool, int num_pages);          // takes every slice: weights, pages, step buffers, scratch
+    void load_weights(const std::string& model_path);     // by tensor name; one error lists all faults
+    // Runs the batch's tokens from the cache; returns the float32 logits [n_logit_rows, vocab] on the device.
+    const float* forward(const Batch& b, cudaStream_t s);
+    int read_status();                                    // what a kernel noted (0: nothing); synchronises
+
+  private:
+    struct Layer {
+        void *w_qkv = nullptr, *w_o = nullptr, *w_gate_up = nullptr, *w_down = nullptr;
+        float *b_qkv = nullptr, *gain_in = nullptr, *gain_post = nullptr;
+    };
+    std::map<std::string, std::vector<int64_t>> expected_tensors() const;
+    void upload(const TensorInfo& t, void* dst, bool as_float32);
+    void linear(const void* x, const void* w, void* out, int m, int n, int k, bool out_f32, cudaStream_t s);
+    void attend(const Batch& b, int layer, cudaStream_t s);
+
+    EngineConfig cfg_;
+    Qwen2Config mc_;
+    bool bf16_;
+    size_t el_;
+    int dt_, sms_ = 148, num_pages_ = 0;
+    float scale_ = 1.0f;
+    std::vector<int> group_windows_, layer_group_, layer_index_in_group_;
+    std::vector<Layer> layers_;
+    std::vector<void*> pages_;
+    void *embed_ = nullptr, *lm_head_ = nullptr;
+    float *final_gain_ = nullptr, *denom_ = nullptr;
+    float* residual_ = nullptr;
+    void *delta_ = nullptr, *h_ = nullptr, *mixed_ = nullptr, *qkv_ = nullptr, *q_ = nullptr, *attn_ = nullptr, *gate_up_ = nullptr,
+         *act_ = nullptr, *normed_ = nullptr;
+    float *logits_ = nullptr, *gemm_partial_ = nullptr, *part_o_ = nullptr, *part_ml_ = nullptr;
+    int *gemm_tickets_ = nullptr, *status_ = nullptr, *attn_tickets_ = nullptr;
+    void* cublas_ = nullptr;
+};
+
+}  // namespace host
+}  // namespace vllm

@@ -1,0 +1,209 @@
+"""The C++ host runtime (include/vllm/vllm.hpp, src/) against the plain implementation and against the
+Python host: explicit batches cut every way, the two tiny workloads under its scheduler with the same token
+ids as the Python engine, preemption, its loader's errors, its pool, its command line."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+import plain_qwen2 as plain
+from helpers import CONFIGS, compare, make_weights, model_folder, token_ids
+
+pytestmark = pytest.mark.gpu
+
+
+class CppReplayer:
+    """helpers.Replayer for the C++ host: request names become small integers."""
+
+    def __init__(self, eng):
+        self.eng, self.fed, self.rows, self.ids = eng, {}, {}, {}
+
+    def step(self, entries, end=()):
+        batch = []
+        for rid, toks, want in entries:
+            if rid not in self.ids:
+                self.ids[rid] = len(self.ids)
+                self.fed[rid] = 0
+            batch.append((self.ids[rid], list(toks), list(want)))
+        logits = self.eng.step_tokens(batch)
+        i = 0
+        for rid, toks, want in entries:
+            for w in want:
+                self.rows[(rid, self.fed[rid] + w)] = logits[i].copy()
+                i += 1
+            self.fed[rid] += len(toks)
+        for rid in end:
+            self.eng.release(self.ids[rid])
+
+    def logits_of(self, rid, positions):
+        return np.stack([self.rows[(rid, p)] for p in positions])
+
+
+def cpp_engine(tmp_path, name, dtype, seed=1, **kw):
+    from vllm_cpp_b200.engine.cpp_host import CppEngine
+    cfg, page = CONFIGS[name]
+    weights = make_weights(cfg, seed, dtype)
+    folder = model_folder(tmp_path, cfg, weights, dtype)
+    args = dict(dtype=dtype, block_size=page, num_gpu_blocks=40, max_num_seqs=8, max_model_len=cfg["max_position_embeddings"],
+                max_num_batched_tokens=1024)
+    args.update(kw)
+    return cfg, weights, folder, CppEngine(folder, **args)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+def test_explicit_batches_cut_every_way(tmp_path, name, dtype):
+    from test_replay_gpu import mixed_trace
+    cfg, page = CONFIGS[name]
+    pages = 4 * (-(-120 // page)) + 1
+    cfg, weights, _, eng = cpp_engine(tmp_path, name, dtype, num_gpu_blocks=max(pages, -(-231 // page) + 1))
+    total = eng.num_total_blocks
+    assert 0 < eng.pool_used_bytes <= eng.pool_total_bytes
+    rp = CppReplayer(eng)
+    # whole, then most of it at once and the last 32 one by one
+    ids = token_ids(cfg, 150, 300)
+    rp.step([("w", ids, range(150))], end=["w"])
+    compare(rp.logits_of("w", range(150)), plain.forward(weights, cfg, ids), dtype, f"{name} whole")
+    rp.step([("d", ids[:118], [117])])
+    for t in range(118, 150):
+        rp.step([("d", ids[t:t + 1], [0])])
+    rp.step([("x", [1, 2], [])], end=["d", "x"])
+    compare(rp.logits_of("d", range(117, 150)), plain.forward(weights, cfg, ids)[117:], dtype, f"{name} decode")
+    # portions down to two tokens
+    ids = token_ids(cfg, 231, 301)
+    at = 0
+    for s in [7, 2, 13, 3, 2, 31, 16, 2, 5, 33, 2, 64, 17, 34]:
+        rp.step([("p", ids[at:at + s], range(s))])
+        at += s
+    assert at == 231
+    rp.step([("y", [3, 4], [])], end=["p", "y"])
+    compare(rp.logits_of("p", range(231)), plain.forward(weights, cfg, ids), dtype, f"{name} portions")
+    assert eng.num_free_blocks == total
+    # four live requests mixed, pages used again
+    todo, steps = mixed_trace(cfg, seed=11)
+    for entries, end in steps:
+        rp.step(entries, end)
+    assert eng.num_free_blocks == total
+    for rid, ids, _ in todo:
+        compare(rp.logits_of(rid, range(len(ids))), plain.forward(weights, cfg, ids), dtype, f"{name} mixed {rid}")
+
+
+def python_llm(folder, name, dtype, **kw):
+    from vllm_cpp_b200 import LLM
+    cfg, page = CONFIGS[name]
+    args = dict(dtype=dtype, block_size=page, num_gpu_blocks=64, max_num_seqs=8, max_model_len=cfg["max_position_embeddings"],
+                max_num_batched_tokens=256)
+    args.update(kw)
+    return LLM(folder, **args)
+
+
+def test_the_tiny_workloads_give_the_same_tokens_on_both_hosts(tmp_path):
+    """Configuration A: prompts 5, 17, 33, greedy, 8 tokens.  Configuration B: prompts 1, 9, 40, 64, 100, a
+    24-token budget mixed with decoding, temperature 0.8 with fixed seeds, 12 tokens; and once more on so few
+    pages that requests are preempted and recomputed.  float32: both hosts launch the same kernels."""
+    from vllm_cpp_b200 import SamplingParams
+    cfg, weights, folder, eng = cpp_engine(tmp_path, "A", "float32", seed=21, num_gpu_blocks=64, max_num_batched_tokens=256)
+    prompts = [token_ids(cfg, n, 50 + n) for n in (5, 17, 33)]
+    got = eng.generate(prompts, max_tokens=8, temperature=0.0, ignore_eos=True)
+    want = python_llm(folder, "A", "float32").generate(prompts, SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))
+    assert got == want and all(len(o) == 8 for o in got)
+    assert eng.num_free_blocks == 64 and not eng.has_pending_work()
+    eng.close()
+
+    cfg, weights, folder, eng = cpp_engine(tmp_path, "B", "float32", seed=21, num_gpu_blocks=64, max_num_batched_tokens=32,
+                                           max_tokens_per_step=24)
+    prompts = [token_ids(cfg, n, 70 + n) for n in (1, 9, 40, 64, 100)]
+    per = [dict(max_tokens=12, temperature=0.8, seed=1000 + i, ignore_eos=True) for i in range(5)]
+    got = eng.generate(prompts, per_request=per)
+    params = [SamplingParams(max_tokens=12, temperature=0.8, seed=1000 + i, ignore_eos=True) for i in range(5)]
+    want = python_llm(folder, "B", "float32", max_tokens_per_step=24, max_num_batched_tokens=32).generate(prompts, params)
+    assert got == want and all(len(o) == 12 for o in got)
+    eng.close()
+    # 7 pages of 32: the five requests need 9 at their longest
+    _, _, _, small = cpp_engine(tmp_path, "B", "float32", seed=21, num_gpu_blocks=7, max_tokens_per_step=24)
+    squeezed = small.generate(prompts, per_request=per)
+    assert small.num_preemptions > 0 and squeezed == want and small.num_free_blocks == 7
+    # top-k, top-p and the repetition penalty take the same path on both hosts
+    per = [dict(max_tokens=10, temperature=1.1, top_k=20, top_p=0.9, repetition_penalty=1.3, seed=7 + i, ignore_eos=True) for i in range(5)]
+    params = [SamplingParams(max_tokens=10, temperature=1.1, top_k=20, top_p=0.9, repetition_penalty=1.3, seed=7 + i, ignore_eos=True)
+              for i in range(5)]
+    _, _, _, eng = cpp_engine(tmp_path, "B", "float32", seed=21, num_gpu_blocks=64)
+    assert eng.generate(prompts, per_request=per) == python_llm(folder, "B", "float32").generate(prompts, params)
+
+
+def test_stop_tokens_abort_and_refusals(tmp_path):
+    from vllm_cpp_b200.engine.cpp_host import CppEngineError
+    cfg, weights, folder, eng = cpp_engine(tmp_path, "A", "float32", seed=21, num_gpu_blocks=64)
+    p = token_ids(cfg, 12, 3)
+    free = eng.generate([p], max_tokens=10, temperature=0.0, ignore_eos=True)[0]
+    stop = free[3]
+    assert eng.generate([p], max_tokens=10, temperature=0.0, stop_token_ids=[stop])[0] == free[:free.index(stop) + 1]
+    a = eng.add_request(p, max_tokens=50, temperature=0.0, ignore_eos=True)
+    b = eng.add_request(p, max_tokens=5, temperature=0.0, ignore_eos=True)
+    eng.step(); eng.step()
+    eng.abort_request(a)
+    seen = []
+    while eng.has_pending_work():
+        seen += eng.step()
+    assert {r for r, _, _ in seen} == {b} and seen[-1][2] == "length" and eng.num_free_blocks == 64
+    for bad, msg in (([], "at least one token"), ([cfg["vocab_size"]], "vocabulary"), (list(range(10)) * 40, "context length")):
+        with pytest.raises(CppEngineError, match=msg):
+            eng.add_request(bad, max_tokens=4)
+    with pytest.raises(CppEngineError, match="context length"):
+        eng.add_request([1, 2, 3], max_tokens=10_000)
+    with pytest.raises(CppEngineError, match="appears twice"):
+        eng.step_tokens([(0, [1], []), (0, [2], [])])
+
+
+def test_loader_and_configuration_errors(tmp_path):
+    import json
+    from vllm_cpp_b200.engine.cpp_host import CppEngine, CppEngineError
+    cfg, page = CONFIGS["B"]
+    w = make_weights(cfg, 0, "float32")
+    broken = dict(w)
+    del broken["model.layers.1.mlp.up_proj.weight"], broken["lm_head.weight"]
+    broken["model.layers.9.extra.weight"] = np.zeros(3, dtype=np.float32)
+    broken["model.layers.0.self_attn.q_proj.bias"] = np.zeros(7, dtype=np.float32)
+    folder = str(tmp_path / "broken")
+    plain.write_model_folder(folder, cfg, broken, store="F32")
+    with pytest.raises(CppEngineError) as e:
+        CppEngine(folder, dtype="float32", block_size=32, num_gpu_blocks=8, max_num_seqs=2, max_model_len=128, max_num_batched_tokens=64)
+    msg = str(e.value)
+    assert "missing tensors (2)" in msg and "model.layers.1.mlp.up_proj.weight" in msg and "lm_head.weight" in msg
+    assert "unexpected tensors (1)" in msg and "model.layers.9.extra.weight" in msg and "wrong shapes (1)" in msg
+    good = str(tmp_path / "good")
+    plain.write_model_folder(good, cfg, w, store="F32")
+    with pytest.raises(CppEngineError, match="Unknown model architecture"):
+        CppEngine(good, model_arch="llama", dtype="float32", block_size=32, num_gpu_blocks=8, max_num_seqs=2, max_model_len=128)
+    with pytest.raises(CppEngineError, match="block_size"):
+        CppEngine(good, dtype="float32", block_size=24, num_gpu_blocks=8, max_num_seqs=2, max_model_len=128)
+    with pytest.raises(CppEngineError, match="dtype"):
+        CppEngine(good, dtype="float16", block_size=32, num_gpu_blocks=8, max_num_seqs=2, max_model_len=128)
+    bad_cfg = str(tmp_path / "bad_cfg")
+    plain.write_model_folder(bad_cfg, dict(cfg, num_attention_heads=5), w, store="F32")
+    with pytest.raises(CppEngineError, match="multiple of"):
+        CppEngine(bad_cfg, dtype="float32", block_size=32, num_gpu_blocks=8, max_num_seqs=2, max_model_len=128)
+    # pages derived from the memory budget: never more than every request at full length needs
+    eng = CppEngine(good, dtype="bfloat16", block_size=32, num_gpu_blocks=0, max_num_seqs=4, max_model_len=512, max_num_batched_tokens=64)
+    assert eng.num_total_blocks == 4 * 16
+
+
+def test_command_line(tmp_path):
+    """vllm_cli with MODEL_PATH and MODEL_ARCH from the environment, flags overriding them."""
+    from vllm_cpp_b200.csrc import build
+    cfg, weights, folder, eng = cpp_engine(tmp_path, "A", "float32", seed=21, num_gpu_blocks=64)
+    prompts = [token_ids(cfg, n, 50 + n) for n in (5, 17)]
+    want = eng.generate(prompts, max_tokens=6, temperature=0.0, ignore_eos=True)
+    eng.close()
+    cli = build.build_engine()["cli"]
+    env = dict(os.environ, MODEL_PATH=folder, MODEL_ARCH="qwen")
+    args = [cli, "--dtype", "float32", "--num-blocks", "64", "--max-model-len", "256", "--max-num-batched-tokens", "256",
+            "--max-tokens", "6", "--ignore-eos"]
+    for p in prompts:
+        args += ["--prompt-ids", ",".join(map(str, p))]
+    out = subprocess.run(args, env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert [[int(t) for t in line.split(",")] for line in out.stdout.strip().splitlines()] == want
+    bad = subprocess.run([cli, "--model", str(tmp_path / "nowhere"), "--prompt-ids", "1"], capture_output=True, text=True, timeout=300)
+    assert bad.returncode == 1 and "Cannot open config" in bad.stderr

@@ -132,6 +132,71 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> str:
     return lib_path
 
 
+# ------------------------------------------------------------------------------------ the C++ host
+_ROOT = os.path.dirname(os.path.dirname(_HERE))
+HOST_SRC, HOST_INCLUDE = os.path.join(_ROOT, "src"), os.path.join(_ROOT, "include")
+HOST_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-fvisibility=hidden"]
+
+
+def _host_sources():
+    return sorted(f for f in os.listdir(HOST_SRC) if f.endswith(".cpp"))
+
+
+def _host_hash(kernels: str) -> str:
+    h = hashlib.sha256(os.path.basename(os.path.dirname(kernels)).encode())
+    for folder, _, files in sorted(os.walk(HOST_SRC)) + sorted(os.walk(HOST_INCLUDE)):
+        for f in sorted(files):
+            h.update(f.encode())
+            with open(os.path.join(folder, f), "rb") as fh:
+                h.update(fh.read())
+    h.update(" ".join(HOST_FLAGS).encode())
+    return h.hexdigest()[:12]
+
+
+def build_engine() -> dict:
+    """Build the C++ host runtime (src/, include/vllm/) against the kernel library: the shared object
+    ``libvcb_engine_<hash>.so`` with vllm::Engine and its C face, and the command line ``vllm_cli``, both
+    beside the kernel library.  Returns {"lib": path, "cli": path}."""
+    if not os.path.isdir(HOST_SRC) or not os.path.isdir(HOST_INCLUDE):
+        raise BuildError(f"the C++ host's sources are not at {HOST_SRC} and {HOST_INCLUDE}")
+    kernels = build()
+    out_dir = os.path.dirname(kernels)
+    tag = _host_hash(kernels)
+    lib, cli = os.path.join(out_dir, f"libvcb_engine_{tag}.so"), os.path.join(out_dir, f"vllm_cli_{tag}")
+    if os.path.isfile(lib) and os.path.isfile(cli):
+        return {"lib": lib, "cli": cli}
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if not cxx:
+        raise BuildError("g++ not found: the C++ host cannot be built")
+    cuda = os.path.dirname(os.path.dirname(_find_nvcc()))
+    with open(os.path.join(_build_root(), ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if os.path.isfile(lib) and os.path.isfile(cli):
+                return {"lib": lib, "cli": cli}
+            _say(f"compiling the C++ host ({len(_host_sources())} sources) into {out_dir}")
+            t0 = time.time()
+            common = HOST_FLAGS + ["-I", HOST_INCLUDE, "-I", HOST_SRC, "-I", os.path.join(cuda, "include")]
+            link = ["-L", out_dir, "-l:" + LIB_NAME, "-L", os.path.join(cuda, "lib64"), "-lcublas", "-lcudart",
+                    "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda, "lib64")]
+            lib_srcs = [os.path.join(HOST_SRC, f) for f in _host_sources() if f != "main.cpp"]
+            for cmd in ([cxx, "-shared"] + common + lib_srcs + ["-o", lib + ".tmp"] + link,
+                        [cxx] + common + [os.path.join(HOST_SRC, "main.cpp"), "-o", cli + ".tmp", "-L", out_dir,
+                                          "-l:" + os.path.basename(lib), "-Wl,-rpath,$ORIGIN"] + link):
+                if cmd[-1] is None:
+                    continue
+                p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+                if p.returncode != 0:
+                    raise BuildError(f"the C++ host did not build:\n{' '.join(cmd)}\n{p.stdout}")
+                if cmd[1] == "-shared":
+                    os.replace(lib + ".tmp", lib)
+            os.replace(cli + ".tmp", cli)
+            _say(f"built the C++ host in {time.time() - t0:.0f}s")
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+    return {"lib": lib, "cli": cli}
+
+
 def load() -> ctypes.CDLL:
     """The loaded kernel library (built first if needed)."""
     global _lib
