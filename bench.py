@@ -253,6 +253,58 @@ def flat_config(cfg, a, nums, extra):
     return out
 
 
+# ------------------------------------------------------------------------------------------- the C++ host
+def run_cpp_host(cfg, a) -> int:
+    """Decode throughput through the C++ host runtime (vllm::Engine behind include/vllm/vllm.hpp): the same model
+    folder, requests with prompts of 2,048 tokens generating up to 4,096, the same runs of timed steps as the
+    e2e figure of the Python host, by the wall clock around Engine::step (which returns the sampled ids)."""
+    import numpy as np
+    import torch
+    from vllm_cpp_b200.engine.cpp_host import CppEngine
+    from vllm_cpp_b200.weights.random_init import write_random_model
+    where = "/dev/shm" if os.path.isdir("/dev/shm") else tempfile.gettempdir()
+    folder = tempfile.mkdtemp(prefix="vcb_cpp_model_", dir=where)
+    try:
+        write_random_model(folder, cfg, seed=0, dtype="bfloat16", device="cuda")
+        torch.cuda.empty_cache()
+        batch, lead = a.batch, 16
+        pages = batch * ((CONTEXT + SLACK) // 16 + 1) + 16
+        t0 = time.time()
+        eng = CppEngine(folder, dtype="bfloat16", block_size=16, num_gpu_blocks=pages, max_num_seqs=max(batch, 8),
+                        max_model_len=CONTEXT + SLACK, max_num_batched_tokens=PREFILL_TOKENS, max_tokens_per_step=PREFILL_TOKENS)
+        load_s = time.time() - t0
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    rng = np.random.default_rng(0)
+    prompt_len = CONTEXT_START - lead
+    for _ in range(batch):
+        eng.add_request(rng.integers(0, cfg["vocab_size"], size=prompt_len).tolist(), max_tokens=CONTEXT + SLACK - prompt_len,
+                        temperature=0.0, ignore_eos=True)
+    produced = [0] * batch
+    def step():
+        outs = eng.step()
+        for rid, _, _ in outs:
+            produced[rid] += 1
+        return len(outs)
+    while min(produced) == 0 or len(set(produced)) > 1 and max(produced) < 2:      # until every request decodes
+        step()
+    runs, timed, seconds = decode_runs(max(1, a.steps)), 0, 0.0
+    for ctx0, k in runs:
+        while prompt_len + min(produced) < ctx0:
+            step()
+        t = time.perf_counter()
+        got = sum(step() for _ in range(k))
+        seconds += time.perf_counter() - t
+        assert got == batch * k, (got, batch, k)
+        timed += k
+    print(json.dumps({"host": "cpp", "metric": METRIC, "value": round(batch * timed / seconds, 1), "unit": "tokens/s",
+                      "ms_per_step": round(seconds / timed * 1e3, 4), "steps": timed, "batch": batch,
+                      "config": {"model": f"Qwen2.5-{a.size.upper()} layer sizes", "layers": cfg["num_hidden_layers"],
+                                 "decode_contexts": f"{CONTEXT_START} growing to {CONTEXT}", "load_s": round(load_s, 1),
+                                 "pool_gb": round(eng.pool_total_bytes / 1e9, 2)}}))
+    return 0
+
+
 # ---------------------------------------------------------------------------------------- kernels one by one
 def run_kernels(cfg) -> int:
     """Every kernel of the step alone at the benchmark's layer sizes: microseconds (CUDA events around a CUDA
@@ -502,6 +554,8 @@ def main() -> int:
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the step: every kernel alone at these layer sizes, a text table of microseconds "
                          "and achieved GB/s or TFLOP/s")
+    ap.add_argument("--host", default="python", choices=["python", "cpp"],
+                    help="cpp: decode throughput through the C++ host runtime (vllm::Engine) instead of the Python host")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only (for profiling); the other fields of the line are null")
@@ -543,6 +597,8 @@ def main() -> int:
         return run_mix(cfg, a)
     if a.kernels:
         return run_kernels(cfg)
+    if a.host == "cpp":
+        return run_cpp_host(cfg, a)
     nums = model_numbers(cfg)
     peaks = load_peaks()
     max_batch = max(64, a.batch)

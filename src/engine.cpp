@@ -59,8 +59,15 @@ struct Engine::Impl {
     int *pen_ids_dev = nullptr, *pen_start_dev = nullptr;
     size_t pen_ids_cap = 0;
     int steps_since_check = 0;
+    // Decode steps in which every request brings one token and wants its logits have a fixed shape for a given
+    // number of requests and attention splits: the first such step runs directly, the second is captured as a
+    // CUDA graph, later ones replay it.  The metadata copy and the sampling stay outside the graph.
+    std::map<std::vector<int>, cudaGraphExec_t> graphs;
+    std::map<std::vector<int>, int> graph_seen;
+    bool use_graphs = true;
 
     ~Impl() {
+        for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
         if (meta_host) cudaFreeHost(meta_host);
         if (samp_host) cudaFreeHost(samp_host);
         if (topk_host) cudaFreeHost(topk_host);
@@ -106,7 +113,8 @@ struct Engine::Impl {
             throw Error("Unknown model architecture: '" + arch + "'; known: Qwen2ForCausalLM, qwen");
         mc = Qwen2Config::from_json(j);
         bf16 = cfg.dtype == "bfloat16";
-        vcb_set_pdl(0);
+        // every kernel of a step starts under the one before it (programmatic dependent launch, csrc/common.cuh)
+        vcb_set_pdl(1);
         model.reset(new Qwen2Model(cfg, mc, bf16));
         max_model_len = (int)std::min<size_t>(cfg.max_model_len, (size_t)mc.max_pos);
         max_blocks = cdiv(max_model_len, (int)cfg.block_size);
@@ -247,7 +255,35 @@ struct Engine::Impl {
         b.token_ids = dev(tok); b.positions = dev(pos); b.req_of_token = dev(rot); b.q_start = dev(qs); b.ctx_lens = dev(cl);
         b.logit_rows = dev(lr);
         for (int* t : tables) b.block_tables.push_back(dev(t));
-        const float* logits = model->forward(b, stream);
+        for (int g = 0; g < cache->num_groups(); ++g) b.decode_splits.push_back(model->decode_splits(g, r, b.longest));
+        const float* logits = nullptr;
+        if (use_graphs && bf16 && b.decode_only && m == r && r <= 128) {
+            std::vector<int> key{r};
+            key.insert(key.end(), b.decode_splits.begin(), b.decode_splits.end());
+            auto it = graphs.find(key);
+            if (it == graphs.end() && graph_seen[key]++ >= 1) {
+                cudaGraph_t graph = nullptr;
+                cuda_check(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+                try {
+                    model->forward(b, stream);
+                } catch (...) {
+                    cudaStreamEndCapture(stream, &graph);
+                    if (graph) cudaGraphDestroy(graph);
+                    throw;
+                }
+                cuda_check(cudaStreamEndCapture(stream, &graph), "cudaStreamEndCapture");
+                cudaGraphExec_t exec = nullptr;
+                const cudaError_t err = cudaGraphInstantiate(&exec, graph, 0);
+                cudaGraphDestroy(graph);
+                cuda_check(err, "cudaGraphInstantiate");
+                it = graphs.emplace(key, exec).first;
+            }
+            if (it != graphs.end()) {
+                cuda_check(cudaGraphLaunch(it->second, stream), "cudaGraphLaunch");
+                logits = model->logits();
+            }
+        }
+        if (!logits) logits = model->forward(b, stream);
         for (const Item& it : items) cache->commit(it.id, (int)it.tokens.size());
         *n_rows_out = m;
         return logits;

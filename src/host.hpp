@@ -257,6 +257,7 @@ struct Batch {
     int n_tiles = 0;
     bool decode_only = false;
     int longest = 0;                                         // longest context after this step
+    std::vector<int> decode_splits;                          // per cache group: context splits of the decode attention
 };
 
 class Qwen2Model;                        // model.cpp

@@ -377,9 +377,7 @@ void Qwen2Model::attend(const Batch& b, int layer, cudaStream_t s) {
     const int page = (int)cfg_.block_size, d = mc_.head_dim;
     if (bf16_ && (d == 64 || d == 128)) {
         if (b.decode_only) {
-            int longest = b.longest;
-            if (window > 0) longest = std::min(longest, window + 64);
-            int nsplit = std::max(1, std::min({(longest + 63) / 64, 2 * sms_ / std::max(1, b.n_reqs * mc_.kv_heads), 32}));
+            const int nsplit = b.decode_splits[g];
             kernel_check(vcb_attention_decode_mma(q_, pages, attn_, b.q_start, b.ctx_lens, bt, b.max_blocks, nullptr, b.n_reqs, nsplit,
                                                   part_o_, part_ml_, attn_tickets_, nullptr, mc_.heads, mc_.kv_heads, d, page, window,
                                                   scale_, num_pages_, status_, s), "attention_decode_mma");
@@ -392,6 +390,12 @@ void Qwen2Model::attend(const Batch& b, int layer, cudaStream_t s) {
     }
     kernel_check(vcb_attention_simt(q_, pages, attn_, b.positions, b.req_of_token, bt, b.max_blocks, b.n_tokens, mc_.heads,
                                     mc_.kv_heads, d, page, window, scale_, num_pages_, status_, dt_, s), "attention_simt");
+}
+
+int Qwen2Model::decode_splits(int group, int n_reqs, int longest) const {
+    const int window = group_windows_[group];
+    if (window > 0) longest = std::min(longest, window + 64);
+    return std::max(1, std::min({(longest + 63) / 64, 2 * sms_ / std::max(1, n_reqs * mc_.kv_heads), 32}));
 }
 
 const float* Qwen2Model::forward(const Batch& b, cudaStream_t s) {

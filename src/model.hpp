@@ -25,6 +25,10 @@ class Qwen2Model {
     void load_weights(const std::string& model_path);     // by tensor name; one error lists all faults
     // Runs the batch's tokens from the cache; returns the float32 logits [n_logit_rows, vocab] on the device.
     const float* forward(const Batch& b, cudaStream_t s);
+    // Context splits per (request, kv head) of the split-KV decode attention in cache group `group`, for a
+    // decode-only step of n_reqs requests whose longest context is `longest`: enough to fill the device once.
+    int decode_splits(int group, int n_reqs, int longest) const;
+    const float* logits() const { return logits_; }
     int read_status();                                    // what a kernel noted (0: nothing); synchronises
 
   private:
