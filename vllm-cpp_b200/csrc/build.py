@@ -179,7 +179,7 @@ def build_engine() -> dict:
             common = HOST_FLAGS + ["-I", HOST_INCLUDE, "-I", HOST_SRC, "-I", os.path.join(cuda, "include")]
             link = ["-L", out_dir, "-l:" + LIB_NAME, "-L", os.path.join(cuda, "lib64"), "-lcublas", "-lcudart",
                     "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda, "lib64")]
-            lib_srcs = [os.path.join(HOST_SRC, f) for f in _host_sources() if f != "main.cpp"]
+            lib_srcs = [os.path.join(HOST_SRC, f) for f in _host_sources() if f not in ("main.cpp", "sim_api.cpp")]
             for cmd in ([cxx, "-shared"] + common + lib_srcs + ["-o", lib + ".tmp"] + link,
                         [cxx] + common + [os.path.join(HOST_SRC, "main.cpp"), "-o", cli + ".tmp", "-L", out_dir,
                                           "-l:" + os.path.basename(lib), "-Wl,-rpath,$ORIGIN"] + link):
@@ -195,6 +195,35 @@ def build_engine() -> dict:
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)
     return {"lib": lib, "cli": cli}
+
+
+def build_scheduler_sim() -> str:
+    """The C++ cache manager and scheduler alone as a small library (src/cache.cpp + src/sim_api.cpp): no device
+    is needed to build or to run it.  Tests step it beside the Python scheduler."""
+    h = hashlib.sha256()
+    for f in ("cache.cpp", "sim_api.cpp", "host.hpp"):
+        with open(os.path.join(HOST_SRC, f), "rb") as fh:
+            h.update(fh.read())
+    for folder, _, files in sorted(os.walk(HOST_INCLUDE)):
+        for f in sorted(files):
+            with open(os.path.join(folder, f), "rb") as fh:
+                h.update(fh.read())
+    root = _build_root()
+    lib = os.path.join(root, f"libvcb_scheduler_sim_{h.hexdigest()[:12]}.so")
+    if os.path.isfile(lib):
+        return lib
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if not cxx:
+        raise BuildError("g++ not found")
+    cuda = os.path.dirname(os.path.dirname(_find_nvcc()))
+    cmd = [cxx, "-shared"] + HOST_FLAGS + ["-I", HOST_INCLUDE, "-I", HOST_SRC, "-I", os.path.join(cuda, "include"),
+                                          os.path.join(HOST_SRC, "cache.cpp"), os.path.join(HOST_SRC, "sim_api.cpp"),
+                                          "-o", lib + f".tmp{os.getpid()}"]
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if p.returncode != 0:
+        raise BuildError(f"the scheduler library did not build:\n{' '.join(cmd)}\n{p.stdout}")
+    os.replace(lib + f".tmp{os.getpid()}", lib)
+    return lib
 
 
 def load() -> ctypes.CDLL:
