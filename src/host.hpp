@@ -52,6 +52,13 @@ int vcb_gemm_f32(const float* a, const float* w, float* c, int m, int n, int k, 
 int vcb_gemm_bf16_tcgen05(const void* p, int rows_p, int ldp, const void* p_tiled, const void* q, int rows_q, int ldq, int k,
                           void* out, int ldc, int out_f32, int swapped, int bn, int max_ctas, float* partial, int* tickets,
                           int n_tickets, int* status, void* stream);
+int vcb_gemm_bf16_tcgen05_fused(const void* p, int rows_p, int ldp, const void* p_tiled, const void* q, int rows_q, int ldq, int k,
+                                void* out, int ldc, int out_f32, int swapped, int bn, int max_ctas, float* partial, int* tickets,
+                                int n_tickets, int* status, const float* scale_sumsq, int scale_parts, int scale_ld, int scale_width,
+                                float scale_eps, float* residual, int ldr, const float* gain, float* sumsq_out, int sumsq_ld,
+                                int gated, void* stream);
+long long vcb_tiled_weight_bytes(int rows, int k, int gated);
+int vcb_tile_weights(const void* w, int rows, int k, int ld, int gated, void* out, void* stream);
 int vcb_repetition_penalty(float* logits, int ld, const int* ids, const int* row_start, const float* penalty, int n_rows,
                            int vocab, void* stream);
 int vcb_sample(const float* logits, int ld, int vocab, const float* temperature, const float* uniform, int* out, int n_rows,

@@ -170,7 +170,22 @@ size_t Qwen2Model::weight_bytes() const {
     auto r = DevicePool::rounded;
     size_t n = r(V * H * el_) + (mc_.tie ? 0 : r(V * H * el_)) + r(H * 4) + r((size_t)mc_.head_dim / 2 * 4);
     n += (size_t)mc_.layers * (r((q + 2 * kv) * H * el_) + r((q + 2 * kv) * 4) + r(H * q * el_) + r(2 * I * H * el_) + r(H * I * el_) + 2 * r(H * 4));
-    return n;
+    return n + image_bytes();
+}
+
+bool Qwen2Model::fuses(int n_tokens) const {
+    const int H = mc_.hidden, q = mc_.heads * mc_.head_dim, I = mc_.inter;
+    return bf16_ && n_tokens <= (int)std::min<size_t>(cfg_.fused_decode_tokens, 64) && H % 8 == 0 && q % 8 == 0 && I % 8 == 0;
+}
+
+size_t Qwen2Model::image_bytes() const {
+    if (!bf16_ || cfg_.fused_decode_tokens == 0 || mc_.hidden % 8 || (mc_.heads * mc_.head_dim) % 8 || mc_.inter % 8) return 0;
+    const int H = mc_.hidden, q = mc_.heads * mc_.head_dim, kv = mc_.kv_heads * mc_.head_dim, I = mc_.inter;
+    auto r = DevicePool::rounded;
+    size_t per_layer = r((size_t)vcb_tiled_weight_bytes(q + 2 * kv, H, 0)) + r((size_t)vcb_tiled_weight_bytes(H, q, 0)) +
+                       r((size_t)vcb_tiled_weight_bytes(2 * I, H, I)) + r((size_t)vcb_tiled_weight_bytes(H, I, 0));
+    return (size_t)mc_.layers * per_layer + r((size_t)vcb_tiled_weight_bytes(mc_.vocab, H, 0)) +
+           r((size_t)2 * sumsq_parts(H) * 64 * 4) + r((size_t)sumsq_parts(H) * 64 * 4);
 }
 
 size_t Qwen2Model::bytes_per_page() const {
@@ -206,6 +221,17 @@ void Qwen2Model::place(DevicePool& pool, int num_pages) {
         L.w_down = pool.alloc(H * I * el_, "a down projection");
         L.gain_in = pool.alloc_n<float>(H, "a norm's gain");
         L.gain_post = pool.alloc_n<float>(H, "a norm's gain");
+    }
+    if (image_bytes()) {
+        for (auto& L : layers_) {
+            L.t_qkv = pool.alloc((size_t)vcb_tiled_weight_bytes((int)(q + 2 * kv), (int)H, 0), "a tiled q/k/v matrix");
+            L.t_o = pool.alloc((size_t)vcb_tiled_weight_bytes((int)H, (int)q, 0), "a tiled output projection");
+            L.t_gate_up = pool.alloc((size_t)vcb_tiled_weight_bytes((int)(2 * I), (int)H, (int)I), "a tiled gate-and-up matrix");
+            L.t_down = pool.alloc((size_t)vcb_tiled_weight_bytes((int)H, (int)I, 0), "a tiled down projection");
+        }
+        t_lm_head_ = pool.alloc((size_t)vcb_tiled_weight_bytes((int)V, (int)H, 0), "the tiled output matrix");
+        carry_ = pool.alloc_n<float>((size_t)2 * sumsq_parts((int)H) * 64, "sums of squares");
+        ss_inner_ = pool.alloc_n<float>((size_t)sumsq_parts((int)H) * 64, "sums of squares");
     }
     // pages: per group [layers of the group][page][k|v][kv head][page x head size]
     for (size_t g = 0; g < group_windows_.size(); ++g) {
@@ -339,6 +365,81 @@ void Qwen2Model::load_weights(const std::string& model_path) {
         upload(at(p + "input_layernorm.weight"), L.gain_in, true);
         upload(at(p + "post_attention_layernorm.weight"), L.gain_post, true);
     }
+    make_images();
+}
+
+// The second copy of the matrices for steps of few tokens: cut into 128 x 64 tiles, each stored as the tensor
+// core reads it from shared memory, gate rows paired with their up rows (csrc/gemm_tcgen05.cu tile_weights_kernel).
+void Qwen2Model::make_images() {
+    if (!t_lm_head_) return;
+    const int H = mc_.hidden, q = mc_.heads * mc_.head_dim, kv = mc_.kv_heads * mc_.head_dim, I = mc_.inter;
+    for (auto& L : layers_) {
+        kernel_check(vcb_tile_weights(L.w_qkv, q + 2 * kv, H, H, 0, L.t_qkv, nullptr), "tile_weights");
+        kernel_check(vcb_tile_weights(L.w_o, H, q, q, 0, L.t_o, nullptr), "tile_weights");
+        kernel_check(vcb_tile_weights(L.w_gate_up, 2 * I, H, H, I, L.t_gate_up, nullptr), "tile_weights");
+        kernel_check(vcb_tile_weights(L.w_down, H, I, I, 0, L.t_down, nullptr), "tile_weights");
+    }
+    kernel_check(vcb_tile_weights(lm_head_, mc_.vocab, H, H, 0, t_lm_head_, nullptr), "tile_weights");
+    cuda_check(cudaDeviceSynchronize(), "tiling the weights");
+}
+
+void Qwen2Model::fused_product(const void* x, const void* w, const void* tiled, void* out, int m, int n, int k, bool out_f32,
+                               RowScale scale, const float* gain, float* sumsq_out, int gated, cudaStream_t s) {
+    const int bn = m <= 16 ? 16 : m <= 32 ? 32 : 64;
+    const int ctas = bn == 16 ? sms_ : 2 * sms_;
+    // swapped form: the weights are the 128-row operand; a gated product writes [m, gated] columns
+    kernel_check(vcb_gemm_bf16_tcgen05_fused(w, n, k, tiled, x, m, k, k, out, gated ? gated : n, out_f32 ? 1 : 0, 1, bn, ctas,
+                                             gemm_partial_, gemm_tickets_, 16384, status_, scale.sumsq, scale.parts, 64,
+                                             mc_.hidden, (float)mc_.eps, gain ? residual_ : nullptr, mc_.hidden, gain, sumsq_out, 64,
+                                             gated, s), "gemm_bf16_tcgen05_fused");
+}
+
+// A step of few tokens with no norm, activation or addition kernel inside a layer: norm(x) W^T =
+// rsqrt(mean(x^2) + eps) * ((x * gain) W^T), so the product that ends a residual branch adds its result into the
+// float32 residual stream, stores residual * (the next norm's gain) as the next product's input and leaves the
+// rows' sums of squares; the next product multiplies its rows by the factor.  (parts/block.py in the Python host.)
+const float* Qwen2Model::forward_fused(const Batch& b, cudaStream_t s) {
+    const int n = b.n_tokens, H = mc_.hidden, q = mc_.heads * mc_.head_dim, kv = mc_.kv_heads * mc_.head_dim, I = mc_.inter;
+    const float eps = (float)mc_.eps;
+    const int parts = sumsq_parts(H);
+    kernel_check(vcb_embedding(embed_, b.token_ids, residual_, n, H, dt_, s), "embedding");
+    RowScale incoming;                                   // set: delta holds residual * gain_in of this layer, factor pending
+    int cur = 0;
+    for (int l = 0; l < mc_.layers; ++l) {
+        const Layer& L = layers_[l];
+        const int g = layer_group_[l];
+        void* pages = static_cast<uint8_t*>(pages_[g]) + (size_t)layer_index_in_group_[l] * num_pages_ * (size_t)kv * cfg_.block_size * el_ * 2;
+        const void* x = delta_;
+        if (!incoming.sumsq) {
+            kernel_check(vcb_add_rmsnorm(residual_, nullptr, L.gain_in, h_, nullptr, n, H, eps, dt_, s), "add_rmsnorm");
+            x = h_;
+        }
+        fused_product(x, L.w_qkv, L.t_qkv, qkv_, n, q + 2 * kv, H, false, incoming, nullptr, nullptr, 0, s);
+        kernel_check(vcb_rope_cache_write(qkv_, L.b_qkv, b.positions, b.req_of_token, b.block_tables[g], b.max_blocks, denom_, q_, pages,
+                                          n, mc_.heads, mc_.kv_heads, mc_.head_dim, mc_.head_dim, 0, (int)cfg_.block_size, 1, num_pages_,
+                                          status_, dt_, s), "rope_cache_write");
+        attend(b, l, s);
+        // the output projection ends the attention branch and prepares the feed-forward's norm
+        fused_product(attn_, L.w_o, L.t_o, mixed_, n, H, q, false, RowScale(), L.gain_post, ss_inner_, 0, s);
+        fused_product(mixed_, L.w_gate_up, L.t_gate_up, act_, n, 2 * I, H, false, RowScale{ss_inner_, parts}, nullptr, nullptr, I, s);
+        if (l + 1 < mc_.layers) {
+            // the down projection ends the feed-forward branch and prepares the next layer's first norm
+            float* out_ss = carry_ + (size_t)cur * parts * 64;
+            fused_product(act_, L.w_down, L.t_down, delta_, n, H, I, false, RowScale(), layers_[l + 1].gain_in, out_ss, 0, s);
+            incoming = RowScale{out_ss, parts};
+            cur ^= 1;
+        } else {
+            fused_product(act_, L.w_down, L.t_down, delta_, n, H, I, false, RowScale(), nullptr, nullptr, 0, s);
+            incoming = RowScale();
+        }
+    }
+    if (b.n_logit_rows == 0) return logits_;
+    kernel_check(vcb_add_rmsnorm(residual_, delta_, final_gain_, normed_, b.logit_rows, b.n_logit_rows, H, eps, dt_, s), "add_rmsnorm");
+    if (b.n_logit_rows <= 64)
+        fused_product(normed_, lm_head_, t_lm_head_, logits_, b.n_logit_rows, mc_.vocab, H, true, RowScale(), nullptr, nullptr, 0, s);
+    else
+        linear(normed_, lm_head_, logits_, b.n_logit_rows, mc_.vocab, H, true, s);
+    return logits_;
 }
 
 // out [m, n] = x [m, k] @ w [n, k]^T.  float32: the engine's FMA product.  bfloat16 with up to 128 rows: the
@@ -399,6 +500,7 @@ int Qwen2Model::decode_splits(int group, int n_reqs, int longest) const {
 }
 
 const float* Qwen2Model::forward(const Batch& b, cudaStream_t s) {
+    if (t_lm_head_ && fuses(b.n_tokens)) return forward_fused(b, s);
     const int n = b.n_tokens, H = mc_.hidden, q = mc_.heads * mc_.head_dim, kv = mc_.kv_heads * mc_.head_dim, I = mc_.inter;
     const float eps = (float)mc_.eps;
     kernel_check(vcb_embedding(embed_, b.token_ids, residual_, n, H, dt_, s), "embedding");

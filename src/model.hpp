@@ -34,11 +34,22 @@ class Qwen2Model {
   private:
     struct Layer {
         void *w_qkv = nullptr, *w_o = nullptr, *w_gate_up = nullptr, *w_down = nullptr;
+        void *t_qkv = nullptr, *t_o = nullptr, *t_gate_up = nullptr, *t_down = nullptr;     // pre-tiled images (fused decode)
         float *b_qkv = nullptr, *gain_in = nullptr, *gain_post = nullptr;
     };
     std::map<std::string, std::vector<int64_t>> expected_tensors() const;
     void upload(const TensorInfo& t, void* dst, bool as_float32);
     void linear(const void* x, const void* w, void* out, int m, int n, int k, bool out_f32, cudaStream_t s);
+    // the few-token product with what it can take over: the rows' norm factor on its input (scale), the end of a
+    // residual branch (residual, gain, sumsq_out), silu(gate) * up (gated > 0); see csrc/gemm_tcgen05.cu
+    struct RowScale { const float* sumsq = nullptr; int parts = 0; };
+    void fused_product(const void* x, const void* w, const void* tiled, void* out, int m, int n, int k, bool out_f32, RowScale scale,
+                       const float* gain, float* sumsq_out, int gated, cudaStream_t s);
+    bool fuses(int n_tokens) const;
+    const float* forward_fused(const Batch& b, cudaStream_t s);
+    void make_images();
+    size_t image_bytes() const;
+    int sumsq_parts(int features) const { return 4 * ((features + 127) / 128); }
     void attend(const Batch& b, int layer, cudaStream_t s);
 
     EngineConfig cfg_;
@@ -58,6 +69,8 @@ class Qwen2Model {
     float *logits_ = nullptr, *gemm_partial_ = nullptr, *part_o_ = nullptr, *part_ml_ = nullptr;
     int *gemm_tickets_ = nullptr, *status_ = nullptr, *attn_tickets_ = nullptr;
     void* cublas_ = nullptr;
+    void* t_lm_head_ = nullptr;
+    float *carry_ = nullptr, *ss_inner_ = nullptr;       // sums of squares handed from product to product
 };
 
 }  // namespace host

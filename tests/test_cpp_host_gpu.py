@@ -51,13 +51,17 @@ def cpp_engine(tmp_path, name, dtype, seed=1, **kw):
     return cfg, weights, folder, CppEngine(folder, **args)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "bfloat16-plain"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_explicit_batches_cut_every_way(tmp_path, name, dtype):
+    """bfloat16: steps of up to 64 tokens run with the norms, additions and SwiGLU inside the products (the
+    default is 16); "bfloat16-plain" switches that off, so every step runs the plain sequence of kernels."""
     from test_replay_gpu import mixed_trace
     cfg, page = CONFIGS[name]
     pages = 4 * (-(-120 // page)) + 1
-    cfg, weights, _, eng = cpp_engine(tmp_path, name, dtype, num_gpu_blocks=max(pages, -(-231 // page) + 1))
+    fused = dtype != "bfloat16-plain"
+    dtype = dtype.split("-")[0]
+    cfg, weights, _, eng = cpp_engine(tmp_path, name, dtype, num_gpu_blocks=max(pages, -(-231 // page) + 1), fused_decode_tokens=64 if fused else 0)
     total = eng.num_total_blocks
     assert 0 < eng.pool_used_bytes <= eng.pool_total_bytes
     rp = CppReplayer(eng)
