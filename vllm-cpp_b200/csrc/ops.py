@@ -432,11 +432,12 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=
               "gemm_bf16_tcgen05: the gated form needs few tokens, a gated tile image and a bfloat16 result")
     sms = sm_count()
     if max_ctas is None:
-        # Tiles of 32 and 64 columns: two CTAs of the product on every SM (its ring is then four or five
-        # stages deep each).  A stage carries the tokens' operand beside the weights', half as much again at
-        # 64 tokens, and one CTA's ring does not hold enough bytes in flight for the memory's rate
-        # (measured at 64 tokens, 7B sizes: gate-and-up 49.9 -> 44.6 us, qkv 14.8 -> 12.8; at 128 it is slower).
-        max_ctas = 2 * sms if bn in (32, 64) else sms
+        # What the measurement at load chose for this shape (choose_ctas), else: tiles of 32 and 64 columns
+        # run two CTAs of the product on every SM (its ring is then four or five stages deep each).  A stage
+        # carries the tokens' operand beside the weights', half as much again at 64 tokens, and one CTA's ring
+        # does not hold enough bytes in flight for the memory's rate (measured at 64 tokens, 7B sizes:
+        # gate-and-up 49.9 -> 44.6 us, qkv 14.8 -> 12.8; at 128 it is slower).
+        max_ctas = _cta_choice.get((n, k, bn, bool(gated)), 2 * sms if bn in (32, 64) else sms)
     partial = scratch("gemm_partial", sms * 2 * 256 * 128, out.device)
     tickets = zeroed_ints("gemm_tickets", GEMM_MAX_TICKETS, out.device)
     _check(lib().vcb_gemm_bf16_tcgen05_fused(p.data_ptr(), p.shape[0], p.stride(0),
@@ -594,6 +595,40 @@ def measure_layer(products, hidden: int, fusable_norms: int, dtype=torch.bfloat1
         times[bucket] = (time_in_graph(ours), time_in_graph(theirs))
     check_status()
     return times
+
+
+# (features, k, tile columns, gated) -> persistent CTAs of the tcgen05 product, where a measurement chose them
+_cta_choice = {}
+
+
+def cta_candidates(features: int, k: int, gated: int = 0):
+    """Grid sizes worth measuring for a few-token product: one CTA per SM (the next kernel's CTAs then sit
+    beside this one's and prefetch), two per SM, and in between the counts that cut every 128-row tile into
+    the same number of whole runs of k slabs (no CTA then holds pieces of two tiles, and a count equal to the
+    number of tiles needs no merge at all)."""
+    sms = sm_count()
+    tiles = -(-gated // 64) if gated else -(-features // 128)
+    slabs = -(-k // 64)
+    out = {sms, 2 * sms}
+    for per_tile in range(1, slabs // 4 + 1):
+        if slabs % per_tile == 0 and sms * 3 // 4 <= tiles * per_tile <= 2 * sms:
+            out.add(tiles * per_tile)
+    return sorted(out)
+
+
+def choose_ctas(weights, bucket: int, tokens: int, gated: int = 0, out_dtype=torch.bfloat16) -> int:
+    """Measure the tcgen05 product on ``weights`` (matrices of one shape, used in rotation) at every candidate
+    grid size, record the fastest for this shape and bucket, and return it."""
+    n, k = weights[0].shape
+    x = torch.randn(tokens, k, device=weights[0].device).to(torch.bfloat16)
+    out = torch.empty(tokens, gated or n, dtype=out_dtype, device=weights[0].device)
+    best, best_t = None, None
+    for ctas in cta_candidates(n, k, gated):
+        t = time_in_graph(lambda i: gemm_bf16_tcgen05(x, weights[i % len(weights)], out, max_ctas=ctas, gated=bool(gated)))
+        if best_t is None or t < best_t * 0.98:           # a larger grid must win by more than the noise
+            best, best_t = ctas, t
+    _cta_choice[(n, k, tcgen05_plan(tokens, n, k)[1], bool(gated))] = best
+    return best
 
 
 def choose_linear(features: int, k: int, bucket: int, out_dtype, tcgen05: bool) -> None:

@@ -56,6 +56,12 @@ def prepare_products(model, tune: bool = True, image_budget: Optional[int] = Non
         for m in groups[key][:8]:             # the kernel is measured as it will run: on the images
             ops.tile_weights(m, key[1])
     if measure:
+        # first the grid of the engine's own product per shape, at the token counts decode steps have
+        for key, mats in groups.items():
+            if key in imaged:
+                for bucket, tokens in ops.TOKEN_BUCKETS[:3]:
+                    ops.choose_ctas(mats[:8], bucket, tokens, gated_of[key],
+                                    torch.float32 if mats[0] is model.lm_head else torch.bfloat16)
         whole = {}
         if len(tunable) == len(layer_shapes) and tunable:
             whole = ops.measure_layer([(mats[:8], gated_of[key]) for key, mats in tunable.items()], model.hidden,
