@@ -381,12 +381,67 @@ void Qwen2Model::make_images() {
     }
     kernel_check(vcb_tile_weights(lm_head_, mc_.vocab, H, H, 0, t_lm_head_, nullptr), "tile_weights");
     cuda_check(cudaDeviceSynchronize(), "tiling the weights");
+    tune_grids();
+}
+
+int Qwen2Model::grid_for(int n, int k, int gated) const {
+    auto it = grids_.find({n, k, gated});
+    return it == grids_.end() ? sms_ : it->second;
+}
+
+// The grid of each few-token product, measured once at load as the Python host does (ops.choose_ctas): one
+// CTA per SM, two per SM, and in between the counts that cut every 128-row tile into the same number of whole
+// runs of k slabs.  Timed with CUDA events over the layers' matrices in turn, so that the L2 cache serves none.
+void Qwen2Model::tune_grids() {
+    const int H = mc_.hidden, q = mc_.heads * mc_.head_dim, kv = mc_.kv_heads * mc_.head_dim, I = mc_.inter;
+    struct Shape { int n, k, gated; };
+    cudaEvent_t e0, e1;
+    cuda_check(cudaEventCreate(&e0), "cudaEventCreate");
+    cuda_check(cudaEventCreate(&e1), "cudaEventCreate");
+    // inputs and outputs of the trial products: a transient allocation of its own, given back below
+    void *x = nullptr, *out = nullptr;
+    cuda_check(cudaMalloc(&x, (size_t)8 * std::max({H, q, I}) * 2), "cudaMalloc");
+    cuda_check(cudaMalloc(&out, (size_t)8 * std::max({q + 2 * kv, H, 2 * I}) * 2), "cudaMalloc");
+    cuda_check(cudaMemset(x, 0, (size_t)8 * std::max({H, q, I}) * 2), "clearing a buffer");
+    for (const Shape& sh : {Shape{q + 2 * kv, H, 0}, Shape{H, q, 0}, Shape{2 * I, H, I}, Shape{H, I, 0}}) {
+        const int tiles = sh.gated ? (sh.gated + 63) / 64 : (sh.n + 127) / 128, slabs = (sh.k + 63) / 64;
+        std::set<int> candidates{sms_, 2 * sms_};
+        for (int per_tile = 1; per_tile <= slabs / 4; ++per_tile)
+            if (slabs % per_tile == 0 && tiles * per_tile >= sms_ * 3 / 4 && tiles * per_tile <= 2 * sms_) candidates.insert(tiles * per_tile);
+        const std::vector<int> key{sh.n, sh.k, sh.gated};
+        int best_ctas = sms_;
+        float best_ms = 0;
+        for (int ctas : candidates) {
+            grids_[key] = ctas;
+            float ms = 0;
+            for (int rep = 0; rep < 2; ++rep) {                   // the second pass is the one that counts
+                cuda_check(cudaEventRecord(e0, nullptr), "cudaEventRecord");
+                for (const Layer& L : layers_) {
+                    const void *w = sh.gated ? L.w_gate_up : sh.n == q + 2 * kv && sh.k == H ? L.w_qkv : sh.k == I ? L.w_down : L.w_o;
+                    const void *t = sh.gated ? L.t_gate_up : sh.n == q + 2 * kv && sh.k == H ? L.t_qkv : sh.k == I ? L.t_down : L.t_o;
+                    fused_product(x, w, t, out, 8, sh.n, sh.k, false, RowScale(), nullptr, nullptr, sh.gated, nullptr);
+                }
+                cuda_check(cudaEventRecord(e1, nullptr), "cudaEventRecord");
+                cuda_check(cudaEventSynchronize(e1), "cudaEventSynchronize");
+                cuda_check(cudaEventElapsedTime(&ms, e0, e1), "cudaEventElapsedTime");
+            }
+            if (best_ms == 0 || ms < best_ms * 0.98f) {           // a larger grid must win by more than the noise
+                best_ms = ms;
+                best_ctas = ctas;
+            }
+        }
+        grids_[key] = best_ctas;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(x);
+    cudaFree(out);
 }
 
 void Qwen2Model::fused_product(const void* x, const void* w, const void* tiled, void* out, int m, int n, int k, bool out_f32,
                                RowScale scale, const float* gain, float* sumsq_out, int gated, cudaStream_t s) {
     const int bn = m <= 16 ? 16 : m <= 32 ? 32 : 64;
-    const int ctas = bn == 16 ? sms_ : 2 * sms_;
+    const int ctas = bn == 16 ? grid_for(n, k, gated) : 2 * sms_;
     // swapped form: the weights are the 128-row operand; a gated product writes [m, gated] columns
     kernel_check(vcb_gemm_bf16_tcgen05_fused(w, n, k, tiled, x, m, k, k, out, gated ? gated : n, out_f32 ? 1 : 0, 1, bn, ctas,
                                              gemm_partial_, gemm_tickets_, 16384, status_, scale.sumsq, scale.parts, 64,
