@@ -741,7 +741,8 @@ def main() -> int:
         print(json.dumps({"metric": METRIC, "only": "decode", "batch": a.batch, "ms_per_step": round(ms, 4),
                           "value": round(value, 1), "unit": "tokens/s", "gpu_launches": launches,
                           "runs": [[c, k, round(t / k, 4)] for c, k, t in results],
-                          "product_grids": {f"{n}x{k} tile {bn}{' gated' if g else ''}": c for (n, k, bn, g), c in sorted(ops._cta_choice.items())},
+                          "product_grids": {f"{n}x{k} tile {bn}{' gated' if g else ''}{' residual' if r else ''}": c
+                                            for (n, k, bn, g, r), c in sorted(ops._cta_choice.items())},
                           "cuda_graphs": not a.no_cuda_graphs, "clocks": clock_info}))
         return 0
     n_timed = sum(k for _, k, _ in results)

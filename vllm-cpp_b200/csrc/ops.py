@@ -437,7 +437,7 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan=
         # carries the tokens' operand beside the weights', half as much again at 64 tokens, and one CTA's ring
         # does not hold enough bytes in flight for the memory's rate (measured at 64 tokens, 7B sizes:
         # gate-and-up 49.9 -> 44.6 us, qkv 14.8 -> 12.8; at 128 it is slower).
-        max_ctas = _cta_choice.get((n, k, bn, bool(gated)), 2 * sms if bn in (32, 64) else sms)
+        max_ctas = _cta_choice.get((n, k, bn, bool(gated), fuse is not None), 2 * sms if bn in (32, 64) else sms)
     partial = scratch("gemm_partial", sms * 2 * 256 * 128, out.device)
     tickets = zeroed_ints("gemm_tickets", GEMM_MAX_TICKETS, out.device)
     _check(lib().vcb_gemm_bf16_tcgen05_fused(p.data_ptr(), p.shape[0], p.stride(0),
@@ -597,7 +597,8 @@ def measure_layer(products, hidden: int, fusable_norms: int, dtype=torch.bfloat1
     return times
 
 
-# (features, k, tile columns, gated) -> persistent CTAs of the tcgen05 product, where a measurement chose them
+# (features, k, tile columns, gated, ends a residual branch) -> persistent CTAs of the tcgen05 product, where a
+# measurement chose them
 _cta_choice = {}
 
 
@@ -616,18 +617,22 @@ def cta_candidates(features: int, k: int, gated: int = 0):
     return sorted(out)
 
 
-def choose_ctas(weights, bucket: int, tokens: int, gated: int = 0, out_dtype=torch.bfloat16) -> int:
+def choose_ctas(weights, bucket: int, tokens: int, gated: int = 0, out_dtype=torch.bfloat16, residual: bool = False) -> int:
     """Measure the tcgen05 product on ``weights`` (matrices of one shape, used in rotation) at every candidate
-    grid size, record the fastest for this shape and bucket, and return it."""
+    grid size, record the fastest for this shape and bucket, and return it.  ``residual``: the product as it
+    ends a residual branch (ResidualNorm), whose merge does more than the plain one's."""
     n, k = weights[0].shape
-    x = torch.randn(tokens, k, device=weights[0].device).to(torch.bfloat16)
-    out = torch.empty(tokens, gated or n, dtype=out_dtype, device=weights[0].device)
+    dev_ = weights[0].device
+    x = torch.randn(tokens, k, device=dev_).to(torch.bfloat16)
+    out = torch.empty(tokens, gated or n, dtype=out_dtype, device=dev_)
+    fuse = ResidualNorm(torch.zeros(tokens, n, device=dev_), torch.ones(n, device=dev_),
+                        torch.empty(sumsq_parts(n), tokens, device=dev_), 1e-6) if residual else None
     best, best_t = None, None
     for ctas in cta_candidates(n, k, gated):
-        t = time_in_graph(lambda i: gemm_bf16_tcgen05(x, weights[i % len(weights)], out, max_ctas=ctas, gated=bool(gated)))
+        t = time_in_graph(lambda i: gemm_bf16_tcgen05(x, weights[i % len(weights)], out, max_ctas=ctas, gated=bool(gated), fuse=fuse))
         if best_t is None or t < best_t * 0.98:           # a larger grid must win by more than the noise
             best, best_t = ctas, t
-    _cta_choice[(n, k, tcgen05_plan(tokens, n, k)[1], bool(gated))] = best
+    _cta_choice[(n, k, tcgen05_plan(tokens, n, k)[1], bool(gated), residual)] = best
     return best
 
 

@@ -60,8 +60,10 @@ def prepare_products(model, tune: bool = True, image_budget: Optional[int] = Non
         for key, mats in groups.items():
             if key in imaged:
                 for bucket, tokens in ops.TOKEN_BUCKETS[:3]:
-                    ops.choose_ctas(mats[:8], bucket, tokens, gated_of[key],
-                                    torch.float32 if mats[0] is model.lm_head else torch.bfloat16)
+                    is_head = mats[0] is model.lm_head
+                    ops.choose_ctas(mats[:8], bucket, tokens, gated_of[key], torch.float32 if is_head else torch.bfloat16)
+                    if key[0][0] == model.hidden and not gated_of[key] and not is_head:
+                        ops.choose_ctas(mats[:8], bucket, tokens, residual=True)     # as it ends a residual branch
         whole = {}
         if len(tunable) == len(layer_shapes) and tunable:
             whole = ops.measure_layer([(mats[:8], gated_of[key]) for key, mats in tunable.items()], model.hidden,
