@@ -272,7 +272,7 @@ def run_cpp_host(cfg, a) -> int:
         t0 = time.time()
         eng = CppEngine(folder, dtype="bfloat16", block_size=16, num_gpu_blocks=pages, max_num_seqs=max(batch, 8),
                         max_model_len=CONTEXT + SLACK, max_num_batched_tokens=PREFILL_TOKENS, max_tokens_per_step=PREFILL_TOKENS,
-                        fused_decode_tokens=int(os.environ.get("VCB_FUSED_DECODE_TOKENS", "16")))
+                        fused_decode_tokens=int(os.environ.get("VCB_FUSED_DECODE_TOKENS", "64")))
         load_s = time.time() - t0
     finally:
         shutil.rmtree(folder, ignore_errors=True)

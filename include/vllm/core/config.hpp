@@ -29,10 +29,9 @@ struct EngineConfig {
     bool preempted_to_front = false;      // added: where a preempted request re-enters the waiting queue
     // added: bfloat16 steps of up to this many tokens (at most 64; 0: none) run with the layer's norms, residual
     // additions and SwiGLU inside the products' epilogues, on a second, pre-tiled copy of the weight matrices
-    // (twice the weights' memory).  Measured at Qwen2.5-7B sizes: faster at 16 tokens (3.79 against 4.05 ms a
-    // step), slower at 32 (4.61 against 4.48) and 64, where the merge of the products' wider partial tiles costs
-    // more than the kernels it saves.
-    size_t fused_decode_tokens = 16;
+    // (twice the weights' memory).  Measured at Qwen2.5-7B sizes, contexts of 2,048 to 4,096: 3.79 against 4.05 ms
+    // a step at 16 tokens, 4.23 against 4.47 at 32, 5.30 against 5.59 at 64.
+    size_t fused_decode_tokens = 64;
 
     // Sampling defaults (per-request values override them)
     float temperature = 1.0f;

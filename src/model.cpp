@@ -384,10 +384,13 @@ void Qwen2Model::make_images() {
     tune_grids();
 }
 
-int Qwen2Model::grid_for(int n, int k, int gated) const {
-    auto it = grids_.find({n, k, gated});
-    return it == grids_.end() ? sms_ : it->second;
+int Qwen2Model::grid_for(int n, int k, int gated, int bn) const {
+    auto it = grids_.find({n, k, gated, bn});
+    return it == grids_.end() ? (bn == 16 ? sms_ : 2 * sms_) : it->second;
 }
+
+// columns of the tensor-core tile for a step of m tokens
+static int tile_columns(int m) { return m <= 16 ? 16 : m <= 32 ? 32 : 64; }
 
 // The grid of each few-token product, measured once at load as the Python host does (ops.choose_ctas): one
 // CTA per SM, two per SM, and in between the counts that cut every 128-row tile into the same number of whole
@@ -399,38 +402,45 @@ void Qwen2Model::tune_grids() {
     cuda_check(cudaEventCreate(&e0), "cudaEventCreate");
     cuda_check(cudaEventCreate(&e1), "cudaEventCreate");
     // inputs and outputs of the trial products: a transient allocation of its own, given back below
+    const int limit = (int)std::min<size_t>(cfg_.fused_decode_tokens, 64);
+    const size_t x_bytes = (size_t)64 * std::max({H, q, I}) * 2, out_bytes = (size_t)64 * std::max({q + 2 * kv, H, 2 * I}) * 2;
     void *x = nullptr, *out = nullptr;
-    cuda_check(cudaMalloc(&x, (size_t)8 * std::max({H, q, I}) * 2), "cudaMalloc");
-    cuda_check(cudaMalloc(&out, (size_t)8 * std::max({q + 2 * kv, H, 2 * I}) * 2), "cudaMalloc");
-    cuda_check(cudaMemset(x, 0, (size_t)8 * std::max({H, q, I}) * 2), "clearing a buffer");
-    for (const Shape& sh : {Shape{q + 2 * kv, H, 0}, Shape{H, q, 0}, Shape{2 * I, H, I}, Shape{H, I, 0}}) {
-        const int tiles = sh.gated ? (sh.gated + 63) / 64 : (sh.n + 127) / 128, slabs = (sh.k + 63) / 64;
-        std::set<int> candidates{sms_, 2 * sms_};
-        for (int per_tile = 1; per_tile <= slabs / 4; ++per_tile)
-            if (slabs % per_tile == 0 && tiles * per_tile >= sms_ * 3 / 4 && tiles * per_tile <= 2 * sms_) candidates.insert(tiles * per_tile);
-        const std::vector<int> key{sh.n, sh.k, sh.gated};
-        int best_ctas = sms_;
-        float best_ms = 0;
-        for (int ctas : candidates) {
-            grids_[key] = ctas;
-            float ms = 0;
-            for (int rep = 0; rep < 2; ++rep) {                   // the second pass is the one that counts
-                cuda_check(cudaEventRecord(e0, nullptr), "cudaEventRecord");
-                for (const Layer& L : layers_) {
-                    const void *w = sh.gated ? L.w_gate_up : sh.n == q + 2 * kv && sh.k == H ? L.w_qkv : sh.k == I ? L.w_down : L.w_o;
-                    const void *t = sh.gated ? L.t_gate_up : sh.n == q + 2 * kv && sh.k == H ? L.t_qkv : sh.k == I ? L.t_down : L.t_o;
-                    fused_product(x, w, t, out, 8, sh.n, sh.k, false, RowScale(), nullptr, nullptr, sh.gated, nullptr);
+    cuda_check(cudaMalloc(&x, x_bytes), "cudaMalloc");
+    cuda_check(cudaMalloc(&out, out_bytes), "cudaMalloc");
+    cuda_check(cudaMemset(x, 0, x_bytes), "clearing a buffer");
+    // one measurement per width of the tensor-core tile (16, 32, 64 columns), at a token count that takes it
+    for (int m : {8, 32, 64}) {
+        if (m > std::max(limit, 8)) break;
+        const int bn = tile_columns(m);
+        for (const Shape& sh : {Shape{q + 2 * kv, H, 0}, Shape{H, q, 0}, Shape{2 * I, H, I}, Shape{H, I, 0}}) {
+            const int tiles = sh.gated ? (sh.gated + 63) / 64 : (sh.n + 127) / 128, slabs = (sh.k + 63) / 64;
+            std::set<int> candidates{sms_, 2 * sms_};
+            for (int per_tile = 1; per_tile <= slabs / 4; ++per_tile)
+                if (slabs % per_tile == 0 && tiles * per_tile >= sms_ * 3 / 4 && tiles * per_tile <= 2 * sms_) candidates.insert(tiles * per_tile);
+            const std::vector<int> key{sh.n, sh.k, sh.gated, bn};
+            int best_ctas = sms_;
+            float best_ms = 0;
+            for (int ctas : candidates) {
+                grids_[key] = ctas;
+                float ms = 0;
+                for (int rep = 0; rep < 2; ++rep) {                   // the second pass is the one that counts
+                    cuda_check(cudaEventRecord(e0, nullptr), "cudaEventRecord");
+                    for (const Layer& L : layers_) {
+                        const void *w = sh.gated ? L.w_gate_up : sh.n == q + 2 * kv && sh.k == H ? L.w_qkv : sh.k == I ? L.w_down : L.w_o;
+                        const void *t = sh.gated ? L.t_gate_up : sh.n == q + 2 * kv && sh.k == H ? L.t_qkv : sh.k == I ? L.t_down : L.t_o;
+                        fused_product(x, w, t, out, m, sh.n, sh.k, false, RowScale(), nullptr, nullptr, sh.gated, nullptr);
+                    }
+                    cuda_check(cudaEventRecord(e1, nullptr), "cudaEventRecord");
+                    cuda_check(cudaEventSynchronize(e1), "cudaEventSynchronize");
+                    cuda_check(cudaEventElapsedTime(&ms, e0, e1), "cudaEventElapsedTime");
                 }
-                cuda_check(cudaEventRecord(e1, nullptr), "cudaEventRecord");
-                cuda_check(cudaEventSynchronize(e1), "cudaEventSynchronize");
-                cuda_check(cudaEventElapsedTime(&ms, e0, e1), "cudaEventElapsedTime");
+                if (best_ms == 0 || ms < best_ms * 0.98f) {           // a larger grid must win by more than the noise
+                    best_ms = ms;
+                    best_ctas = ctas;
+                }
             }
-            if (best_ms == 0 || ms < best_ms * 0.98f) {           // a larger grid must win by more than the noise
-                best_ms = ms;
-                best_ctas = ctas;
-            }
+            grids_[key] = best_ctas;
         }
-        grids_[key] = best_ctas;
     }
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
@@ -440,8 +450,8 @@ void Qwen2Model::tune_grids() {
 
 void Qwen2Model::fused_product(const void* x, const void* w, const void* tiled, void* out, int m, int n, int k, bool out_f32,
                                RowScale scale, const float* gain, float* sumsq_out, int gated, cudaStream_t s) {
-    const int bn = m <= 16 ? 16 : m <= 32 ? 32 : 64;
-    const int ctas = bn == 16 ? grid_for(n, k, gated) : 2 * sms_;
+    const int bn = tile_columns(m);
+    const int ctas = grid_for(n, k, gated, bn);
     // swapped form: the weights are the 128-row operand; a gated product writes [m, gated] columns
     kernel_check(vcb_gemm_bf16_tcgen05_fused(w, n, k, tiled, x, m, k, k, out, gated ? gated : n, out_f32 ? 1 : 0, 1, bn, ctas,
                                              gemm_partial_, gemm_tickets_, 16384, status_, scale.sumsq, scale.parts, 64,

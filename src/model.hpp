@@ -49,7 +49,7 @@ class Qwen2Model {
     const float* forward_fused(const Batch& b, cudaStream_t s);
     void make_images();
     void tune_grids();                           // measures, per product shape, the grid of the few-token product
-    int grid_for(int n, int k, int gated) const;
+    int grid_for(int n, int k, int gated, int bn) const;
     size_t image_bytes() const;
     int sumsq_parts(int features) const { return 4 * ((features + 127) / 128); }
     void attend(const Batch& b, int layer, cudaStream_t s);
@@ -72,7 +72,7 @@ class Qwen2Model {
     int *gemm_tickets_ = nullptr, *status_ = nullptr, *attn_tickets_ = nullptr;
     void* cublas_ = nullptr;
     void* t_lm_head_ = nullptr;
-    std::map<std::vector<int>, int> grids_;      // (features, k, gated) -> persistent CTAs at tiles of 16 columns
+    std::map<std::vector<int>, int> grids_;      // (features, k, gated, tile columns) -> persistent CTAs
     float *carry_ = nullptr, *ss_inner_ = nullptr;       // sums of squares handed from product to product
 };
 

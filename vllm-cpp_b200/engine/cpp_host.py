@@ -54,7 +54,7 @@ class CppEngine:
     def __init__(self, model_path: str, dtype: str = "bfloat16", model_arch: str = "", block_size: int = 16,
                  num_gpu_blocks: int = 0, max_num_seqs: int = 64, max_model_len: int = 8192,
                  max_num_batched_tokens: int = 16384, max_tokens_per_step: int = 512, seed: int = 0,
-                 gpu_memory_utilization: int = 90, preempted_to_front: bool = False, fused_decode_tokens: int = 16):
+                 gpu_memory_utilization: int = 90, preempted_to_front: bool = False, fused_decode_tokens: int = 64):
         self._l = lib()
         self._h = self._l.vcbe_create(model_path.encode(), model_arch.encode(), dtype.encode(), block_size, num_gpu_blocks,
                                       max_num_seqs, max_model_len, max_num_batched_tokens, max_tokens_per_step, seed,
