@@ -321,25 +321,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         float* xch = rstd_s + 128;                                                  // [64][8]: up halves
         if (a.scale_sumsq) {
             // The factor of every token: rsqrt(sum of the partials / width + eps), summed in a fixed order.
-            // A lane per token and a quarter of the partials per warp, nothing between the loads that
-            // would order them: a warp per token with a shuffle after each costs one trip to the L2
-            // cache per token and warp, 11 us for 64 tokens.  The quarters meet in shared memory (the
+            // The 128 threads share the (token, partial) pairs: thread t takes token t % W (W: the power of
+            // two that holds the tokens, so that neighbours read neighbours) and every (128 / W)-th partial,
+            // and requests eight values before it adds the first.  A loop that adds as it loads, or a
+            // shuffle between the loads, costs one trip to the L2 cache per value: 11 us for 64 tokens.
+            // Threads of a warp that hold the same token meet by shuffles, the warps in shared memory (the
             // exchange area of the gated epilogue, which is used only after this).
-            float* quarter = xch;                                                   // [4][128]
-            for (int j = lane; j < a.rows_q && j < BN; j += 32) {
-                float s0 = 0.0f, s1 = 0.0f;
-                int part = lg;
-                for (; part + 4 < a.scale_parts; part += 8) {
-                    s0 += __ldcg(a.scale_sumsq + (size_t)part * a.scale_ld + j);
-                    s1 += __ldcg(a.scale_sumsq + (size_t)(part + 4) * a.scale_ld + j);
+            float* warp_sums = xch;                                                 // [4][32]
+            const int n_tok = min(a.rows_q, BN);
+            int W = 1;
+            while (W < n_tok) W <<= 1;
+            const int j = r & (W - 1), p0 = r / W, p_step = 128 / W;
+            float sum = 0.0f;
+            for (int part = p0; part < a.scale_parts; part += 8 * p_step) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int p = part + u * p_step;
+                    v[u] = (p < a.scale_parts && j < n_tok) ? __ldcg(a.scale_sumsq + (size_t)p * a.scale_ld + j) : 0.0f;
                 }
-                if (part < a.scale_parts) s0 += __ldcg(a.scale_sumsq + (size_t)part * a.scale_ld + j);
-                quarter[lg * 128 + j] = s0 + s1;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) sum += v[u];
             }
+            for (int o = 16; o >= W; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            warp_sums[lg * 32 + lane] = sum;
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            for (int j = r; j < a.rows_q && j < BN; j += 128) {
-                const float sum = (quarter[j] + quarter[128 + j]) + (quarter[256 + j] + quarter[384 + j]);
-                rstd_s[j] = rsqrtf(sum * a.scale_inv_width + a.scale_eps);
+            if (r < n_tok) {
+                float total = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w)
+                    if (((w * 32 + (r & 31)) & (W - 1)) == r) total += warp_sums[w * 32 + (r & 31)];
+                rstd_s[r] = rsqrtf(total * a.scale_inv_width + a.scale_eps);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
