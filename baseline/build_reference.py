@@ -25,6 +25,24 @@ DRIVER = os.path.join(OUT, "ref_driver")
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 
+def default_source() -> str:
+    """Where the reference's checkout lies: $VLLM_CPP_REFERENCE, else ``reference_path`` of BASELINE.json
+    at the repository's root, else ``reference/`` beside the repository."""
+    env = os.environ.get("VLLM_CPP_REFERENCE")
+    if env:
+        return env
+    root = os.path.dirname(HERE)
+    try:
+        import json
+        with open(os.path.join(root, "BASELINE.json")) as f:
+            path = json.load(f).get("reference_path")
+        if path:
+            return path
+    except (OSError, ValueError):
+        pass
+    return os.path.join(os.path.dirname(root), "reference")
+
+
 def run(cmd, **kw):
     print("+ " + " ".join(cmd), file=sys.stderr, flush=True)
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, **kw)
@@ -57,11 +75,11 @@ def build(source: str) -> str:
     return DRIVER
 
 
-def driver_path(source: str = "/root/reference") -> str:
+def driver_path(source: str = "") -> str:
     """The built driver; builds it first if it is missing and a checkout of the reference is at hand."""
     if os.path.isfile(DRIVER) and os.access(DRIVER, os.X_OK):
         return DRIVER
-    return build(source)
+    return build(source or default_source())
 
 
 def driver_env() -> dict:
@@ -72,5 +90,5 @@ def driver_env() -> dict:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--source", default="/root/reference")
+    ap.add_argument("--source", default=default_source())
     print(build(ap.parse_args().source))
