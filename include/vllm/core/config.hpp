@@ -15,6 +15,8 @@ struct EngineConfig {
     std::string model_path;               // a folder with config.json and model.safetensors
     std::string model_arch;               // "": config.json's architectures[0]; the reference takes it from --arch only
     std::string dtype = "bfloat16";       // added: "bfloat16" or "float32" (a true 32-bit path)
+    int device = 0;                       // added: the CUDA device this engine runs on
+    std::string load_format = "safetensors";   // added: "random" fills the weights from `seed` (model_path needs config.json only)
 
     // Memory
     size_t gpu_memory_utilization = 90;   // percentage (0-100] of the device's memory this engine may hold
@@ -38,7 +40,7 @@ struct EngineConfig {
     float top_p = 1.0f;
     int32_t top_k = -1;                   // -1 means disabled
     float repetition_penalty = 1.0f;
-    uint64_t seed = 0;                    // added: requests without a seed of their own derive one from it
+    uint64_t seed = 0;                    // added: requests without a seed of their own derive one from it; the random weights' seed
 };
 
 }  // namespace vllm

@@ -25,7 +25,8 @@ VCBE_EXPORT const char* vcbe_last_error() { return g_error.c_str(); }
 
 VCBE_EXPORT void* vcbe_create(const char* model_path, const char* model_arch, const char* dtype, int block_size, int num_gpu_blocks,
                               int max_num_seqs, int max_model_len, int max_num_batched_tokens, int max_tokens_per_step,
-                              unsigned long long seed, int gpu_memory_utilization, int preempted_to_front, int fused_decode_tokens) {
+                              unsigned long long seed, int gpu_memory_utilization, int preempted_to_front, int fused_decode_tokens,
+                              const char* load_format) {
     vllm::EngineConfig cfg;
     cfg.model_path = model_path ? model_path : "";
     cfg.model_arch = model_arch ? model_arch : "";
@@ -40,6 +41,7 @@ VCBE_EXPORT void* vcbe_create(const char* model_path, const char* model_arch, co
     cfg.gpu_memory_utilization = (size_t)gpu_memory_utilization;
     cfg.preempted_to_front = preempted_to_front != 0;
     cfg.fused_decode_tokens = (size_t)fused_decode_tokens;
+    if (load_format && *load_format) cfg.load_format = load_format;
     auto* e = new vllm::Engine(cfg);
     if (!e->initialize()) {
         g_error = e->last_error();

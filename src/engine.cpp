@@ -80,6 +80,8 @@ struct Engine::Impl {
     void validate() const {
         auto need = [](bool ok, const std::string& msg) { if (!ok) throw Error(msg); };
         need(cfg.dtype == "bfloat16" || cfg.dtype == "float32", "dtype must be 'bfloat16' or 'float32', got '" + cfg.dtype + "'");
+        need(cfg.load_format == "safetensors" || cfg.load_format == "random",
+             "load_format must be 'safetensors' or 'random', got '" + cfg.load_format + "'");
         need(cfg.block_size > 0, "KV block size must be greater than zero");
         need(cfg.block_size % 16 == 0 && cfg.block_size <= 256, "block_size must be a multiple of 16 and at most 256");
         need(cfg.gpu_memory_utilization > 0 && cfg.gpu_memory_utilization <= 100, "gpu_memory_utilization is a percentage in (0, 100]");
@@ -97,7 +99,9 @@ struct Engine::Impl {
         int count = 0;
         if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
             throw Error("no CUDA device: this engine runs on a B200 (sm_100a) only; there is no CPU path");
-        cuda_check(cudaSetDevice(0), "cudaSetDevice");
+        if (cfg.device < 0 || cfg.device >= count)
+            throw Error("device " + std::to_string(cfg.device) + " does not exist (" + std::to_string(count) + " visible)");
+        cuda_check(cudaSetDevice(cfg.device), "cudaSetDevice");
         if (cfg.model_path.empty()) throw Error("model_path is empty");
         const json::Value j = json::parse_file(cfg.model_path + "/config.json");
         if (j.kind != json::Value::Object) throw Error(cfg.model_path + "/config.json must hold a JSON object");
@@ -159,7 +163,8 @@ struct Engine::Impl {
         cuda_check(cudaMallocHost(&topk_host, rows * 4), "pinned sampler options");
         cuda_check(cudaMallocHost(&ids_host, rows * 4), "pinned ids");
         cuda_check(cudaStreamCreate(&stream), "cudaStreamCreate");
-        model->load_weights(cfg.model_path);
+        if (cfg.load_format == "random") model->random_weights(cfg.seed);
+        else model->load_weights(cfg.model_path);
         cache.reset(new CacheManager(model->group_windows(), (int)cfg.block_size, num_pages, (int)cfg.max_num_seqs));
         scheduler.reset(new Scheduler(*cache, cfg));
         initialized = true;

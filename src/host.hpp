@@ -59,6 +59,8 @@ int vcb_gemm_bf16_tcgen05_fused(const void* p, int rows_p, int ldp, const void* 
                                 int gated, void* stream);
 long long vcb_tiled_weight_bytes(int rows, int k, int gated);
 int vcb_tile_weights(const void* w, int rows, int k, int ld, int gated, void* out, void* stream);
+int vcb_random_normal(void* out, unsigned long long n, unsigned long long first, unsigned long long key, float mean,
+                      float std_, int dtype, void* stream);
 int vcb_repetition_penalty(float* logits, int ld, const int* ids, const int* row_start, const float* penalty, int n_rows,
                            int vocab, void* stream);
 int vcb_sample(const float* logits, int ld, int vocab, const float* temperature, const float* uniform, int* out, int n_rows,
@@ -71,6 +73,10 @@ namespace vllm {
 namespace host {
 
 enum { DT_F32 = 0, DT_BF16 = 1 };      // the kernels' dtype codes
+
+// The key of a tensor's stream of random values: the first eight bytes (little-endian) of SHA-256 of
+// "<seed>:<name>", as weights/random_init.py computes it.
+uint64_t tensor_key(uint64_t seed, const std::string& name);
 
 struct Error : std::runtime_error {
     using std::runtime_error::runtime_error;
@@ -246,7 +252,7 @@ class Scheduler {
 // ----------------------------------------------------------------------------------------------- model
 struct Qwen2Config {                     // the config.json keys of Qwen2ForCausalLM (src/model/qwen.cpp:33-47 reads eight of them)
     int hidden = 0, layers = 0, heads = 0, kv_heads = 0, head_dim = 0, inter = 0, vocab = 0, max_pos = 0;
-    double rope_theta = 0, eps = 1e-6;
+    double rope_theta = 0, eps = 1e-6, init_range = 0.02;    // init_range: 'initializer_range', the random weights' spread
     bool tie = false, use_window = false;
     int window = 0, max_window_layers = 0;
     std::vector<TokenId> eos_ids;

@@ -37,6 +37,10 @@ int main(int argc, char** argv) {
         if (arg == "--model") cfg.model_path = value();
         else if (arg == "--arch") cfg.model_arch = value();
         else if (arg == "--dtype") cfg.dtype = value();
+        else if (arg == "--load-format") cfg.load_format = value();
+        else if (arg == "--seed") cfg.seed = std::stoull(value());
+        else if (arg == "--device") cfg.device = std::stoi(value());
+        else if (arg == "--repetition-penalty") sp.repetition_penalty = std::stof(value());
         else if (arg == "--block-size") cfg.block_size = std::stoul(value());
         else if (arg == "--num-blocks") cfg.num_gpu_blocks = std::stoul(value());
         else if (arg == "--gpu-memory-utilization") cfg.gpu_memory_utilization = std::stoul(value());

@@ -75,6 +75,10 @@ Qwen2Config Qwen2Config::from_json(const json::Value& j) {
         if (e->kind != json::Value::Number || !(e->num > 0)) problems.push_back("'rms_norm_eps' must be a positive number");
         else c.eps = e->num;
     }
+    if (const json::Value* r = j.find("initializer_range")) {
+        if (r->kind != json::Value::Number || !(r->num >= 0)) problems.push_back("'initializer_range' must be a non-negative number");
+        else c.init_range = r->num;
+    }
     if (const json::Value* a = j.find("hidden_act"))
         if (a->kind != json::Value::String || a->str != "silu") problems.push_back("hidden_act is not supported (only 'silu')");
     if (const json::Value* rs = j.find("rope_scaling"))
@@ -365,6 +369,62 @@ void Qwen2Model::load_weights(const std::string& model_path) {
         upload(at(p + "input_layernorm.weight"), L.gain_in, true);
         upload(at(p + "post_attention_layernorm.weight"), L.gain_post, true);
     }
+    make_images();
+}
+
+// Random weights from a seed, the values weights/random_init.py gives every tensor for the same seed (element i of
+// a tensor is a function of the seed, the tensor's name and i; csrc/random_init.cu): matrices and biases
+// N(0, initializer_range), gains 1 + N(0, initializer_range).  Biases and gains of a bfloat16 model take the value
+// a bfloat16 checkpoint would hold.
+void Qwen2Model::random_weights(uint64_t seed) {
+    const size_t H = mc_.hidden, q = (size_t)mc_.heads * mc_.head_dim, kv = (size_t)mc_.kv_heads * mc_.head_dim, I = mc_.inter;
+    const float std_ = (float)mc_.init_range;
+    const auto shapes = expected_tensors();
+    auto numel = [&](const std::string& name) {
+        size_t n = 1;
+        for (int64_t d : shapes.at(name)) n *= (size_t)d;
+        return n;
+    };
+    auto matrix = [&](const std::string& name, void* dst) {
+        kernel_check(vcb_random_normal(dst, numel(name), 0, tensor_key(seed, name), 0.0f, std_, bf16_ ? DT_BF16 : DT_F32, nullptr), "random_normal");
+    };
+    std::vector<uint16_t> rounded;
+    std::vector<float> widened;
+    auto vector32 = [&](const std::string& name, float* dst, float mean) {
+        const size_t n = numel(name);
+        if (!bf16_) {
+            kernel_check(vcb_random_normal(dst, n, 0, tensor_key(seed, name), mean, std_, DT_F32, nullptr), "random_normal");
+            return;
+        }
+        // through bfloat16: generated into the (larger) float32 destination, read back, widened, stored again
+        kernel_check(vcb_random_normal(dst, n, 0, tensor_key(seed, name), mean, std_, DT_BF16, nullptr), "random_normal");
+        rounded.resize(n);
+        widened.resize(n);
+        cuda_check(cudaMemcpy(rounded.data(), dst, n * 2, cudaMemcpyDeviceToHost), "copy of a tensor");
+        for (size_t i = 0; i < n; ++i) { const uint32_t u = (uint32_t)rounded[i] << 16; std::memcpy(&widened[i], &u, 4); }
+        cuda_check(cudaMemcpy(dst, widened.data(), n * 4, cudaMemcpyHostToDevice), "copy of a tensor");
+    };
+    auto offset = [&](void* base, size_t elems) { return static_cast<void*>(static_cast<uint8_t*>(base) + elems * el_); };
+    matrix("model.embed_tokens.weight", embed_);
+    if (!mc_.tie) matrix("lm_head.weight", lm_head_);
+    vector32("model.norm.weight", final_gain_, 1.0f);
+    for (int l = 0; l < mc_.layers; ++l) {
+        const std::string p = "model.layers." + std::to_string(l) + ".";
+        Layer& L = layers_[l];
+        matrix(p + "self_attn.q_proj.weight", L.w_qkv);
+        matrix(p + "self_attn.k_proj.weight", offset(L.w_qkv, q * H));
+        matrix(p + "self_attn.v_proj.weight", offset(L.w_qkv, (q + kv) * H));
+        vector32(p + "self_attn.q_proj.bias", L.b_qkv, 0.0f);
+        vector32(p + "self_attn.k_proj.bias", L.b_qkv + q, 0.0f);
+        vector32(p + "self_attn.v_proj.bias", L.b_qkv + q + kv, 0.0f);
+        matrix(p + "self_attn.o_proj.weight", L.w_o);
+        matrix(p + "mlp.gate_proj.weight", L.w_gate_up);
+        matrix(p + "mlp.up_proj.weight", offset(L.w_gate_up, I * H));
+        matrix(p + "mlp.down_proj.weight", L.w_down);
+        vector32(p + "input_layernorm.weight", L.gain_in, 1.0f);
+        vector32(p + "post_attention_layernorm.weight", L.gain_post, 1.0f);
+    }
+    cuda_check(cudaDeviceSynchronize(), "random weights");
     make_images();
 }
 

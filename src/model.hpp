@@ -23,6 +23,7 @@ class Qwen2Model {
 
     void place(DevicePool& pool, int num_pages);          // takes every slice: weights, pages, step buffers, scratch
     void load_weights(const std::string& model_path);     // by tensor name; one error lists all faults
+    void random_weights(uint64_t seed);                   // the tensors weights/random_init.py makes for this seed
     // Runs the batch's tokens from the cache; returns the float32 logits [n_logit_rows, vocab] on the device.
     const float* forward(const Batch& b, cudaStream_t s);
     // Context splits per (request, kv head) of the split-KV decode attention in cache group `group`, for a

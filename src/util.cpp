@@ -209,5 +209,71 @@ void* DevicePool::alloc(size_t bytes, const char* what) {
     return base_ + start;
 }
 
+// ---------------------------------------------------------------------------- SHA-256 (FIPS 180-4), for tensor_key
+namespace {
+inline uint32_t rotr(uint32_t x, int n) { return (x >> n) | (x << (32 - n)); }
+
+// The round constants are the first 32 bits of the fractional parts of the cube roots of the first 64 primes,
+// the initial state those of the square roots of the first eight; computed here rather than listed.
+struct Sha256Tables {
+    uint32_t k[64], h0[8];
+    Sha256Tables() {
+        int primes[64], n = 0;
+        for (int c = 2; n < 64; ++c) {
+            bool prime = true;
+            for (int d = 2; d * d <= c; ++d) if (c % d == 0) { prime = false; break; }
+            if (prime) primes[n++] = c;
+        }
+        for (int i = 0; i < 64; ++i) k[i] = frac_bits(cbrtl((long double)primes[i]));
+        for (int i = 0; i < 8; ++i) h0[i] = frac_bits(sqrtl((long double)primes[i]));
+    }
+    static uint32_t frac_bits(long double x) {
+        x -= floorl(x);
+        return (uint32_t)floorl(x * 4294967296.0L);
+    }
+};
+
+void sha256(const std::string& msg, uint8_t out[32]) {
+    static const Sha256Tables t;
+    uint32_t h[8];
+    std::memcpy(h, t.h0, sizeof h);
+    std::string m = msg;
+    m.push_back((char)0x80);
+    while (m.size() % 64 != 56) m.push_back((char)0);
+    const uint64_t bits = (uint64_t)msg.size() * 8;
+    for (int i = 7; i >= 0; --i) m.push_back((char)((bits >> (8 * i)) & 0xFF));
+    for (size_t off = 0; off < m.size(); off += 64) {
+        uint32_t w[64];
+        for (int i = 0; i < 16; ++i)
+            w[i] = ((uint32_t)(uint8_t)m[off + 4 * i] << 24) | ((uint32_t)(uint8_t)m[off + 4 * i + 1] << 16) |
+                   ((uint32_t)(uint8_t)m[off + 4 * i + 2] << 8) | (uint32_t)(uint8_t)m[off + 4 * i + 3];
+        for (int i = 16; i < 64; ++i) {
+            const uint32_t s0 = rotr(w[i - 15], 7) ^ rotr(w[i - 15], 18) ^ (w[i - 15] >> 3);
+            const uint32_t s1 = rotr(w[i - 2], 17) ^ rotr(w[i - 2], 19) ^ (w[i - 2] >> 10);
+            w[i] = w[i - 16] + s0 + w[i - 7] + s1;
+        }
+        uint32_t a = h[0], b = h[1], c = h[2], d = h[3], e = h[4], f = h[5], g = h[6], hh = h[7];
+        for (int i = 0; i < 64; ++i) {
+            const uint32_t S1 = rotr(e, 6) ^ rotr(e, 11) ^ rotr(e, 25), ch = (e & f) ^ (~e & g);
+            const uint32_t t1 = hh + S1 + ch + t.k[i] + w[i];
+            const uint32_t S0 = rotr(a, 2) ^ rotr(a, 13) ^ rotr(a, 22), maj = (a & b) ^ (a & c) ^ (b & c);
+            const uint32_t t2 = S0 + maj;
+            hh = g; g = f; f = e; e = d + t1; d = c; c = b; b = a; a = t1 + t2;
+        }
+        h[0] += a; h[1] += b; h[2] += c; h[3] += d; h[4] += e; h[5] += f; h[6] += g; h[7] += hh;
+    }
+    for (int i = 0; i < 8; ++i)
+        for (int j = 0; j < 4; ++j) out[4 * i + j] = (uint8_t)(h[i] >> (24 - 8 * j));
+}
+}  // namespace
+
+uint64_t tensor_key(uint64_t seed, const std::string& name) {
+    uint8_t digest[32];
+    sha256(std::to_string(seed) + ":" + name, digest);
+    uint64_t key = 0;
+    for (int i = 7; i >= 0; --i) key = (key << 8) | digest[i];
+    return key;
+}
+
 }  // namespace host
 }  // namespace vllm

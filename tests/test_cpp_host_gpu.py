@@ -54,8 +54,8 @@ def cpp_engine(tmp_path, name, dtype, seed=1, **kw):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16", "bfloat16-plain"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_explicit_batches_cut_every_way(tmp_path, name, dtype):
-    """bfloat16: steps of up to 64 tokens run with the norms, additions and SwiGLU inside the products (the
-    default is 16); "bfloat16-plain" switches that off, so every step runs the plain sequence of kernels."""
+    """bfloat16: steps of up to 64 tokens run with the norms, additions and SwiGLU inside the products;
+    "bfloat16-plain" switches that off, so every step runs the plain sequence of kernels."""
     from test_replay_gpu import mixed_trace
     cfg, page = CONFIGS[name]
     pages = 4 * (-(-120 // page)) + 1
@@ -211,3 +211,47 @@ def test_command_line(tmp_path):
     assert [[int(t) for t in line.split(",")] for line in out.stdout.strip().splitlines()] == want
     bad = subprocess.run([cli, "--model", str(tmp_path / "nowhere"), "--prompt-ids", "1"], capture_output=True, text=True, timeout=300)
     assert bad.returncode == 1 and "Cannot open config" in bad.stderr
+    # random weights from a seed: a folder with config.json alone
+    import json
+    from vllm_cpp_b200.engine.cpp_host import CppEngine
+    bare = tmp_path / "bare"
+    bare.mkdir()
+    (bare / "config.json").write_text(json.dumps(cfg))
+    eng = CppEngine(str(bare), dtype="float32", num_gpu_blocks=64, max_model_len=256, max_num_batched_tokens=256,
+                    load_format="random", seed=3)
+    want = eng.generate(prompts, max_tokens=6, temperature=0.0, ignore_eos=True)
+    eng.close()
+    out = subprocess.run([cli, "--model", str(bare), "--load-format", "random", "--seed", "3"] + args[1:], env=env,
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert [[int(t) for t in line.split(",")] for line in out.stdout.strip().splitlines()] == want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_weights_are_those_of_the_python_host(tmp_path, dtype):
+    """load_format "random": the C++ host fills its weights from the seed with the same generator as
+    write_random_model, so a folder written for that seed and a C++ engine that is given only config.json
+    hold the same numbers: equal logits to the bit in float32 (the same kernels on the same values), and in
+    bfloat16 as close as two runs of the same engine on the same weights."""
+    import json
+    from vllm_cpp_b200.engine.cpp_host import CppEngine
+    from vllm_cpp_b200.weights.random_init import write_random_model
+    cfg, page = CONFIGS["B"]
+    cfg = dict(cfg, initializer_range=0.05)
+    written = str(tmp_path / "written")
+    write_random_model(written, cfg, seed=5, dtype=dtype)
+    bare = tmp_path / "bare"
+    bare.mkdir()
+    (bare / "config.json").write_text(json.dumps(cfg))
+    args = dict(dtype=dtype, block_size=page, num_gpu_blocks=24, max_num_seqs=4, max_model_len=256, max_num_batched_tokens=256)
+    ids = token_ids(cfg, 70, 9)
+    got = {}
+    for name, folder, extra in (("loaded", written, {}), ("random", str(bare), dict(load_format="random", seed=5)),
+                                ("other seed", str(bare), dict(load_format="random", seed=6))):
+        eng = CppEngine(folder, **args, **extra)
+        got[name] = eng.step_tokens([(0, ids[:50], [0, 49]), (1, ids[50:], [19])])
+        eng.close()
+    assert np.array_equal(got["loaded"], got["random"])
+    assert np.abs(got["loaded"] - got["other seed"]).max() > 1e-3
+    with pytest.raises(Exception, match="load_format"):
+        CppEngine(str(bare), **args, load_format="gguf")

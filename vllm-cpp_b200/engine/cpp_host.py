@@ -30,7 +30,7 @@ def lib():
         P, I, F, L, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_ulonglong
         C = ctypes.c_char_p
         l.vcbe_last_error.restype = C
-        l.vcbe_create.argtypes, l.vcbe_create.restype = [C, C, C, I, I, I, I, I, I, U, I, I, I], P
+        l.vcbe_create.argtypes, l.vcbe_create.restype = [C, C, C, I, I, I, I, I, I, U, I, I, I, C], P
         l.vcbe_destroy.argtypes = [P]
         l.vcbe_add_request.argtypes, l.vcbe_add_request.restype = [P, P, I, I, F, F, I, F, I, U, I, P, I], L
         l.vcbe_step.argtypes, l.vcbe_step.restype = [P, P, P, P, I], I
@@ -54,11 +54,15 @@ class CppEngine:
     def __init__(self, model_path: str, dtype: str = "bfloat16", model_arch: str = "", block_size: int = 16,
                  num_gpu_blocks: int = 0, max_num_seqs: int = 64, max_model_len: int = 8192,
                  max_num_batched_tokens: int = 16384, max_tokens_per_step: int = 512, seed: int = 0,
-                 gpu_memory_utilization: int = 90, preempted_to_front: bool = False, fused_decode_tokens: int = 64):
+                 gpu_memory_utilization: int = 90, preempted_to_front: bool = False, fused_decode_tokens: int = 64,
+                 load_format: str = "safetensors"):
+        """``load_format``: "random" fills the weights from ``seed`` (the tensors ``write_random_model`` would
+        store for it); ``model_path`` then needs config.json only."""
         self._l = lib()
         self._h = self._l.vcbe_create(model_path.encode(), model_arch.encode(), dtype.encode(), block_size, num_gpu_blocks,
                                       max_num_seqs, max_model_len, max_num_batched_tokens, max_tokens_per_step, seed,
-                                      gpu_memory_utilization, 1 if preempted_to_front else 0, fused_decode_tokens)
+                                      gpu_memory_utilization, 1 if preempted_to_front else 0, fused_decode_tokens,
+                                      load_format.encode())
         if not self._h:
             raise CppEngineError(self._l.vcbe_last_error().decode())
         self.max_num_seqs = max_num_seqs
