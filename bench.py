@@ -255,24 +255,21 @@ def flat_config(cfg, a, nums, extra):
 
 # ------------------------------------------------------------------------------------------- the C++ host
 def run_cpp_host(cfg, a) -> int:
-    """Decode throughput through the C++ host runtime (vllm::Engine behind include/vllm/vllm.hpp): the same model
-    folder, requests with prompts of 2,048 tokens generating up to 4,096, the same runs of timed steps as the
+    """Decode throughput through the C++ host runtime (vllm::Engine behind include/vllm/vllm.hpp): the same random
+    weights, requests with prompts of 2,048 tokens generating up to 4,096, the same runs of timed steps as the
     e2e figure of the Python host, by the wall clock around Engine::step (which returns the sampled ids)."""
     import numpy as np
-    import torch
     from vllm_cpp_b200.engine.cpp_host import CppEngine
-    from vllm_cpp_b200.weights.random_init import write_random_model
-    where = "/dev/shm" if os.path.isdir("/dev/shm") else tempfile.gettempdir()
-    folder = tempfile.mkdtemp(prefix="vcb_cpp_model_", dir=where)
+    folder = tempfile.mkdtemp(prefix="vcb_cpp_model_")          # config.json alone: the weights come from the seed
     try:
-        write_random_model(folder, cfg, seed=0, dtype="bfloat16", device="cuda")
-        torch.cuda.empty_cache()
+        with open(os.path.join(folder, "config.json"), "w") as f:
+            json.dump(cfg, f)
         batch, lead = a.batch, 16
         pages = batch * ((CONTEXT + SLACK) // 16 + 1) + 16
         t0 = time.time()
         eng = CppEngine(folder, dtype="bfloat16", block_size=16, num_gpu_blocks=pages, max_num_seqs=max(batch, 8),
                         max_model_len=CONTEXT + SLACK, max_num_batched_tokens=PREFILL_TOKENS, max_tokens_per_step=PREFILL_TOKENS,
-                        fused_decode_tokens=int(os.environ.get("VCB_FUSED_DECODE_TOKENS", "64")))
+                        fused_decode_tokens=int(os.environ.get("VCB_FUSED_DECODE_TOKENS", "64")), load_format="random", seed=0)
         load_s = time.time() - t0
     finally:
         shutil.rmtree(folder, ignore_errors=True)
