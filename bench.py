@@ -536,6 +536,7 @@ def run_reference(cfg, a) -> int:
 
 # ------------------------------------------------------------------------------------------------ our arm
 def main() -> int:
+    global CONTEXT_START, CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
@@ -555,6 +556,9 @@ def main() -> int:
     ap.add_argument("--host", default="python", choices=["python", "cpp"],
                     help="cpp: decode throughput through the C++ host runtime (vllm::Engine) instead of the Python host")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--contexts", default="",
+                    help="START,END: the decode measurement's contexts grow from START to END tokens instead of "
+                         f"{CONTEXT_START},{CONTEXT} (with --only decode; the default is the benchmark's configuration)")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only (for profiling); the other fields of the line are null")
     ap.add_argument("--no-pdl", action="store_true", help="ordinary launches instead of programmatic dependent launch")
@@ -571,6 +575,10 @@ def main() -> int:
                     help="--impl reference: begin no further measurement after this many seconds")
     ap.add_argument("--reference-b64", action="store_true", help="--impl reference: measure batch 64 too (many minutes)")
     a = ap.parse_args()
+    if a.contexts:
+        CONTEXT_START, CONTEXT = (int(v) for v in a.contexts.split(","))
+        if a.only != "decode" or not 0 < CONTEXT_START < CONTEXT:
+            ap.error("--contexts START,END goes with --only decode and needs 0 < START < END")
     cfg = dict(QWEN25_7B, **SIZES[a.size])
     if a.size == "7b" or a.layers != QWEN25_7B["num_hidden_layers"]:
         cfg["num_hidden_layers"] = a.layers
@@ -599,7 +607,7 @@ def main() -> int:
         return run_cpp_host(cfg, a)
     nums = model_numbers(cfg)
     peaks = load_peaks()
-    max_batch = max(64, a.batch)
+    max_batch = a.batch if a.only == "decode" else max(64, a.batch)     # the points at batch 1 and 64 use the same engine
     pages = max_batch * ((CONTEXT + SLACK) // 16 + 1) + PREFILL_TOKENS // 16 + 16
     ecfg = EngineConfig(load_format="random", model_config=cfg, seed=0, dtype="bfloat16", block_size=16,
                         num_gpu_blocks=None if a.utilization else pages,
@@ -737,6 +745,10 @@ def main() -> int:
             write_timeline(a.timeline, a.batch, runner, cache, rng, vocab)
         print(json.dumps({"metric": METRIC, "only": "decode", "batch": a.batch, "ms_per_step": round(ms, 4),
                           "value": round(value, 1), "unit": "tokens/s", "gpu_launches": launches,
+                          "contexts": [CONTEXT_START, CONTEXT],
+                          "roofline": {"achieved": round(step_bytes / (ms * sum(k for _, k, _ in results) * 1e-3) / 1e9, 1),
+                                       "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                       "frac": round(step_bytes / (ms * sum(k for _, k, _ in results) * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)},
                           "runs": [[c, k, round(t / k, 4)] for c, k, t in results],
                           "product_grids": {f"{n}x{k} tile {bn}{' gated' if g else ''}{' residual' if r else ''}": c
                                             for (n, k, bn, g, r), c in sorted(ops._cta_choice.items())},

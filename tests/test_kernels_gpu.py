@@ -553,7 +553,9 @@ def test_gemm_bf16_tcgen05_fused_norm(ops, m, n, k, ctas):
 
 
 @pytest.mark.parametrize("m,inter,k,ctas", [(8, 18944 // 4, 512, 148), (1, 64, 64, 148), (5, 200, 200, 3), (33, 176, 1024, 7),
-                                            (16, 1000, 576, 148), (100, 224, 96, 11), (128, 128, 64, 148)])
+                                            (16, 1000, 576, 148), (100, 224, 96, 11), (128, 128, 64, 148),
+                                            # whole tiles of 32 and 64 columns: the epilogue that works in rounds of 32
+                                            (40, 200, 256, 148), (64, 192, 128, 2), (17, 100, 64, 148), (49, 328, 512, 6)])
 @pytest.mark.parametrize("scaled", [False, True])
 def test_gemm_bf16_tcgen05_gated(ops, m, inter, k, ctas, scaled):
     """The gate-and-up product with the activation in its epilogue against silu(x g^T) * (x u^T) done

@@ -318,7 +318,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         int tile, s0, s1, n = 0;
         pdl_wait();                                 // nothing is written before the previous kernel is done
         float* rstd_s = reinterpret_cast<float*>(const_cast<int*>(flags + 2));      // [min(BN, 128)]
-        float* xch = rstd_s + 128;                                                  // [64][8]: up halves
+        float* xch = rstd_s + 128;                    // [64][8]: up halves; tiles of 32 columns and more: [2][16][64]
         if (a.scale_sumsq) {
             // The factor of every token: rsqrt(sum of the partials / width + eps), summed in a fixed order.
             // The 128 threads share the (token, partial) pairs: thread t takes token t % W (W: the power of
@@ -446,8 +446,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             // a CTA's run starts inside at most one tile and ends inside at most one: two scratch slots
             float* part = whole ? nullptr
                                 : a.partial + ((size_t)cta * 2 + (cta * U >= tile * S ? 0 : 1)) * BN * BM;
+            bool stored = false;
+            if constexpr (BN >= 32) {
+                // A whole gated tile of 32 or more columns: 32 columns a round, both halves of the CTA at work.
+                // The gate rows' threads finish the round's first 16 columns, the up rows' threads the other
+                // 16; each half hands the other the values it needs through shared memory, column-major so
+                // that a warp's accesses fall into different banks.  (Eight columns a round with the up half
+                // only writing, as emit does it, costs about 1 us per eight columns.)
+                if (a.gated && !part) {
+                    float* from_gate = xch;             // [16][64]: gate values of the round's last 16 columns
+                    float* from_up = xch + 16 * 64;     // [16][64]: up values of its first 16
+                    const int half_row = r & 63, feature = tile_p * 64 + half_row;
+                    const bool is_gate = r < 64;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
+                    for (int c0 = 0; c0 < BN && q0 + c0 < a.rows_q; c0 += 32) {
+                        uint32_t lo[16], hi[16];
+                        tc_ld16(tmem_d + ((uint32_t)(lg * 32) << 16) + buf * BN + c0, lo);
+                        tc_ld16(tmem_d + ((uint32_t)(lg * 32) << 16) + buf * BN + c0 + 16, hi);
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            if (is_gate) from_gate[e * 64 + half_row] = __uint_as_float(hi[e]);
+                            else from_up[e * 64 + half_row] = __uint_as_float(lo[e]);
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (feature < a.gated) {
+                            const int cb = q0 + c0 + (is_gate ? 0 : 16);
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                const int j = cb + e;
+                                if (j >= a.rows_q) break;
+                                const float f = a.scale_sumsq ? rstd_s[j] : 1.0f;
+                                const float z = (is_gate ? __uint_as_float(lo[e]) : from_gate[e * 64 + half_row]) * f;
+                                const float u = (is_gate ? from_up[e * 64 + half_row] : __uint_as_float(hi[e])) * f;
+                                reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)j * a.ldc + feature] =
+                                    __float2bfloat16_rn(z / (1.0f + expf(-z)) * u);
+                            }
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");   // read before the next round overwrites
+                    }
+                    stored = true;
+                }
+            }
+#pragma unroll 1
+            for (int c = 0; c < BN && !stored; c += 16) {
                 uint32_t v[16];
                 tc_ld16(tmem_d + ((uint32_t)(lg * 32) << 16) + buf * BN + c, v);
                 if (part) {
@@ -616,7 +657,8 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int bo
 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int ctas, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * (P_BYTES + BN * BK * 2) + 1024 + 3072;
+    // stages, 1 KB to align them, barriers with the epilogue's factor and exchange areas (2 KB, 8 KB for wide tiles)
+    constexpr size_t smem = (size_t)STAGES * (P_BYTES + BN * BK * 2) + 1024 + (BN >= 32 ? 9216 : 3072);
     static unsigned long long configured = 0;
     if (int e = vcb_allow_dynamic_smem(gemm_tcgen05_kernel<BN, STAGES>, (int)smem, &configured)) return e;
     vcb_launch(gemm_tcgen05_kernel<BN, STAGES>, ctas, GEMM_THREADS, smem, s, mp, mq, a);
