@@ -752,6 +752,7 @@ def main() -> int:
                           "runs": [[c, k, round(t / k, 4)] for c, k, t in results],
                           "product_grids": {f"{n}x{k} tile {bn}{' gated' if g else ''}{' residual' if r else ''}": c
                                             for (n, k, bn, g, r), c in sorted(ops._cta_choice.items())},
+                          "layer_products_us": getattr(engine.model, "tuning_report", {}).get("layer_products_us"),
                           "cuda_graphs": not a.no_cuda_graphs, "clocks": clock_info}))
         return 0
     n_timed = sum(k for _, k, _ in results)

@@ -355,8 +355,13 @@ __global__ void rope_cache_kernel(RopeCacheArgs a, int heads_per_block) {
 // multiple of 16): 16-byte accesses, the angles' sines and cosines computed once per token and shared
 // by all heads.  One CTA per (token, group of heads); a thread owns chunk c of the first half of a
 // head and its partner chunk in the second half.
+// The one-token variant is held to 40 registers: its CTAs then fit beside two CTAs of the product before it
+// (150 registers x 192 threads each) and set themselves up while that one runs, also when a step has so many
+// tokens that the product fills every SM twice; otherwise they start only when it has ended (6 against 3 us at
+// 64 tokens).
 template <int TOK>
-__global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block, int n_tokens) {
+__global__ void __launch_bounds__(256, TOK == 1 ? 6 : 1)
+rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block, int n_tokens) {
     extern __shared__ float2 trig[];                    // [TOK][d / 2] (cos, sin)
     // Positions, denominators and the block table belong to the step (copied in before its first
     // kernel), not to the kernel before this one: the table of sines and cosines is made while that

@@ -554,20 +554,22 @@ def measure_linear(weights, out_dtype=torch.bfloat16, gated: int = 0):
 def measure_layer(products, hidden: int, fusable_norms: int, dtype=torch.bfloat16) -> dict:
     """{bucket: (microseconds of a layer's products as this library runs them, as the library would)}.
     ``products``: for every product of a layer, in the order they run, (matrices of that product
-    across layers, gated) with tiled images made.  This library's side is its tcgen05 product for each
-    (with a norm's factor applied, as the blocks link them; the activation inside the gated ones);
-    the library's side is a product each, the activation kernel after a gated one and
-    ``fusable_norms`` norm kernels, which the other side does not need."""
+    across layers, gated, reads a norm's output, ends a residual branch) with tiled images made.  This
+    library's side is its tcgen05 product for each, linked as the blocks link them: the rows' factor
+    applied by a product that reads a norm's output (RowScale), the addition into the residual stream,
+    the next norm's gain and the sums of squares in the epilogue of one that ends a branch
+    (ResidualNorm), the activation inside the gated ones.  The library's side is a product each, the
+    activation kernel after a gated one and ``fusable_norms`` norm kernels, which the other side does
+    not need."""
     dev_ = products[0][0][0].device
     times = {}
     for bucket, m in TOKEN_BUCKETS:
-        xs, outs, acts, scales = {}, [], [], {}
+        xs, outs, acts = {}, [], []
         ok = True
-        for mats, gated in products:
+        for mats, gated, _, _ in products:
             n, k = mats[0].shape
             if k not in xs:
                 xs[k] = torch.randn(m, k, device=dev_).to(dtype)
-                scales[k] = RowScale(torch.ones(sumsq_parts(k), m, device=dev_), sumsq_parts(k), k, 1e-6)
             outs.append(torch.empty(m, n, dtype=dtype, device=dev_))
             acts.append(torch.empty(m, gated, dtype=dtype, device=dev_) if gated else None)
             ok = ok and _tcgen05_ok(xs[k], mats[0], outs[-1])
@@ -577,14 +579,19 @@ def measure_layer(products, hidden: int, fusable_norms: int, dtype=torch.bfloat1
         delta = torch.zeros(m, hidden, dtype=dtype, device=dev_)
         normed = torch.empty(m, hidden, dtype=dtype, device=dev_)
         gain = torch.ones(hidden, device=dev_)
+        sumsq = torch.ones(sumsq_parts(hidden), m, device=dev_)
+        scale = RowScale(sumsq, sumsq_parts(hidden), hidden, 1e-6)
+        ends = ResidualNorm(res, gain, torch.empty(sumsq_parts(hidden), m, device=dev_), 1e-6)
 
         def ours(i):
-            for j, (mats, gated) in enumerate(products):
+            for j, (mats, gated, reads_norm, ends_branch) in enumerate(products):
                 w = mats[i % len(mats)]
-                gemm_bf16_tcgen05(xs[w.shape[1]], w, acts[j] if gated else outs[j], x_scale=scales[w.shape[1]], gated=bool(gated))
+                gemm_bf16_tcgen05(xs[w.shape[1]], w, acts[j] if gated else outs[j],
+                                  x_scale=scale if reads_norm and w.shape[1] == hidden else None,
+                                  fuse=ends if ends_branch and w.shape[0] == hidden and not gated else None, gated=bool(gated))
 
         def theirs(i):
-            for j, (mats, gated) in enumerate(products):
+            for j, (mats, gated, _, _) in enumerate(products):
                 w = mats[i % len(mats)]
                 _library_mm(xs[w.shape[1]], w, outs[j])
                 if gated:

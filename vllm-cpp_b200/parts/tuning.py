@@ -20,6 +20,9 @@ import torch
 from ..csrc import ops
 
 
+WIDE_TILE_MARGIN = 0.9
+
+
 def prepare_products(model, tune: bool = True, image_budget: Optional[int] = None) -> None:
     """``image_budget``: bytes the images may take (None: no limit).  Gated images come first (without
     one the activation stays a kernel of its own), then the others by size; a matrix without an
@@ -66,11 +69,24 @@ def prepare_products(model, tune: bool = True, image_budget: Optional[int] = Non
                         ops.choose_ctas(mats[:8], bucket, tokens, residual=True)     # as it ends a residual branch
         whole = {}
         if len(tunable) == len(layer_shapes) and tunable:
-            whole = ops.measure_layer([(mats[:8], gated_of[key]) for key, mats in tunable.items()], model.hidden,
-                                      fusable_norms, model.dtype)
+            # the products in the order a layer runs them; a part's first product reads the norm before the
+            # part, its last one ends the part's residual branch
+            chain = []
+            for part in model.blocks[0].parts.values():
+                listed = [(v, gated) for v, gated in part.product_weights() if v.dtype == torch.bfloat16]
+                for i, (v, gated) in enumerate(listed):
+                    key = (tuple(v.shape), gated)
+                    chain.append((tunable[key][:8], gated_of[key], i == 0, i == len(listed) - 1))
+            whole = ops.measure_layer(chain, model.hidden, fusable_norms, model.dtype)
+        model.tuning_report = {"layer_products_us": {b: (round(o, 1), round(t, 1)) for b, (o, t) in whole.items()}}
         times = None
         for bucket, _ in ops.TOKEN_BUCKETS:
-            if bucket in whole and whole[bucket][0] <= whole[bucket][1]:
+            # Tiles of 32 columns and more run two CTAs an SM, which do not fit beside the attention kernel's:
+            # in a step such a product cannot set itself up under the kernel before it as it does in the
+            # measured chain, and starts 3-4 us later (seen in the step's timeline at 7B sizes).  The layer as a
+            # whole has to win by that much.
+            margin = 1.0 if bucket <= 16 else WIDE_TILE_MARGIN
+            if bucket in whole and whole[bucket][0] <= margin * whole[bucket][1]:
                 for key in tunable:                   # the layer as a whole is faster on the engine's kernel
                     ops.choose_linear(key[0][0], key[0][1], bucket, torch.bfloat16, True)
                 continue
