@@ -536,7 +536,7 @@ def run_reference(cfg, a) -> int:
 
 # ------------------------------------------------------------------------------------------------ our arm
 def main() -> int:
-    global CONTEXT_START, CONTEXT
+    global CONTEXT_START, CONTEXT, PREFILL_TOKENS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
@@ -556,6 +556,8 @@ def main() -> int:
     ap.add_argument("--host", default="python", choices=["python", "cpp"],
                     help="cpp: decode throughput through the C++ host runtime (vllm::Engine) instead of the Python host")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--prefill-tokens", type=int, default=0,
+                    help=f"with --only prefill: tokens of the one prompt instead of {PREFILL_TOKENS}")
     ap.add_argument("--contexts", default="",
                     help="START,END: the decode measurement's contexts grow from START to END tokens instead of "
                          f"{CONTEXT_START},{CONTEXT} (with --only decode; the default is the benchmark's configuration)")
@@ -579,6 +581,11 @@ def main() -> int:
         CONTEXT_START, CONTEXT = (int(v) for v in a.contexts.split(","))
         if a.only != "decode" or not 0 < CONTEXT_START < CONTEXT:
             ap.error("--contexts START,END goes with --only decode and needs 0 < START < END")
+    if a.prefill_tokens:
+        if a.only != "prefill" or a.prefill_tokens < 2:
+            ap.error("--prefill-tokens N goes with --only prefill")
+        PREFILL_TOKENS = a.prefill_tokens
+        CONTEXT_START, CONTEXT = max(CONTEXT_START, PREFILL_TOKENS), max(CONTEXT, PREFILL_TOKENS + 64)
     cfg = dict(QWEN25_7B, **SIZES[a.size])
     if a.size == "7b" or a.layers != QWEN25_7B["num_hidden_layers"]:
         cfg["num_hidden_layers"] = a.layers
@@ -607,7 +614,7 @@ def main() -> int:
         return run_cpp_host(cfg, a)
     nums = model_numbers(cfg)
     peaks = load_peaks()
-    max_batch = a.batch if a.only == "decode" else max(64, a.batch)     # the points at batch 1 and 64 use the same engine
+    max_batch = a.batch if a.only != "all" else max(64, a.batch)        # the points at batch 1 and 64 use the same engine
     pages = max_batch * ((CONTEXT + SLACK) // 16 + 1) + PREFILL_TOKENS // 16 + 16
     ecfg = EngineConfig(load_format="random", model_config=cfg, seed=0, dtype="bfloat16", block_size=16,
                         num_gpu_blocks=None if a.utilization else pages,
@@ -729,10 +736,18 @@ def main() -> int:
             engine.abort_request(i)
         return produced / seconds, h2d, 4 * batch
 
+    def prefill_flops(t):
+        """The products of every layer and the output product of the one wanted row, and causal attention."""
+        return 2.0 * (nums["matrix_params"] - vocab * cfg["hidden_size"]) * t + 2.0 * vocab * cfg["hidden_size"] \
+            + cfg["num_hidden_layers"] * 4.0 * cfg["num_attention_heads"] * nums["d"] * (t * (t + 1) / 2)
+
     if a.only == "prefill":
         ms = time_prefill(max(1, min(steps, 3)), 2)
-        print(json.dumps({"metric": METRIC, "only": "prefill", "prefill_ms": round(ms, 3),
-                          "value": round(PREFILL_TOKENS / (ms * 1e-3), 1), "unit": "tokens/s"}))
+        tf = prefill_flops(PREFILL_TOKENS) / (ms * 1e-3) / 1e12
+        print(json.dumps({"metric": METRIC, "only": "prefill", "tokens": PREFILL_TOKENS, "prefill_ms": round(ms, 3),
+                          "value": round(PREFILL_TOKENS / (ms * 1e-3), 1), "unit": "tokens/s", "tflops": round(tf, 1),
+                          "frac": round(tf / peaks["bf16_tflops"], 4),
+                          "frac_of_sustained_peak": round(tf / peaks["bf16_tflops_sustained"], 4)}))
         return 0
     clocks = ClockSampler()
     clocks.start()
@@ -774,9 +789,7 @@ def main() -> int:
     prefill_ms = time_prefill(3, 2)
     clock_info = clocks.stop()
     t = PREFILL_TOKENS
-    flops = 2.0 * (nums["matrix_params"] - vocab * cfg["hidden_size"]) * t + 2.0 * vocab * cfg["hidden_size"] \
-        + cfg["num_hidden_layers"] * 4.0 * cfg["num_attention_heads"] * nums["d"] * (t * (t + 1) / 2)
-    tflops = flops / (prefill_ms * 1e-3) / 1e12
+    tflops = prefill_flops(t) / (prefill_ms * 1e-3) / 1e12
     prefill = {"value": round(t / (prefill_ms * 1e-3), 1), "tokens": t, "ms": round(prefill_ms, 3),
                # one step timed alone between synchronisations: the burst peak is its denominator
                "frac": round(tflops / peaks["bf16_tflops"], 4),
