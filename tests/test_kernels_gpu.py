@@ -437,6 +437,37 @@ def test_greedy_sampling_over_a_large_vocabulary(ops, vocab):
     assert out.cpu().numpy().tolist() == want
 
 
+@pytest.mark.parametrize("vocab", [152064, 40003, 130])
+def test_temperature_sampling_over_a_large_vocabulary(ops, vocab):
+    """The draw by inverse CDF in the order of the ids, every warp summing a slab of the row: rows of a wider
+    buffer (so that some rows are not 16-byte aligned), flat and peaked rows, draws at both ends and in the
+    middle.  The id must be the one whose interval of the cumulative sum (in float64) holds u, up to the
+    rounding of a float32 sum."""
+    rng = np.random.default_rng(12)
+    rows = 6
+    buf = (2 * rng.standard_normal((rows, vocab + 5))).astype(np.float32)
+    logits = buf[:, :vocab]
+    logits[1] *= 0.01                                  # nearly flat
+    logits[2, vocab - 1] = 25.0                        # all mass at the end
+    logits[3, vocab // 2 + 1] = 12.0                   # most mass in the middle
+    temps = np.array([1.0, 0.5, 1.0, 2.0, 0.8, 1.5], dtype=np.float32)
+    full = dev(buf)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    x = logits.astype(np.float64) / temps[:, None].astype(np.float64)
+    p = np.exp(x - x.max(axis=1, keepdims=True))
+    c = np.cumsum(p / p.sum(axis=1, keepdims=True), axis=1)
+    for u in [0.0, 1e-7, 0.25, 0.5, 0.75, 0.999, 0.99999994] + rng.random(12).tolist():
+        uu = np.full(rows, u, dtype=np.float32)
+        ops.sample(full[:, :vocab], dev(temps), dev(uu), out)
+        got = out.cpu().numpy()
+        for r in range(rows):
+            g = int(got[r])
+            assert 0 <= g < vocab
+            below = c[r, g - 1] if g > 0 else 0.0
+            assert below - 2e-5 <= float(uu[r]) < c[r, g] + 2e-5, (vocab, r, u, g, below, c[r, g])
+            assert p[r, g] > 0
+
+
 def test_sampling_top_k_top_p_and_penalty(ops):
     rng = np.random.default_rng(10)
     vocab, rows = 997, 8

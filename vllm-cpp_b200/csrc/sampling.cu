@@ -46,34 +46,6 @@ __device__ __forceinline__ void argmax_combine(float& bv, int& bi, float ov, int
     if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
 }
 
-// Inclusive scan of one float per thread over the CTA; returns this thread's
-// inclusive value, *total gets the sum.  scratch: 33 floats.
-__device__ __forceinline__ float block_inclusive_scan(float v, float* scratch, float* total) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    float x = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const float y = __shfl_up_sync(0xffffffffu, x, o);
-        if (lane >= o) x += y;
-    }
-    __syncthreads();
-    if (lane == 31) scratch[warp] = x;
-    __syncthreads();
-    if (warp == 0) {
-        float w = lane < nwarps ? scratch[lane] : 0.0f;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const float y = __shfl_up_sync(0xffffffffu, w, o);
-            if (lane >= o) w += y;
-        }
-        scratch[lane] = w;                 // inclusive sums of the warps
-    }
-    __syncthreads();
-    const float before = warp > 0 ? scratch[warp - 1] : 0.0f;
-    *total = scratch[nwarps - 1];
-    return x + before;
-}
-
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temperature,
               const float* __restrict__ uniform, int* __restrict__ out) {
@@ -142,38 +114,101 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
         return;
     }
 
-    // exp((l - max) / T) summed over a contiguous range of ids per thread, so
-    // that the running sum follows the order of the ids.
+    // e_i = exp((l_i - max) / T).  Every warp owns a contiguous slab of ids, so the warps' sums, taken in the
+    // order of the warps, follow the order of the ids; inside its slab a warp reads rows of 128 ids (a float4
+    // a lane, four rows in flight), each lane adding up what it reads.  The slab that holds the draw is then
+    // walked once more by its warp, row by row in the order of the ids.
     const float inv_t = 1.0f / temp;
     const float xmax = temp != 1.0f ? lmax * inv_t : lmax;
-    const int chunk = (vocab + blockDim.x - 1) / blockDim.x;
-    const int lo = min(vocab, (int)threadIdx.x * chunk), hi = min(vocab, lo + chunk);
+    const bool scaled = temp != 1.0f;
+    auto weight = [&](float v) { return expf((scaled ? v * inv_t : v) - xmax); };
+    const bool aligned = (((uintptr_t)l) & 15) == 0;
+    const int slab = ((vocab + nwarps - 1) / nwarps + 127) & ~127;
+    const int lo = min(vocab, warp * slab), hi = min(vocab, lo + slab);
+    // the four weights of this lane in the row that starts at id `base` (zero beyond the slab)
+    auto row_weights = [&](int base, float (&e)[4]) {
+        const int i = base + lane * 4;
+        if (aligned && i + 3 < hi) {
+            const float4 v = *reinterpret_cast<const float4*>(l + i);
+            e[0] = weight(v.x); e[1] = weight(v.y); e[2] = weight(v.z); e[3] = weight(v.w);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) e[k] = i + k < hi ? weight(l[i + k]) : 0.0f;
+        }
+    };
     float local = 0.0f;
-    for (int i = lo; i < hi; ++i) {
-        const float x = temp != 1.0f ? l[i] * inv_t : l[i];
-        local += expf(x - xmax);
+    {
+        constexpr int U = 4;
+        int base = lo;
+        if (aligned) {
+            for (; base + U * 128 <= hi; base += U * 128) {
+                float4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) v[u] = *reinterpret_cast<const float4*>(l + base + u * 128 + lane * 4);
+#pragma unroll
+                for (int u = 0; u < U; ++u) local += (weight(v[u].x) + weight(v[u].y)) + (weight(v[u].z) + weight(v[u].w));
+            }
+        }
+        for (; base < hi; base += 128) {
+            float e[4];
+            row_weights(base, e);
+            local += (e[0] + e[1]) + (e[2] + e[3]);
+        }
     }
-    float total;
-    const float incl = block_inclusive_scan(local, scratch, &total);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);      // the slab's sum, in all lanes
+    if (lane == 0) scratch[warp] = local;
+    __syncthreads();
+    if (warp == 0) {
+        float w = lane < nwarps ? scratch[lane] : 0.0f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float y = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += y;
+        }
+        scratch[lane] = w;                 // inclusive sums of the slabs
+    }
+    if (threadIdx.x == 0) winner = nwarps;
+    __syncthreads();
+    const float total = scratch[nwarps - 1];
+    const float incl = scratch[warp];
     const float target = uniform[row] * total;
-    if (threadIdx.x == 0) winner = blockDim.x;
+    if (lane == 0 && hi > lo && target < incl) atomicMin(&winner, warp);
     __syncthreads();
-    if (hi > lo && target < incl) atomicMin(&winner, (int)threadIdx.x);
-    __syncthreads();
-    if (winner == (int)blockDim.x) {             // u * total >= total after rounding: the last id
+    if (winner == nwarps) {                      // u * total >= total after rounding: the last id
         if (threadIdx.x == 0) out[row] = vocab - 1;
         return;
     }
-    if ((int)threadIdx.x == winner) {
-        float c = incl - local;
-        int tok = hi - 1;
-        for (int i = lo; i < hi; ++i) {
-            const float x = temp != 1.0f ? l[i] * inv_t : l[i];
-            c += expf(x - xmax);
-            if (target < c) { tok = i; break; }
+    if (warp != winner) return;
+    float c = incl - local;                      // the sum before this slab
+    int tok = hi - 1;                            // if rounding keeps the walk's sums below the draw: the slab's last id
+    for (int base = lo; base < hi; base += 128) {
+        float e[4];
+        row_weights(base, e);
+        const float p1 = e[0], p2 = p1 + e[1], p3 = p2 + e[2], p4 = p3 + e[3];
+        float upto = p4;                         // inclusive sum of the lanes' four
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float y = __shfl_up_sync(0xffffffffu, upto, o);
+            if (lane >= o) upto += y;
         }
-        out[row] = tok;
+        const float before = c + (upto - p4);
+        const int i = base + lane * 4;
+        int hit = -1;
+        if (i < hi) {
+            if (target < before + p1) hit = i;
+            else if (target < before + p2 && i + 1 < hi) hit = i + 1;
+            else if (target < before + p3 && i + 2 < hi) hit = i + 2;
+            else if (target < before + p4 && i + 3 < hi) hit = i + 3;
+        }
+        const unsigned found = __ballot_sync(0xffffffffu, hit >= 0);
+        if (found) {
+            tok = __shfl_sync(0xffffffffu, hit, __ffs(found) - 1);
+            break;
+        }
+        c += __shfl_sync(0xffffffffu, upto, 31);
     }
+    if (lane == 0) out[row] = tok;
 }
 
 VCB_EXPORT int vcb_sample(const float* logits, int ld, int vocab, const float* temperature,
