@@ -360,8 +360,7 @@ __global__ void rope_cache_kernel(RopeCacheArgs a, int heads_per_block) {
 // tokens that the product fills every SM twice; otherwise they start only when it has ended (6 against 3 us at
 // 64 tokens).
 template <int TOK>
-__global__ void __launch_bounds__(256, TOK == 1 ? 6 : 1)
-rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block, int n_tokens) {
+__device__ __forceinline__ void rope_cache_vec_body(const RopeCacheArgs& a, int heads_per_block, int n_tokens) {
     extern __shared__ float2 trig[];                    // [TOK][d / 2] (cos, sin)
     // Positions, denominators and the block table belong to the step (copied in before its first
     // kernel), not to the kernel before this one: the table of sines and cosines is made while that
@@ -407,9 +406,18 @@ rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block, int n_tokens) {
     }
     float ba[8], bb[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        ba[e] = (mine && a.bias) ? a.bias[h * a.d + c * 8 + e] : 0.0f;
-        bb[e] = (mine && a.bias) ? a.bias[h * a.d + half + c * 8 + e] : 0.0f;
+    for (int e = 0; e < 8; ++e) ba[e] = bb[e] = 0.0f;
+    if (mine && a.bias) {
+        const float* pa = a.bias + h * a.d + c * 8;
+        if ((((uintptr_t)a.bias) & 15) == 0) {             // d is a multiple of 16 here: both runs of eight are 16-byte aligned
+            const float4 a0 = *reinterpret_cast<const float4*>(pa), a1 = *reinterpret_cast<const float4*>(pa + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(pa + half), b1 = *reinterpret_cast<const float4*>(pa + half + 4);
+            ba[0] = a0.x; ba[1] = a0.y; ba[2] = a0.z; ba[3] = a0.w; ba[4] = a1.x; ba[5] = a1.y; ba[6] = a1.z; ba[7] = a1.w;
+            bb[0] = b0.x; bb[1] = b0.y; bb[2] = b0.z; bb[3] = b0.w; bb[4] = b1.x; bb[5] = b1.y; bb[6] = b1.z; bb[7] = b1.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { ba[e] = pa[e]; bb[e] = pa[half + e]; }
+        }
     }
     __syncthreads();
     pdl_wait();
@@ -454,6 +462,16 @@ rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block, int n_tokens) {
     }
 }
 
+template <int TOK>
+__global__ void rope_cache_vec_kernel(RopeCacheArgs a, int heads_per_block, int n_tokens) {
+    rope_cache_vec_body<TOK>(a, heads_per_block, n_tokens);
+}
+
+// one token a CTA, at most 40 registers a thread (see above)
+__global__ void __launch_bounds__(256, 6) rope_cache_vec_one_kernel(RopeCacheArgs a, int heads_per_block, int n_tokens) {
+    rope_cache_vec_body<1>(a, heads_per_block, n_tokens);
+}
+
 VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const int* positions,
                                     const int* req_of_token, const int* block_table, int bt_stride,
                                     const float* denom, void* q_out, void* cache, int n_tokens,
@@ -477,7 +495,7 @@ VCB_EXPORT int vcb_rope_cache_write(const void* qkv, const float* bias, const in
             vcb_launch(rope_cache_vec_kernel<4>, dim3((n_tokens + 3) / 4, grid_y.x), threads, (size_t)4 * half * sizeof(float2),
                        s, a, per, n_tokens);
         else
-            vcb_launch(rope_cache_vec_kernel<1>, dim3(n_tokens, grid_y.x), threads, (size_t)half * sizeof(float2), s, a, per,
+            vcb_launch(rope_cache_vec_one_kernel, dim3(n_tokens, grid_y.x), threads, (size_t)half * sizeof(float2), s, a, per,
                        n_tokens);
         return vcb_last_error();
     }
