@@ -159,9 +159,9 @@ class Part:
         return out
 
     def product_weights(self):
-        """The weight matrices of this part's products as (matrix, gated) pairs, for the model's
-        choice of kernels at load: ``gated`` is 0, or the number of gate features of a
-        gate-and-up matrix that the part multiplies with ops.linear_gated."""
+        """The weight matrices of this part's products as (matrix, gated) pairs in the order the part runs
+        them, for the model's choice of kernels at load: ``gated`` is 0, or the number of gate features of
+        a gate-and-up matrix that the part multiplies with ops.linear_gated."""
         return [(v, 0) for v in vars(self).values() if isinstance(v, torch.Tensor) and v.dim() == 2]
 
     def step_arrays(self):

@@ -9,7 +9,8 @@ products with the kernels between them, else each product on its own merits; the
 chosen by itself.  The reference's engine uses cuBLAS for every product (src/layers/linear.cpp:70-77).
 
 The parts say which of their tensors are products (``Part.product_weights``: by default every 2-D
-tensor); nothing here knows a part's kind.
+tensor, in the order the part runs them; the first reads the norm before the part, the last ends the
+part's residual branch); nothing here knows a part's kind.
 """
 from __future__ import annotations
 
@@ -20,6 +21,8 @@ import torch
 from ..csrc import ops
 
 
+# What the all-own layer's time may be of the library's for buckets whose tiles are 32 columns and more
+# (see prepare_products).
 WIDE_TILE_MARGIN = 0.9
 
 
