@@ -392,24 +392,25 @@ def run_kernels(cfg) -> int:
     from vllm_cpp_b200.engine.runner import HostStep
     from vllm_cpp_b200.parts.attention import PagedAttention
     part = PagedAttention(h, nh, nkv, d, True, False, 0, PartSpec("none"), bf, dev)
-    for batch in (8, 64):
-        c = CONTEXT - 1
-        blocks = CONTEXT // page
+    mixed = [128 + round(i * (4352 - 128) / 31) for i in range(32)]
+    for batch, contexts, label in ((8, [CONTEXT - 1] * 8, f"contexts of {CONTEXT}"), (64, [CONTEXT - 1] * 64, f"contexts of {CONTEXT}"),
+                                   (32, mixed, "contexts of 128 to 4,352")):
+        blocks = -(-(max(contexts) + 1) // page)
         cache = rnd(batch * blocks + 1, 2, nkv, page * d, scale=0.5)
         q, out = rnd(batch, nh * d), torch.empty(batch, nh * d, dtype=bf, device=dev)
         bt = torch.arange(batch * blocks, dtype=torch.int32, device=dev).view(batch, blocks)
         q_start = torch.arange(batch + 1, dtype=torch.int32, device=dev)
-        ctx = torch.full((batch,), c, dtype=torch.int32, device=dev)
-        host = HostStep([1] * batch, [c] * batch, page)
-        per = part.step_arrays()[part._splits_key()](host)
+        ctx = torch.tensor(contexts, dtype=torch.int32, device=dev)
+        host = HostStep([1] * batch, list(contexts), page)
+        split_tiles = torch.from_numpy(part.step_arrays()[part._splits_key()](host)).to(dev)
         nsplit = host.shapes[part._splits_key()]
-        split_tiles = torch.from_numpy(per).to(dev)
         need = batch * nh * nsplit
         po, pml = torch.empty(need * d, device=dev), torch.empty(need * 2, device=dev)
         tickets = torch.zeros(batch * nkv, dtype=torch.int32, device=dev)
-        add(f"decode attention, batch {batch}, contexts of {CONTEXT}", lambda i: ops.attention_decode_mma(
+        add(f"decode attention, batch {batch}, {label}", lambda i: ops.attention_decode_mma(
             q, cache, out, q_start, ctx, bt, None, batch, nsplit, po, pml, tickets, num_heads=nh, num_kv_heads=nkv, head_dim=d,
-            page_size=page, window=0, scale=d ** -0.5, split_tiles=split_tiles), 4, bytes_=batch * CONTEXT * 2 * nkv * d * 2)
+            page_size=page, window=0, scale=d ** -0.5, split_tiles=split_tiles), 4,
+            bytes_=sum(c + 1 for c in contexts) * 2 * nkv * d * 2)
         del cache
     logits = rnd(64, vocab, dtype=torch.float32)
     temp, uni, ids = torch.zeros(64, device=dev), torch.zeros(64, device=dev), torch.empty(64, dtype=torch.int32, device=dev)
