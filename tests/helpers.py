@@ -52,6 +52,34 @@ GOLDEN_PROMPTS = (5, 17, 33)
 
 CONFIGS = {"A": (TINY_A, 16), "B": (TINY_B, 32), "C": (TINY_C, 16), "D": (TINY_D, 32), "E": (TINY_E, 16)}   # name -> (config, page size)
 
+def random_config(rng):
+    """A Qwen2 configuration drawn at random: head sizes in steps of 16, any number of heads and groups, widths
+    and vocabularies with odd factors, a head size given apart from the width or not, windows on some layers."""
+    d = int(rng.choice([16, 32, 48, 64, 80, 96, 112, 128]))
+    heads = int(rng.integers(1, 9))
+    kv = int(rng.choice([k for k in range(1, heads + 1) if heads % k == 0]))
+    layers = int(rng.integers(1, 5))
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": layers,
+           "num_attention_heads": heads, "num_key_value_heads": kv,
+           "intermediate_size": int(rng.integers(40, 300)), "vocab_size": int(rng.integers(60, 2000)),
+           "rope_theta": float(rng.choice([1e4, 1e6, 5e5, 123456.0])), "rms_norm_eps": float(rng.choice([1e-5, 1e-6, 3e-6])),
+           "tie_word_embeddings": bool(rng.integers(0, 2)), "max_position_embeddings": int(rng.integers(256, 600)),
+           "hidden_act": "silu"}
+    if rng.random() < 0.4:
+        cfg["hidden_size"] = heads * d
+        if rng.random() < 0.5:
+            cfg["head_dim"] = d
+    else:
+        cfg["hidden_size"] = int(rng.integers(24, 220))
+        cfg["head_dim"] = d
+    if rng.random() < 0.5:
+        cfg.update(use_sliding_window=True, sliding_window=int(rng.integers(8, 100)),
+                   max_window_layers=int(rng.integers(0, layers + 1)))
+    else:
+        cfg["use_sliding_window"] = False
+    return cfg
+
+
 # |engine - plain| <= TOL * max|plain| over the compared rows
 TOL = {"float32": 1e-4, "bfloat16": 3e-2}
 MEAN_TOL = {"float32": 2e-5, "bfloat16": 6e-3}
