@@ -37,11 +37,15 @@ def ops():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_embedding(ops, dtype):
+@pytest.mark.parametrize("hidden", [88, 77, 3584, 5120, 8200])
+def test_embedding(ops, dtype, hidden):
+    """Widths that take the 16-byte path with two and with four vectors a thread (bfloat16, a multiple of 8), and
+    widths that do not."""
     rng = np.random.default_rng(0)
-    table = as_stored(rng.standard_normal((301, 88)), dtype)
+    table = as_stored(rng.standard_normal((301, hidden)), dtype)
     ids = rng.integers(0, 301, size=37).astype(np.int32)
-    out = torch.empty((37, 88), dtype=torch.float32, device="cuda")
+    ids[0], ids[1] = 0, 300
+    out = torch.full((37, hidden), float("nan"), dtype=torch.float32, device="cuda")
     ops.embedding(dev(table, DT[dtype]), dev(ids), out)
     assert np.array_equal(out.cpu().numpy(), plain.embedding(ids, table).astype(np.float32))
 

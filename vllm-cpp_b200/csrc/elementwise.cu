@@ -26,11 +26,47 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_f32<T>(row[i]);
 }
 
+// The same for bfloat16 rows of a multiple of 8 elements: 16-byte loads, all of a thread's in flight before the
+// first is widened and stored (NV vectors a thread).
+template <int NV>
+__global__ void embedding_bf16x8_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
+                                        float* __restrict__ residual, int hidden) {
+    pdl_start();
+    const int t = blockIdx.x;
+    const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)ids[t] * hidden);
+    float4* out = reinterpret_cast<float4*>(residual + (size_t)t * hidden);
+    const int nvec = hidden >> 3;
+    uint4 v[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        v[k] = i < nvec ? row[i] : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i >= nvec) break;
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
+        const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]), c = __bfloat1622float2(p[2]),
+                     d = __bfloat1622float2(p[3]);
+        out[2 * i] = make_float4(a.x, a.y, b.x, b.y);
+        out[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+    }
+}
+
 VCB_EXPORT int vcb_embedding(const void* table, const int* ids, float* residual, int n_tokens,
                              int hidden, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_BF16 && hidden % 8 == 0 && hidden / 8 <= 4 * 256 && !(((uintptr_t)table | (uintptr_t)residual) & 15)) {
+        const int nvec = hidden / 8;
+        if (nvec <= 2 * 256)
+            vcb_launch(embedding_bf16x8_kernel<2>, n_tokens, nvec <= 2 * 128 ? 128 : 256, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden);
+        else
+            vcb_launch(embedding_bf16x8_kernel<4>, n_tokens, 256, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden);
+        return vcb_last_error();
+    }
     if (dtype == VCB_F32)
         vcb_launch(embedding_kernel<float>, n_tokens, threads, 0, s, (const float*)table, ids, residual, hidden);
     else if (dtype == VCB_BF16)
