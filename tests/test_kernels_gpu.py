@@ -51,7 +51,7 @@ def test_embedding(ops, dtype, hidden):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("hidden", [48, 200, 3584, 5000])
+@pytest.mark.parametrize("hidden", [48, 200, 3584, 5000, 16384, 20000])
 def test_add_rmsnorm(ops, dtype, hidden):
     rng = np.random.default_rng(1)
     res = rng.standard_normal((9, hidden)).astype(np.float32)

@@ -136,7 +136,7 @@ template <> struct Vec4<__nv_bfloat16> {
 };
 
 template <typename T, int NV>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+__global__ void __launch_bounds__(NV == 8 ? 512 : 256) add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                        const float* __restrict__ gain, T* __restrict__ out,
                                        const int* __restrict__ row_index, int hidden, float eps) {
     __shared__ float scratch[33];
@@ -148,17 +148,21 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
     T* dst = out + (size_t)o * hidden;
     const bool write_back = (row_index == nullptr) && (delta != nullptr);
     const int nvec = hidden >> 2;
-    float4 x[NV];
+    float4 x[NV], dv[NV];
     float ss = 0.0f;
+    // every load of the row first: a store between two loads would order them
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        x[k] = i < nvec ? Vec4<float>::load(res + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        dv[k] = (dl && i < nvec) ? Vec4<T>::load(dl + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         const int i = threadIdx.x + k * blockDim.x;
         if (i < nvec) {
-            float4 v = Vec4<float>::load(res + 4 * i);
-            if (dl) {
-                const float4 d = Vec4<T>::load(dl + 4 * i);
-                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
-            }
+            float4 v = x[k];
+            if (dl) { v.x += dv[k].x; v.y += dv[k].y; v.z += dv[k].z; v.w += dv[k].w; }
             if (write_back) Vec4<float>::store(res + 4 * i, v);
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             x[k] = v;
@@ -188,8 +192,8 @@ static void launch_add_rmsnorm(float* residual, const T* delta, const float* gai
         vcb_launch(add_rmsnorm_vec_kernel<T, 4>, n_rows, 128, 0, s, residual, delta, gain, out, row_index, hidden, eps);
     else if (aligned && nvec <= 256 * 4)
         vcb_launch(add_rmsnorm_vec_kernel<T, 4>, n_rows, 256, 0, s, residual, delta, gain, out, row_index, hidden, eps);
-    else if (aligned && nvec <= 1024 * 8)
-        vcb_launch(add_rmsnorm_vec_kernel<T, 8>, n_rows, 1024, 0, s, residual, delta, gain, out, row_index, hidden, eps);
+    else if (aligned && nvec <= 512 * 8)        // a row and its addend in registers: 64 of them a thread at eight vectors
+        vcb_launch(add_rmsnorm_vec_kernel<T, 8>, n_rows, 512, 0, s, residual, delta, gain, out, row_index, hidden, eps);
     else {
         const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
         vcb_launch(add_rmsnorm_kernel<T>, n_rows, threads, 0, s, residual, delta, gain, out, row_index, hidden, eps);
