@@ -472,6 +472,52 @@ def test_temperature_sampling_over_a_large_vocabulary(ops, vocab):
             assert p[r, g] > 0
 
 
+@pytest.mark.parametrize("std", [0.05, 0.3, 2.0])
+def test_top_p_and_top_k_over_a_large_flat_vocabulary(ops, std):
+    """152,064 ids of similar weight: a single id's share is then a few rounding steps of the running sums, and
+    the thresholds' digit-by-digit search meets prefixes under which, by rounding, no digit reaches the bound.
+    Every draw must be an id of the kept set whose interval of the renormalised cumulative sum (float64, in the
+    order of falling probability, ties by lower id) holds u up to the rounding of a float32 sum."""
+    rng = np.random.default_rng(14)
+    vocab, rows = 152064, 8
+    logits = (std * rng.standard_normal((rows, vocab))).astype(np.float32)
+    temps = np.array([0.8, 1.0, 0.8, 1.3, 0.8, 1.0, 0.7, 0.8], dtype=np.float32)
+    top_p = np.array([0.9, 0.5, 0.99, 0.9, 1.0, 0.3, 0.9, 0.9], dtype=np.float32)
+    top_k = np.array([-1, -1, -1, 5000, 100, -1, 40000, -1], dtype=np.int32)
+    x = logits.astype(np.float64) / temps[:, None]
+    e = np.exp(x - x.max(axis=1, keepdims=True))
+    ranks, cdfs, keeps = [], [], []
+    for r in range(rows):
+        order = np.lexsort((np.arange(vocab), -e[r]))
+        c = np.cumsum(e[r][order])
+        n_keep = vocab if top_k[r] <= 0 else min(int(top_k[r]), vocab)
+        if top_p[r] < 1.0 or top_k[r] > 0:
+            n_keep = min(n_keep, int(np.searchsorted(c[:n_keep], top_p[r] * c[n_keep - 1], side="left")) + 1)
+        rank = np.empty(vocab, dtype=np.int64)
+        rank[order] = np.arange(vocab)
+        ranks.append(rank); cdfs.append(c[:n_keep] / c[n_keep - 1]); keeps.append(n_keep)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    d_logits, d_t, d_p, d_k = dev(logits), dev(temps), dev(top_p), dev(top_k)
+    for trial in range(150):
+        u = rng.random(rows).astype(np.float32)
+        if trial == 0:
+            u[:] = 0.0
+        if trial == 1:
+            u[:] = np.float32(0.99999994)
+        ops.sample(d_logits, d_t, dev(u), out)
+        ops.sample_filtered(d_logits, d_t, dev(u), d_p, d_k, out)
+        got = out.cpu().numpy()
+        for r in range(rows):
+            g = int(got[r])
+            assert 0 <= g < vocab, (std, trial, r, g, float(u[r]))
+            pos = int(ranks[r][g])
+            # the kept set's edge may move by the ids whose weight a rounding step of the sum covers
+            assert pos < keeps[r] + max(2, keeps[r] // 2000), (std, trial, r, pos, keeps[r])
+            pos = min(pos, keeps[r] - 1)
+            below = cdfs[r][pos - 1] if pos > 0 else 0.0
+            assert below - 1e-4 <= float(u[r]) < cdfs[r][pos] + 1e-4, (std, trial, r, float(u[r]), below, cdfs[r][pos])
+
+
 def test_sampling_top_k_top_p_and_penalty(ops):
     rng = np.random.default_rng(10)
     vocab, rows = 997, 8

@@ -318,8 +318,16 @@ __device__ unsigned long long filt_search(const float* __restrict__ e, int vocab
                     chosen_s = s; chosen_c = c;
                 }
             }
-            if (!found) {        // rounding at the very end of the row: take everything
-                chosen = 0; chosen_above_s = s - sh.tsum[0]; chosen_above_c = c - sh.tcnt[0];
+            if (!found) {
+                // The digits above were chosen because their running sum met the bound; here the same ids,
+                // added up bin by bin, fall short of it by a rounding step of the sum (which is as large as a
+                // single id's share once the row has 10^5 ids of similar weight).  The bound then lies at the
+                // end of this prefix's range: take all of it, which is the lowest digit that has any id.
+                // (Digit 0 regardless would lead to a key that no id has.)
+                int lowest = 0;
+                while (lowest < 15 && sh.tcnt[lowest] == 0) ++lowest;
+                chosen = lowest;
+                chosen_above_s = s - sh.tsum[lowest]; chosen_above_c = c - sh.tcnt[lowest];
                 chosen_s = s; chosen_c = c;
             }
             sh.digit = chosen;
