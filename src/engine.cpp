@@ -341,7 +341,7 @@ struct Engine::Impl {
         cuda_check(cudaStreamSynchronize(stream), "waiting for the step");
         if (++steps_since_check >= 64) {
             steps_since_check = 0;
-            if (int code = model->read_status()) throw Error("a kernel left status " + std::to_string(code) + " (a bounded wait ran out, or a block table named a page that is not there)");
+            if (int code = model->read_status()) throw Error("a kernel left status " + std::to_string(code) + " (a bounded wait ran out, 11: a block table named a page that is not there, 12: a token id outside the vocabulary)");
         }
         return std::vector<TokenId>(ids_host, ids_host + m);
     }

@@ -29,7 +29,8 @@
 // cudaError_t value or 10001 "bad argument" / 10002 "size not supported")
 extern "C" {
 void vcb_set_pdl(int on);
-int vcb_embedding(const void* table, const int* ids, float* residual, int n_tokens, int hidden, int dtype, void* stream);
+int vcb_embedding(const void* table, const int* ids, float* residual, int n_tokens, int hidden, int vocab, int* status, int dtype,
+                  void* stream);
 int vcb_add_rmsnorm(float* residual, const void* delta, const float* gain, void* out, const int* row_index, int n_rows,
                     int hidden, float eps, int dtype, void* stream);
 int vcb_silu_mul(const void* gu, void* out, int n_tokens, int inter, int dtype, void* stream);

@@ -527,7 +527,7 @@ const float* Qwen2Model::forward_fused(const Batch& b, cudaStream_t s) {
     const int n = b.n_tokens, H = mc_.hidden, q = mc_.heads * mc_.head_dim, kv = mc_.kv_heads * mc_.head_dim, I = mc_.inter;
     const float eps = (float)mc_.eps;
     const int parts = sumsq_parts(H);
-    kernel_check(vcb_embedding(embed_, b.token_ids, residual_, n, H, dt_, s), "embedding");
+    kernel_check(vcb_embedding(embed_, b.token_ids, residual_, n, H, mc_.vocab, status_, dt_, s), "embedding");
     RowScale incoming;                                   // set: delta holds residual * gain_in of this layer, factor pending
     int cur = 0;
     for (int l = 0; l < mc_.layers; ++l) {
@@ -631,7 +631,7 @@ const float* Qwen2Model::forward(const Batch& b, cudaStream_t s) {
     if (t_lm_head_ && fuses(b.n_tokens)) return forward_fused(b, s);
     const int n = b.n_tokens, H = mc_.hidden, q = mc_.heads * mc_.head_dim, kv = mc_.kv_heads * mc_.head_dim, I = mc_.inter;
     const float eps = (float)mc_.eps;
-    kernel_check(vcb_embedding(embed_, b.token_ids, residual_, n, H, dt_, s), "embedding");
+    kernel_check(vcb_embedding(embed_, b.token_ids, residual_, n, H, mc_.vocab, status_, dt_, s), "embedding");
     bool pending = false;                                 // delta holds an addition to the residual stream not made yet
     for (int l = 0; l < mc_.layers; ++l) {
         const Layer& L = layers_[l];

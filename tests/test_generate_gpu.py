@@ -209,3 +209,47 @@ def test_preemption_under_captured_steps_in_bfloat16(tmp_path, name):
         # same tokens as with plenty of pages up to the first near tie that rounding decided otherwise
         same = next((k for k, (x, y) in enumerate(zip(got[i], ref)) if x != y), 48)
         assert same >= 8, f"request {i} leaves the roomy run's tokens after {same}"
+
+
+def test_a_scratch_buffer_that_moves_makes_captured_steps_stale(tmp_path):
+    """A captured step holds the addresses of the kernels' scratch buffers.  When a later step, launched
+    directly because its shape is new, makes one of them grow, every graph captured before must go: the old
+    memory is given back to the driver at the next capture.  Here the growth is forced inside the first run
+    of a new shape; the graphs of the old shapes must be gone afterwards, and the old shapes must still give
+    the plain implementation's tokens when they come again."""
+    from vllm_cpp_b200 import SamplingParams
+    from vllm_cpp_b200.csrc import ops
+    cfg, weights, llm = make_llm(tmp_path, "E", "bfloat16", use_cuda_graphs=True, num_gpu_blocks=96)
+    eng, runner = llm.engine, llm.engine.runner
+    sp = SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True)
+    prompts = [token_ids(cfg, n, 70 + n) for n in (40, 41, 42)]
+
+    def generate(some):
+        ids = [eng.add_request(p, sp) for p in some]
+        got = {i: [] for i in ids}
+        while eng.has_pending_work():
+            for o in eng.step():
+                got[o.seq_id].extend(o.tokens)
+        return [got[i] for i in ids]
+
+    first = generate(prompts[:2])                       # two requests: their decode shape is captured
+    before = {k: g for k, g in runner.graphs.items()}
+    assert before
+    forward, grown = runner.model.forward, []
+
+    def forward_that_grows_a_buffer(*a, **kw):
+        if not grown and not __import__("torch").cuda.is_current_stream_capturing():
+            grown.append(ops.scratch("attn_part_o", ops._scratch["attn_part_o"].numel() * 2 + 1, "cuda"))
+        return forward(*a, **kw)
+
+    runner.model.forward = forward_that_grows_a_buffer
+    try:
+        generate(prompts)                               # three requests: a new shape, whose first run moves the buffer
+    finally:
+        runner.model.forward = forward
+    assert grown
+    assert all(runner.graphs.get(k) is not g for k, g in before.items()), "a graph captured before the buffer moved is still there"
+    again = generate(prompts[:2])
+    assert again == first
+    for p, out in zip(prompts[:2], again):
+        check_greedy(weights, cfg, p, out, "bfloat16")

@@ -50,6 +50,24 @@ def test_embedding(ops, dtype, hidden):
     assert np.array_equal(out.cpu().numpy(), plain.embedding(ids, table).astype(np.float32))
 
 
+@pytest.mark.parametrize("dtype,hidden", [("float32", 88), ("bfloat16", 88), ("bfloat16", 77)])
+def test_embedding_refuses_ids_outside_the_table(ops, dtype, hidden):
+    """Ids that never passed the host (a step launched ahead feeds sampled ids on the device): one outside the
+    table reads nothing, leaves a row of zeros and code 12 in the status word; the other rows are right."""
+    rng = np.random.default_rng(1)
+    table = as_stored(rng.standard_normal((50, hidden)), dtype)
+    ids = np.array([3, -1, 49, 50, 1048575, 0], dtype=np.int32)
+    out = torch.full((6, hidden), float("nan"), dtype=torch.float32, device="cuda")
+    ops.check_status()
+    ops.embedding(dev(table, DT[dtype]), dev(ids), out)
+    with pytest.raises(ops.KernelError, match="token id outside the vocabulary"):
+        ops.check_status()
+    got = out.cpu().numpy()
+    assert np.array_equal(got[[0, 2, 5]], table[[3, 49, 0]].astype(np.float32))
+    assert not got[[1, 3, 4]].any()
+    ops.check_status()                                  # cleared
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("hidden", [48, 200, 3584, 5000, 16384, 20000])
 def test_add_rmsnorm(ops, dtype, hidden):

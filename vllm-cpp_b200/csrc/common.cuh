@@ -20,7 +20,7 @@ enum { VCB_F32 = 0, VCB_BF16 = 1 };
 enum { VCB_ERR_BAD_ARG = 10001, VCB_ERR_UNSUPPORTED = 10002 };
 
 // Codes that kernels leave in the device status word (csrc/ops.py STATUS_MEANING names them all).
-enum { VCB_STATUS_BAD_PAGE = 11 };
+enum { VCB_STATUS_BAD_PAGE = 11, VCB_STATUS_BAD_TOKEN = 12 };
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }

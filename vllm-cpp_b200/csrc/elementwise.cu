@@ -15,32 +15,44 @@ VCB_EXPORT void vcb_set_pdl(int on) { vcb_pdl_enabled = on ? 1 : 0; }
 
 // ---------------------------------------------------------------- embedding
 // residual[t, :] = float(table[ids[t], :]).  The residual stream is float in
-// both precisions.  Ids are validated on the host.
+// both precisions.  The host checks the ids it feeds; ids that stay on the device (a step launched
+// before the step that samples them has been read) are checked here: an id outside [0, vocab)
+// reads no row, leaves zeros and VCB_STATUS_BAD_TOKEN in the status word.
+__device__ __forceinline__ bool token_ok(int id, int vocab, int* status) {
+    if ((unsigned)id < (unsigned)vocab) return true;
+    if (status && threadIdx.x == 0) atomicCAS(status, 0, VCB_STATUS_BAD_TOKEN);
+    return false;
+}
+
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ residual, int hidden) {
+                                 float* __restrict__ residual, int hidden, int vocab, int* status) {
     pdl_start();
     const int t = blockIdx.x;
-    const T* row = table + (size_t)ids[t] * hidden;
+    const int id = ids[t];
+    const bool ok = token_ok(id, vocab, status);
+    const T* row = table + (size_t)(ok ? id : 0) * hidden;
     float* out = residual + (size_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_f32<T>(row[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = ok ? to_f32<T>(row[i]) : 0.0f;
 }
 
 // The same for bfloat16 rows of a multiple of 8 elements: 16-byte loads, all of a thread's in flight before the
 // first is widened and stored (NV vectors a thread).
 template <int NV>
 __global__ void embedding_bf16x8_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
-                                        float* __restrict__ residual, int hidden) {
+                                        float* __restrict__ residual, int hidden, int vocab, int* status) {
     pdl_start();
     const int t = blockIdx.x;
-    const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)ids[t] * hidden);
+    const int id = ids[t];
+    const bool ok = token_ok(id, vocab, status);
+    const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)(ok ? id : 0) * hidden);
     float4* out = reinterpret_cast<float4*>(residual + (size_t)t * hidden);
     const int nvec = hidden >> 3;
     uint4 v[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         const int i = threadIdx.x + k * blockDim.x;
-        v[k] = i < nvec ? row[i] : make_uint4(0, 0, 0, 0);
+        v[k] = (ok && i < nvec) ? row[i] : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
@@ -54,23 +66,26 @@ __global__ void embedding_bf16x8_kernel(const __nv_bfloat16* __restrict__ table,
     }
 }
 
+// vocab: rows of the table; status (may be null): the device's status word.
 VCB_EXPORT int vcb_embedding(const void* table, const int* ids, float* residual, int n_tokens,
-                             int hidden, int dtype, void* stream) {
+                             int hidden, int vocab, int* status, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
+    if (vocab <= 0) return VCB_ERR_BAD_ARG;
     const int threads = hidden >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VCB_BF16 && hidden % 8 == 0 && hidden / 8 <= 4 * 256 && !(((uintptr_t)table | (uintptr_t)residual) & 15)) {
         const int nvec = hidden / 8;
         if (nvec <= 2 * 256)
-            vcb_launch(embedding_bf16x8_kernel<2>, n_tokens, nvec <= 2 * 128 ? 128 : 256, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden);
+            vcb_launch(embedding_bf16x8_kernel<2>, n_tokens, nvec <= 2 * 128 ? 128 : 256, 0, s, (const __nv_bfloat16*)table, ids, residual,
+                       hidden, vocab, status);
         else
-            vcb_launch(embedding_bf16x8_kernel<4>, n_tokens, 256, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden);
+            vcb_launch(embedding_bf16x8_kernel<4>, n_tokens, 256, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden, vocab, status);
         return vcb_last_error();
     }
     if (dtype == VCB_F32)
-        vcb_launch(embedding_kernel<float>, n_tokens, threads, 0, s, (const float*)table, ids, residual, hidden);
+        vcb_launch(embedding_kernel<float>, n_tokens, threads, 0, s, (const float*)table, ids, residual, hidden, vocab, status);
     else if (dtype == VCB_BF16)
-        vcb_launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden);
+        vcb_launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden, vocab, status);
     else
         return VCB_ERR_BAD_ARG;
     return vcb_last_error();

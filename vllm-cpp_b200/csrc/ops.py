@@ -143,13 +143,14 @@ def _dev(t: torch.Tensor, name: str, dtype=None) -> int:
 
 # --------------------------------------------------------------------- ops
 def embedding(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor) -> None:
-    """residual[t] = float(table[ids[t]]); ids int32 [n], residual float32 [n, hidden]."""
+    """residual[t] = float(table[ids[t]]); ids int32 [n], residual float32 [n, hidden].  An id outside the
+    table leaves a row of zeros and code 12 in the status word."""
     n, hidden = residual.shape
     _need(table.dim() == 2 and table.shape[1] == hidden, "embedding table width differs from the residual's")
     _need(ids.numel() == n, "one id per residual row")
     _check(lib().vcb_embedding(_dev(table, "table"), _dev(ids, "ids", torch.int32),
-                               _dev(residual, "residual", torch.float32), n, hidden,
-                               dtype_code(table.dtype), _stream()), "embedding")
+                               _dev(residual, "residual", torch.float32), n, hidden, table.shape[0],
+                               status_tensor(table.device).data_ptr(), dtype_code(table.dtype), _stream()), "embedding")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor,
@@ -312,6 +313,8 @@ STATUS_MEANING = {1: "the TMA producer waited too long for a free stage", 2: "th
                   8: "a product's merge waited too long for the tile's other segments",
                   9: "tcgen05 prefill attention waited too long on one of its barriers",
                   10: "tcgen05 prefill attention found its shared memory not aligned to 1024 bytes",
+                  12: "a token id outside the vocabulary reached the embedding on the device (a sampled id of the step "
+                      "before, which the host had not yet seen); its row was left zero",
                   11: "a block table named a page that the cache does not have (a released or missing entry); "
                       "nothing was written through it and attention read page 0 in its place"}
 
@@ -325,13 +328,14 @@ def status_tensor(device) -> torch.Tensor:
 
 
 def check_status() -> None:
-    """Raise if a kernel gave up on a wait since the last check (synchronises)."""
+    """Raise if a kernel noted something in the status word since the last check: a bounded wait that ran
+    out, a page or a token id that does not exist (synchronises)."""
     if _status is None:
         return
     code = int(_status.item())
     if code:
         _status.zero_()
-        raise KernelError(f"a kernel gave up on a bounded wait: {STATUS_MEANING.get(code, code)}")
+        raise KernelError(f"a kernel left status {code}: {STATUS_MEANING.get(code, code)}")
 
 
 def tcgen05_plan(tokens: int, features: int, k: int):

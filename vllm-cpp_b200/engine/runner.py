@@ -75,6 +75,9 @@ class ModelRunner:
             builders = getattr(owner, "step_arrays", None)
             if builders:
                 self.array_builders.update(builders())
+            reserve = getattr(owner, "reserve", None)
+            if reserve and torch.device(device).type == "cuda":
+                reserve(max_num_batched_tokens, max_num_seqs, device)
         cap = self._meta_ints(self.max_tokens, self.max_seqs, self.max_tokens) + 64 * 1024
         self.meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
         self.meta_dev = torch.empty(cap, dtype=torch.int32, device=device)
@@ -147,7 +150,14 @@ class ModelRunner:
                 self._graph_seen[key] = 1
                 self.ws.reset()
                 out = self.model.forward(step, self.views, self.ws, self.logits)
-                self._graph_sig = self._buffers_signature()
+                after = self._buffers_signature()
+                if after != self._graph_sig:
+                    # This run moved a buffer (a scratch area grew): every graph captured before holds the
+                    # old address, and the old memory goes back to the driver at the next capture
+                    # (torch.cuda.graph empties the allocator's cache first).  They are dropped, not kept.
+                    self.graphs.clear()
+                    self._graph_seen = {key: 1}
+                    self._graph_sig = after
                 return out
             graph = torch.cuda.CUDAGraph()
             self.ws.reset()

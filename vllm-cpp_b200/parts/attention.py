@@ -193,6 +193,13 @@ class PagedAttention(Mixer):
         kernels before and after share the SMs, and a CTA that finds no place waits for a second round."""
         return max(n_reqs, (2 * ops.sm_count() * 7 // 8) // self.nkv)
 
+    def reserve(self, n_tokens, n_reqs, device):
+        if self._tensor_core_path():
+            most = n_reqs * self.nh * ops.DECODE_MAX_SPLITS
+            ops.scratch("attn_part_o", most * self.d, device)
+            ops.scratch("attn_part_ml", most * 2, device)
+            ops.zeroed_ints("attn_tickets", n_reqs * self.nkv, device)
+
     def _splits_key(self):
         return f"attn_splits_kv{self.nkv}_w{self.window}"
 

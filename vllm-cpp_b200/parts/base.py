@@ -172,6 +172,11 @@ class Part:
         of the key under which a decode step is captured).  Any part of any family may have some."""
         return {}
 
+    def reserve(self, n_tokens: int, n_reqs: int, device) -> None:
+        """Called once when the engine is built: allocate at its largest what the part keeps outside the
+        step's workspace (scratch that kernels merge partial results through), so that it does not move
+        later: a buffer that moves makes every captured step stale."""
+
     def workspace_bytes(self, n_tokens: int, n_reqs: int) -> int:
         """Most bytes of step workspace (Workspace.take) this part takes at once for a step of
         ``n_tokens`` tokens of ``n_reqs`` requests; the engine sizes its memory plan with it."""
