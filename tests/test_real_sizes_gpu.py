@@ -240,3 +240,60 @@ def test_a_step_of_2048_tokens_with_portions_and_decoded_tokens(engine):
     check(rp, size, "b", reqs["b"], [32], "2048-token step b")
     check(rp, size, "c", reqs["c"], [300, 855, 1399], "2048-token step c")
     check(rp, size, "d", reqs["d"][:1546], [600, 1000, 1545], "2048-token step d")
+
+
+@pytest.mark.parametrize("host", ["python", "cpp"])
+def test_many_requests_on_few_pages_with_every_sampling_option(tmp_path, host):
+    """Continuous batching at 7B layer sizes under pressure: 96 requests of mixed lengths on a sixth of the
+    pages they would need together (so requests are preempted and recomputed), 32 at a time, 256 tokens a
+    step, greedy, temperature, top-p and top-k rows side by side over the vocabulary of 152,064, decode steps
+    of every batch size captured as graphs.  Two runs give the same tokens; every id is a real one; every
+    request gets its length; nothing is left in the cache.  (This is the workload that showed a top-p draw
+    returning id 2^20 - 1 on a flat row, and captured steps kept after a scratch buffer had moved.)"""
+    import json
+    cfg = SIZES["7b"]
+    n_req, budget, seqs = 96, 256, 32
+    rng = np.random.default_rng(12)
+    lens, gens = rng.integers(8, 600, size=n_req), rng.integers(4, 80, size=n_req)
+    pages = int(sum(-(-(int(a) + int(b)) // PAGE) for a, b in zip(lens, gens))) // 6
+    prompts = [rng.integers(0, cfg["vocab_size"], size=int(n)).tolist() for n in lens]
+
+    def options(i):
+        return dict(max_tokens=int(gens[i]), temperature=0.8 if i % 3 else 0.0, top_p=0.9 if i % 5 == 0 else 1.0,
+                    top_k=50 if i % 7 == 0 else -1, seed=1000 + i, ignore_eos=True)
+
+    if host == "python":
+        from vllm_cpp_b200 import EngineConfig, SamplingParams
+        from vllm_cpp_b200.csrc import ops
+        from vllm_cpp_b200.engine.llm_engine import Engine
+        eng = Engine(EngineConfig(load_format="random", model_config=cfg, seed=SEED, dtype="bfloat16", block_size=PAGE,
+                                  num_gpu_blocks=pages, max_num_seqs=seqs, max_model_len=1024, max_num_batched_tokens=budget,
+                                  max_tokens_per_step=budget))
+
+        def run():
+            ids = [eng.add_request(p, SamplingParams(**options(i))) for i, p in enumerate(prompts)]
+            outs = {i: [] for i in ids}
+            while eng.has_pending_work():
+                for o in eng.step():
+                    outs[o.seq_id].extend(o.tokens)
+            torch.cuda.synchronize()
+            ops.check_status()
+            return [outs[i] for i in ids]
+        free, preemptions = (lambda: eng.cache.num_free_pages()), (lambda: eng.scheduler.num_preemptions)
+    else:
+        from vllm_cpp_b200.engine.cpp_host import CppEngine
+        (tmp_path / "config.json").write_text(json.dumps(cfg))
+        eng = CppEngine(str(tmp_path), dtype="bfloat16", block_size=PAGE, num_gpu_blocks=pages, max_num_seqs=seqs,
+                        max_model_len=1024, max_num_batched_tokens=budget, max_tokens_per_step=budget,
+                        load_format="random", seed=SEED)
+
+        def run():
+            return eng.generate(prompts, per_request=[options(i) for i in range(n_req)])
+        free, preemptions = (lambda: eng.num_free_blocks), (lambda: eng.num_preemptions)
+    first = run()
+    assert preemptions() > 0
+    second = run()
+    assert first == second
+    assert [len(t) for t in first] == [int(g) for g in gens]
+    assert all(0 <= t < cfg["vocab_size"] for out in first for t in out)
+    assert free() == pages
