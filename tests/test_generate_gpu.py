@@ -253,3 +253,29 @@ def test_a_scratch_buffer_that_moves_makes_captured_steps_stale(tmp_path):
     assert again == first
     for p, out in zip(prompts[:2], again):
         check_greedy(weights, cfg, p, out, "bfloat16")
+
+
+def test_captured_steps_are_bounded_in_number(tmp_path, monkeypatch):
+    """Only so many captured steps are kept; the least recently replayed goes first and is captured again when
+    its shape returns.  With room for two, a run that sees several shapes gives the tokens of direct launches."""
+    import vllm_cpp_b200.engine.runner as runner_module
+    from vllm_cpp_b200 import SamplingParams
+    monkeypatch.setattr(runner_module, "MAX_CAPTURED_STEPS", 2)
+    cfg, page = CONFIGS["E"]
+    prompts = [token_ids(cfg, n, 30 + n) for n in (250, 12, 90, 3, 180)]
+    params = [SamplingParams(max_tokens=n, temperature=0.0, ignore_eos=True) for n in (40, 60, 25, 60, 33)]
+    runs = {}
+    for graphs in (False, True):
+        _, _, llm = make_llm(tmp_path, "E", "bfloat16", use_cuda_graphs=graphs, num_gpu_blocks=96)
+        eng = llm.engine
+        ids = [eng.add_request(p, sp) for p, sp in zip(prompts, params)]
+        got = {i: [] for i in ids}
+        most = 0
+        while eng.has_pending_work():
+            for o in eng.step():
+                got[o.seq_id].extend(o.tokens)
+            most = max(most, len(eng.runner.graphs))
+        runs[graphs] = [got[i] for i in ids]
+        if graphs:
+            assert most == 2
+    assert runs[False] == runs[True]

@@ -45,6 +45,8 @@ def test_slices_and_pages_of_configuration_b():
         ("top-k/top-p scratch [max_num_seqs, vocab]", 4 * 384 * 4),
         ("product scratch (partial tiles, tickets)", 148 * 2 * 256 * 128 * 4 + 16384 * 4),
         ("decode attention scratch (split merge)", 4 * 3 * 32 * 34 * 4 + 4096),
+        # at most 256 captured steps of 8 launches a layer call and 4 around them, 8 KiB each
+        ("captured decode steps (up to 256)", 256 * (8 * 3 + 4) * 8192),
         ("reserve for libraries and context", 384 * MIB),
     ]
     others = sum(b for _, b in expect)

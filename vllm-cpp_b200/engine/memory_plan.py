@@ -51,8 +51,15 @@ class MemoryPlan:
         return "\n".join(lines)
 
 
+# Captured decode steps: at most this many are kept (the least recently replayed goes first), and each is
+# counted at this many bytes per launch it holds (measured: 64 graphs of a 4-layer model took 10-18 MiB).
+MAX_CAPTURED_STEPS = 256
+CAPTURED_BYTES_PER_LAUNCH = 8 * 1024
+
+
 def step_slices(cfg: EngineConfig, hidden: int, vocab: int, el: int, workspace_bytes: int, n_paged_groups: int,
-                max_heads: int, max_head_dim: int, sm_count: int, state_bytes_per_slot: int) -> List[Tuple[str, int]]:
+                max_heads: int, max_head_dim: int, sm_count: int, state_bytes_per_slot: int,
+                launches_per_step: int = 0) -> List[Tuple[str, int]]:
     """The slices besides weights and pages, for a model of these sizes: (name, bytes)."""
     n, r = cfg.max_num_batched_tokens, cfg.max_num_seqs
     max_blocks = cdiv(cfg.max_model_len, cfg.block_size)
@@ -67,6 +74,8 @@ def step_slices(cfg: EngineConfig, hidden: int, vocab: int, el: int, workspace_b
         ("product scratch (partial tiles, tickets)", _round(sm_count * 2 * 256 * 128 * 4) + _round(16384 * 4)),
         ("decode attention scratch (split merge)", _round(r * max_heads * 32 * (max_head_dim + 2) * 4) + _round(max(1024, r * max_heads) * 4)),
         ("state slots", _round(r * state_bytes_per_slot) if state_bytes_per_slot else 0),
+        (f"captured decode steps (up to {MAX_CAPTURED_STEPS})",
+         _round(MAX_CAPTURED_STEPS * launches_per_step * CAPTURED_BYTES_PER_LAUNCH) if cfg.use_cuda_graphs else 0),
         ("reserve for libraries and context", LIBRARY_RESERVE),
     ]
     return [(name, b) for name, b in rows if b]
@@ -100,7 +109,8 @@ def plan_for_model(cfg: EngineConfig, model, total: int, in_place: int, max_mode
                 for s in specs if isinstance(s, StateSpec))
     heads = [(getattr(p, "nh", 0), getattr(p, "d", 0)) for blk in model.blocks for p in blk.parts.values()]
     slices = step_slices(cfg, model.hidden, model.vocab, el, workspace, len({s for s in specs if hasattr(s, "num_kv_heads")}),
-                         max((h for h, _ in heads), default=0), max((d for _, d in heads), default=0), sm_count, state)
+                         max((h for h, _ in heads), default=0), max((d for _, d in heads), default=0), sm_count, state,
+                         launches_per_step=8 * len(model.spec.run_order) + 4)
     weights = sum(t.numel() * t.element_size() for t in model.tensors())
     images = sum(t.numel() * t.element_size() for t in model.tile_images())
     return plan(cfg, total, in_place, slices, CacheManager.bytes_per_page(specs, cfg.block_size, model.dtype), max_model_len,

@@ -30,6 +30,7 @@ import torch
 
 from ..cache.manager import CacheManager, cdiv
 from ..parts.base import StepContext, Workspace
+from .memory_plan import MAX_CAPTURED_STEPS
 
 
 @dataclass
@@ -172,6 +173,12 @@ class ModelRunner:
             ops.add_launches(-captured)     # recorded, not run
             entry = (graph, captured)
             self.graphs[key] = entry
+            while len(self.graphs) > MAX_CAPTURED_STEPS:           # the least recently replayed goes
+                oldest = next(iter(self.graphs))
+                del self.graphs[oldest]
+                self._graph_seen.pop(oldest, None)
+        else:
+            self.graphs[key] = self.graphs.pop(key)                # most recently used last
         graph, captured = entry
         graph.replay()
         ops.add_launches(captured)
