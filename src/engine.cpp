@@ -62,12 +62,16 @@ struct Engine::Impl {
     // Decode steps in which every request brings one token and wants its logits have a fixed shape for a given
     // number of requests and attention splits: the first such step runs directly, the second is captured as a
     // CUDA graph, later ones replay it.  The metadata copy and the sampling stay outside the graph.
-    std::map<std::vector<int>, cudaGraphExec_t> graphs;
+    // At most kMaxGraphs are kept; the least recently launched goes first.
+    struct CapturedStep { cudaGraphExec_t exec; uint64_t last_use; };
+    static constexpr size_t kMaxGraphs = 256;
+    std::map<std::vector<int>, CapturedStep> graphs;
     std::map<std::vector<int>, int> graph_seen;
+    uint64_t graph_clock = 0;
     bool use_graphs = true;
 
     ~Impl() {
-        for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
+        for (auto& kv : graphs) cudaGraphExecDestroy(kv.second.exec);
         if (meta_host) cudaFreeHost(meta_host);
         if (samp_host) cudaFreeHost(samp_host);
         if (topk_host) cudaFreeHost(topk_host);
@@ -281,10 +285,19 @@ struct Engine::Impl {
                 const cudaError_t err = cudaGraphInstantiate(&exec, graph, 0);
                 cudaGraphDestroy(graph);
                 cuda_check(err, "cudaGraphInstantiate");
-                it = graphs.emplace(key, exec).first;
+                if (graphs.size() >= kMaxGraphs) {
+                    auto oldest = graphs.begin();
+                    for (auto g = graphs.begin(); g != graphs.end(); ++g)
+                        if (g->second.last_use < oldest->second.last_use) oldest = g;
+                    cudaGraphExecDestroy(oldest->second.exec);       // the driver frees it once its last launch is done
+                    graph_seen.erase(oldest->first);
+                    graphs.erase(oldest);
+                }
+                it = graphs.emplace(key, CapturedStep{exec, 0}).first;
             }
             if (it != graphs.end()) {
-                cuda_check(cudaGraphLaunch(it->second, stream), "cudaGraphLaunch");
+                it->second.last_use = ++graph_clock;
+                cuda_check(cudaGraphLaunch(it->second.exec, stream), "cudaGraphLaunch");
                 logits = model->logits();
             }
         }
