@@ -537,7 +537,7 @@ def run_reference(cfg, a) -> int:
 
 # ------------------------------------------------------------------------------------------------ our arm
 def main() -> int:
-    global CONTEXT_START, CONTEXT, PREFILL_TOKENS
+    global CONTEXT_START, CONTEXT, PREFILL_TOKENS, SLACK
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
@@ -587,6 +587,7 @@ def main() -> int:
             ap.error("--prefill-tokens N goes with --only prefill")
         PREFILL_TOKENS = a.prefill_tokens
         CONTEXT_START, CONTEXT = max(CONTEXT_START, PREFILL_TOKENS), max(CONTEXT, PREFILL_TOKENS + 64)
+    SLACK = max(SLACK, a.batch + 32)          # requests begin a prompt's step apart: the first is a batch of steps ahead of the last
     cfg = dict(QWEN25_7B, **SIZES[a.size])
     if a.size == "7b" or a.layers != QWEN25_7B["num_hidden_layers"]:
         cfg["num_hidden_layers"] = a.layers
