@@ -266,10 +266,11 @@ void Qwen2Model::place(DevicePool& pool, int num_pages) {
     cuda_check(cudaMemset(gemm_tickets_, 0, 16384 * 4), "clearing tickets");
     cuda_check(cudaMemset(status_, 0, 4), "clearing the status word");
     cuda_check(cudaMemset(attn_tickets_, 0, std::max<size_t>(1024, cfg_.max_num_seqs * (size_t)mc_.kv_heads) * 4), "clearing tickets");
-    // divisors of the rotation: theta^(2j/d) in float, as src/model/qwen.cpp:124 computes them
+    // divisors of the rotation: theta and the exponent 2j/d in float as src/model/qwen.cpp:124 has them, the power in
+    // double and then rounded, which is the same float on every host (parts/position.py does the same)
     std::vector<float> denom(mc_.head_dim / 2);
     for (int j = 0; j < mc_.head_dim / 2; ++j)
-        denom[j] = powf((float)mc_.rope_theta, (2.0f * (float)j) / (float)mc_.head_dim);
+        denom[j] = (float)pow((double)(float)mc_.rope_theta, (double)((2.0f * (float)j) / (float)mc_.head_dim));
     cuda_check(cudaMemcpy(denom_, denom.data(), denom.size() * 4, cudaMemcpyHostToDevice), "copy of the divisors");
     scale_ = 1.0f / sqrtf((float)mc_.head_dim);                     // src/layers/attention.cpp:126
 }

@@ -255,3 +255,49 @@ def test_random_weights_are_those_of_the_python_host(tmp_path, dtype):
     assert np.abs(got["loaded"] - got["other seed"]).max() > 1e-3
     with pytest.raises(Exception, match="load_format"):
         CppEngine(str(bare), **args, load_format="gguf")
+
+
+def test_both_hosts_give_the_same_tokens_under_pressure_in_float32(tmp_path):
+    """150 requests on pages for six of them, 24 at a time, 200 tokens a step, a model of middling size with a
+    windowed layer, an odd vocabulary of 32,003 and every sampling option (greedy, temperature, top-p, top-k,
+    repetition penalty): in float32 the two hosts run the same kernels on the same numbers under the same
+    scheduling decisions, so every request must get the same tokens from both, preempted or not.  (A last-bit
+    difference in one host's rotation divisors was enough to part them here.)"""
+    from vllm_cpp_b200 import EngineConfig, SamplingParams
+    from vllm_cpp_b200.engine.cpp_host import CppEngine
+    from vllm_cpp_b200.engine.llm_engine import Engine
+    from vllm_cpp_b200.weights.random_init import write_random_model
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 3, "vocab_size": 32003,
+           "rope_theta": 1000000.0, "tie_word_embeddings": True, "use_sliding_window": True, "sliding_window": 96,
+           "max_window_layers": 1, "max_position_embeddings": 4096, "hidden_act": "silu", "initializer_range": 0.05,
+           "hidden_size": 520, "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64,
+           "intermediate_size": 1400, "rms_norm_eps": 1e-6}
+    folder = str(tmp_path / "model")
+    write_random_model(folder, cfg, seed=4, dtype="float32", device="cuda")
+    n_req = 150
+    rng = np.random.default_rng(8)
+    lens, gens = rng.integers(4, 500, size=n_req), rng.integers(2, 90, size=n_req)
+    prompts = [rng.integers(0, cfg["vocab_size"], size=int(n)).tolist() for n in lens]
+
+    def options(i):
+        return dict(max_tokens=int(gens[i]), temperature=0.9 if i % 3 else 0.0, top_p=0.85 if i % 5 == 0 else 1.0,
+                    top_k=40 if i % 7 == 0 else -1, repetition_penalty=1.3 if i % 4 == 0 else 1.0, seed=77 + i, ignore_eos=True)
+
+    common = dict(dtype="float32", block_size=16, num_gpu_blocks=240, max_num_seqs=24, max_model_len=640,
+                  max_num_batched_tokens=200, max_tokens_per_step=200)
+    eng = Engine(EngineConfig(model_path=folder, **common))
+    ids = [eng.add_request(p, SamplingParams(**options(i))) for i, p in enumerate(prompts)]
+    outs = {i: [] for i in ids}
+    while eng.has_pending_work():
+        for o in eng.step():
+            outs[o.seq_id].extend(o.tokens)
+    from_python = [outs[i] for i in ids]
+    assert eng.scheduler.num_preemptions > 10 and eng.cache.num_free_pages() == 240
+    del eng
+    cpp = CppEngine(folder, **common)
+    from_cpp = cpp.generate(prompts, per_request=[options(i) for i in range(n_req)])
+    assert cpp.num_preemptions > 10 and cpp.num_free_blocks == 240
+    cpp.close()
+    assert [len(t) for t in from_python] == [int(g) for g in gens]
+    differ = [i for i in range(n_req) if from_python[i] != from_cpp[i]]
+    assert not differ, differ

@@ -35,7 +35,10 @@ class RotaryEmbedding(PositionEncoding):
         self.theta, self.rotary_dim, self.pairing = float(theta), rotary_dim, pairing
         j = np.arange(rotary_dim // 2, dtype=np.float32)
         exponent = (np.float32(2.0) * j) / np.float32(rotary_dim)
-        denom = np.power(np.float32(theta), exponent).astype(np.float32)
+        # theta and the exponent as the reference has them, in float (src/model/qwen.cpp:124); the power itself in
+        # double and then rounded, so that every host that computes it gets the same float (powf differs from one
+        # library to the next in the last bit, which is enough to move a sampled token)
+        denom = np.power(np.float64(np.float32(theta)), exponent.astype(np.float64)).astype(np.float32)
         self.denom = torch.from_numpy(denom).to(device)
 
     def fused(self) -> Optional[dict]:
