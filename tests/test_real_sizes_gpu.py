@@ -302,8 +302,8 @@ def test_many_requests_on_few_pages_with_every_sampling_option(tmp_path, host):
 def test_captured_and_launched_ahead_steps_give_the_tokens_of_direct_launches_under_pressure():
     """The same workload as above on the Python host twice: decode steps captured as graphs and launched before
     the step before them has been read, and every kernel launched directly, one step at a time.  With the
-    products' choice pinned (what is measured at load may differ between two engines by timing noise, and then
-    sums are taken in another order), both must sample the same tokens: a windowed layer, preemptions, greedy,
+    products' choice pinned (tune_products=False: what is measured at load may differ between two engines by
+    timing noise, and then sums are taken in another order), both must sample the same tokens: a windowed layer, preemptions, greedy,
     temperature, top-p, top-k and repetition-penalty rows."""
     from vllm_cpp_b200 import EngineConfig, SamplingParams
     from vllm_cpp_b200.csrc import ops
@@ -320,26 +320,23 @@ def test_captured_and_launched_ahead_steps_give_the_tokens_of_direct_launches_un
                     top_k=50 if i % 7 == 0 else -1, repetition_penalty=1.2 if i % 11 == 0 else 1.0, seed=1000 + i, ignore_eos=True)
 
     results, shapes = {}, 0
-    ops.set_linear_tuning(False)
-    try:
-        for fast in (True, False):
-            eng = Engine(EngineConfig(load_format="random", model_config=cfg, seed=1, dtype="bfloat16", block_size=PAGE,
-                                      num_gpu_blocks=pages, max_num_seqs=seqs, max_model_len=900, max_num_batched_tokens=budget,
-                                      max_tokens_per_step=budget, use_cuda_graphs=fast, overlap_decode_steps=fast))
-            ids = [eng.add_request(p, SamplingParams(**options(i))) for i, p in enumerate(prompts)]
-            outs = {i: [] for i in ids}
-            while eng.has_pending_work():
-                for o in eng.step():
-                    outs[o.seq_id].extend(o.tokens)
-            torch.cuda.synchronize()
-            ops.check_status()
-            results[fast] = [outs[i] for i in ids]
-            assert eng.scheduler.num_preemptions > 0 and eng.cache.num_free_pages() == pages
-            if fast:
-                shapes = len(eng.runner.graphs)
-            del eng
-    finally:
-        ops.set_linear_tuning(True)
+    for fast in (True, False):
+        eng = Engine(EngineConfig(load_format="random", model_config=cfg, seed=1, dtype="bfloat16", block_size=PAGE,
+                                  num_gpu_blocks=pages, max_num_seqs=seqs, max_model_len=900, max_num_batched_tokens=budget,
+                                  max_tokens_per_step=budget, use_cuda_graphs=fast, overlap_decode_steps=fast,
+                                  tune_products=False))
+        ids = [eng.add_request(p, SamplingParams(**options(i))) for i, p in enumerate(prompts)]
+        outs = {i: [] for i in ids}
+        while eng.has_pending_work():
+            for o in eng.step():
+                outs[o.seq_id].extend(o.tokens)
+        torch.cuda.synchronize()
+        ops.check_status()
+        results[fast] = [outs[i] for i in ids]
+        assert eng.scheduler.num_preemptions > 0 and eng.cache.num_free_pages() == pages
+        if fast:
+            shapes = len(eng.runner.graphs)
+        del eng
     assert shapes >= 8
     differ = [i for i in range(n_req) if results[True][i] != results[False][i]]
     assert not differ, differ

@@ -69,6 +69,11 @@ class EngineConfig:
     top_k: int = -1
     repetition_penalty: float = 1.0
 
+    # Measure at load which product kernel and which grid are fastest for each shape on this device (bfloat16).
+    # What is measured may come out differently by timing noise from one engine to the next on the same device;
+    # sums are then taken in another order and a sampled token may differ in the last bit's favour.  False pins
+    # every few-token product to the engine's own kernel on its default grid: the same tokens from every engine.
+    tune_products: bool = True
     # Capture pure-decode steps in CUDA graphs.
     use_cuda_graphs: bool = True
     # While every running request decodes, launch the next step before this step's tokens

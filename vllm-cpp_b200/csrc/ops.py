@@ -664,6 +664,15 @@ def choose_linear(features: int, k: int, bucket: int, out_dtype, tcgen05: bool) 
     _linear_choice[(features, k, bucket, out_dtype)] = bool(tcgen05)
 
 
+def forget_choices(features: int, k: int) -> None:
+    """Drop what was measured for products of this shape (kernel per bucket, grid per tile width): the defaults
+    apply again."""
+    for key in [key for key in _linear_choice if key[0] == features and key[1] == k]:
+        del _linear_choice[key]
+    for key in [key for key in _cta_choice if key[0] == features and key[1] == k]:
+        del _cta_choice[key]
+
+
 def linear_tuning() -> bool:
     return _linear_tuning
 

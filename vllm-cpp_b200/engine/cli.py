@@ -50,6 +50,8 @@ def parse_args(argv=None):
     ap.add_argument("--top-k", type=int, default=d.top_k)
     ap.add_argument("--repetition-penalty", type=float, default=d.repetition_penalty)
     ap.add_argument("--sample-seed", type=int, default=None)
+    ap.add_argument("--no-tuning", action="store_true",
+                    help="do not measure product kernels and grids at load: the same tokens from every run")
     ap.add_argument("--ignore-eos", action="store_true")
     return ap.parse_args(argv)
 
@@ -70,7 +72,7 @@ def main(argv=None) -> int:
               seed=a.seed, block_size=a.block_size, num_gpu_blocks=a.num_gpu_blocks,
               gpu_memory_utilization=a.gpu_memory_utilization, max_num_seqs=a.max_num_seqs,
               max_model_len=a.max_model_len, max_num_batched_tokens=a.max_num_batched_tokens,
-              max_tokens_per_step=a.max_tokens_per_step)
+              max_tokens_per_step=a.max_tokens_per_step, tune_products=not a.no_tuning)
     t1 = time.time()
     sp = SamplingParams(max_tokens=a.max_tokens, temperature=a.temperature, top_p=a.top_p, top_k=a.top_k,
                         repetition_penalty=a.repetition_penalty, seed=a.sample_seed, ignore_eos=a.ignore_eos)

@@ -63,7 +63,7 @@ def build(cfg: EngineConfig) -> Tuple[DecoderModel, CacheManager, ModelRunner]:
         torch.cuda.empty_cache()
         free, total = torch.cuda.mem_get_info(device)
         usable = int(total * cfg.gpu_memory_utilization / 100) - (total - free)
-        model.prepare_products(image_budget=max(0, usable // 3))
+        model.prepare_products(tune=cfg.tune_products, image_budget=max(0, usable // 3))
         max_model_len = min(cfg.max_model_len, model.spec.max_position_embeddings)
         # Every slice besides the pages is counted (engine/memory_plan.py); the workspace is allocated at the
         # size the plan gives it.  With an explicit num_gpu_blocks the plan only sizes the workspace.

@@ -58,6 +58,9 @@ def prepare_products(model, tune: bool = True, image_budget: Optional[int] = Non
     gated_of = {key: (key[1] if key in imaged else 0) for key in groups}     # a gated product only with its image
 
     measure = tune and ops.linear_tuning()
+    if not measure:
+        for (shape, _gated) in groups:            # what another engine of this process measured for these shapes
+            ops.forget_choices(shape[0], shape[1])
     for key in imaged:
         for m in groups[key][:8]:             # the kernel is measured as it will run: on the images
             ops.tile_weights(m, key[1])
