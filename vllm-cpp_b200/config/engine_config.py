@@ -78,7 +78,9 @@ class EngineConfig:
     use_cuda_graphs: bool = True
     # While every running request decodes, launch the next step before this step's tokens
     # have reached the host (they are fed to it on the device), so the GPU never waits for
-    # the host between steps.  The tokens are the same either way.
+    # the host between steps.  The tokens are the same either way in float32; in bfloat16 too, unless a request
+    # meets a stop token while the step after is already on its way: that step then runs with one request more
+    # than it would have had, and a product over 17 rows does not round as one over 16.
     overlap_decode_steps: bool = True
     # Time the phases of every step (schedule, pack, launch, sample, wait on the host; forward and
     # sampling on the device with CUDA events) into StepStats.phase_ms.  The reference has a scoped
