@@ -301,3 +301,42 @@ def test_both_hosts_give_the_same_tokens_under_pressure_in_float32(tmp_path):
     assert [len(t) for t in from_python] == [int(g) for g in gens]
     differ = [i for i in range(n_req) if from_python[i] != from_cpp[i]]
     assert not differ, differ
+
+
+@pytest.mark.parametrize("host", ["python", "cpp"])
+@pytest.mark.parametrize("name,window,dtype", [("C", 24, "float32"), ("E", 70, "bfloat16"), ("D", 40, "bfloat16")])
+def test_a_request_far_longer_than_the_pool_lives_on_its_window(tmp_path, name, window, dtype, host):
+    """Every layer windowed: 700 tokens (portions, then one by one, decode steps captured on the Python host) on
+    a pool of the window's pages and a few more, less than half of what the context would need; pages the window has
+    passed are given back and used again.  Logits against the plain implementation at every position."""
+    from helpers import Replayer
+    from vllm_cpp_b200 import EngineConfig
+    from vllm_cpp_b200.engine import factory
+    from vllm_cpp_b200.engine.cpp_host import CppEngine
+    page = CONFIGS[name][1]
+    cfg = dict(CONFIGS[name][0], use_sliding_window=True, sliding_window=window, max_window_layers=0, max_position_embeddings=2048)
+    weights = make_weights(cfg, 3, dtype)
+    folder = model_folder(tmp_path, cfg, weights, dtype)
+    n = 700
+    ids = token_ids(cfg, n, 5)
+    pages = -(-window // page) + 6
+    assert pages * page * 2 < n
+    if host == "python":
+        model, cache, runner = factory.build(EngineConfig(model_path=folder, dtype=dtype, block_size=page, num_gpu_blocks=pages,
+                                                          max_num_seqs=2, max_model_len=2048, max_num_batched_tokens=64,
+                                                          use_cuda_graphs=True))
+        rp, free = Replayer(runner, cache), (lambda: cache.num_free_pages())
+    else:
+        eng = CppEngine(folder, dtype=dtype, block_size=page, num_gpu_blocks=pages, max_num_seqs=2, max_model_len=2048,
+                        max_num_batched_tokens=64)
+        rp, free = CppReplayer(eng), (lambda: eng.num_free_blocks)
+    at = 0
+    for c in (40, 2, 17, 33):
+        rp.step([("r", ids[at:at + c], range(c))])
+        at += c
+    while at < n:
+        rp.step([("r", ids[at:at + 1], [0])])
+        at += 1
+    compare(rp.logits_of("r", range(n)), plain.forward(weights, cfg, ids), dtype, f"{name} {dtype} {host}")
+    rp.step([("x", [1, 2], [])], end=["r", "x"])
+    assert free() == pages
