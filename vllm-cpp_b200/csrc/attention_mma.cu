@@ -293,7 +293,7 @@ attention_decode_kernel(MmaAttnArgs a) {
     bool gave_up = false;
 
     for (int mt = 0; mt * 16 < G; ++mt) {
-        __syncthreads();                                 // barriers initialised; last round's merge has been read
+        __syncthreads();                                 // barriers initialised; the merge of the pass before has been read
         if (!producer) {
             // Q rows of this group: row i -> head g*G + mt*16 + i (written by the previous kernel)
             pdl_wait();
@@ -388,7 +388,7 @@ attention_decode_kernel(MmaAttnArgs a) {
         // of this kernel would be read in two rounds.
         pdl_launch_dependents();
         __syncthreads();                                 // every copy has landed and been read: reuse the tiles
-        const int Gm = min(16, G - mt * 16);             // rows of this round that are heads
+        const int Gm = min(16, G - mt * 16);             // rows of this pass that are heads
         if (!producer) {
             l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
             l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
